@@ -1,0 +1,145 @@
+"""The split-key planner (host side of the attention kernels): every (row, KV head, visible
+key) is covered by exactly one item, CTA spans are balanced, partial slots are contiguous.
+Expectations on *when* to split come from the reference's planner test
+(crates/yaxus-backend-gpu/src/plan.rs:427-443): decode passes are split across keys."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from yaxus_b200 import _lib
+from yaxus_b200 import workloads as W
+from yaxus_b200.kvcache import PassMeta
+
+U64_MAX = (1 << 64) - 1
+
+
+def probe(meta, hkv, group, window=0, key_lo=0, key_hi=U64_MAX, max_rows=16, n_ctas=148, share=1, esize=2):
+    L = _lib.cuda_lib()
+    info = _lib.PlanInfo()
+    cap = 200000
+    buf = np.zeros(cap * _lib.PROBE_ITEM_WORDS, np.uint32)
+    p = lambda a: np.ascontiguousarray(a, np.uint32).ctypes.data_as(ctypes.POINTER(ctypes.c_uint32))
+    pos, off, pages = (np.ascontiguousarray(x, np.uint32) for x in (meta.pos, meta.pt_off, meta.pages))
+    rc = L.yx_plan_probe(len(pos), p(pos), p(off), p(pages), len(pages), hkv, group, window or 0, key_lo, key_hi,
+                         max_rows, n_ctas, share, esize, ctypes.byref(info), p(buf), cap)
+    assert rc == 0
+    items = buf[: info.n_items * _lib.PROBE_ITEM_WORDS].reshape(info.n_items, _lib.PROBE_ITEM_WORDS)
+    return info, items
+
+
+def check_cover(meta, items, hkv, window, key_lo=0, key_hi=U64_MAX):
+    T = meta.rows
+    seen = {}
+    for it in items:
+        tb, te, klo, khi, pt, kvh, nr = (int(x) for x in it[:7])
+        for r in range(nr):
+            row = int(it[9 + r])
+            p = int(meta.pos[row])
+            lo = max(0, p + 1 - window) if window else 0
+            a = max(lo, klo, tb * 64, key_lo)
+            b = min(p, khi, te * 64 - 1, key_hi - 1)
+            # the item's page table must agree with the row's over the keys it reads for it
+            for key in range(a, b + 1, 64):
+                assert meta.pages[pt + key // 128] == meta.pages[int(meta.pt_off[row]) + key // 128]
+            if a <= b:
+                seen.setdefault((row, kvh), []).append((a, b))
+    for row in range(T):
+        p = int(meta.pos[row])
+        lo = max(0, p + 1 - window) if window else 0
+        lo, hi = max(lo, key_lo), min(p, key_hi - 1)
+        for kvh in range(hkv):
+            spans = sorted(seen.get((row, kvh), []))
+            if lo > hi:
+                assert not spans
+                continue
+            assert spans and spans[0][0] == lo and spans[-1][1] == hi, (row, kvh, spans, lo, hi)
+            for (a0, b0), (a1, b1) in zip(spans[:-1], spans[1:]):
+                assert a1 == b0 + 1   # no gap, no overlap
+
+
+def check_slots(items, info, group_rows):
+    used = set()
+    for it in items:
+        nr, kvh = int(it[6]), int(it[5])
+        for r in range(nr):
+            s = int(it[9 + 16 + r])
+            assert s < info.n_parts and s not in used
+            used.add(s)
+    assert len(used) == info.n_parts
+
+
+def check_balance(items, info):
+    per = np.zeros(info.n_ctas, np.int64)
+    for it in items:
+        per[int(it[8])] += int(it[1]) - int(it[0])
+    assert per.sum() == info.tiles
+    if info.tiles >= info.n_ctas:
+        assert per.max() - per.min() <= 1
+
+
+@pytest.mark.parametrize("share", [0, 1])
+def test_batched_decode_plan(share):
+    s = W.batched_decode(fill=False)
+    info, items = probe(s.meta, s.hkv, s.hq // s.hkv, share=share)
+    check_cover(s.meta, items, s.hkv, None)
+    check_slots(items, info, 1)
+    check_balance(items, info)
+    assert info.n_ctas == 148
+    assert info.logical_kv_bytes == s.logical_kv_bytes()
+    assert info.unique_kv_bytes == s.unique_kv_bytes()
+    if share:
+        assert info.shared_groups == 1
+        # the shared prefix is streamed once: tiles = unique tokens / 64 per KV head
+        assert info.tiles * 64 * 2 * 128 * 2 < 1.02 * s.unique_kv_bytes() + 16 * 8 * 64 * 512
+        assert any(int(it[6]) == 16 and int(it[7]) == 64 for it in items)
+    else:
+        assert info.shared_groups == 0
+        assert all(int(it[6]) == 1 and int(it[7]) == 16 for it in items)
+
+
+def test_verify_plan_groups_rows_of_a_sequence():
+    s = W.verify(fill=False)
+    info, items = probe(s.meta, s.hkv, 4)
+    check_cover(s.meta, items, s.hkv, None)
+    check_slots(items, info, 5)
+    check_balance(items, info)
+    assert all(int(it[6]) == 5 and int(it[7]) == 32 for it in items)   # 5 rows x 4 heads -> 32 padded rows
+
+
+@pytest.mark.parametrize("window", [None, 100, 2048])
+def test_windows_and_ragged_passes(window):
+    rows = [(0, p) for p in range(300, 340)] + [(1, 5)] + [(2, 4095)] + [(3, 0)]
+    tables = [np.arange(10, 13), np.array([40]), np.arange(50, 82), np.array([7])]
+    meta = PassMeta.from_rows(rows, tables)
+    for max_rows in (1, 4, 16):
+        info, items = probe(meta, 2, 4, window=window, max_rows=max_rows, n_ctas=37)
+        check_cover(meta, items, 2, window)
+        check_slots(items, info, max_rows)
+        check_balance(items, info)
+
+
+def test_key_range_restriction():
+    s = W.long_decode(ctx=8192, fill=False)
+    for world in (1, 2, 4, 8):
+        for rank in range(world):
+            _, _, klo, khi = W.partition_pages(64, world, rank)
+            for window in (None, 2048):
+                info, items = probe(s.meta, 8, 4, window=window, key_lo=klo, key_hi=khi)
+                check_cover(s.meta, items, 8, window, klo, khi)
+                check_balance(items, info)
+                if window and khi <= 8192 - 2048:
+                    assert info.n_items == 0 and info.n_parts == 0   # a rank with no live key
+
+
+def test_decode_is_split_across_keys():
+    # plan.rs:432-434: a single decode row over a long context is cut into many pieces.
+    meta = PassMeta.from_rows([(0, 1000)], [np.arange(8)])
+    info, items = probe(meta, 8, 2)
+    assert info.n_items == info.tiles == 8 * 16 and info.n_ctas == 128
+
+
+def test_empty_pass():
+    meta = PassMeta()
+    info, items = probe(meta, 8, 4)
+    assert info.n_items == 0 and info.tiles == 0

@@ -1,0 +1,61 @@
+"""Builds libyaxus_cuda.so (sm_100a) and the host-side library in-tree with nvcc / g++."""
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+OUT = os.path.join(HERE, "libyaxus_cuda.so")
+HOST_OUT = os.path.join(HERE, "libyaxus_host.so")
+CUDA_SOURCES = ["api.cu", "kv_ops.cu", "attend_simt.cu", "attend_mma.cu", "combine.cu", "dist.cu", "planner.cpp",
+                "probe.cpp"]
+HOST_SOURCES = [os.path.join("host", "kv_cache.cpp")]
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC,-Wall,-Wno-unknown-pragmas", "--expt-relaxed-constexpr",
+]
+
+
+def _stale(out, deps):
+    return not os.path.exists(out) or any(os.path.getmtime(d) > os.path.getmtime(out) for d in deps)
+
+
+def _deps(sources):
+    deps = [os.path.join(CSRC, s) for s in sources]
+    for root, _, files in os.walk(CSRC):
+        deps += [os.path.join(root, f) for f in files if f.endswith((".h", ".hpp", ".cuh"))]
+    deps.append(os.path.join(HERE, "..", "include", "yaxus_cuda.h"))
+    return deps
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compiles every CUDA source for sm_100a into yaxus_b200/libyaxus_cuda.so."""
+    if force or _stale(OUT, _deps(CUDA_SOURCES)):
+        objs = []
+        os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
+        procs = []
+        for s in CUDA_SOURCES:
+            obj = os.path.join(HERE, "build", s.replace("/", "_") + ".o")
+            objs.append(obj)
+            cmd = ["nvcc", *NVCC_FLAGS, "-x", "cu", "-c", os.path.join(CSRC, s), "-o", obj]
+            if verbose:
+                cmd.insert(1, "-Xptxas=-v")
+            procs.append((s, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+        failed = False
+        for s, p in procs:
+            out, _ = p.communicate()
+            if p.returncode != 0 or verbose:
+                print(f"--- {s}\n{out}")
+            failed |= p.returncode != 0
+        if failed:
+            raise RuntimeError("nvcc failed")
+        subprocess.run(["nvcc", "-shared", "-o", OUT, *objs, "-ldl"], check=True)
+    if force or _stale(HOST_OUT, _deps(HOST_SOURCES)):
+        cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-Wall", "-o", HOST_OUT,
+               *[os.path.join(CSRC, s) for s in HOST_SOURCES]]
+        subprocess.run(cmd, check=True)
+    return OUT
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -1,0 +1,588 @@
+// The C ABI of libyaxus_cuda: contexts, KV storage, pass metadata and the attention entry
+// points.  Kernels live in kv_ops.cu, attend_simt.cu, attend_mma.cu and combine.cu.
+#include <string.h>
+
+#include <algorithm>
+#include <new>
+
+#include "yx_internal.h"
+
+namespace yx {
+
+int fail(yx_ctx *ctx, int code, const std::string &msg) {
+    if (ctx && ctx->status == YX_OK) {
+        ctx->status = code;
+        ctx->error = msg;
+    }
+    return code;
+}
+
+int check_cuda(yx_ctx *ctx, cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return YX_OK;
+    int code = e == cudaErrorMemoryAllocation ? YX_ERR_OOM : YX_ERR_CUDA;
+    return fail(ctx, code, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+int ensure_buffer(yx_ctx *ctx, void **buf, size_t *cap, size_t bytes) {
+    if (bytes <= *cap && *buf) return YX_OK;
+    size_t want = std::max<size_t>(bytes, 256);
+    want = want + want / 2;
+    if (*buf) {
+        // Kernels queued earlier may still use the old buffer.
+        if (int rc = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "sync before growing a buffer")) return rc;
+        cudaFree(*buf);
+        *buf = nullptr;
+        *cap = 0;
+    }
+    void *p = nullptr;
+    if (int rc = check_cuda(ctx, cudaMalloc(&p, want), "cudaMalloc (workspace)")) return rc;
+    *buf = p;
+    *cap = want;
+    return YX_OK;
+}
+
+// The reference writes pass metadata through its command stream so that it lands after the
+// kernels of earlier passes (crates/yaxus-backend-gpu/src/dev/wgpu/mod.rs:284-294).  Here a
+// ring of pinned buffers does the same: the caller's arrays are copied at once, the
+// host-to-device copy is ordered on the stream, and a buffer is reused only after its copy.
+int upload_ordered(yx_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes) {
+    if (bytes == 0) return YX_OK;
+    if (ctx->ring.empty()) ctx->ring.resize(8);
+    yx_ctx::Stage &st = ctx->ring[ctx->ring_next];
+    ctx->ring_next = (ctx->ring_next + 1) % ctx->ring.size();
+    if (st.busy) {
+        if (int rc = check_cuda(ctx, cudaEventSynchronize(st.done), "wait for a staging buffer")) return rc;
+        st.busy = false;
+    }
+    if (st.cap < bytes) {
+        if (st.host) cudaFreeHost(st.host);
+        st.host = nullptr;
+        st.cap = 0;
+        size_t want = std::max<size_t>(bytes + bytes / 2, 4096);
+        if (int rc = check_cuda(ctx, cudaMallocHost(&st.host, want), "cudaMallocHost (staging)")) return rc;
+        st.cap = want;
+    }
+    if (!st.done)
+        if (int rc = check_cuda(ctx, cudaEventCreateWithFlags(&st.done, cudaEventDisableTiming), "cudaEventCreate")) return rc;
+    memcpy(st.host, src_host, bytes);
+    if (int rc = check_cuda(ctx, cudaMemcpyAsync(dst_dev, st.host, bytes, cudaMemcpyHostToDevice, ctx->stream), "upload"))
+        return rc;
+    if (int rc = check_cuda(ctx, cudaEventRecord(st.done, ctx->stream), "cudaEventRecord")) return rc;
+    st.busy = true;
+    return YX_OK;
+}
+
+namespace {
+
+bool valid_dtype(int d) { return d == YX_F32 || d == YX_F16 || d == YX_BF16; }
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev) cudaSetDevice(dev);
+        else prev = -1;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+int fold_device_status(yx_ctx *ctx) {
+    if (ctx->dev_status && ctx->dev_status->code != 0) {
+        yx_dev_status s = *ctx->dev_status;
+        ctx->dev_status->code = 0;
+        return fail(ctx, YX_ERR_DEVICE,
+                    "a kernel reported a failed check: code " + std::to_string(s.code) + " at " +
+                        std::to_string(s.where) + " (" + std::to_string(s.a) + ", " + std::to_string(s.b) + ")");
+    }
+    return YX_OK;
+}
+
+// Finds or builds the split-key plan of the current pass for these parameters, and makes
+// sure it is on the device.
+int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
+    for (auto &cp : ctx->plans) {
+        if (cp.pass_serial == ctx->pass_serial && cp.hkv == pp.hkv && cp.group == pp.group &&
+            cp.max_rows == pp.max_rows && cp.n_ctas == pp.n_ctas && cp.window == pp.window &&
+            cp.key_lo == pp.key_lo && cp.key_hi == pp.key_hi && cp.share == pp.share_prefix && cp.esize == pp.esize) {
+            *out = &cp;
+            return YX_OK;
+        }
+    }
+    // Reuse the slot of an older pass, else add one (a pass rarely needs more than two:
+    // full-attention layers and sliding-window layers).
+    yx_ctx::CachedPlan *slot = nullptr;
+    for (auto &cp : ctx->plans)
+        if (cp.pass_serial != ctx->pass_serial) {
+            slot = &cp;
+            break;
+        }
+    if (!slot) {
+        if (ctx->plans.size() >= 8) {
+            slot = &ctx->plans[0];
+        } else {
+            ctx->plans.emplace_back();
+            slot = &ctx->plans.back();
+        }
+    }
+    try {
+        build_split_plan(ctx->pass, pp, slot->plan);
+    } catch (const std::string &msg) {
+        slot->pass_serial = 0;
+        return fail(ctx, YX_ERR_INVALID, "attention plan: " + msg);
+    } catch (const std::bad_alloc &) {
+        slot->pass_serial = 0;
+        return fail(ctx, YX_ERR_OOM, "attention plan: out of host memory");
+    }
+    slot->pass_serial = ctx->pass_serial;
+    slot->hkv = pp.hkv;
+    slot->group = pp.group;
+    slot->max_rows = pp.max_rows;
+    slot->n_ctas = pp.n_ctas;
+    slot->window = pp.window;
+    slot->key_lo = pp.key_lo;
+    slot->key_hi = pp.key_hi;
+    slot->share = pp.share_prefix;
+    slot->esize = pp.esize;
+
+    const Plan &pl = slot->plan;
+    size_t items_b = pl.items.size() * sizeof(Item);
+    size_t cta_b = (pl.cta_begin.size() * sizeof(uint32_t) + 15) / 16 * 16;
+    size_t mer_b = pl.merges.size() * sizeof(Merge);
+    size_t total = items_b + cta_b + mer_b;
+    if (int rc = ensure_buffer(ctx, (void **)&slot->dev, &slot->dev_cap, total)) {
+        slot->pass_serial = 0;
+        return rc;
+    }
+    std::vector<char> blob(total);
+    if (items_b) memcpy(blob.data(), pl.items.data(), items_b);
+    memcpy(blob.data() + items_b, pl.cta_begin.data(), pl.cta_begin.size() * sizeof(uint32_t));
+    if (mer_b) memcpy(blob.data() + items_b + cta_b, pl.merges.data(), mer_b);
+    if (int rc = upload_ordered(ctx, slot->dev, blob.data(), total)) {
+        slot->pass_serial = 0;
+        return rc;
+    }
+    slot->d_items = (Item *)slot->dev;
+    slot->d_cta_begin = (uint32_t *)(slot->dev + items_b);
+    slot->d_merges = (Merge *)(slot->dev + items_b + cta_b);
+    *out = slot;
+    return YX_OK;
+}
+
+int pick_path(const yx_ctx *ctx, const yx_kv *kv) {
+    int f = ctx->tuning.force_path;
+    if (kv->dtype == YX_F32) return 1;
+    if (f == 1) return 1;
+    return 2;
+}
+
+// Shared body of yx_attend / yx_attend_partial: split-key kernel, then the merge.
+int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, int hq, int64_t window,
+                uint64_t key_lo, uint64_t key_hi, void *out, int out_dtype, float *m_out, float *l_out,
+                float *o_out) {
+    if (!ctx || !kv) return YX_ERR_INVALID;
+    if (ctx->status != YX_OK) return ctx->status;
+    if (!ctx->have_pass) return fail(ctx, YX_ERR_STATE, "attention without begin_pass");
+    if (layer < 0 || layer >= kv->n_layers) return fail(ctx, YX_ERR_INVALID, "layer out of range");
+    if (!valid_dtype(q_dtype) || !valid_dtype(out_dtype)) return fail(ctx, YX_ERR_INVALID, "bad dtype");
+    if (hq <= 0 || hq % kv->hkv != 0) return fail(ctx, YX_ERR_INVALID, "hq must be a positive multiple of hkv");
+    const int group = hq / kv->hkv;
+    if (group > 16) return fail(ctx, YX_ERR_UNSUPPORTED, "more than 16 query heads per KV head");
+    if (ctx->pass.rows == 0) return YX_OK;
+    if (!q || (!out && !o_out)) return fail(ctx, YX_ERR_INVALID, "null tensor");
+    if (window < 0) window = kv->layers[layer].window;
+    for (uint32_t r = 0; r < ctx->pass.rows; r++)
+        if (ctx->pass.pos[r] >= kv->max_pos) return fail(ctx, YX_ERR_INVALID, "a row's position exceeds max_pos");
+    DeviceGuard guard(ctx->device);
+
+    const int path = pick_path(ctx, kv);
+    const int64_t launches0 = ctx->launches;
+    PlanParams pp{};
+    pp.hkv = kv->hkv;
+    pp.group = group;
+    pp.window = window > 0 ? window : 0;
+    pp.key_lo = key_lo;
+    pp.key_hi = key_hi;
+    pp.esize = kv->esize;
+    const int per_sm = ctx->tuning.ctas_per_sm > 0 ? ctx->tuning.ctas_per_sm : (path == 1 ? 4 : 1);
+    pp.n_ctas = ctx->sm_count * per_sm;
+    pp.max_rows = path == 1 ? 1 : std::max(1, std::min(MAX_ITEM_ROWS, 64 / group));
+    pp.share_prefix = path != 1 && ctx->tuning.share_prefix != 2;
+    yx_ctx::CachedPlan *cp = nullptr;
+    if (int rc = get_plan(ctx, pp, &cp)) return rc;
+    const Plan &pl = cp->plan;
+
+    // Every page id the plan will read must be inside the arena.
+    for (uint32_t p : ctx->pass.pages)
+        if (p >= kv->pages && key_lo == 0 && key_hi == UINT64_MAX)
+            return fail(ctx, YX_ERR_INVALID, "page id outside the KV arena");
+
+    size_t o_bytes = (size_t)std::max<uint32_t>(pl.n_parts, 1) * group * D * sizeof(float);
+    size_t ml_bytes = (size_t)std::max<uint32_t>(pl.n_parts, 1) * group * 2 * sizeof(float);
+    if (int rc = ensure_buffer(ctx, (void **)&ctx->ws_o, &ctx->ws_o_cap, o_bytes)) return rc;
+    if (int rc = ensure_buffer(ctx, (void **)&ctx->ws_ml, &ctx->ws_ml_cap, ml_bytes)) return rc;
+
+    AttendArgs a{};
+    a.q = q;
+    a.q_dtype = q_dtype;
+    a.hq = hq;
+    a.group = group;
+    a.k_arena = kv->k(layer);
+    a.v_arena = kv->v(layer);
+    a.hkv = kv->hkv;
+    a.kv_dtype = kv->dtype;
+    a.kv_pages = kv->pages;
+    a.window = pp.window;
+    a.key_lo = key_lo;
+    a.key_hi = key_hi;
+    a.items = cp->d_items;
+    a.cta_begin = cp->d_cta_begin;
+    a.n_ctas = pl.n_ctas;
+    a.part_o = ctx->ws_o;
+    a.part_ml = ctx->ws_ml;
+    if (!pl.items.empty()) {
+        int rc = path == 1 ? launch_attend_simt(ctx, a) : launch_attend_mma(ctx, a);
+        if (rc) return rc;
+    }
+    if (int rc = launch_combine(ctx, cp->d_merges, ctx->ws_o, ctx->ws_ml, (int)ctx->pass.rows, hq, group, out,
+                                out_dtype, m_out, l_out, o_out))
+        return rc;
+    ctx->last_plan = pl.info;
+    ctx->last_plan.path = path;
+    ctx->last_plan.launches = (int)(ctx->launches - launches0);
+    return YX_OK;
+}
+
+}  // namespace
+}  // namespace yx
+
+using namespace yx;
+
+extern "C" {
+
+int yx_ctx_create(int device, void *stream, yx_ctx **out) {
+    if (!out) return YX_ERR_INVALID;
+    *out = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) return YX_ERR_CUDA;   // no CPU fallback
+    if (device < 0 || device >= n) return YX_ERR_INVALID;
+    cudaDeviceProp prop{};
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return YX_ERR_CUDA;
+    if (prop.major != 10) return YX_ERR_UNSUPPORTED;   // built for sm_100a only
+    yx_ctx *ctx = new (std::nothrow) yx_ctx();
+    if (!ctx) return YX_ERR_OOM;
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    DeviceGuard guard(device);
+    if (stream) {
+        ctx->stream = (cudaStream_t)stream;
+    } else {
+        if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+            delete ctx;
+            return YX_ERR_CUDA;
+        }
+        ctx->own_stream = true;
+    }
+    if (cudaHostAlloc((void **)&ctx->dev_status, sizeof(yx_dev_status), cudaHostAllocMapped) != cudaSuccess) {
+        if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
+        delete ctx;
+        return YX_ERR_OOM;
+    }
+    memset(ctx->dev_status, 0, sizeof(yx_dev_status));
+    *out = ctx;
+    return YX_OK;
+}
+
+void yx_ctx_destroy(yx_ctx *ctx) {
+    if (!ctx) return;
+    DeviceGuard guard(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    yx_comm_destroy(ctx);
+    for (auto &st : ctx->ring) {
+        if (st.host) cudaFreeHost(st.host);
+        if (st.done) cudaEventDestroy(st.done);
+    }
+    for (auto &cp : ctx->plans)
+        if (cp.dev) cudaFree(cp.dev);
+    if (ctx->d_meta) cudaFree(ctx->d_meta);
+    if (ctx->ws_o) cudaFree(ctx->ws_o);
+    if (ctx->ws_ml) cudaFree(ctx->ws_ml);
+    if (ctx->q_tmp) cudaFree(ctx->q_tmp);
+    if (ctx->gather_buf) cudaFree(ctx->gather_buf);
+    if (ctx->dev_status) cudaFreeHost(ctx->dev_status);
+    if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+int yx_status(const yx_ctx *ctx) { return ctx ? ctx->status : YX_ERR_INVALID; }
+const char *yx_last_error(const yx_ctx *ctx) { return ctx ? ctx->error.c_str() : "null context"; }
+void yx_clear_error(yx_ctx *ctx) {
+    if (ctx) {
+        ctx->status = YX_OK;
+        ctx->error.clear();
+    }
+}
+
+int yx_sync(yx_ctx *ctx) {
+    if (!ctx) return YX_ERR_INVALID;
+    DeviceGuard guard(ctx->device);
+    if (int rc = check_cuda(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize")) return rc;
+    if (int rc = fold_device_status(ctx)) return rc;
+    return ctx->status;
+}
+
+void *yx_stream(const yx_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
+
+int yx_set_tuning(yx_ctx *ctx, const yx_tuning *t) {
+    if (!ctx) return YX_ERR_INVALID;
+    ctx->tuning = t ? *t : yx_tuning{};
+    for (auto &cp : ctx->plans) cp.pass_serial = 0;
+    return YX_OK;
+}
+
+int yx_last_plan(const yx_ctx *ctx, yx_plan_info *out) {
+    if (!ctx || !out) return YX_ERR_INVALID;
+    *out = ctx->last_plan;
+    return YX_OK;
+}
+
+int64_t yx_launch_count(const yx_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
+// ---- tensors ---------------------------------------------------------------------------
+
+int yx_tensor_alloc(yx_ctx *ctx, size_t bytes, void **out_dev) {
+    if (!ctx || !out_dev) return YX_ERR_INVALID;
+    DeviceGuard guard(ctx->device);
+    *out_dev = nullptr;
+    return check_cuda(ctx, cudaMalloc(out_dev, std::max<size_t>(bytes, 16)), "cudaMalloc (tensor)");
+}
+
+int yx_tensor_free(yx_ctx *ctx, void *dev) {
+    if (!ctx) return YX_ERR_INVALID;
+    DeviceGuard guard(ctx->device);
+    return dev ? check_cuda(ctx, cudaFree(dev), "cudaFree") : YX_OK;
+}
+
+int yx_upload(yx_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes) {
+    if (!ctx || (bytes && (!dst_dev || !src_host))) return YX_ERR_INVALID;
+    DeviceGuard guard(ctx->device);
+    return check_cuda(ctx, cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream), "upload");
+}
+
+int yx_download(yx_ctx *ctx, void *dst_host, const void *src_dev, size_t bytes, int wait) {
+    if (!ctx || (bytes && (!dst_host || !src_dev))) return YX_ERR_INVALID;
+    DeviceGuard guard(ctx->device);
+    if (int rc = check_cuda(ctx, cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, ctx->stream), "download"))
+        return rc;
+    return wait ? yx_sync(ctx) : YX_OK;
+}
+
+int yx_host_alloc(yx_ctx *ctx, size_t bytes, void **out_host) {
+    if (!ctx || !out_host) return YX_ERR_INVALID;
+    DeviceGuard guard(ctx->device);
+    return check_cuda(ctx, cudaMallocHost(out_host, std::max<size_t>(bytes, 16)), "cudaMallocHost");
+}
+
+int yx_host_free(yx_ctx *ctx, void *host) {
+    if (!ctx) return YX_ERR_INVALID;
+    return host ? check_cuda(ctx, cudaFreeHost(host), "cudaFreeHost") : YX_OK;
+}
+
+// ---- KV storage ------------------------------------------------------------------------
+
+int yx_kv_create(yx_ctx *ctx, int n_layers, const yx_layer *layers, uint32_t pages, int hkv, int head_dim,
+                 int dtype, uint32_t max_pos, yx_kv **out) {
+    if (!ctx || !out) return YX_ERR_INVALID;
+    *out = nullptr;
+    if (n_layers <= 0 || !layers || pages == 0 || hkv <= 0) return fail(ctx, YX_ERR_INVALID, "new_kv: bad sizes");
+    if (head_dim != D) return fail(ctx, YX_ERR_UNSUPPORTED, "new_kv: head_dim must be 128");
+    if (!valid_dtype(dtype)) return fail(ctx, YX_ERR_INVALID, "new_kv: bad dtype");
+    DeviceGuard guard(ctx->device);
+    yx_kv *kv = new (std::nothrow) yx_kv();
+    if (!kv) return fail(ctx, YX_ERR_OOM, "new_kv: out of host memory");
+    kv->n_layers = n_layers;
+    kv->hkv = hkv;
+    kv->dtype = dtype;
+    kv->esize = dtype == YX_F32 ? 4 : 2;
+    kv->pages = pages;
+    kv->max_pos = max_pos;
+    kv->layers.assign(layers, layers + n_layers);
+    kv->layer_bytes = (size_t)pages * hkv * kv_block_elems() * kv->esize;
+    size_t total = kv->layer_bytes * n_layers;
+    int rc = check_cuda(ctx, cudaMalloc((void **)&kv->k_base, total), "new_kv: cudaMalloc K");
+    if (!rc) rc = check_cuda(ctx, cudaMalloc((void **)&kv->v_base, total), "new_kv: cudaMalloc V");
+    if (!rc) rc = check_cuda(ctx, cudaMalloc(&kv->rope_dev, sizeof(yx_rope) * n_layers), "new_kv: cudaMalloc rope");
+    // Zeroed like the reference's arenas (cpu lib.rs:466-468).
+    if (!rc) rc = check_cuda(ctx, cudaMemsetAsync(kv->k_base, 0, total, ctx->stream), "new_kv: zero K");
+    if (!rc) rc = check_cuda(ctx, cudaMemsetAsync(kv->v_base, 0, total, ctx->stream), "new_kv: zero V");
+    if (!rc) {
+        std::vector<yx_rope> ropes(n_layers);
+        for (int l = 0; l < n_layers; l++) ropes[l] = layers[l].rope;
+        rc = upload_ordered(ctx, kv->rope_dev, ropes.data(), sizeof(yx_rope) * n_layers);
+    }
+    if (rc) {
+        yx_kv_destroy(ctx, kv);
+        return rc;
+    }
+    *out = kv;
+    return YX_OK;
+}
+
+void yx_kv_destroy(yx_ctx *ctx, yx_kv *kv) {
+    if (!kv) return;
+    if (ctx) {
+        DeviceGuard guard(ctx->device);
+        cudaStreamSynchronize(ctx->stream);
+        if (kv->k_base) cudaFree(kv->k_base);
+        if (kv->v_base) cudaFree(kv->v_base);
+        if (kv->rope_dev) cudaFree(kv->rope_dev);
+    }
+    delete kv;
+}
+
+int yx_kv_copy_page(yx_ctx *ctx, yx_kv *kv, uint32_t src, uint32_t dst) {
+    if (!ctx || !kv) return YX_ERR_INVALID;
+    if (ctx->status != YX_OK) return ctx->status;
+    if (src >= kv->pages || dst >= kv->pages) return fail(ctx, YX_ERR_INVALID, "copy_page: page outside the arena");
+    if (src == dst) return YX_OK;
+    DeviceGuard guard(ctx->device);
+    return launch_copy_page(ctx, kv, src, dst);
+}
+
+static int page_io(yx_ctx *ctx, yx_kv *kv, int layer, uint32_t first, uint32_t n_pages, void *k_host, void *v_host,
+                   bool write) {
+    if (!ctx || !kv || !k_host || !v_host) return YX_ERR_INVALID;
+    if (layer < 0 || layer >= kv->n_layers || n_pages == 0 || (uint64_t)first + n_pages > kv->pages)
+        return fail(ctx, YX_ERR_INVALID, "page io: out of range");
+    DeviceGuard guard(ctx->device);
+    size_t bytes = (size_t)n_pages * PAGE * kv->hkv * D * kv->esize;
+    void *lin = nullptr;
+    if (int rc = check_cuda(ctx, cudaMalloc(&lin, 2 * bytes), "page io: cudaMalloc")) return rc;
+    char *k_lin = (char *)lin, *v_lin = k_lin + bytes;
+    int rc = YX_OK;
+    if (write) {
+        rc = check_cuda(ctx, cudaMemcpyAsync(k_lin, k_host, bytes, cudaMemcpyHostToDevice, ctx->stream), "page io");
+        if (!rc) rc = check_cuda(ctx, cudaMemcpyAsync(v_lin, v_host, bytes, cudaMemcpyHostToDevice, ctx->stream), "page io");
+        if (!rc) rc = launch_page_io(ctx, kv, layer, first, n_pages, k_lin, v_lin, true);
+    } else {
+        rc = launch_page_io(ctx, kv, layer, first, n_pages, k_lin, v_lin, false);
+        if (!rc) rc = check_cuda(ctx, cudaMemcpyAsync(k_host, k_lin, bytes, cudaMemcpyDeviceToHost, ctx->stream), "page io");
+        if (!rc) rc = check_cuda(ctx, cudaMemcpyAsync(v_host, v_lin, bytes, cudaMemcpyDeviceToHost, ctx->stream), "page io");
+    }
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    cudaFree(lin);
+    if (rc) return rc;
+    return check_cuda(ctx, e, "page io: sync");
+}
+
+int yx_kv_read_pages(yx_ctx *ctx, yx_kv *kv, int layer, uint32_t first, uint32_t n_pages, void *k_host, void *v_host) {
+    return page_io(ctx, kv, layer, first, n_pages, k_host, v_host, false);
+}
+int yx_kv_write_pages(yx_ctx *ctx, yx_kv *kv, int layer, uint32_t first, uint32_t n_pages, const void *k_host,
+                      const void *v_host) {
+    return page_io(ctx, kv, layer, first, n_pages, (void *)k_host, (void *)v_host, true);
+}
+
+// ---- a pass ----------------------------------------------------------------------------
+
+int yx_begin_pass(yx_ctx *ctx, uint32_t rows, const uint32_t *pos, const uint32_t *kv_slot, const uint32_t *pt_off,
+                  const uint32_t *pages, uint32_t n_pages) {
+    if (!ctx) return YX_ERR_INVALID;
+    if (ctx->status != YX_OK) return ctx->status;
+    if (rows && (!pos || !kv_slot || !pt_off)) return fail(ctx, YX_ERR_INVALID, "begin_pass: null array");
+    if (n_pages && !pages) return fail(ctx, YX_ERR_INVALID, "begin_pass: null page table");
+    if (rows > 65535) return fail(ctx, YX_ERR_UNSUPPORTED, "begin_pass: more than 65535 rows");
+    for (uint32_t r = 0; r < rows; r++) {
+        if ((uint64_t)pt_off[r] + pos[r] / PAGE >= n_pages)
+            return fail(ctx, YX_ERR_INVALID, "begin_pass: a row's page table runs past `pages`");
+        // kv_slot must be the slot of the row's own position (PassMeta, lib.rs:69-70).
+        if (kv_slot[r] != pages[pt_off[r] + pos[r] / PAGE] * (uint32_t)PAGE + pos[r] % PAGE)
+            return fail(ctx, YX_ERR_INVALID, "begin_pass: kv_slot is not slot(pages, pos)");
+    }
+    DeviceGuard guard(ctx->device);
+    PassHost &p = ctx->pass;
+    p.rows = rows;
+    p.pos.assign(pos, pos + rows);
+    p.kv_slot.assign(kv_slot, kv_slot + rows);
+    p.pt_off.assign(pt_off, pt_off + rows);
+    p.pages.assign(pages, pages + n_pages);
+    ctx->pass_serial++;
+    ctx->have_pass = true;
+
+    size_t words = (size_t)3 * rows + n_pages;
+    if (int rc = ensure_buffer(ctx, (void **)&ctx->d_meta, &ctx->d_meta_cap, std::max<size_t>(words, 4) * 4)) return rc;
+    std::vector<uint32_t> blob(words);
+    if (rows) {
+        memcpy(blob.data(), pos, rows * 4);
+        memcpy(blob.data() + rows, kv_slot, rows * 4);
+        memcpy(blob.data() + 2 * (size_t)rows, pt_off, rows * 4);
+    }
+    if (n_pages) memcpy(blob.data() + 3 * (size_t)rows, pages, (size_t)n_pages * 4);
+    ctx->d_pos = ctx->d_meta;
+    ctx->d_slot = ctx->d_meta + rows;
+    ctx->d_ptoff = ctx->d_meta + 2 * (size_t)rows;
+    ctx->d_pages = ctx->d_meta + 3 * (size_t)rows;
+    return upload_ordered(ctx, ctx->d_meta, blob.data(), words * 4);
+}
+
+int yx_kv_append(yx_ctx *ctx, yx_kv *kv, int layer, const void *k_rows, const void *v_rows, int src_dtype) {
+    if (!ctx || !kv) return YX_ERR_INVALID;
+    if (ctx->status != YX_OK) return ctx->status;
+    if (!ctx->have_pass) return fail(ctx, YX_ERR_STATE, "kv_append without begin_pass");
+    if (layer < 0 || layer >= kv->n_layers) return fail(ctx, YX_ERR_INVALID, "layer out of range");
+    if (src_dtype != YX_F32 && src_dtype != kv->dtype)
+        return fail(ctx, YX_ERR_INVALID, "kv_append: rows must be f32 or of the cache's type");
+    if (ctx->pass.rows == 0) return YX_OK;
+    if (!k_rows || !v_rows) return fail(ctx, YX_ERR_INVALID, "null tensor");
+    for (uint32_t s : ctx->pass.kv_slot)
+        if (s / PAGE >= kv->pages) return fail(ctx, YX_ERR_INVALID, "kv_slot outside the KV arena");
+    DeviceGuard guard(ctx->device);
+    return launch_append(ctx, kv, layer, k_rows, v_rows, src_dtype);
+}
+
+int yx_attend(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, int hq, int64_t window, void *out,
+              int out_dtype) {
+    return attend_impl(ctx, kv, layer, q, q_dtype, hq, window, 0, UINT64_MAX, out, out_dtype, nullptr, nullptr, nullptr);
+}
+
+int yx_attend_partial(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, int hq, int64_t window,
+                      uint64_t key_lo, uint64_t key_hi, float *m, float *l, float *o) {
+    if (!m || !l || !o) return ctx ? fail(ctx, YX_ERR_INVALID, "null partial output") : YX_ERR_INVALID;
+    return attend_impl(ctx, kv, layer, q, q_dtype, hq, window, key_lo, key_hi, nullptr, YX_F32, m, l, o);
+}
+
+int yx_attention(yx_ctx *ctx, yx_kv *kv, int layer, const float *qkv, const float *q_norm, const float *k_norm,
+                 int hq, float eps, float *out) {
+    if (!ctx || !kv) return YX_ERR_INVALID;
+    if (ctx->status != YX_OK) return ctx->status;
+    if (!ctx->have_pass) return fail(ctx, YX_ERR_STATE, "attention without begin_pass");
+    if (layer < 0 || layer >= kv->n_layers) return fail(ctx, YX_ERR_INVALID, "layer out of range");
+    if (hq <= 0 || hq % kv->hkv != 0) return fail(ctx, YX_ERR_INVALID, "hq must be a positive multiple of hkv");
+    if (ctx->pass.rows == 0) return YX_OK;
+    if (!qkv || !q_norm || !k_norm || !out) return fail(ctx, YX_ERR_INVALID, "null tensor");
+    for (uint32_t s : ctx->pass.kv_slot)
+        if (s / PAGE >= kv->pages) return fail(ctx, YX_ERR_INVALID, "kv_slot outside the KV arena");
+    DeviceGuard guard(ctx->device);
+    size_t q_bytes = (size_t)ctx->pass.rows * hq * D * sizeof(float);
+    if (int rc = ensure_buffer(ctx, (void **)&ctx->q_tmp, &ctx->q_tmp_cap, q_bytes)) return rc;
+    // write_rows, then attend (cpu lib.rs:526-529): all rows' K/V land before any row attends.
+    if (int rc = launch_qk_rope_append(ctx, kv, layer, qkv, q_norm, k_norm, hq, eps, ctx->q_tmp)) return rc;
+    int64_t launches0 = ctx->launches - 1;
+    int rc = attend_impl(ctx, kv, layer, ctx->q_tmp, YX_F32, hq, -1, 0, UINT64_MAX, out, YX_F32, nullptr, nullptr, nullptr);
+    ctx->last_plan.launches = (int)(ctx->launches - launches0);
+    return rc;
+}
+
+int yx_lse_combine(yx_ctx *ctx, int n_parts, const float *m, const float *l, const float *o, size_t n, void *out,
+                   int out_dtype) {
+    if (!ctx) return YX_ERR_INVALID;
+    if (ctx->status != YX_OK) return ctx->status;
+    if (n_parts <= 0 || !m || !l || !o || !out || !valid_dtype(out_dtype))
+        return fail(ctx, YX_ERR_INVALID, "lse_combine: bad arguments");
+    if (n == 0) return YX_OK;
+    DeviceGuard guard(ctx->device);
+    return launch_combine_strided(ctx, n_parts, m, l, o, n, n, n * D, n, out, out_dtype);
+}
+
+}  // extern "C"

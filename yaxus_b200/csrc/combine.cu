@@ -1,0 +1,113 @@
+// Merge of split-key partials: the reference's `attn_combine`
+// (crates/yaxus-backend-gpu/src/shaders.rs:1581-1637).  One warp per (row, query head), a
+// lane holds four of the 128 dims.  Parts with l <= 0 are dropped by value, because an empty
+// part's o was never written (shaders.rs:1597-1598).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "yx_internal.h"
+
+namespace yx {
+namespace {
+
+__device__ __forceinline__ void store_out(void *out, int out_dtype, size_t elem, float4 v) {
+    if (out_dtype == YX_F32) {
+        *(float4 *)((float *)out + elem) = v;
+    } else if (out_dtype == YX_F16) {
+        __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+        uint2 pk = make_uint2(*(uint32_t *)&a, *(uint32_t *)&b);
+        *(uint2 *)((uint16_t *)out + elem) = pk;
+    } else {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 pk = make_uint2(*(uint32_t *)&a, *(uint32_t *)&b);
+        *(uint2 *)((uint16_t *)out + elem) = pk;
+    }
+}
+
+// Parts of (row, head) are slots first..first+count of its (row, kv head); the triple of
+// slot s and head-in-group g sits at index s * group + g.
+__global__ void combine_kernel(const Merge *__restrict__ merges, const float *__restrict__ part_o,
+                               const float *__restrict__ part_ml, uint32_t n, int hq, int group, void *out,
+                               int out_dtype, float *m_out, float *l_out, float *o_out) {
+    uint32_t idx = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    int lane = threadIdx.x & 31;
+    if (idx >= n) return;
+    uint32_t row = idx / (uint32_t)hq;
+    int h = (int)(idx % (uint32_t)hq), kvh = h / group, g = h % group;
+    Merge mg = merges[(size_t)row * (hq / group) + kvh];
+    float mx = -1e30f, l = 0.0f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t c = 0; c < mg.count; c++) {
+        size_t s = (size_t)(mg.first + c) * group + g;
+        float em = part_ml[s * 2], el = part_ml[s * 2 + 1];
+        if (!(el > 0.0f)) continue;
+        float4 po = *(const float4 *)(part_o + s * D + lane * 4);
+        float nm = fmaxf(mx, em);
+        float r = __expf(mx - nm), w = __expf(em - nm);
+        l = l * r + el * w;
+        acc.x = acc.x * r + po.x * w;
+        acc.y = acc.y * r + po.y * w;
+        acc.z = acc.z * r + po.z * w;
+        acc.w = acc.w * r + po.w * w;
+        mx = nm;
+    }
+    if (out) {
+        float inv = 1.0f / l;   // a row always sees its own key, so l > 0 for whole attention
+        store_out(out, out_dtype, (size_t)idx * D + lane * 4, make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv));
+    }
+    if (o_out) {
+        *(float4 *)(o_out + (size_t)idx * D + lane * 4) = acc;
+        if (lane == 0) {
+            m_out[idx] = mx;
+            l_out[idx] = l;
+        }
+    }
+}
+
+// Part c of element idx: m[c * sm + idx], l[c * sl + idx], o[c * so + idx * 128 ..].
+__global__ void combine_flat_kernel(int n_parts, const float *__restrict__ m, const float *__restrict__ l,
+                                    const float *__restrict__ o, size_t sm, size_t sl, size_t so, size_t n, void *out,
+                                    int out_dtype) {
+    size_t idx = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    int lane = threadIdx.x & 31;
+    if (idx >= n) return;
+    float mx = -1e30f, ls = 0.0f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c = 0; c < n_parts; c++) {
+        float em = m[(size_t)c * sm + idx], el = l[(size_t)c * sl + idx];
+        if (!(el > 0.0f)) continue;
+        float4 po = *(const float4 *)(o + (size_t)c * so + idx * D + lane * 4);
+        float nm = fmaxf(mx, em);
+        float r = __expf(mx - nm), w = __expf(em - nm);
+        ls = ls * r + el * w;
+        acc.x = acc.x * r + po.x * w;
+        acc.y = acc.y * r + po.y * w;
+        acc.z = acc.z * r + po.z * w;
+        acc.w = acc.w * r + po.w * w;
+        mx = nm;
+    }
+    float inv = 1.0f / ls;
+    store_out(out, out_dtype, idx * D + lane * 4, make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv));
+}
+
+}  // namespace
+
+int launch_combine(yx_ctx *ctx, const Merge *merges, const float *part_o, const float *part_ml, int rows, int hq,
+                   int group, void *out, int out_dtype, float *m_out, float *l_out, float *o_out) {
+    uint32_t n = (uint32_t)rows * (uint32_t)hq;
+    uint32_t blocks = (n * 32 + 127) / 128;
+    combine_kernel<<<blocks, 128, 0, ctx->stream>>>(merges, part_o, part_ml, n, hq, group, out, out_dtype, m_out,
+                                                   l_out, o_out);
+    ctx->launches++;
+    return check_cuda(ctx, cudaGetLastError(), "combine kernel");
+}
+
+int launch_combine_strided(yx_ctx *ctx, int n_parts, const float *m, const float *l, const float *o, size_t sm,
+                           size_t sl, size_t so, size_t n, void *out, int out_dtype) {
+    size_t blocks = (n * 32 + 127) / 128;
+    combine_flat_kernel<<<(unsigned)blocks, 128, 0, ctx->stream>>>(n_parts, m, l, o, sm, sl, so, n, out, out_dtype);
+    ctx->launches++;
+    return check_cuda(ctx, cudaGetLastError(), "combine_flat kernel");
+}
+
+}  // namespace yx

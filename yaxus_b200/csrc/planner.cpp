@@ -1,0 +1,280 @@
+// Host-side planner of the split-key attention kernels: the counterpart of the reference's
+// `AttentionCase::plan` (crates/yaxus-backend-gpu/src/plan.rs:275-309), re-thought for a
+// persistent kernel on 148 SMs.
+//
+// The reference cuts every row's context into fixed chunks of 16/32 keys and launches one
+// workgroup per (row, KV head, chunk).  Here the keys of all rows are laid end to end as one
+// sequence of 64-key tiles and that sequence is cut into one equal span per persistent CTA
+// ("stream-K"), so every CTA streams the same number of bytes whatever the mix of context
+// lengths, and a (row, head) gets as many partial triples as CTAs touched it.
+//
+// Rows whose page tables name the same physical pages over a common prefix (what
+// `KvCache::fork` shares, crates/yaxus-model/src/kv.rs:277-295) are put in one item over that
+// prefix, so the shared pages are read once for all of them.
+#include <algorithm>
+#include <string>
+#include <unordered_map>
+
+#include "yx_internal.h"
+
+namespace yx {
+namespace {
+
+struct Group {          // consecutive rows of one sequence
+    uint32_t row0, n;
+    uint32_t pt_off;
+    uint32_t lo, hi;    // keys any of its rows may see, inclusive (after the range restriction)
+    bool live;
+};
+
+struct Unit {           // rows x one key range, before it is cut across CTAs (all KV heads)
+    std::vector<uint16_t> rows;
+    uint32_t pt_off;
+    uint32_t lo, hi;    // inclusive
+};
+
+inline uint32_t row_lo(uint32_t pos, int64_t window) {
+    // cpu lib.rs:402-405: (p + 1).saturating_sub(w)
+    if (window <= 0) return 0;
+    uint64_t p1 = (uint64_t)pos + 1;
+    return p1 > (uint64_t)window ? (uint32_t)(p1 - (uint64_t)window) : 0u;
+}
+
+int padded_rows(int q_rows) { return q_rows <= 16 ? 16 : (q_rows <= 32 ? 32 : 64); }
+
+}  // namespace
+
+void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
+    const uint32_t T = pass.rows;
+    if (pp.hkv <= 0 || pp.group <= 0) throw std::string("bad head counts");
+    if (pp.max_rows < 1 || pp.max_rows > MAX_ITEM_ROWS) throw std::string("bad rows per item");
+    if (T > 65535) throw std::string("a pass holds at most 65535 rows");
+    out = Plan();
+
+    // 1. Row groups: runs of rows with the same page table.
+    std::vector<Group> groups;
+    for (uint32_t i = 0; i < T;) {
+        uint32_t j = i + 1;
+        while (j < T && pass.pt_off[j] == pass.pt_off[i]) j++;
+        groups.push_back({i, j - i, pass.pt_off[i], 0, 0, false});
+        i = j;
+    }
+    // Every page-table entry a row can reach must exist.
+    for (const Group &g : groups) {
+        for (uint32_t r = g.row0; r < g.row0 + g.n; r++) {
+            uint64_t need = (uint64_t)g.pt_off + pass.pos[r] / PAGE + 1;
+            if (need > pass.pages.size()) throw std::string("a row's page table runs past `pages`");
+        }
+    }
+
+    // 2. Units.  First the per-sequence ones, rows chunked to max_rows.
+    std::vector<Unit> units;
+    struct Solo { size_t unit; uint32_t group; };
+    std::vector<Solo> solos;   // units that hold all rows of one group (candidates for sharing)
+    for (uint32_t gi = 0; gi < groups.size(); gi++) {
+        const Group &g = groups[gi];
+        for (uint32_t a = 0; a < g.n; a += pp.max_rows) {
+            uint32_t b = std::min<uint32_t>(g.n, a + pp.max_rows);
+            Unit u;
+            u.pt_off = g.pt_off;
+            uint64_t lo = UINT64_MAX, hi = 0;
+            for (uint32_t r = g.row0 + a; r < g.row0 + b; r++) {
+                u.rows.push_back((uint16_t)r);
+                lo = std::min<uint64_t>(lo, row_lo(pass.pos[r], pp.window));
+                hi = std::max<uint64_t>(hi, pass.pos[r]);
+            }
+            lo = std::max<uint64_t>(lo, pp.key_lo);
+            if (pp.key_hi != UINT64_MAX) {
+                if (pp.key_hi == 0) continue;
+                hi = std::min<uint64_t>(hi, pp.key_hi - 1);
+            }
+            if (lo > hi) continue;   // no live key: the rows keep zero partials
+            u.lo = (uint32_t)lo;
+            u.hi = (uint32_t)hi;
+            if (a == 0 && b == g.n) solos.push_back({units.size(), gi});
+            units.push_back(std::move(u));
+        }
+    }
+
+    uint64_t logical = 0;   // keys read if every unit streamed its own copy
+    for (const Unit &u : units) logical += (uint64_t)u.hi - u.lo + 1;
+
+    // 3. Shared prefixes.  Cluster whole-group units by their first page; within a cluster
+    //    the common run of identical page ids is read once for all member rows.
+    int shared_groups = 0;
+    if (pp.share_prefix && pp.max_rows > 1 && solos.size() > 1) {
+        std::unordered_map<uint64_t, std::vector<size_t>> by_first;   // first page id -> solos
+        std::vector<uint64_t> order;
+        for (size_t si = 0; si < solos.size(); si++) {
+            const Unit &u = units[solos[si].unit];
+            uint32_t first_pg = u.lo / PAGE;
+            uint64_t key = ((uint64_t)first_pg << 32) | pass.pages[u.pt_off + first_pg];
+            auto it = by_first.find(key);
+            if (it == by_first.end()) {
+                order.push_back(key);
+                by_first[key] = {si};
+            } else {
+                it->second.push_back(si);
+            }
+        }
+        std::vector<Unit> shared_units;
+        for (uint64_t key : order) {
+            const std::vector<size_t> &members = by_first[key];
+            if (members.size() < 2) continue;
+            // Pack members into clusters of at most max_rows rows.
+            size_t at = 0;
+            while (at < members.size()) {
+                size_t end = at;
+                size_t rows = 0;
+                while (end < members.size() && rows + units[solos[members[end]].unit].rows.size() <= (size_t)pp.max_rows) {
+                    rows += units[solos[members[end]].unit].rows.size();
+                    end++;
+                }
+                if (end - at < 2) {
+                    at = std::max(end, at + 1);
+                    continue;
+                }
+                // Common run of pages, starting at the first page of the latest-starting member.
+                uint32_t pg0 = 0, pg_end = UINT32_MAX;
+                for (size_t k = at; k < end; k++) {
+                    const Unit &u = units[solos[members[k]].unit];
+                    pg0 = std::max(pg0, u.lo / PAGE);
+                    pg_end = std::min(pg_end, u.hi / PAGE + 1);   // pages this member has at all
+                }
+                const Unit &u0 = units[solos[members[at]].unit];
+                uint32_t common = pg0;
+                while (common < pg_end) {
+                    uint32_t id = pass.pages[u0.pt_off + common];
+                    bool same = true;
+                    for (size_t k = at + 1; k < end && same; k++)
+                        same = pass.pages[units[solos[members[k]].unit].pt_off + common] == id;
+                    if (!same) break;
+                    common++;
+                }
+                // A page that some member is still writing in this pass (its last, partly
+                // filled page) is never shared by construction of the page tables: a shared
+                // page is copied before it is written (kv.rs:299-326).
+                if (common > pg0) {
+                    Unit su;
+                    su.pt_off = u0.pt_off;
+                    uint32_t lo = UINT32_MAX, hi = 0;
+                    for (size_t k = at; k < end; k++) {
+                        Unit &u = units[solos[members[k]].unit];
+                        for (uint16_t r : u.rows) su.rows.push_back(r);
+                        lo = std::min(lo, u.lo);
+                        // keys of the shared run this member can see
+                        uint32_t h = std::min<uint32_t>(u.hi, common * PAGE - 1);
+                        hi = std::max(hi, h);
+                    }
+                    su.lo = std::max<uint32_t>(lo, pg0 * PAGE);
+                    su.hi = hi;
+                    if (su.lo <= su.hi) {
+                        // Members start after the shared run (or before it, for the keys in
+                        // front of pg0, which stay private).
+                        bool ok = true;
+                        for (size_t k = at; k < end; k++)
+                            if (units[solos[members[k]].unit].lo < pg0 * PAGE) ok = false;
+                        if (ok) {
+                            for (size_t k = at; k < end; k++) {
+                                Unit &u = units[solos[members[k]].unit];
+                                if (u.hi < common * PAGE) {
+                                    u.rows.clear();   // wholly inside the shared run
+                                } else {
+                                    u.lo = std::max<uint32_t>(u.lo, common * PAGE);
+                                }
+                            }
+                            shared_units.push_back(std::move(su));
+                            shared_groups++;
+                        }
+                    }
+                }
+                at = end;
+            }
+        }
+        // Shared units first: they are the long-running items.
+        std::vector<Unit> all;
+        for (Unit &u : shared_units) all.push_back(std::move(u));
+        for (Unit &u : units)
+            if (!u.rows.empty()) all.push_back(std::move(u));
+        units.swap(all);
+    }
+
+    // 4. Cut the tile sequence (units x KV heads) into one span per CTA.
+    uint64_t total_tiles = 0;
+    for (const Unit &u : units) total_tiles += (uint64_t)(u.hi / TILE_KEYS - u.lo / TILE_KEYS + 1) * pp.hkv;
+    int n_ctas = (int)std::min<uint64_t>((uint64_t)std::max(1, pp.n_ctas), std::max<uint64_t>(total_tiles, 1));
+    out.n_ctas = n_ctas;
+    out.cta_begin.assign(n_ctas + 1, 0);
+    out.merges.assign((size_t)T * pp.hkv, Merge{0, 0});
+
+    uint64_t done = 0;
+    int cta = 0;
+    auto span_end = [&](int c) { return total_tiles * (uint64_t)(c + 1) / (uint64_t)n_ctas; };
+    std::unordered_map<uint64_t, uint32_t> seen;   // (physical page, half) -> most keys read
+    for (const Unit &u : units) {
+        uint32_t t0 = u.lo / TILE_KEYS, t1 = u.hi / TILE_KEYS + 1;
+        for (uint32_t t = t0; t < t1; t++) {
+            uint32_t a = std::max(u.lo, t * TILE_KEYS), b = std::min(u.hi, t * TILE_KEYS + TILE_KEYS - 1);
+            uint32_t n = b - a + 1;
+            uint64_t key = ((uint64_t)pass.pages[u.pt_off + t * TILE_KEYS / PAGE] << 1) | (t & 1);
+            uint32_t &s = seen[key];
+            s = std::max(s, n);
+        }
+        for (int kh = 0; kh < pp.hkv; kh++) {
+            uint32_t t = t0;
+            while (t < t1) {
+                while (cta < n_ctas - 1 && done >= span_end(cta)) {
+                    cta++;
+                    out.cta_begin[cta] = (uint32_t)out.items.size();
+                }
+                uint64_t room = span_end(cta) - done;
+                if (cta == n_ctas - 1) room = UINT64_MAX;
+                uint32_t take = (uint32_t)std::min<uint64_t>(room, t1 - t);
+                Item it{};
+                it.tile_begin = t;
+                it.tile_end = t + take;
+                it.key_lo = u.lo;
+                it.key_hi = u.hi;
+                it.pt_off = u.pt_off;
+                it.kv_head = (uint16_t)kh;
+                it.n_rows = (uint16_t)u.rows.size();
+                it.mt = (uint32_t)padded_rows((int)u.rows.size() * pp.group);
+                for (size_t r = 0; r < u.rows.size(); r++) {
+                    it.rows[r] = u.rows[r];
+                    out.merges[(size_t)u.rows[r] * pp.hkv + kh].count++;
+                }
+                out.items.push_back(it);
+                t += take;
+                done += take;
+            }
+        }
+    }
+    for (int c = cta + 1; c <= n_ctas; c++) out.cta_begin[c] = (uint32_t)out.items.size();
+
+    // 5. Partial slots: contiguous per (row, kv head).
+    uint32_t next = 0;
+    for (Merge &m : out.merges) {
+        m.first = next;
+        next += m.count;
+        m.count = 0;
+    }
+    out.n_parts = next;
+    for (Item &it : out.items)
+        for (int r = 0; r < it.n_rows; r++) {
+            Merge &m = out.merges[(size_t)it.rows[r] * pp.hkv + it.kv_head];
+            it.part[r] = m.first + m.count++;
+        }
+
+    uint64_t uniq = 0;
+    for (auto &kv : seen) uniq += kv.second;
+    out.info.n_ctas = n_ctas;
+    out.info.n_items = (int)out.items.size();
+    out.info.n_parts = (int)out.n_parts;
+    out.info.tiles = (int64_t)total_tiles;
+    const int64_t per_key = (int64_t)2 * D * pp.esize * pp.hkv;   // K and V of every KV head
+    out.info.unique_kv_bytes = (int64_t)uniq * per_key;
+    out.info.logical_kv_bytes = (int64_t)logical * per_key;
+    out.info.shared_groups = shared_groups;
+}
+
+}  // namespace yx

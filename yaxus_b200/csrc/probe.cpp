@@ -1,0 +1,55 @@
+// Test hook: the split-key planner on host arrays, without a device.
+#include <string.h>
+
+#include "yx_internal.h"
+
+extern "C" int yx_plan_probe(uint32_t rows, const uint32_t *pos, const uint32_t *pt_off, const uint32_t *pages,
+                             uint32_t n_pages, int hkv, int group, int64_t window, uint64_t key_lo, uint64_t key_hi,
+                             int max_rows, int n_ctas, int share_prefix, int esize, yx_plan_info *info,
+                             uint32_t *items_out, uint32_t max_items) {
+    if (rows && (!pos || !pt_off)) return YX_ERR_INVALID;
+    yx::PassHost pass;
+    pass.rows = rows;
+    pass.pos.assign(pos, pos + rows);
+    pass.pt_off.assign(pt_off, pt_off + rows);
+    pass.pages.assign(pages, pages + n_pages);
+    yx::PlanParams pp{};
+    pp.hkv = hkv;
+    pp.group = group;
+    pp.window = window > 0 ? window : 0;
+    pp.key_lo = key_lo;
+    pp.key_hi = key_hi;
+    pp.max_rows = max_rows;
+    pp.n_ctas = n_ctas;
+    pp.share_prefix = share_prefix != 0;
+    pp.esize = esize;
+    yx::Plan plan;
+    try {
+        yx::build_split_plan(pass, pp, plan);
+    } catch (const std::string &) {
+        return YX_ERR_INVALID;
+    }
+    if (info) *info = plan.info;
+    if (items_out) {
+        uint32_t cta = 0;
+        for (uint32_t i = 0; i < plan.items.size() && i < max_items; i++) {
+            while (cta + 1 < plan.cta_begin.size() && plan.cta_begin[cta + 1] <= i) cta++;
+            const yx::Item &it = plan.items[i];
+            uint32_t *o = items_out + (size_t)i * YX_PROBE_ITEM_WORDS;
+            o[0] = it.tile_begin;
+            o[1] = it.tile_end;
+            o[2] = it.key_lo;
+            o[3] = it.key_hi;
+            o[4] = it.pt_off;
+            o[5] = it.kv_head;
+            o[6] = it.n_rows;
+            o[7] = it.mt;
+            o[8] = cta;
+            for (int r = 0; r < yx::MAX_ITEM_ROWS; r++) {
+                o[9 + r] = it.rows[r];
+                o[9 + yx::MAX_ITEM_ROWS + r] = it.part[r];
+            }
+        }
+    }
+    return YX_OK;
+}

@@ -1,0 +1,229 @@
+// Internal declarations shared by the translation units of libyaxus_cuda.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/yaxus_cuda.h"
+
+namespace yx {
+
+constexpr int PAGE = YX_PAGE;   // tokens per page (crates/yaxus-model/src/kv.rs:17)
+constexpr int D = YX_HEAD_DIM;  // head_dim
+constexpr int TILE_KEYS = 64;   // keys per streamed tile (half a page)
+constexpr int MAX_ITEM_ROWS = 16;
+
+// ----------------------------------------------------------------------------------------
+// KV storage layout (private to the library; `Kv` is opaque to yaxus-model).
+//
+// Per layer there is one K and one V arena.  A (page, kv head) block holds the page's 128
+// tokens of that head contiguously, so that a split-key CTA streams whole blocks with bulk
+// copies instead of gathering 256-byte pieces from token-major rows.
+//   f32  : [page][hkv][tok 128][128 f32]                      (64 KiB per block)
+//   16bit: [page][hkv][dhalf 2][tok 128][64 elements = 128 B] (32 KiB per block)
+//          with the eight 16-byte chunks of every 128-byte row stored at chunk ^ (tok & 7).
+// The 16-bit form is exactly the 128-byte-swizzled shared-memory layout that ldmatrix reads
+// without bank conflicts and that tcgen05 matrix descriptors name as SWIZZLE_128B, so a bulk
+// copy of any run of rows lands ready for the tensor cores.
+// ----------------------------------------------------------------------------------------
+__host__ __device__ inline size_t kv_block_elems() { return (size_t)PAGE * D; }
+
+// Element offset of (page, kvh, tok, dim) inside a layer's arena, 16-bit storage.
+__host__ __device__ inline size_t kv_off16(uint32_t page, int hkv, int kvh, int tok, int dim) {
+    size_t blk = ((size_t)page * hkv + kvh) * kv_block_elems();
+    int dh = dim >> 6, c = (dim & 63) >> 3, e = dim & 7;
+    return blk + (size_t)dh * (PAGE * 64) + (size_t)tok * 64 + (size_t)((c ^ (tok & 7)) << 3) + e;
+}
+// Element offset, f32 storage.
+__host__ __device__ inline size_t kv_off32(uint32_t page, int hkv, int kvh, int tok, int dim) {
+    return ((size_t)page * hkv + kvh) * kv_block_elems() + (size_t)tok * D + dim;
+}
+
+// ----------------------------------------------------------------------------------------
+// Plan of one attention call (host-built, uploaded with the pass).
+// ----------------------------------------------------------------------------------------
+
+// One piece of split-key work: some rows of the pass (they share a page table over the
+// item's keys) against the keys of tiles [tile_begin, tile_end) of one KV head.
+struct alignas(16) Item {
+    uint32_t tile_begin;   // in units of TILE_KEYS keys of logical position
+    uint32_t tile_end;     // exclusive
+    uint32_t key_lo;       // first key any row of the item may see (inclusive)
+    uint32_t key_hi;       // last key any row of the item may see (inclusive)
+    uint32_t pt_off;       // offset of the page table in the pass's `pages`
+    uint16_t kv_head;
+    uint16_t n_rows;
+    uint16_t rows[MAX_ITEM_ROWS];        // pass rows
+    uint32_t part[MAX_ITEM_ROWS];        // partial slot of each row for this KV head
+    uint32_t mt;                         // padded query rows (n_rows * group rounded up): 16, 32 or 64
+    uint32_t pad_;
+};
+static_assert(sizeof(Item) == 128, "Item is 128 bytes");
+
+// Where the combine kernel finds the partials of one (row, kv head).
+struct Merge {
+    uint32_t first;  // first partial slot
+    uint32_t count;  // slots
+};
+
+struct Plan {
+    int path = 0;
+    int n_ctas = 0;
+    std::vector<Item> items;
+    std::vector<uint32_t> cta_begin;    // n_ctas + 1 offsets into items
+    std::vector<Merge> merges;          // [rows][hkv]
+    uint32_t n_parts = 0;
+    yx_plan_info info{};
+};
+
+struct PassHost {
+    uint32_t rows = 0;
+    std::vector<uint32_t> pos, kv_slot, pt_off, pages;
+};
+
+struct PlanParams {
+    int hkv, group;          // group = hq / hkv
+    int64_t window;          // <= 0: none
+    uint64_t key_lo, key_hi; // extra restriction [key_lo, key_hi) (UINT64_MAX = none)
+    int max_rows;            // rows per item (1 for the SIMT kernel)
+    int n_ctas;              // persistent CTAs to fill
+    bool share_prefix;
+    int esize;               // bytes per stored element
+};
+
+// Builds the split-key plan.  Throws std::string on a malformed pass.
+void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out);
+
+}  // namespace yx
+
+// ----------------------------------------------------------------------------------------
+// Objects behind the opaque handles.
+// ----------------------------------------------------------------------------------------
+struct yx_kv {
+    int n_layers = 0, hkv = 0, dtype = 0, esize = 4;
+    uint32_t pages = 0, max_pos = 0;
+    size_t layer_bytes = 0;            // bytes of one K (or V) arena
+    std::vector<yx_layer> layers;
+    char *k_base = nullptr;            // [layer][arena]
+    char *v_base = nullptr;
+    void *rope_dev = nullptr;          // yx_rope per layer
+    char *k(int layer) const { return k_base + (size_t)layer * layer_bytes; }
+    char *v(int layer) const { return v_base + (size_t)layer * layer_bytes; }
+};
+
+struct yx_dev_status {
+    int code;      // first failed device check (0 = none)
+    int where;     // kernel-specific location
+    int a, b;
+};
+
+struct ncclComm;
+
+struct yx_ctx {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    int status = 0;
+    std::string error;
+    yx_tuning tuning{};
+    yx_plan_info last_plan{};
+    int64_t launches = 0;
+    bool smem_configured[8] = {};          // per-kernel opt-in to large dynamic shared memory
+
+    yx_dev_status *dev_status = nullptr;   // pinned, mapped
+
+    // pass metadata
+    yx::PassHost pass;
+    bool have_pass = false;
+    uint64_t pass_serial = 0;
+    uint32_t *d_meta = nullptr;            // pos | kv_slot | pt_off | pages
+    size_t d_meta_cap = 0;
+    uint32_t *d_pos = nullptr, *d_slot = nullptr, *d_ptoff = nullptr, *d_pages = nullptr;
+
+    // pinned staging ring for stream-ordered uploads
+    struct Stage {
+        void *host = nullptr;
+        size_t cap = 0;
+        cudaEvent_t done = nullptr;
+        bool busy = false;
+    };
+    std::vector<Stage> ring;
+    size_t ring_next = 0;
+
+    // cached plans of the current pass
+    struct CachedPlan {
+        uint64_t pass_serial = 0;
+        int hkv = 0, group = 0, max_rows = 0, n_ctas = 0, esize = 0;
+        int64_t window = 0;
+        uint64_t key_lo = 0, key_hi = 0;
+        bool share = false;
+        yx::Plan plan;
+        char *dev = nullptr;       // items | cta_begin | merges
+        size_t dev_cap = 0;
+        yx::Item *d_items = nullptr;
+        uint32_t *d_cta_begin = nullptr;
+        yx::Merge *d_merges = nullptr;
+    };
+    std::vector<CachedPlan> plans;
+
+    // scratch: partial triples
+    float *ws_o = nullptr;   // [n_parts][group][128]
+    float *ws_ml = nullptr;  // [n_parts][group][2]
+    size_t ws_o_cap = 0, ws_ml_cap = 0;
+    float *q_tmp = nullptr;  // normalised, rotated q of yx_attention
+    size_t q_tmp_cap = 0;
+
+    // multi-GPU
+    ncclComm *comm = nullptr;
+    int n_ranks = 1, rank = 0;
+    float *gather_buf = nullptr;
+    size_t gather_cap = 0;
+};
+
+namespace yx {
+
+int fail(yx_ctx *ctx, int code, const std::string &msg);
+int check_cuda(yx_ctx *ctx, cudaError_t e, const char *what);
+// Stream-ordered upload of `bytes` from pageable host memory through the pinned ring.
+int upload_ordered(yx_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes);
+int ensure_buffer(yx_ctx *ctx, void **buf, size_t *cap, size_t bytes);
+
+// Kernel launchers (each returns a yx_error and counts its launches in ctx->launches).
+int launch_append(yx_ctx *ctx, yx_kv *kv, int layer, const void *k_rows, const void *v_rows, int src_dtype);
+int launch_qk_rope_append(yx_ctx *ctx, yx_kv *kv, int layer, const float *qkv, const float *q_norm,
+                          const float *k_norm, int hq, float eps, float *q_out);
+int launch_copy_page(yx_ctx *ctx, yx_kv *kv, uint32_t src, uint32_t dst);
+int launch_page_io(yx_ctx *ctx, yx_kv *kv, int layer, uint32_t first_page, uint32_t n_pages, void *k_lin, void *v_lin,
+                   bool write);
+
+struct AttendArgs {
+    const void *q;
+    int q_dtype;
+    int hq;
+    int group;
+    const char *k_arena;
+    const char *v_arena;
+    int hkv;
+    int kv_dtype;
+    uint32_t kv_pages;
+    int64_t window;
+    uint64_t key_lo, key_hi;
+    const Item *items;
+    const uint32_t *cta_begin;
+    int n_ctas;
+    float *part_o;
+    float *part_ml;
+};
+int launch_attend_simt(yx_ctx *ctx, const AttendArgs &a);
+int launch_attend_mma(yx_ctx *ctx, const AttendArgs &a);
+int launch_combine(yx_ctx *ctx, const Merge *merges, const float *part_o, const float *part_ml, int rows,
+                   int hq, int group, void *out, int out_dtype, float *m_out, float *l_out, float *o_out);
+// Parts with strides (in floats) sm, sl, so between consecutive parts of m, l and o.
+int launch_combine_strided(yx_ctx *ctx, int n_parts, const float *m, const float *l, const float *o, size_t sm,
+                           size_t sl, size_t so, size_t n, void *out, int out_dtype);
+
+}  // namespace yx
