@@ -103,6 +103,13 @@ int yx_set_tuning(yx_ctx *ctx, const yx_tuning *tuning);
 int yx_last_plan(const yx_ctx *ctx, yx_plan_info *out);
 /* Kernels this context has launched so far. */
 int64_t yx_launch_count(const yx_ctx *ctx);
+/* Per-kernel device time, the counterpart of the reference's YAXUS_PROFILE=2 timestamp
+ * queries (crates/yaxus-backend-gpu/src/profile.rs:1-64).  Between begin and end every
+ * split-key kernel and every combine kernel is bracketed by CUDA events on the stream;
+ * yx_profile_end waits for the stream and returns the summed milliseconds and the number of
+ * attention calls measured (at most 4096; later calls are not timed). */
+int yx_profile_begin(yx_ctx *ctx);
+int yx_profile_end(yx_ctx *ctx, float *split_ms, float *combine_ms, int *calls);
 
 /* ---- tensors: the backend's `Tensor` plumbing and `SyncReadback::to_host`
  *      (crates/yaxus-model/src/lib.rs:177-185) ------------------------------------------ */

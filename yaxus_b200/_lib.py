@@ -52,6 +52,8 @@ SIGNATURES = {
     "yx_set_tuning": (c_int, [c_void_p, POINTER(Tuning)]),
     "yx_last_plan": (c_int, [c_void_p, POINTER(PlanInfo)]),
     "yx_launch_count": (c_int64, [c_void_p]),
+    "yx_profile_begin": (c_int, [c_void_p]),
+    "yx_profile_end": (c_int, [c_void_p, POINTER(c_float), POINTER(c_float), POINTER(c_int)]),
     "yx_tensor_alloc": (c_int, [c_void_p, c_size_t, POINTER(c_void_p)]),
     "yx_tensor_free": (c_int, [c_void_p, c_void_p]),
     "yx_upload": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t]),

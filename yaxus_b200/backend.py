@@ -155,6 +155,17 @@ class CudaBackend:
     def launch_count(self) -> int:
         return self._L.yx_launch_count(self._ctx)
 
+    def profile_begin(self) -> None:
+        self._L.yx_profile_begin(self._ctx)
+
+    def profile_end(self):
+        """(split-key kernel ms, combine kernel ms, attention calls) since profile_begin."""
+        a, b, n = ctypes.c_float(0), ctypes.c_float(0), ctypes.c_int(0)
+        rc = self._L.yx_profile_end(self._ctx, ctypes.byref(a), ctypes.byref(b), ctypes.byref(n))
+        if rc != _lib.YX_OK:
+            raise BackendError(rc, self.last_error())
+        return a.value, b.value, n.value
+
     # ---- Backend::new_kv / copy_page / begin_pass / attention ---------------------------
     def new_kv(self, hkv: int, layers: Sequence[LayerMeta], pages: int, max_pos: int, dtype: int = F32,
                head_dim: int = HEAD_DIM) -> Kv:

@@ -23,6 +23,14 @@ int check_cuda(yx_ctx *ctx, cudaError_t e, const char *what) {
     return fail(ctx, code, std::string(what) + ": " + cudaGetErrorString(e));
 }
 
+void profile_mark(yx_ctx *ctx, int which) {
+    if (!ctx->profiling) return;
+    size_t idx = ctx->prof_used * 4 + which;
+    if (idx >= ctx->prof_events.size()) return;
+    cudaEventRecord(ctx->prof_events[idx], ctx->stream);
+    if (which == 3) ctx->prof_used++;
+}
+
 int ensure_buffer(yx_ctx *ctx, void **buf, size_t *cap, size_t bytes) {
     if (bytes <= *cap && *buf) return YX_OK;
     size_t want = std::max<size_t>(bytes, 256);
@@ -241,13 +249,17 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     a.n_ctas = pl.n_ctas;
     a.part_o = ctx->ws_o;
     a.part_ml = ctx->ws_ml;
+    profile_mark(ctx, 0);
     if (!pl.items.empty()) {
         int rc = path == 1 ? launch_attend_simt(ctx, a) : launch_attend_mma(ctx, a);
         if (rc) return rc;
     }
+    profile_mark(ctx, 1);
+    profile_mark(ctx, 2);
     if (int rc = launch_combine(ctx, cp->d_merges, ctx->ws_o, ctx->ws_ml, (int)ctx->pass.rows, hq, group, out,
                                 out_dtype, m_out, l_out, o_out))
         return rc;
+    profile_mark(ctx, 3);
     ctx->last_plan = pl.info;
     ctx->last_plan.path = path;
     ctx->last_plan.launches = (int)(ctx->launches - launches0);
@@ -311,6 +323,8 @@ void yx_ctx_destroy(yx_ctx *ctx) {
     if (ctx->q_tmp) cudaFree(ctx->q_tmp);
     if (ctx->gather_buf) cudaFree(ctx->gather_buf);
     if (ctx->dev_status) cudaFreeHost(ctx->dev_status);
+    for (auto &e : ctx->prof_events)
+        if (e) cudaEventDestroy(e);
     if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -348,6 +362,36 @@ int yx_last_plan(const yx_ctx *ctx, yx_plan_info *out) {
 }
 
 int64_t yx_launch_count(const yx_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
+int yx_profile_begin(yx_ctx *ctx) {
+    if (!ctx) return YX_ERR_INVALID;
+    DeviceGuard guard(ctx->device);
+    if (ctx->prof_events.empty()) {
+        ctx->prof_events.resize(4 * 4096, nullptr);
+        for (auto &e : ctx->prof_events)
+            if (int rc = check_cuda(ctx, cudaEventCreate(&e), "cudaEventCreate (profile)")) return rc;
+    }
+    ctx->prof_used = 0;
+    ctx->profiling = true;
+    return YX_OK;
+}
+
+int yx_profile_end(yx_ctx *ctx, float *split_ms, float *combine_ms, int *calls) {
+    if (!ctx) return YX_ERR_INVALID;
+    DeviceGuard guard(ctx->device);
+    ctx->profiling = false;
+    if (int rc = yx_sync(ctx)) return rc;
+    float a = 0.f, b = 0.f;
+    for (size_t i = 0; i < ctx->prof_used; i++) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, ctx->prof_events[4 * i], ctx->prof_events[4 * i + 1]) == cudaSuccess) a += ms;
+        if (cudaEventElapsedTime(&ms, ctx->prof_events[4 * i + 2], ctx->prof_events[4 * i + 3]) == cudaSuccess) b += ms;
+    }
+    if (split_ms) *split_ms = a;
+    if (combine_ms) *combine_ms = b;
+    if (calls) *calls = (int)ctx->prof_used;
+    return YX_OK;
+}
 
 // ---- tensors ---------------------------------------------------------------------------
 

@@ -136,6 +136,11 @@ struct yx_ctx {
 
     yx_dev_status *dev_status = nullptr;   // pinned, mapped
 
+    // per-kernel timing (yx_profile_begin / yx_profile_end)
+    bool profiling = false;
+    std::vector<cudaEvent_t> prof_events;  // 4 per call: split start/stop, combine start/stop
+    size_t prof_used = 0;
+
     // pass metadata
     yx::PassHost pass;
     bool have_pass = false;
@@ -187,6 +192,8 @@ struct yx_ctx {
 namespace yx {
 
 int fail(yx_ctx *ctx, int code, const std::string &msg);
+// When profiling, records the next timing event of the current attention call (which = 0..3).
+void profile_mark(yx_ctx *ctx, int which);
 int check_cuda(yx_ctx *ctx, cudaError_t e, const char *what);
 // Stream-ordered upload of `bytes` from pageable host memory through the pinned ring.
 int upload_ordered(yx_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes);
