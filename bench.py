@@ -66,6 +66,9 @@ class ClockSampler:
 
     def stop(self):
         if self.proc:
+            t0 = time.time()
+            while not self.rows and time.time() - t0 < 3.0:   # a very short run: wait for one sample
+                time.sleep(0.05)
             self.proc.terminate()
         sm, mx, reasons = [], [], set()
         for r in self.rows:
@@ -191,11 +194,11 @@ def run_cuda(args):
         step(0)
         if not split_kv or world == 1:
             max_err = assert_close(b.to_host(out), oracle_step(Oracle(), s), what="bench parity")
+    sampler = ClockSampler(local)
+    sampler.start()
     for i in range(max(args.warmup, 3)):
         step(i)
     barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
     launches0 = b.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -209,11 +212,11 @@ def run_cuda(args):
     info = b.last_plan()
 
     # per-kernel time of the dominant kernel, measured live with CUDA events
+    clocks = sampler.stop()
     b.profile_begin()
-    for i in range(args.steps):
+    for i in range(min(args.steps, 4096)):
         step(i)
     split_ms, combine_ms, calls = b.profile_end()
-    clocks = sampler.stop()
     kernel_ms = split_ms / max(calls, 1)
 
     # end to end through the boundary call: pass metadata and qkv rows from pinned host
@@ -305,8 +308,8 @@ def cpu_baseline(s):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=20000)
+    ap.add_argument("--warmup", type=int, default=200)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--workload", default="batched_decode")
     ap.add_argument("--no-check", action="store_true")

@@ -69,7 +69,9 @@ typedef struct yx_tuning {
     int32_t ctas_per_sm;     /* persistent CTAs per SM for the split-key kernels */
     int32_t share_prefix;    /* 0 default (on), 1 on, 2 off: read pages shared by several rows once */
     int32_t tile_min_rows;   /* rows of one sequence from which the tcgen05 tile kernel is used */
-    int32_t reserved[4];
+    int32_t cost32;          /* planner cost of a 64-key tile of an item with 32 padded query rows, */
+    int32_t cost64;          /* and with 64, in 16ths of the cost of a 16-row item's tile */
+    int32_t reserved[2];
 } yx_tuning;
 
 /* What the last yx_attend / yx_attention call planned; for tests and benchmarks. */
@@ -88,7 +90,8 @@ typedef struct yx_plan_info {
 /* ---- context ------------------------------------------------------------------------ */
 
 /* One context per GPU (the reference's `Gpu` device object, crates/yaxus-backend-gpu/src/lib.rs:235-246).
- * `stream` is a cudaStream_t to enqueue on, or NULL to create a private non-blocking stream. */
+ * `stream` is a cudaStream_t to enqueue on, or NULL to create a private non-blocking stream
+ * (to share the legacy default stream pass cudaStreamLegacy, not NULL). */
 int yx_ctx_create(int device, void *stream, yx_ctx **out);
 void yx_ctx_destroy(yx_ctx *ctx);
 /* Sticky first error; YX_OK / "" when none. */
@@ -200,8 +203,8 @@ int yx_attend_allgather(yx_ctx *ctx, yx_kv *kv, int layer, const void *q_dev, in
 #define YX_PROBE_ITEM_WORDS 41
 int yx_plan_probe(uint32_t rows, const uint32_t *pos_host, const uint32_t *pt_off_host, const uint32_t *pages_host,
                   uint32_t n_pages, int hkv, int group, int64_t window, uint64_t key_lo, uint64_t key_hi,
-                  int max_rows, int n_ctas, int share_prefix, int esize, yx_plan_info *info, uint32_t *items_out,
-                  uint32_t max_items);
+                  int max_rows, int n_ctas, int share_prefix, int esize, int cost32, int cost64, yx_plan_info *info,
+                  uint32_t *items_out, uint32_t max_items);
 
 #ifdef __cplusplus
 }

@@ -14,7 +14,8 @@ from yaxus_b200.kvcache import PassMeta
 U64_MAX = (1 << 64) - 1
 
 
-def probe(meta, hkv, group, window=0, key_lo=0, key_hi=U64_MAX, max_rows=16, n_ctas=148, share=1, esize=2):
+def probe(meta, hkv, group, window=0, key_lo=0, key_hi=U64_MAX, max_rows=16, n_ctas=148, share=1, esize=2, cost32=16,
+          cost64=32):
     L = _lib.cuda_lib()
     info = _lib.PlanInfo()
     cap = 200000
@@ -22,7 +23,7 @@ def probe(meta, hkv, group, window=0, key_lo=0, key_hi=U64_MAX, max_rows=16, n_c
     p = lambda a: np.ascontiguousarray(a, np.uint32).ctypes.data_as(ctypes.POINTER(ctypes.c_uint32))
     pos, off, pages = (np.ascontiguousarray(x, np.uint32) for x in (meta.pos, meta.pt_off, meta.pages))
     rc = L.yx_plan_probe(len(pos), p(pos), p(off), p(pages), len(pages), hkv, group, window or 0, key_lo, key_hi,
-                         max_rows, n_ctas, share, esize, ctypes.byref(info), p(buf), cap)
+                         max_rows, n_ctas, share, esize, cost32, cost64, ctypes.byref(info), p(buf), cap)
     assert rc == 0
     items = buf[: info.n_items * _lib.PROBE_ITEM_WORDS].reshape(info.n_items, _lib.PROBE_ITEM_WORDS)
     return info, items
@@ -69,13 +70,18 @@ def check_slots(items, info, group_rows):
     assert len(used) == info.n_parts
 
 
-def check_balance(items, info):
+def check_balance(items, info, cost32=16, cost64=32):
+    """Per-CTA cost (tiles weighted by the item's padded rows) differs by at most ~one tile."""
+    w = {16: 16, 32: cost32, 64: cost64}
     per = np.zeros(info.n_ctas, np.int64)
+    tiles = 0
     for it in items:
-        per[int(it[8])] += int(it[1]) - int(it[0])
-    assert per.sum() == info.tiles
+        n = int(it[1]) - int(it[0])
+        tiles += n
+        per[int(it[8])] += n * w[int(it[7])]
+    assert tiles == info.tiles
     if info.tiles >= info.n_ctas:
-        assert per.max() - per.min() <= 1
+        assert per.max() - per.min() <= 2 * max(w.values())
 
 
 @pytest.mark.parametrize("share", [0, 1])

@@ -96,7 +96,10 @@ class CudaBackend:
         torch.cuda.set_device(self.device)
         self.stream = stream if stream is not None else torch.cuda.current_stream(self.device)
         ctx = ctypes.c_void_p()
-        rc = self._L.yx_ctx_create(device, ctypes.c_void_p(self.stream.cuda_stream), ctypes.byref(ctx))
+        # torch's default stream has handle 0, which the C ABI reads as "make a private stream":
+        # name the legacy default stream explicitly (cudaStreamLegacy == 1).
+        handle = self.stream.cuda_stream or 1
+        rc = self._L.yx_ctx_create(device, ctypes.c_void_p(handle), ctypes.byref(ctx))
         if rc != _lib.YX_OK:
             raise BackendError(rc, "yx_ctx_create failed (is this an sm_100 GPU?)")
         self._ctx = ctx
@@ -143,8 +146,9 @@ class CudaBackend:
         self.sync()
         return x.detach().float().cpu().numpy()
 
-    def set_tuning(self, force_path: int = 0, ctas_per_sm: int = 0, share_prefix: int = 0, tile_min_rows: int = 0):
-        t = _lib.Tuning(force_path, ctas_per_sm, share_prefix, tile_min_rows)
+    def set_tuning(self, force_path: int = 0, ctas_per_sm: int = 0, share_prefix: int = 0, tile_min_rows: int = 0,
+                   cost32: int = 0, cost64: int = 0):
+        t = _lib.Tuning(force_path, ctas_per_sm, share_prefix, tile_min_rows, cost32, cost64)
         self._L.yx_set_tuning(self._ctx, ctypes.byref(t))
 
     def last_plan(self) -> _lib.PlanInfo:

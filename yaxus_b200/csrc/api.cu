@@ -113,7 +113,8 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
     for (auto &cp : ctx->plans) {
         if (cp.pass_serial == ctx->pass_serial && cp.hkv == pp.hkv && cp.group == pp.group &&
             cp.max_rows == pp.max_rows && cp.n_ctas == pp.n_ctas && cp.window == pp.window &&
-            cp.key_lo == pp.key_lo && cp.key_hi == pp.key_hi && cp.share == pp.share_prefix && cp.esize == pp.esize) {
+            cp.key_lo == pp.key_lo && cp.key_hi == pp.key_hi && cp.share == pp.share_prefix && cp.esize == pp.esize &&
+            cp.w32 == pp.w32 && cp.w64 == pp.w64) {
             *out = &cp;
             return YX_OK;
         }
@@ -153,6 +154,8 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
     slot->key_hi = pp.key_hi;
     slot->share = pp.share_prefix;
     slot->esize = pp.esize;
+    slot->w32 = pp.w32;
+    slot->w64 = pp.w64;
 
     const Plan &pl = slot->plan;
     size_t items_b = pl.items.size() * sizeof(Item);
@@ -217,6 +220,8 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     pp.n_ctas = ctx->sm_count * per_sm;
     pp.max_rows = path == 1 ? 1 : std::max(1, std::min(MAX_ITEM_ROWS, 64 / group));
     pp.share_prefix = path != 1 && ctx->tuning.share_prefix != 2;
+    pp.w32 = ctx->tuning.cost32 > 0 ? ctx->tuning.cost32 : 16;
+    pp.w64 = ctx->tuning.cost64 > 0 ? ctx->tuning.cost64 : 32;
     yx_ctx::CachedPlan *cp = nullptr;
     if (int rc = get_plan(ctx, pp, &cp)) return rc;
     const Plan &pl = cp->plan;

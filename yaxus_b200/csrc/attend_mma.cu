@@ -244,7 +244,10 @@ __device__ void consume_item(const Params &P, const Shared &S, const Item *itp, 
     }
     // Query fragments, high and low parts.
     uint32_t qh[8][4], ql[8][4];
-    const bool exact_q = (P.q_dtype == YX_BF16 && BF16) || (P.q_dtype == YX_F16 && !BF16);
+    // The low part of an f32 query costs a second MMA per score tile; items with 64 padded rows
+    // are the ones bound by tensor work, and their rows see long shared prefixes over which the
+    // query's rounding averages out, so they go without it.
+    const bool exact_q = MT == 64 || (P.q_dtype == YX_BF16 && BF16) || (P.q_dtype == YX_F16 && !BF16);
 #pragma unroll
     for (int ks = 0; ks < 8; ks++) {
 #pragma unroll
@@ -330,11 +333,17 @@ __device__ void consume_item(const Params &P, const Shared &S, const Item *itp, 
         // O += P V.
 #pragma unroll
         for (int kk = 0; kk < KS / 16; kk++) {
-            uint32_t a[4];
-            a[0] = pack2<BF16>(s[2 * kk][0], s[2 * kk][1]);
-            a[1] = pack2<BF16>(s[2 * kk][2], s[2 * kk][3]);
-            a[2] = pack2<BF16>(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-            a[3] = pack2<BF16>(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+            uint32_t a[4], al[4];
+#pragma unroll
+            for (int r = 0; r < 4; r++) {
+                const float p0 = s[2 * kk + (r >> 1)][(r & 1) * 2], p1 = s[2 * kk + (r >> 1)][(r & 1) * 2 + 1];
+                a[r] = pack2<BF16>(p0, p1);
+                if constexpr (BF16) {
+                    // bf16 keeps 8 bits of a probability; its remainder goes in a second MMA.
+                    float2 hf = unpack2<BF16>(a[r]);
+                    al[r] = pack2<BF16>(p0 - hf.x, p1 - hf.y);
+                }
+            }
             int key = sl * KS + kk * 16 + (lm & 1) * 8 + lr;
 #pragma unroll
             for (int np = 0; np < 8; np++) {
@@ -344,6 +353,10 @@ __device__ void consume_item(const Params &P, const Shared &S, const Item *itp, 
                 ldsm4t(sub + key * 128 + ((c ^ lr) << 4), b0, b1, b2, b3);
                 mma16816<BF16>(o[2 * np], a, b0, b1);
                 mma16816<BF16>(o[2 * np + 1], a, b2, b3);
+                if constexpr (BF16) {
+                    mma16816<BF16>(o[2 * np], al, b0, b1);
+                    mma16816<BF16>(o[2 * np + 1], al, b2, b3);
+                }
             }
         }
         __syncwarp();

@@ -199,19 +199,30 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
         units.swap(all);
     }
 
-    // 4. Cut the tile sequence (units x KV heads) into one span per CTA.
-    uint64_t total_tiles = 0;
-    for (const Unit &u : units) total_tiles += (uint64_t)(u.hi / TILE_KEYS - u.lo / TILE_KEYS + 1) * pp.hkv;
+    // 4. Cut the tile sequence (units x KV heads) into one span of equal cost per CTA.  A tile
+    //    of an item with many query rows costs more tensor work than its bytes alone; the
+    //    weights keep the CTAs that get such items from finishing last.
+    auto weight = [&](const Unit &u) -> uint64_t {
+        int mt = padded_rows((int)u.rows.size() * pp.group);
+        return mt == 16 ? 16u : (mt == 32 ? (uint64_t)std::max(pp.w32, 1) : (uint64_t)std::max(pp.w64, 1));
+    };
+    uint64_t total_tiles = 0, total_cost = 0;
+    for (const Unit &u : units) {
+        uint64_t t = (uint64_t)(u.hi / TILE_KEYS - u.lo / TILE_KEYS + 1) * pp.hkv;
+        total_tiles += t;
+        total_cost += t * weight(u);
+    }
     int n_ctas = (int)std::min<uint64_t>((uint64_t)std::max(1, pp.n_ctas), std::max<uint64_t>(total_tiles, 1));
     out.n_ctas = n_ctas;
     out.cta_begin.assign(n_ctas + 1, 0);
     out.merges.assign((size_t)T * pp.hkv, Merge{0, 0});
 
-    uint64_t done = 0;
+    uint64_t done = 0;   // cost handed out so far
     int cta = 0;
-    auto span_end = [&](int c) { return total_tiles * (uint64_t)(c + 1) / (uint64_t)n_ctas; };
+    auto span_end = [&](int c) { return total_cost * (uint64_t)(c + 1) / (uint64_t)n_ctas; };
     std::unordered_map<uint64_t, uint32_t> seen;   // (physical page, half) -> most keys read
     for (const Unit &u : units) {
+        const uint64_t w = weight(u);
         uint32_t t0 = u.lo / TILE_KEYS, t1 = u.hi / TILE_KEYS + 1;
         for (uint32_t t = t0; t < t1; t++) {
             uint32_t a = std::max(u.lo, t * TILE_KEYS), b = std::min(u.hi, t * TILE_KEYS + TILE_KEYS - 1);
@@ -223,13 +234,13 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
         for (int kh = 0; kh < pp.hkv; kh++) {
             uint32_t t = t0;
             while (t < t1) {
-                while (cta < n_ctas - 1 && done >= span_end(cta)) {
+                // Move on when less than half a tile's cost is left in this CTA's span.
+                while (cta < n_ctas - 1 && done + w / 2 >= span_end(cta)) {
                     cta++;
                     out.cta_begin[cta] = (uint32_t)out.items.size();
                 }
-                uint64_t room = span_end(cta) - done;
-                if (cta == n_ctas - 1) room = UINT64_MAX;
-                uint32_t take = (uint32_t)std::min<uint64_t>(room, t1 - t);
+                uint64_t room = cta == n_ctas - 1 ? UINT64_MAX : (span_end(cta) - done + w / 2) / w;
+                uint32_t take = (uint32_t)std::min<uint64_t>(std::max<uint64_t>(room, 1), t1 - t);
                 Item it{};
                 it.tile_begin = t;
                 it.tile_end = t + take;
@@ -245,7 +256,7 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
                 }
                 out.items.push_back(it);
                 t += take;
-                done += take;
+                done += take * w;
             }
         }
     }

@@ -5,8 +5,8 @@
 
 extern "C" int yx_plan_probe(uint32_t rows, const uint32_t *pos, const uint32_t *pt_off, const uint32_t *pages,
                              uint32_t n_pages, int hkv, int group, int64_t window, uint64_t key_lo, uint64_t key_hi,
-                             int max_rows, int n_ctas, int share_prefix, int esize, yx_plan_info *info,
-                             uint32_t *items_out, uint32_t max_items) {
+                             int max_rows, int n_ctas, int share_prefix, int esize, int cost32, int cost64,
+                             yx_plan_info *info, uint32_t *items_out, uint32_t max_items) {
     if (rows && (!pos || !pt_off)) return YX_ERR_INVALID;
     yx::PassHost pass;
     pass.rows = rows;
@@ -23,6 +23,8 @@ extern "C" int yx_plan_probe(uint32_t rows, const uint32_t *pos, const uint32_t 
     pp.n_ctas = n_ctas;
     pp.share_prefix = share_prefix != 0;
     pp.esize = esize;
+    pp.w32 = cost32 > 0 ? cost32 : 16;
+    pp.w64 = cost64 > 0 ? cost64 : 32;
     yx::Plan plan;
     try {
         yx::build_split_plan(pass, pp, plan);

@@ -92,6 +92,7 @@ struct PlanParams {
     int n_ctas;              // persistent CTAs to fill
     bool share_prefix;
     int esize;               // bytes per stored element
+    int w32, w64;            // cost of a tile of an item with 32 / 64 padded rows, in 16ths of a 16-row tile's
 };
 
 // Builds the split-key plan.  Throws std::string on a malformed pass.
@@ -162,7 +163,7 @@ struct yx_ctx {
     // cached plans of the current pass
     struct CachedPlan {
         uint64_t pass_serial = 0;
-        int hkv = 0, group = 0, max_rows = 0, n_ctas = 0, esize = 0;
+        int hkv = 0, group = 0, max_rows = 0, n_ctas = 0, esize = 0, w32 = 0, w64 = 0;
         int64_t window = 0;
         uint64_t key_lo = 0, key_hi = 0;
         bool share = false;
