@@ -169,46 +169,74 @@ struct Params {
     yx_dev_status *status;
 };
 
+// An item is 32 words: a warp reads it with one coalesced load, lane i holding word i, and
+// takes fields out with shuffles.  Word indices follow `struct Item`.
+constexpr int W_TILE_BEGIN = 0, W_TILE_END = 1, W_KEY_LO = 2, W_KEY_HI = 3, W_PT_OFF = 4, W_HEAD_ROWS = 5,
+              W_ROWS = 6, W_PART = 14, W_MT = 30;
+__device__ __forceinline__ uint32_t item_word(const Item *items, uint32_t ii, int lane) {
+    return reinterpret_cast<const uint32_t *>(items + ii)[lane];
+}
+__device__ __forceinline__ uint32_t field(uint32_t w, int idx) { return __shfl_sync(0xffffffffu, w, idx); }
+
 // ---- producer ---------------------------------------------------------------------------
-__device__ void produce(const Params &P, const Shared &S, uint32_t ib, uint32_t ie) {
+// The whole warp runs this; lane 0 waits and issues the copies.  The page ids of up to 32
+// tiles are fetched with one coalesced load, so no copy waits on a page-table lookup of its
+// own, and the next item's header is in flight while this item streams.
+__device__ void produce(const Params &P, const Shared &S, uint32_t ib, uint32_t ie, int lane) {
     Pipe pipe{0, 0};
     const size_t block_bytes = (size_t)PAGE * D * 2;
+    uint32_t w_next = ib < ie ? item_word(P.items, ib, lane) : 0u;
     for (uint32_t ii = ib; ii < ie; ii++) {
-        const Item *it = P.items + ii;
-        const uint32_t tb = it->tile_begin, te = it->tile_end, klo = it->key_lo, khi = it->key_hi;
-        const uint32_t pt_off = it->pt_off, kvh = it->kv_head;
-        for (uint32_t t = tb; t < te; t++) {
-            mbar_wait(S.empty + 8 * pipe.stage, pipe.phase ^ 1u, S.abort_flag, P.status, 1);
-            if (*S.abort_flag) return;
-            uint32_t a = max(klo, t * TILE_KEYS), b = min(khi, t * TILE_KEYS + TILE_KEYS - 1);
-            uint32_t r0 = a - t * TILE_KEYS, n = b - a + 1;
-            uint32_t page = P.pages[pt_off + (t >> 1)];
-            uint32_t bar = S.full + 8 * pipe.stage;
-            if (page >= P.kv_pages) {   // recorded; the tile keeps stale (finite) data
-                if (atomicCAS(&P.status->code, 0, 1) == 0) {
-                    P.status->where = 200;
-                    P.status->a = (int)page;
-                    P.status->b = (int)ii;
+        const uint32_t w = w_next;
+        if (ii + 1 < ie) w_next = item_word(P.items, ii + 1, lane);
+        const uint32_t tb = field(w, W_TILE_BEGIN), te = field(w, W_TILE_END);
+        const uint32_t klo = field(w, W_KEY_LO), khi = field(w, W_KEY_HI);
+        const uint32_t pt_off = field(w, W_PT_OFF), kvh = field(w, W_HEAD_ROWS) & 0xffffu;
+        for (uint32_t c = tb; c < te; c += 32) {
+            const uint32_t mine = c + lane;
+            const uint32_t my_page = mine < te ? P.pages[pt_off + (mine >> 1)] : 0u;
+            const int n_tiles = (int)min(32u, te - c);
+            for (int j = 0; j < n_tiles; j++) {
+                const uint32_t t = c + j;
+                const uint32_t page = __shfl_sync(0xffffffffu, my_page, j);
+                int stop = 0;
+                if (lane == 0) {
+                    mbar_wait(S.empty + 8 * pipe.stage, pipe.phase ^ 1u, S.abort_flag, P.status, 1);
+                    stop = *S.abort_flag;
+                    if (!stop) {
+                        uint32_t a = max(klo, t * TILE_KEYS), b = min(khi, t * TILE_KEYS + TILE_KEYS - 1);
+                        uint32_t r0 = a - t * TILE_KEYS, n = b - a + 1;
+                        uint32_t bar = S.full + 8 * pipe.stage;
+                        if (page >= P.kv_pages) {   // recorded; the tile keeps stale (finite) data
+                            if (atomicCAS(&P.status->code, 0, 1) == 0) {
+                                P.status->where = 200;
+                                P.status->a = (int)page;
+                                P.status->b = (int)ii;
+                            }
+                            mbar_expect_tx(bar, 0);
+                        } else {
+                            uint32_t bytes = n * 128;
+                            size_t off = ((size_t)page * P.hkv + kvh) * block_bytes +
+                                         (size_t)((t & 1) * TILE_KEYS + r0) * 128;
+                            uint32_t dst = S.stages + pipe.stage * STAGE_BYTES + r0 * 128;
+                            mbar_expect_tx(bar, 4 * bytes);
+                            bulk_g2s(dst, P.k_arena + off, bytes, bar);
+                            bulk_g2s(dst + SUB_BYTES, P.k_arena + off + PAGE * 128, bytes, bar);
+                            bulk_g2s(dst + 2 * SUB_BYTES, P.v_arena + off, bytes, bar);
+                            bulk_g2s(dst + 3 * SUB_BYTES, P.v_arena + off + PAGE * 128, bytes, bar);
+                        }
+                    }
                 }
-                mbar_expect_tx(bar, 0);
-            } else {
-                uint32_t bytes = n * 128;
-                size_t off = ((size_t)page * P.hkv + kvh) * block_bytes + (size_t)((t & 1) * TILE_KEYS + r0) * 128;
-                uint32_t dst = S.stages + pipe.stage * STAGE_BYTES + r0 * 128;
-                mbar_expect_tx(bar, 4 * bytes);
-                bulk_g2s(dst, P.k_arena + off, bytes, bar);
-                bulk_g2s(dst + SUB_BYTES, P.k_arena + off + PAGE * 128, bytes, bar);
-                bulk_g2s(dst + 2 * SUB_BYTES, P.v_arena + off, bytes, bar);
-                bulk_g2s(dst + 3 * SUB_BYTES, P.v_arena + off + PAGE * 128, bytes, bar);
+                if (__shfl_sync(0xffffffffu, stop, 0)) return;
+                pipe.advance();
             }
-            pipe.advance();
         }
     }
 }
 
 // ---- consumers --------------------------------------------------------------------------
 template <int MT, bool BF16>
-__device__ void consume_item(const Params &P, const Shared &S, const Item *itp, Pipe &pipe, int warp, int lane) {
+__device__ void consume_item(const Params &P, const Shared &S, const uint32_t w, Pipe &pipe, int warp, int lane) {
     constexpr int NMT = MT / 16;          // 16-row tiles of queries
     constexpr int NSL = CONSUMERS / NMT;  // key slices of a tile
     constexpr int KS = TILE_KEYS / NSL;   // keys per slice
@@ -216,29 +244,33 @@ __device__ void consume_item(const Params &P, const Shared &S, const Item *itp, 
     const int mi = warp % NMT, sl = warp / NMT;
     const int g = lane >> 2, t4 = lane & 3;
     const int group = P.group;
-    const uint32_t tb = itp->tile_begin, te = itp->tile_end;
-    const int kvh = itp->kv_head;
-    const int q_rows = (int)itp->n_rows * group;
+    const uint32_t tb = field(w, W_TILE_BEGIN), te = field(w, W_TILE_END);
+    const uint32_t item_lo = field(w, W_KEY_LO), item_hi = field(w, W_KEY_HI);
+    const uint32_t head_rows = field(w, W_HEAD_ROWS);
+    const int kvh = (int)(head_rows & 0xffffu);
+    const int q_rows = (int)(head_rows >> 16) * group;
     const float sl2 = 0.08838834764831845f * 1.4426950408889634f;   // log2(e) / sqrt(128)
 
     // The two query rows this thread owns in the accumulator fragments.
-    uint32_t klo[2], khi[2];
+    uint32_t klo[2], khi[2], part[2];
     size_t q_elem[2];
     bool valid[2];
 #pragma unroll
     for (int rs = 0; rs < 2; rs++) {
         int qr = mi * 16 + g + rs * 8;
         valid[rs] = qr < q_rows;
+        const int ri = valid[rs] ? qr / group : 0;   // index into the item's rows
+        const uint32_t row = (field(w, W_ROWS + (ri >> 1)) >> (16 * (ri & 1))) & 0xffffu;
+        part[rs] = field(w, W_PART + ri);
         klo[rs] = 0;
         khi[rs] = 0xffffffffu;
         q_elem[rs] = 0;
         if (valid[rs]) {
-            uint32_t row = itp->rows[qr / group];
             uint32_t p = P.pos[row];
             uint32_t lo = 0;
             if (P.window > 0 && p + 1 > P.window) lo = p + 1 - P.window;
-            klo[rs] = max(lo, itp->key_lo);
-            khi[rs] = min(p, itp->key_hi);
+            klo[rs] = max(lo, item_lo);
+            khi[rs] = min(p, item_hi);
             q_elem[rs] = ((size_t)row * P.hq + (size_t)kvh * group + (qr % group)) * D;
         }
     }
@@ -272,9 +304,15 @@ __device__ void consume_item(const Params &P, const Shared &S, const Item *itp, 
         const uint32_t sb = S.stages + pipe.stage * STAGE_BYTES;
 
         // S = Q K^T over this warp's KS keys.
-        float s[NT][4];
+        // The low parts of the queries accumulate on their own, so that no MMA waits on more
+        // than the eight before it in its chain.
+        float s[NT][4], s2[MT == 64 ? 1 : NT][4];
 #pragma unroll
         for (int j = 0; j < NT; j++) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+        if constexpr (MT != 64) {
+#pragma unroll
+            for (int j = 0; j < NT; j++) s2[j][0] = s2[j][1] = s2[j][2] = s2[j][3] = 0.f;
+        }
 #pragma unroll
         for (int ks = 0; ks < 8; ks++) {
             const uint32_t sub = sb + (ks >> 2) * SUB_BYTES;
@@ -286,11 +324,19 @@ __device__ void consume_item(const Params &P, const Shared &S, const Item *itp, 
                 ldsm4(sub + key * 128 + ((c ^ lr) << 4), b0, b1, b2, b3);
                 mma16816<BF16>(s[2 * np], qh[ks], b0, b1);
                 mma16816<BF16>(s[2 * np + 1], qh[ks], b2, b3);
-                if (!exact_q) {
-                    mma16816<BF16>(s[2 * np], ql[ks], b0, b1);
-                    mma16816<BF16>(s[2 * np + 1], ql[ks], b2, b3);
+                if constexpr (MT != 64) {
+                    if (!exact_q) {
+                        mma16816<BF16>(s2[2 * np], ql[ks], b0, b1);
+                        mma16816<BF16>(s2[2 * np + 1], ql[ks], b2, b3);
+                    }
                 }
             }
+        }
+        if constexpr (MT != 64) {
+#pragma unroll
+            for (int j = 0; j < NT; j++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) s[j][e] += s2[j][e];
         }
         // Mask keys outside each row's [klo, khi].
         const uint32_t key0 = t * TILE_KEYS + sl * KS + 2 * t4;
@@ -425,7 +471,7 @@ __device__ void consume_item(const Params &P, const Shared &S, const Item *itp, 
         for (int rs = 0; rs < 2; rs++) {
             if (!valid[rs]) continue;
             int qr = mi * 16 + g + rs * 8;
-            size_t slot = (size_t)itp->part[qr / group] * group + (qr % group);
+            size_t slot = (size_t)part[rs] * group + (qr % group);
             float *po = P.part_o + slot * D;
 #pragma unroll
             for (int n = 0; n < 16; n++) *(float2 *)(po + n * 8 + 2 * t4) = make_float2(o[n][2 * rs], o[n][2 * rs + 1]);
@@ -466,16 +512,18 @@ __global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const Params P) 
 
     const uint32_t ib = P.cta_begin[blockIdx.x], ie = P.cta_begin[blockIdx.x + 1];
     if (warp == CONSUMERS) {
-        if (lane == 0) produce(P, S, ib, ie);
+        produce(P, S, ib, ie, lane);
         return;
     }
     Pipe pipe{0, 0};
+    uint32_t w_next = ib < ie ? item_word(P.items, ib, lane) : 0u;
     for (uint32_t ii = ib; ii < ie; ii++) {
-        const Item *it = P.items + ii;
-        switch (it->mt) {
-            case 16: consume_item<16, BF16>(P, S, it, pipe, warp, lane); break;
-            case 32: consume_item<32, BF16>(P, S, it, pipe, warp, lane); break;
-            default: consume_item<64, BF16>(P, S, it, pipe, warp, lane); break;
+        const uint32_t w = w_next;
+        if (ii + 1 < ie) w_next = item_word(P.items, ii + 1, lane);   // in flight while this item runs
+        switch (field(w, W_MT)) {
+            case 16: consume_item<16, BF16>(P, S, w, pipe, warp, lane); break;
+            case 32: consume_item<32, BF16>(P, S, w, pipe, warp, lane); break;
+            default: consume_item<64, BF16>(P, S, w, pipe, warp, lane); break;
         }
     }
     if (abort_flag) {

@@ -25,7 +25,9 @@ __device__ __forceinline__ void store_out(void *out, int out_dtype, size_t elem,
 }
 
 // Parts of (row, head) are slots first..first+count of its (row, kv head); the triple of
-// slot s and head-in-group g sits at index s * group + g.
+// slot s and head-in-group g sits at index s * group + g.  Lane c reads the (m, l) of part c,
+// the warp agrees on the maximum and the weights, and only then are the o vectors read, all
+// loads independent of one another: the merge costs two memory latencies, not two per part.
 __global__ void combine_kernel(const Merge *__restrict__ merges, const float *__restrict__ part_o,
                                const float *__restrict__ part_ml, uint32_t n, int hq, int group, void *out,
                                int out_dtype, float *m_out, float *l_out, float *o_out) {
@@ -37,19 +39,42 @@ __global__ void combine_kernel(const Merge *__restrict__ merges, const float *__
     Merge mg = merges[(size_t)row * (hq / group) + kvh];
     float mx = -1e30f, l = 0.0f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (uint32_t c = 0; c < mg.count; c++) {
-        size_t s = (size_t)(mg.first + c) * group + g;
-        float em = part_ml[s * 2], el = part_ml[s * 2 + 1];
-        if (!(el > 0.0f)) continue;
-        float4 po = *(const float4 *)(part_o + s * D + lane * 4);
-        float nm = fmaxf(mx, em);
-        float r = __expf(mx - nm), w = __expf(em - nm);
-        l = l * r + el * w;
-        acc.x = acc.x * r + po.x * w;
-        acc.y = acc.y * r + po.y * w;
-        acc.z = acc.z * r + po.z * w;
-        acc.w = acc.w * r + po.w * w;
+    for (uint32_t c0 = 0; c0 < mg.count; c0 += 32) {
+        const uint32_t c = c0 + lane;
+        float em = -1e30f, el = 0.0f;
+        if (c < mg.count) {
+            float2 v = *(const float2 *)(part_ml + ((size_t)(mg.first + c) * group + g) * 2);
+            em = v.x;
+            el = v.y;
+        }
+        const bool live = el > 0.0f;
+        float cm = live ? em : -1e30f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, o));
+        const float nm = fmaxf(mx, cm);
+        const float r = __expf(mx - nm);
+        const float w = live ? __expf(em - nm) : 0.0f;
+        float ls = el * w;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
+        l = l * r + ls;
+        acc.x *= r;
+        acc.y *= r;
+        acc.z *= r;
+        acc.w *= r;
         mx = nm;
+        const int nc = (int)min(32u, mg.count - c0);
+#pragma unroll 4
+        for (int j = 0; j < nc; j++) {
+            const float wj = __shfl_sync(0xffffffffu, w, j);
+            if (wj > 0.0f) {   // an empty part's o was never written
+                float4 po = *(const float4 *)(part_o + ((size_t)(mg.first + c0 + j) * group + g) * D + lane * 4);
+                acc.x += po.x * wj;
+                acc.y += po.y * wj;
+                acc.z += po.z * wj;
+                acc.w += po.w * wj;
+            }
+        }
     }
     if (out) {
         float inv = 1.0f / l;   // a row always sees its own key, so l > 0 for whole attention
