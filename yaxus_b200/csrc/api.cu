@@ -100,6 +100,8 @@ int fold_device_status(yx_ctx *ctx) {
     if (ctx->dev_status && ctx->dev_status->code != 0) {
         yx_dev_status s = *ctx->dev_status;
         ctx->dev_status->code = 0;
+        // A kernel that gave up may have left arrival counters of the fused merge non-zero.
+        if (ctx->counters) cudaMemsetAsync(ctx->counters, 0, ctx->counters_cap, ctx->stream);
         return fail(ctx, YX_ERR_DEVICE,
                     "a kernel reported a failed check: code " + std::to_string(s.code) + " at " +
                         std::to_string(s.where) + " (" + std::to_string(s.a) + ", " + std::to_string(s.b) + ")");
@@ -114,7 +116,7 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
         if (cp.pass_serial == ctx->pass_serial && cp.hkv == pp.hkv && cp.group == pp.group &&
             cp.max_rows == pp.max_rows && cp.n_ctas == pp.n_ctas && cp.window == pp.window &&
             cp.key_lo == pp.key_lo && cp.key_hi == pp.key_hi && cp.share == pp.share_prefix && cp.esize == pp.esize &&
-            cp.w32 == pp.w32 && cp.w64 == pp.w64) {
+            cp.w32 == pp.w32 && cp.w64 == pp.w64 && cp.resolve == pp.resolve) {
             *out = &cp;
             return YX_OK;
         }
@@ -156,27 +158,45 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
     slot->esize = pp.esize;
     slot->w32 = pp.w32;
     slot->w64 = pp.w64;
+    slot->resolve = pp.resolve;
 
     const Plan &pl = slot->plan;
-    size_t items_b = pl.items.size() * sizeof(Item);
-    size_t cta_b = (pl.cta_begin.size() * sizeof(uint32_t) + 15) / 16 * 16;
-    size_t mer_b = pl.merges.size() * sizeof(Merge);
-    size_t total = items_b + cta_b + mer_b;
+    auto pad16 = [](size_t n) { return (n + 15) / 16 * 16; };
+    const size_t items_b = pp.resolve ? 0 : pl.items.size() * sizeof(Item);
+    const size_t cta_b = pp.resolve ? 0 : pad16(pl.cta_begin.size() * sizeof(uint32_t));
+    const size_t mer_b = pad16(pl.merges.size() * sizeof(Merge));
+    const size_t hdr_b = pad16(pl.cta_hdr.size() * sizeof(CtaHdr));
+    const size_t til_b = pad16(pl.tiles.size() * sizeof(TileDesc));
+    const size_t rec_b = pl.recs.size() * sizeof(ItemRec);
+    const size_t total = items_b + cta_b + mer_b + hdr_b + til_b + rec_b;
     if (int rc = ensure_buffer(ctx, (void **)&slot->dev, &slot->dev_cap, total)) {
         slot->pass_serial = 0;
         return rc;
     }
     std::vector<char> blob(total);
-    if (items_b) memcpy(blob.data(), pl.items.data(), items_b);
-    memcpy(blob.data() + items_b, pl.cta_begin.data(), pl.cta_begin.size() * sizeof(uint32_t));
-    if (mer_b) memcpy(blob.data() + items_b + cta_b, pl.merges.data(), mer_b);
+    size_t at = 0;
+    auto put = [&](const void *src, size_t bytes, size_t padded) {
+        if (bytes) memcpy(blob.data() + at, src, bytes);
+        size_t here = at;
+        at += padded;
+        return here;
+    };
+    const size_t o_items = put(pl.items.data(), items_b, items_b);
+    const size_t o_cta = put(pl.cta_begin.data(), cta_b ? pl.cta_begin.size() * sizeof(uint32_t) : 0, cta_b);
+    const size_t o_mer = put(pl.merges.data(), pl.merges.size() * sizeof(Merge), mer_b);
+    const size_t o_hdr = put(pl.cta_hdr.data(), pl.cta_hdr.size() * sizeof(CtaHdr), hdr_b);
+    const size_t o_til = put(pl.tiles.data(), pl.tiles.size() * sizeof(TileDesc), til_b);
+    const size_t o_rec = put(pl.recs.data(), rec_b, rec_b);
     if (int rc = upload_ordered(ctx, slot->dev, blob.data(), total)) {
         slot->pass_serial = 0;
         return rc;
     }
-    slot->d_items = (Item *)slot->dev;
-    slot->d_cta_begin = (uint32_t *)(slot->dev + items_b);
-    slot->d_merges = (Merge *)(slot->dev + items_b + cta_b);
+    slot->d_items = (Item *)(slot->dev + o_items);
+    slot->d_cta_begin = (uint32_t *)(slot->dev + o_cta);
+    slot->d_merges = (Merge *)(slot->dev + o_mer);
+    slot->d_cta_hdr = (CtaHdr *)(slot->dev + o_hdr);
+    slot->d_tiles = (TileDesc *)(slot->dev + o_til);
+    slot->d_recs = (ItemRec *)(slot->dev + o_rec);
     *out = slot;
     return YX_OK;
 }
@@ -221,7 +241,8 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     pp.max_rows = path == 1 ? 1 : std::max(1, std::min(MAX_ITEM_ROWS, 64 / group));
     pp.share_prefix = path != 1 && ctx->tuning.share_prefix != 2;
     pp.w32 = ctx->tuning.cost32 > 0 ? ctx->tuning.cost32 : 16;
-    pp.w64 = ctx->tuning.cost64 > 0 ? ctx->tuning.cost64 : 32;
+    pp.w64 = ctx->tuning.cost64 > 0 ? ctx->tuning.cost64 : 16;
+    pp.resolve = path == 2;
     yx_ctx::CachedPlan *cp = nullptr;
     if (int rc = get_plan(ctx, pp, &cp)) return rc;
     const Plan &pl = cp->plan;
@@ -235,6 +256,16 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     size_t ml_bytes = (size_t)std::max<uint32_t>(pl.n_parts, 1) * group * 2 * sizeof(float);
     if (int rc = ensure_buffer(ctx, (void **)&ctx->ws_o, &ctx->ws_o_cap, o_bytes)) return rc;
     if (int rc = ensure_buffer(ctx, (void **)&ctx->ws_ml, &ctx->ws_ml_cap, ml_bytes)) return rc;
+    if (path == 2) {
+        // Arrival counters of the fused merge: zero when allocated, and every launch leaves
+        // them zero again.
+        size_t need = (size_t)ctx->pass.rows * kv->hkv * sizeof(uint32_t);
+        if (need > ctx->counters_cap || !ctx->counters) {
+            if (int rc = ensure_buffer(ctx, (void **)&ctx->counters, &ctx->counters_cap, need)) return rc;
+            if (int rc = check_cuda(ctx, cudaMemsetAsync(ctx->counters, 0, ctx->counters_cap, ctx->stream), "zero counters"))
+                return rc;
+        }
+    }
 
     AttendArgs a{};
     a.q = q;
@@ -254,17 +285,36 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     a.n_ctas = pl.n_ctas;
     a.part_o = ctx->ws_o;
     a.part_ml = ctx->ws_ml;
+    a.cta_hdr = cp->d_cta_hdr;
+    a.tiles = cp->d_tiles;
+    a.recs = cp->d_recs;
+    a.single_use = pl.single_use;
+    a.counters = ctx->counters;
+    a.out = out;
+    a.out_dtype = out_dtype;
+    a.m_out = m_out;
+    a.l_out = l_out;
+    a.o_out = o_out;
     profile_mark(ctx, 0);
-    if (!pl.items.empty()) {
-        int rc = path == 1 ? launch_attend_simt(ctx, a) : launch_attend_mma(ctx, a);
-        if (rc) return rc;
+    if (path == 2) {
+        // Rows without a live key in the range get no item, so nothing would write them.
+        if (o_out && pl.has_empty_rows)
+            if (int rc = launch_fill_empty(ctx, (size_t)ctx->pass.rows * hq, m_out, l_out, o_out)) return rc;
+        if (!pl.items.empty())
+            if (int rc = launch_attend_mma(ctx, a)) return rc;
+        profile_mark(ctx, 1);
+        profile_mark(ctx, 2);
+        profile_mark(ctx, 3);
+    } else {
+        if (!pl.items.empty())
+            if (int rc = launch_attend_simt(ctx, a)) return rc;
+        profile_mark(ctx, 1);
+        profile_mark(ctx, 2);
+        if (int rc = launch_combine(ctx, cp->d_merges, ctx->ws_o, ctx->ws_ml, (int)ctx->pass.rows, hq, group, out,
+                                    out_dtype, m_out, l_out, o_out))
+            return rc;
+        profile_mark(ctx, 3);
     }
-    profile_mark(ctx, 1);
-    profile_mark(ctx, 2);
-    if (int rc = launch_combine(ctx, cp->d_merges, ctx->ws_o, ctx->ws_ml, (int)ctx->pass.rows, hq, group, out,
-                                out_dtype, m_out, l_out, o_out))
-        return rc;
-    profile_mark(ctx, 3);
     ctx->last_plan = pl.info;
     ctx->last_plan.path = path;
     ctx->last_plan.launches = (int)(ctx->launches - launches0);
@@ -326,6 +376,7 @@ void yx_ctx_destroy(yx_ctx *ctx) {
     if (ctx->ws_o) cudaFree(ctx->ws_o);
     if (ctx->ws_ml) cudaFree(ctx->ws_ml);
     if (ctx->q_tmp) cudaFree(ctx->q_tmp);
+    if (ctx->counters) cudaFree(ctx->counters);
     if (ctx->gather_buf) cudaFree(ctx->gather_buf);
     if (ctx->dev_status) cudaFreeHost(ctx->dev_status);
     for (auto &e : ctx->prof_events)

@@ -3,153 +3,63 @@
 // keep every SM's share of HBM busy from the first microsecond to the last.
 //
 //  * Persistent: one CTA per SM walks the span of 64-key tiles the planner cut for it.
-//  * A producer warp streams K and V tiles from the paged cache into a ring of shared-memory
-//    stages with bulk asynchronous copies (`cp.async.bulk`, the TMA engine's untiled form)
-//    that complete on mbarriers.  The cache layout (yx_internal.h) makes a tile four
-//    contiguous runs that land already 128-byte swizzled, so no tensor map is needed and the
-//    copy of a ragged tile is simply shorter.  The producer runs ahead across item
-//    boundaries; the pipeline never drains between sequences.
+//  * Nothing on the device walks a page table.  The host planner resolves every tile to its
+//    (page, KV head) block; the producer warp reads 32 tile descriptors with one coalesced
+//    load and feeds the copy engine from them, across item boundaries, never draining.
+//  * K and V tiles come in by bulk asynchronous copies (`cp.async.bulk`, the TMA engine's
+//    untiled form) that complete on mbarriers.  The cache layout (yx_internal.h) makes a tile
+//    four contiguous runs that land already 128-byte swizzled, so no tensor map is needed and
+//    the copy of a ragged tile is simply shorter.  Tiles that no other item reads are copied
+//    with an L2 evict-first hint, so that the stream does not push the plan, the queries and
+//    the partial results out of L2.
+//  * A helper warp stages the queries of the next item in shared memory (converted to the
+//    cache's 16-bit type, f32 queries as a high and a low part), so that consumers never wait
+//    on global memory at an item boundary.
 //  * Four consumer warps share each tile.  All query heads of the KV head's group, and all
 //    rows of an item, are the M rows of one `mma.sync` tile (16, 32 or 64 padded rows), so a
 //    K or V byte is read once per item however many heads and rows use it.  Scores and
 //    softmax stay in f32 registers; max and sum reduce with quad shuffles.
-//  * f32 queries are split into a high and a low 16-bit part (two MMAs), so the only rounding
-//    beyond the cache's own is that of the probabilities.
 //  * Each item ends in an (m, l, o) triple per query row, the format of the reference's
-//    split attention (crates/yaxus-backend-gpu/src/shaders.rs:1466-1579); combine.cu merges.
+//    split attention (crates/yaxus-backend-gpu/src/shaders.rs:1466-1579).  The merge of the
+//    triples (the reference's `attn_combine`, shaders.rs:1581-1637) is fused: the CTA that
+//    delivers the last triple of a (row, KV head) merges them and writes the output, found
+//    by an arrival counter in global scratch that the merging CTA resets.
 //
 // Every wait on an mbarrier is bounded: on expiry the CTA records the failure in the
 // context's status word, stops waiting anywhere, finishes structurally and returns.
-#include <cuda_bf16.h>
-#include <cuda_fp16.h>
-
-#include "yx_internal.h"
+#include "yx_device.cuh"
 
 namespace yx {
 namespace {
 
-constexpr int STAGES = 6;
+using namespace dev;
+
+constexpr int STAGES = 5;
 constexpr int SUB_BYTES = TILE_KEYS * 128;        // one 64-dim half of a 64-key tile
 constexpr int STAGE_BYTES = 4 * SUB_BYTES;        // K lo, K hi, V lo, V hi
-constexpr int CONSUMERS = 4;                      // warps
-constexpr int THREADS = (CONSUMERS + 1) * 32;
+constexpr int CONSUMERS = 4;                      // warps 0..3
+constexpr int PRODUCER = CONSUMERS;               // warp 4
+constexpr int QWARP = CONSUMERS + 1;              // warp 5
+constexpr int THREADS = (CONSUMERS + 2) * 32;
+constexpr int Q_SLOTS = 2;
+constexpr int Q_SLOT_BYTES = 16384;               // 64 rows x 256 B, or 32 rows high + 32 rows low
+constexpr int Q_LOW_OFFSET = 8192;
 constexpr int MERGE_FLOATS = 16 * (D + 2);        // one warp's (m, l, o) for 16 rows
-constexpr int MERGE_BYTES = 3 * MERGE_FLOATS * 4;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + ((MERGE_BYTES + 127) / 128) * 128 + 256;
-constexpr long long WAIT_CYCLES = 4000000000ll;   // about two seconds
+constexpr int MERGE_BYTES = ((3 * MERGE_FLOATS * 4 + 127) / 128) * 128;
+constexpr int N_BARRIERS = 2 * STAGES + 2 * Q_SLOTS;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + Q_SLOTS * Q_SLOT_BYTES + MERGE_BYTES + 128 + N_BARRIERS * 8;
 
 struct Shared {
-    uint32_t stages;   // shared-space addresses
-    uint32_t merge;
-    uint32_t full;     // STAGES mbarriers
-    uint32_t empty;    // STAGES mbarriers
+    uint32_t stages, q, merge, flags;   // shared-space addresses
+    uint32_t full, empty, qfull, qempty;
     volatile int *abort_flag;
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-// Bounded wait.  Returns at once when the CTA has given up; on expiry records where.
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          yx_dev_status *status, int where) {
-    if (*abort_flag) return;
-    if (mbar_try(bar, parity)) return;
-    long long t0 = clock64();
-    for (uint32_t spins = 1;; spins++) {
-        if (mbar_try(bar, parity)) return;
-        if ((spins & 255u) == 0) {
-            if (*abort_flag) return;
-            if (clock64() - t0 > WAIT_CYCLES) {
-                *abort_flag = 1;
-                if (atomicCAS(&status->code, 0, 2) == 0) {
-                    status->where = where;
-                    status->a = (int)blockIdx.x;
-                    status->b = (int)parity;
-                }
-                return;
-            }
-        }
-    }
-}
-
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
-
-__device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t &a, uint32_t &b, uint32_t &c, uint32_t &d) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
-                 : "r"(addr));
-}
-__device__ __forceinline__ void ldsm4t(uint32_t addr, uint32_t &a, uint32_t &b, uint32_t &c, uint32_t &d) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
-                 : "r"(addr));
-}
-
-template <bool BF16>
-__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    if constexpr (BF16) {
-        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-    } else {
-        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-    }
-}
-
-template <bool BF16>
-__device__ __forceinline__ uint32_t pack2(float x, float y) {
-    if constexpr (BF16) {
-        __nv_bfloat162 v = __floats2bfloat162_rn(x, y);
-        return *(uint32_t *)&v;
-    } else {
-        __half2 v = __floats2half2_rn(x, y);
-        return *(uint32_t *)&v;
-    }
-}
-template <bool BF16>
-__device__ __forceinline__ float2 unpack2(uint32_t u) {
-    if constexpr (BF16) return __bfloat1622float2(*(__nv_bfloat162 *)&u);
-    else return __half22float2(*(__half2 *)&u);
-}
-
-__device__ __forceinline__ float2 load_q2(const void *q, int q_dtype, size_t elem) {
-    if (q_dtype == YX_F32) return *(const float2 *)((const float *)q + elem);
-    uint32_t raw = *(const uint32_t *)((const uint16_t *)q + elem);
-    if (q_dtype == YX_F16) return __half22float2(*(__half2 *)&raw);
-    return __bfloat1622float2(*(__nv_bfloat162 *)&raw);
-}
 
 struct Pipe {
     int stage;
     uint32_t phase;
-    __device__ __forceinline__ void advance() {
-        if (++stage == STAGES) {
+    __device__ __forceinline__ void advance(int n) {
+        if (++stage == n) {
             stage = 0;
             phase ^= 1u;
         }
@@ -160,137 +70,197 @@ struct Params {
     const void *q;
     int q_dtype, hq, group, hkv;
     const char *k_arena, *v_arena;
-    uint32_t kv_pages;
-    uint32_t window;
-    const uint32_t *pos, *pages;
-    const Item *items;
-    const uint32_t *cta_begin;
+    uint32_t n_blocks;               // (page, kv head) blocks in an arena
+    const CtaHdr *cta_hdr;
+    const TileDesc *tiles;
+    const ItemRec *recs;
+    int single_use;
     float *part_o, *part_ml;
+    uint32_t *counters;
+    void *out;
+    int out_dtype;
+    float *m_out, *l_out, *o_out;
     yx_dev_status *status;
+    unsigned long long *trace;       // optional: 8 timestamps / counters per CTA
 };
 
-// An item is 32 words: a warp reads it with one coalesced load, lane i holding word i, and
-// takes fields out with shuffles.  Word indices follow `struct Item`.
-constexpr int W_TILE_BEGIN = 0, W_TILE_END = 1, W_KEY_LO = 2, W_KEY_HI = 3, W_PT_OFF = 4, W_HEAD_ROWS = 5,
-              W_ROWS = 6, W_PART = 14, W_MT = 30;
-__device__ __forceinline__ uint32_t item_word(const Item *items, uint32_t ii, int lane) {
-    return reinterpret_cast<const uint32_t *>(items + ii)[lane];
-}
 __device__ __forceinline__ uint32_t field(uint32_t w, int idx) { return __shfl_sync(0xffffffffu, w, idx); }
 
-// ---- producer ---------------------------------------------------------------------------
-// The whole warp runs this; lane 0 waits and issues the copies.  The page ids of up to 32
-// tiles are fetched with one coalesced load, so no copy waits on a page-table lookup of its
-// own, and the next item's header is in flight while this item streams.
-__device__ void produce(const Params &P, const Shared &S, uint32_t ib, uint32_t ie, int lane) {
+// ---- producer: tile descriptors -> bulk copies ----------------------------------------------
+__device__ void produce(const Params &P, const Shared &S, const CtaHdr hdr, int lane) {
     Pipe pipe{0, 0};
-    const size_t block_bytes = (size_t)PAGE * D * 2;
-    uint32_t w_next = ib < ie ? item_word(P.items, ib, lane) : 0u;
-    for (uint32_t ii = ib; ii < ie; ii++) {
-        const uint32_t w = w_next;
-        if (ii + 1 < ie) w_next = item_word(P.items, ii + 1, lane);
-        const uint32_t tb = field(w, W_TILE_BEGIN), te = field(w, W_TILE_END);
-        const uint32_t klo = field(w, W_KEY_LO), khi = field(w, W_KEY_HI);
-        const uint32_t pt_off = field(w, W_PT_OFF), kvh = field(w, W_HEAD_ROWS) & 0xffffu;
-        for (uint32_t c = tb; c < te; c += 32) {
-            const uint32_t mine = c + lane;
-            const uint32_t my_page = mine < te ? P.pages[pt_off + (mine >> 1)] : 0u;
-            const int n_tiles = (int)min(32u, te - c);
-            for (int j = 0; j < n_tiles; j++) {
-                const uint32_t t = c + j;
-                const uint32_t page = __shfl_sync(0xffffffffu, my_page, j);
-                int stop = 0;
-                if (lane == 0) {
-                    mbar_wait(S.empty + 8 * pipe.stage, pipe.phase ^ 1u, S.abort_flag, P.status, 1);
-                    stop = *S.abort_flag;
-                    if (!stop) {
-                        uint32_t a = max(klo, t * TILE_KEYS), b = min(khi, t * TILE_KEYS + TILE_KEYS - 1);
-                        uint32_t r0 = a - t * TILE_KEYS, n = b - a + 1;
-                        uint32_t bar = S.full + 8 * pipe.stage;
-                        if (page >= P.kv_pages) {   // recorded; the tile keeps stale (finite) data
-                            if (atomicCAS(&P.status->code, 0, 1) == 0) {
-                                P.status->where = 200;
-                                P.status->a = (int)page;
-                                P.status->b = (int)ii;
-                            }
-                            mbar_expect_tx(bar, 0);
-                        } else {
-                            uint32_t bytes = n * 128;
-                            size_t off = ((size_t)page * P.hkv + kvh) * block_bytes +
-                                         (size_t)((t & 1) * TILE_KEYS + r0) * 128;
-                            uint32_t dst = S.stages + pipe.stage * STAGE_BYTES + r0 * 128;
-                            mbar_expect_tx(bar, 4 * bytes);
-                            bulk_g2s(dst, P.k_arena + off, bytes, bar);
-                            bulk_g2s(dst + SUB_BYTES, P.k_arena + off + PAGE * 128, bytes, bar);
-                            bulk_g2s(dst + 2 * SUB_BYTES, P.v_arena + off, bytes, bar);
-                            bulk_g2s(dst + 3 * SUB_BYTES, P.v_arena + off + PAGE * 128, bytes, bar);
-                        }
+    const uint64_t policy = policy_evict_first();
+    for (uint32_t c = hdr.tile_begin; c < hdr.tile_end; c += 32) {
+        uint2 d = make_uint2(0u, 0u);
+        if (c + lane < hdr.tile_end) d = *(const uint2 *)(P.tiles + c + lane);
+        const int n_tiles = (int)min(32u, hdr.tile_end - c);
+        for (int j = 0; j < n_tiles; j++) {
+            const uint32_t block = __shfl_sync(0xffffffffu, d.x, j);
+            const uint32_t info = __shfl_sync(0xffffffffu, d.y, j);
+            const uint32_t half = info & 1u, r0 = (info >> 1) & 127u, n = (info >> 8) & 255u;
+            int stop = 0;
+            if (lane == 0) {
+                mbar_wait(S.empty + 8 * pipe.stage, pipe.phase ^ 1u, S.abort_flag, P.status, 1);
+                stop = *S.abort_flag;
+            }
+            if (__shfl_sync(0xffffffffu, stop, 0)) return;
+            const uint32_t sb = S.stages + pipe.stage * STAGE_BYTES;
+            if (n < (uint32_t)TILE_KEYS) {
+                // A ragged tile: the V rows the copy leaves alone meet zero probabilities, so
+                // they must hold finite numbers, whatever the stage held before.
+                for (uint32_t i = lane; i < 2u * TILE_KEYS * 8u; i += 32) {
+                    const uint32_t row = (i >> 3) & (TILE_KEYS - 1), sub = i >> 9;
+                    if (row < r0 || row >= r0 + n)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(sb + (2 + sub) * SUB_BYTES + row * 128 + (i & 7) * 16), "r"(0u) : "memory");
+                }
+                __syncwarp();
+            }
+            if (lane == 0) {
+                const uint32_t bar = S.full + 8 * pipe.stage;
+                if (block >= P.n_blocks || r0 + n > (uint32_t)TILE_KEYS || n == 0) {
+                    // Recorded; the copy is skipped and the consumers see stale data.
+                    if (atomicCAS(&P.status->code, 0, 1) == 0) {
+                        P.status->where = 200;
+                        P.status->a = (int)block;
+                        P.status->b = (int)info;
+                    }
+                    mbar_expect_tx(bar, 0);
+                } else {
+                    const uint32_t bytes = n * 128;
+                    const size_t off = (size_t)block * (PAGE * D * 2) + (size_t)(half * TILE_KEYS + r0) * 128;
+                    const uint32_t dst = sb + r0 * 128;
+                    mbar_expect_tx(bar, 4 * bytes);
+                    if (P.single_use) {
+                        bulk_g2s_hint(dst, P.k_arena + off, bytes, bar, policy);
+                        bulk_g2s_hint(dst + SUB_BYTES, P.k_arena + off + PAGE * 128, bytes, bar, policy);
+                        bulk_g2s_hint(dst + 2 * SUB_BYTES, P.v_arena + off, bytes, bar, policy);
+                        bulk_g2s_hint(dst + 3 * SUB_BYTES, P.v_arena + off + PAGE * 128, bytes, bar, policy);
+                    } else {
+                        bulk_g2s(dst, P.k_arena + off, bytes, bar);
+                        bulk_g2s(dst + SUB_BYTES, P.k_arena + off + PAGE * 128, bytes, bar);
+                        bulk_g2s(dst + 2 * SUB_BYTES, P.v_arena + off, bytes, bar);
+                        bulk_g2s(dst + 3 * SUB_BYTES, P.v_arena + off + PAGE * 128, bytes, bar);
                     }
                 }
-                if (__shfl_sync(0xffffffffu, stop, 0)) return;
-                pipe.advance();
             }
+            pipe.advance(STAGES);
         }
     }
 }
 
-// ---- consumers --------------------------------------------------------------------------
+// ---- query staging ---------------------------------------------------------------------------
+// Row r of a slot is 256 bytes (128 16-bit elements); its sixteen 16-byte chunks are stored at
+// (chunk & 8) | ((chunk ^ r) & 7), which lets ldmatrix read A fragments without bank conflicts.
+__device__ __forceinline__ uint32_t q_chunk_off(int row, int chunk) {
+    return (uint32_t)row * 256u + (uint32_t)(((chunk & 8) | ((chunk ^ row) & 7)) << 4);
+}
+
+template <bool BF16>
+__device__ void stage_queries(const Params &P, const Shared &S, const CtaHdr hdr, int lane) {
+    Pipe pipe{0, 0};
+    const bool exact = (P.q_dtype == YX_BF16 && BF16) || (P.q_dtype == YX_F16 && !BF16);
+    for (uint32_t ii = hdr.item_begin; ii < hdr.item_end; ii++) {
+        const uint32_t *rec = P.recs[ii].w;
+        const uint32_t head_rows = rec[IR_HEAD_ROWS], mt = rec[IR_MT];
+        const int kvh = (int)(head_rows & 0xffffu), n_rows = (int)(head_rows >> 16);
+        const int q_rows = n_rows * P.group;
+        int stop = 0;
+        if (lane == 0) {
+            mbar_wait(S.qempty + 8 * pipe.stage, pipe.phase ^ 1u, S.abort_flag, P.status, 3);
+            stop = *S.abort_flag;
+        }
+        if (__shfl_sync(0xffffffffu, stop, 0)) return;
+        const uint32_t slot = S.q + pipe.stage * Q_SLOT_BYTES;
+        const bool low = mt != 64 && !exact;
+        const int chunk = lane >> 1;
+        const uint32_t sub = (lane & 1) * 8;
+        for (int r0 = 0; r0 < (int)mt; r0 += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const int qr = r0 + k;
+                v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (qr < q_rows) {
+                    const uint32_t row = rec[IR_ROW0 + IR_ROW_WORDS * (qr / P.group) + IRR_ROW];
+                    v[k] = load4_as_f32(P.q, P.q_dtype, ((size_t)row * P.hq + (size_t)kvh * P.group + qr % P.group) * D + lane * 4);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const int qr = r0 + k;
+                const uint32_t h0 = pack2<BF16>(v[k].x, v[k].y), h1 = pack2<BF16>(v[k].z, v[k].w);
+                const uint32_t addr = slot + q_chunk_off(qr, chunk) + sub;
+                asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(h0), "r"(h1) : "memory");
+                if (low) {
+                    const float2 f0 = unpack2<BF16>(h0), f1 = unpack2<BF16>(h1);
+                    const uint32_t l0 = pack2<BF16>(v[k].x - f0.x, v[k].y - f0.y), l1 = pack2<BF16>(v[k].z - f1.x, v[k].w - f1.y);
+                    asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr + Q_LOW_OFFSET), "r"(l0), "r"(l1) : "memory");
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(S.qfull + 8 * pipe.stage);
+        pipe.advance(Q_SLOTS);
+    }
+}
+
+// ---- consumers ---------------------------------------------------------------------------------
+// Word `idx` (32..127) of an item record held as three lane-indexed registers.
+__device__ __forceinline__ uint32_t rec_word(uint32_t w1, uint32_t w2, uint32_t w3, int idx) {
+    const uint32_t a = __shfl_sync(0xffffffffu, w1, idx & 31), b = __shfl_sync(0xffffffffu, w2, idx & 31),
+                   c = __shfl_sync(0xffffffffu, w3, idx & 31);
+    return idx < 64 ? a : (idx < 96 ? b : c);
+}
+
 template <int MT, bool BF16>
-__device__ void consume_item(const Params &P, const Shared &S, const uint32_t w, Pipe &pipe, int warp, int lane) {
+__device__ void consume_item(const Params &P, const Shared &S, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3,
+                             Pipe &pipe, Pipe &qpipe, int warp, int lane) {
     constexpr int NMT = MT / 16;          // 16-row tiles of queries
     constexpr int NSL = CONSUMERS / NMT;  // key slices of a tile
     constexpr int KS = TILE_KEYS / NSL;   // keys per slice
     constexpr int NT = KS / 8;            // 8-key score tiles per warp
+    constexpr bool LOW = MT != 64;        // f32 queries carry a low part (not for 64-row items)
     const int mi = warp % NMT, sl = warp / NMT;
     const int g = lane >> 2, t4 = lane & 3;
     const int group = P.group;
-    const uint32_t tb = field(w, W_TILE_BEGIN), te = field(w, W_TILE_END);
-    const uint32_t item_lo = field(w, W_KEY_LO), item_hi = field(w, W_KEY_HI);
-    const uint32_t head_rows = field(w, W_HEAD_ROWS);
-    const int kvh = (int)(head_rows & 0xffffu);
-    const int q_rows = (int)(head_rows >> 16) * group;
+    const uint32_t n_tiles = field(w0, IR_TILES), key_base = field(w0, IR_KEY0);
+    const uint32_t head_rows = field(w0, IR_HEAD_ROWS);
+    const int kvh = (int)(head_rows & 0xffffu), n_rows = (int)(head_rows >> 16);
+    const int q_rows = n_rows * group;
     const float sl2 = 0.08838834764831845f * 1.4426950408889634f;   // log2(e) / sqrt(128)
+    const bool exact_q = !LOW || (P.q_dtype == YX_BF16 && BF16) || (P.q_dtype == YX_F16 && !BF16);
 
     // The two query rows this thread owns in the accumulator fragments.
     uint32_t klo[2], khi[2], part[2];
-    size_t q_elem[2];
     bool valid[2];
 #pragma unroll
     for (int rs = 0; rs < 2; rs++) {
-        int qr = mi * 16 + g + rs * 8;
+        const int qr = mi * 16 + g + rs * 8;
         valid[rs] = qr < q_rows;
-        const int ri = valid[rs] ? qr / group : 0;   // index into the item's rows
-        const uint32_t row = (field(w, W_ROWS + (ri >> 1)) >> (16 * (ri & 1))) & 0xffffu;
-        part[rs] = field(w, W_PART + ri);
-        klo[rs] = 0;
-        khi[rs] = 0xffffffffu;
-        q_elem[rs] = 0;
-        if (valid[rs]) {
-            uint32_t p = P.pos[row];
-            uint32_t lo = 0;
-            if (P.window > 0 && p + 1 > P.window) lo = p + 1 - P.window;
-            klo[rs] = max(lo, item_lo);
-            khi[rs] = min(p, item_hi);
-            q_elem[rs] = ((size_t)row * P.hq + (size_t)kvh * group + (qr % group)) * D;
-        }
+        const int base = IR_ROW0 + IR_ROW_WORDS * (valid[rs] ? qr / group : 0);
+        const uint32_t a = rec_word(w1, w2, w3, base + IRR_KLO), b = rec_word(w1, w2, w3, base + IRR_KHI);
+        part[rs] = rec_word(w1, w2, w3, base + IRR_PART);
+        klo[rs] = valid[rs] ? a : 0u;            // padded rows: zero queries, nothing masked
+        khi[rs] = valid[rs] ? b : 0xffffffffu;
     }
-    // Query fragments, high and low parts.
-    uint32_t qh[8][4], ql[8][4];
-    // The low part of an f32 query costs a second MMA per score tile; items with 64 padded rows
-    // are the ones bound by tensor work, and their rows see long shared prefixes over which the
-    // query's rounding averages out, so they go without it.
-    const bool exact_q = MT == 64 || (P.q_dtype == YX_BF16 && BF16) || (P.q_dtype == YX_F16 && !BF16);
+
+    // Query fragments from the staged slot.
+    uint32_t qh[8][4], ql[LOW ? 8 : 1][4];
+    {
+        mbar_wait(S.qfull + 8 * qpipe.stage, qpipe.phase, S.abort_flag, P.status, 4);
+        const uint32_t slot = S.q + qpipe.stage * Q_SLOT_BYTES;
+        const int row = mi * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
 #pragma unroll
-    for (int ks = 0; ks < 8; ks++) {
-#pragma unroll
-        for (int r = 0; r < 4; r++) {
-            int rs = r & 1, dim = ks * 16 + (r >> 1) * 8 + 2 * t4;
-            float2 v = valid[rs] ? load_q2(P.q, P.q_dtype, q_elem[rs] + dim) : make_float2(0.f, 0.f);
-            uint32_t h = pack2<BF16>(v.x, v.y);
-            float2 hf = unpack2<BF16>(h);
-            qh[ks][r] = h;
-            ql[ks][r] = pack2<BF16>(v.x - hf.x, v.y - hf.y);
+        for (int ks = 0; ks < 8; ks++) {
+            const uint32_t a = slot + q_chunk_off(row, 2 * ks + (lane >> 4));
+            ldsm4(a, qh[ks][0], qh[ks][1], qh[ks][2], qh[ks][3]);
+            if constexpr (LOW) {
+                if (!exact_q) ldsm4(a + Q_LOW_OFFSET, ql[ks][0], ql[ks][1], ql[ks][2], ql[ks][3]);
+            }
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(S.qempty + 8 * qpipe.stage);
+        qpipe.advance(Q_SLOTS);
     }
 
     float o[16][4];
@@ -299,17 +269,17 @@ __device__ void consume_item(const Params &P, const Shared &S, const uint32_t w,
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
     const int lm = lane >> 3, lr = lane & 7;
-    for (uint32_t t = tb; t < te; t++) {
+    for (uint32_t ti = 0; ti < n_tiles; ti++) {
         mbar_wait(S.full + 8 * pipe.stage, pipe.phase, S.abort_flag, P.status, 2);
+        if (P.trace && threadIdx.x == 0 && P.trace[8 * blockIdx.x + 3] == 0) P.trace[8 * blockIdx.x + 3] = gtime();
         const uint32_t sb = S.stages + pipe.stage * STAGE_BYTES;
 
-        // S = Q K^T over this warp's KS keys.
-        // The low parts of the queries accumulate on their own, so that no MMA waits on more
-        // than the eight before it in its chain.
-        float s[NT][4], s2[MT == 64 ? 1 : NT][4];
+        // S = Q K^T over this warp's KS keys.  The low parts of the queries accumulate on their
+        // own, so that no MMA waits on more than the eight before it in its chain.
+        float s[NT][4], s2[LOW ? NT : 1][4];
 #pragma unroll
         for (int j = 0; j < NT; j++) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-        if constexpr (MT != 64) {
+        if constexpr (LOW) {
 #pragma unroll
             for (int j = 0; j < NT; j++) s2[j][0] = s2[j][1] = s2[j][2] = s2[j][3] = 0.f;
         }
@@ -319,12 +289,12 @@ __device__ void consume_item(const Params &P, const Shared &S, const uint32_t w,
             const int c = ((2 * ks) & 7) + (lm & 1);
 #pragma unroll
             for (int np = 0; np < NT / 2; np++) {
-                int key = sl * KS + np * 16 + (lm >> 1) * 8 + lr;
+                const int key = sl * KS + np * 16 + (lm >> 1) * 8 + lr;
                 uint32_t b0, b1, b2, b3;
                 ldsm4(sub + key * 128 + ((c ^ lr) << 4), b0, b1, b2, b3);
                 mma16816<BF16>(s[2 * np], qh[ks], b0, b1);
                 mma16816<BF16>(s[2 * np + 1], qh[ks], b2, b3);
-                if constexpr (MT != 64) {
+                if constexpr (LOW) {
                     if (!exact_q) {
                         mma16816<BF16>(s2[2 * np], ql[ks], b0, b1);
                         mma16816<BF16>(s2[2 * np + 1], ql[ks], b2, b3);
@@ -332,20 +302,20 @@ __device__ void consume_item(const Params &P, const Shared &S, const uint32_t w,
                 }
             }
         }
-        if constexpr (MT != 64) {
+        if constexpr (LOW) {
 #pragma unroll
             for (int j = 0; j < NT; j++)
 #pragma unroll
                 for (int e = 0; e < 4; e++) s[j][e] += s2[j][e];
         }
         // Mask keys outside each row's [klo, khi].
-        const uint32_t key0 = t * TILE_KEYS + sl * KS + 2 * t4;
+        const uint32_t key0 = key_base + ti * TILE_KEYS + sl * KS + 2 * t4;
 #pragma unroll
         for (int j = 0; j < NT; j++)
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                uint32_t key = key0 + j * 8 + (e & 1);
-                int rs = e >> 1;
+                const uint32_t key = key0 + j * 8 + (e & 1);
+                const int rs = e >> 1;
                 if (key < klo[rs] || key > khi[rs]) s[j][e] = -INFINITY;
             }
         // Online softmax, per owned row.
@@ -356,15 +326,15 @@ __device__ void consume_item(const Params &P, const Shared &S, const uint32_t w,
             for (int j = 0; j < NT; j++) mx = fmaxf(mx, fmaxf(s[j][2 * rs], s[j][2 * rs + 1]));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            float mn = fmaxf(m[rs], mx);
-            float mu = mn == -INFINITY ? 0.f : mn;
-            float alpha = exp2f((m[rs] - mu) * sl2);
+            const float mn = fmaxf(m[rs], mx);
+            const float mu = mn == -INFINITY ? 0.f : mn;
+            const float alpha = exp2f((m[rs] - mu) * sl2);
             m[rs] = mn;
             float sum = 0.f;
-            float ms = mu * sl2;
+            const float ms = mu * sl2;
 #pragma unroll
             for (int j = 0; j < NT; j++) {
-                float p0 = exp2f(s[j][2 * rs] * sl2 - ms), p1 = exp2f(s[j][2 * rs + 1] * sl2 - ms);
+                const float p0 = exp2f(s[j][2 * rs] * sl2 - ms), p1 = exp2f(s[j][2 * rs + 1] * sl2 - ms);
                 s[j][2 * rs] = p0;
                 s[j][2 * rs + 1] = p1;
                 sum += p0 + p1;
@@ -386,11 +356,11 @@ __device__ void consume_item(const Params &P, const Shared &S, const uint32_t w,
                 a[r] = pack2<BF16>(p0, p1);
                 if constexpr (BF16) {
                     // bf16 keeps 8 bits of a probability; its remainder goes in a second MMA.
-                    float2 hf = unpack2<BF16>(a[r]);
+                    const float2 hf = unpack2<BF16>(a[r]);
                     al[r] = pack2<BF16>(p0 - hf.x, p1 - hf.y);
                 }
             }
-            int key = sl * KS + kk * 16 + (lm & 1) * 8 + lr;
+            const int key = sl * KS + kk * 16 + (lm & 1) * 8 + lr;
 #pragma unroll
             for (int np = 0; np < 8; np++) {
                 const uint32_t sub = sb + 2 * SUB_BYTES + (np >> 2) * SUB_BYTES;
@@ -407,7 +377,7 @@ __device__ void consume_item(const Params &P, const Shared &S, const uint32_t w,
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(S.empty + 8 * pipe.stage);
-        pipe.advance();
+        pipe.advance(STAGES);
     }
 
     // Row sums across the quad.
@@ -424,7 +394,7 @@ __device__ void consume_item(const Params &P, const Shared &S, const uint32_t w,
             float *w = scratch + ((sl - 1) * NMT + mi) * MERGE_FLOATS;
 #pragma unroll
             for (int rs = 0; rs < 2; rs++) {
-                int r = g + rs * 8;
+                const int r = g + rs * 8;
                 if (t4 == 0) {
                     w[r] = m[rs];
                     w[16 + r] = l[rs];
@@ -438,12 +408,12 @@ __device__ void consume_item(const Params &P, const Shared &S, const uint32_t w,
         if (sl == 0) {
 #pragma unroll
             for (int rs = 0; rs < 2; rs++) {
-                int r = g + rs * 8;
+                const int r = g + rs * 8;
                 float mx = m[rs];
 #pragma unroll
                 for (int x = 1; x < NSL; x++) mx = fmaxf(mx, scratch[((x - 1) * NMT + mi) * MERGE_FLOATS + r]);
-                float mu = mx == -INFINITY ? 0.f : mx;
-                float f = exp2f((m[rs] - mu) * sl2);
+                const float mu = mx == -INFINITY ? 0.f : mx;
+                const float f = exp2f((m[rs] - mu) * sl2);
                 l[rs] *= f;
 #pragma unroll
                 for (int n = 0; n < 16; n++) {
@@ -453,11 +423,11 @@ __device__ void consume_item(const Params &P, const Shared &S, const uint32_t w,
 #pragma unroll
                 for (int x = 1; x < NSL; x++) {
                     const float *w = scratch + ((x - 1) * NMT + mi) * MERGE_FLOATS;
-                    float fx = exp2f((w[r] - mu) * sl2);
+                    const float fx = exp2f((w[r] - mu) * sl2);
                     l[rs] += w[16 + r] * fx;
 #pragma unroll
                     for (int n = 0; n < 16; n++) {
-                        float2 v = *(const float2 *)(w + 32 + r * D + n * 8 + 2 * t4);
+                        const float2 v = *(const float2 *)(w + 32 + r * D + n * 8 + 2 * t4);
                         o[n][2 * rs] += v.x * fx;
                         o[n][2 * rs + 1] += v.y * fx;
                     }
@@ -470,62 +440,131 @@ __device__ void consume_item(const Params &P, const Shared &S, const uint32_t w,
 #pragma unroll
         for (int rs = 0; rs < 2; rs++) {
             if (!valid[rs]) continue;
-            int qr = mi * 16 + g + rs * 8;
-            size_t slot = (size_t)part[rs] * group + (qr % group);
+            const int qr = mi * 16 + g + rs * 8;
+            const size_t slot = (size_t)part[rs] * group + (qr % group);
             float *po = P.part_o + slot * D;
 #pragma unroll
-            for (int n = 0; n < 16; n++) *(float2 *)(po + n * 8 + 2 * t4) = make_float2(o[n][2 * rs], o[n][2 * rs + 1]);
+            for (int n = 0; n < 16; n++) __stcg((float2 *)(po + n * 8 + 2 * t4), make_float2(o[n][2 * rs], o[n][2 * rs + 1]));
             if (t4 == 0) {
-                bool none = m[rs] == -INFINITY;
-                P.part_ml[slot * 2] = none ? -1e30f : m[rs] * 0.08838834764831845f;
-                P.part_ml[slot * 2 + 1] = none ? 0.f : l[rs];
+                const bool none = m[rs] == -INFINITY;
+                __stcg((float2 *)(P.part_ml + slot * 2), make_float2(none ? -1e30f : m[rs] * 0.08838834764831845f, none ? 0.f : l[rs]));
+            }
+        }
+        __threadfence();   // the triples are visible device-wide before this item is counted
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");
+
+    // Fused merge: count this item in for each of its (row, KV head); whoever completes one
+    // merges all of its triples and writes the result.
+    int *flags = (int *)__cvta_shared_to_generic((size_t)S.flags);
+    if (warp == 0) {
+        // every lane takes part in the shuffles of rec_word; lanes beyond n_rows ignore theirs
+        const int base = IR_ROW0 + IR_ROW_WORDS * min(lane, MAX_ITEM_ROWS - 1);
+        const uint32_t row = rec_word(w1, w2, w3, base + IRR_ROW), count = rec_word(w1, w2, w3, base + IRR_COUNT);
+        if (lane < n_rows) {
+            uint32_t *ctr = P.counters + (size_t)row * P.hkv + kvh;
+            const uint32_t old = atomicAdd(ctr, 1u);
+            const bool last = old + 1 == count;
+            if (last) *ctr = 0u;   // nobody else touches it in this launch: left clean for the next
+            flags[lane] = last ? 1 : 0;
+        }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");
+    for (int r = 0; r < n_rows; r++) {
+        if (!flags[r]) continue;   // uniform across the CTA
+        __threadfence();
+        const int base = IR_ROW0 + IR_ROW_WORDS * r;
+        const uint32_t row = rec_word(w1, w2, w3, base + IRR_ROW), first = rec_word(w1, w2, w3, base + IRR_FIRST),
+                       count = rec_word(w1, w2, w3, base + IRR_COUNT);
+        for (int hg = warp; hg < group; hg += CONSUMERS) {
+            float mx, ls;
+            float4 acc;
+            merge_parts(P.part_o, P.part_ml, first, count, group, hg, lane, mx, ls, acc);
+            const size_t idx = (size_t)row * P.hq + (size_t)kvh * group + hg;
+            if (P.out) {
+                const float inv = 1.0f / ls;   // a row always sees its own key: ls > 0 for whole attention
+                store4(P.out, P.out_dtype, idx * D + lane * 4, make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv));
+            }
+            if (P.o_out) {
+                *(float4 *)(P.o_out + idx * D + lane * 4) = acc;
+                if (lane == 0) {
+                    P.m_out[idx] = mx;
+                    P.l_out[idx] = ls;
+                }
             }
         }
     }
-    if constexpr (NSL > 1) asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");
+    // `flags` and the merge scratch are rewritten only after the next item's barriers.
 }
 
 template <bool BF16>
-__global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const Params P) {
+__global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const __grid_constant__ Params P) {
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ int abort_flag;
     Shared S;
     S.stages = smem_u32(smem);
-    S.merge = S.stages + STAGES * STAGE_BYTES;
-    S.full = S.merge + ((MERGE_BYTES + 127) / 128) * 128;
+    S.q = S.stages + STAGES * STAGE_BYTES;
+    S.merge = S.q + Q_SLOTS * Q_SLOT_BYTES;
+    S.flags = S.merge + MERGE_BYTES;
+    S.full = S.flags + 128;
     S.empty = S.full + 8 * STAGES;
+    S.qfull = S.empty + 8 * STAGES;
+    S.qempty = S.qfull + 8 * Q_SLOTS;
     S.abort_flag = &abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Stale rows of a ragged tile are multiplied by zero probabilities: they must be finite.
-    for (int i = threadIdx.x; i < STAGES * STAGE_BYTES / 16; i += THREADS) ((uint4 *)smem)[i] = make_uint4(0, 0, 0, 0);
+    unsigned long long *tr = P.trace ? P.trace + 8 * blockIdx.x : nullptr;
+    if (tr && threadIdx.x == 0) tr[0] = gtime();
+    const CtaHdr hdr = *(const CtaHdr *)(P.cta_hdr + blockIdx.x);   // in flight during the set-up below
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < STAGES; s++) {
             mbar_init(S.full + 8 * s, 1);
             mbar_init(S.empty + 8 * s, CONSUMERS);
         }
+        for (int s = 0; s < Q_SLOTS; s++) {
+            mbar_init(S.qfull + 8 * s, 1);
+            mbar_init(S.qempty + 8 * s, CONSUMERS);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
+    if (tr && threadIdx.x == 0) {
+        tr[1] = gtime();
+        tr[7] = hdr.item_end - hdr.item_begin;
+    }
 
-    const uint32_t ib = P.cta_begin[blockIdx.x], ie = P.cta_begin[blockIdx.x + 1];
-    if (warp == CONSUMERS) {
-        produce(P, S, ib, ie, lane);
+    if (warp == PRODUCER) {
+        produce(P, S, hdr, lane);
+        if (tr && lane == 0) tr[6] = gtime();
         return;
     }
-    Pipe pipe{0, 0};
-    uint32_t w_next = ib < ie ? item_word(P.items, ib, lane) : 0u;
-    for (uint32_t ii = ib; ii < ie; ii++) {
-        const uint32_t w = w_next;
-        if (ii + 1 < ie) w_next = item_word(P.items, ii + 1, lane);   // in flight while this item runs
-        switch (field(w, W_MT)) {
-            case 16: consume_item<16, BF16>(P, S, w, pipe, warp, lane); break;
-            case 32: consume_item<32, BF16>(P, S, w, pipe, warp, lane); break;
-            default: consume_item<64, BF16>(P, S, w, pipe, warp, lane); break;
-        }
+    if (warp == QWARP) {
+        stage_queries<BF16>(P, S, hdr, lane);
+        return;
     }
+    Pipe pipe{0, 0}, qpipe{0, 0};
+    uint32_t n0 = 0, n1 = 0, n2 = 0, n3 = 0;
+    if (hdr.item_begin < hdr.item_end) {
+        const uint32_t *r = P.recs[hdr.item_begin].w;
+        n0 = r[lane], n1 = r[32 + lane], n2 = r[64 + lane], n3 = r[96 + lane];
+    }
+    for (uint32_t ii = hdr.item_begin; ii < hdr.item_end; ii++) {
+        const uint32_t w0 = n0, w1 = n1, w2 = n2, w3 = n3;
+        if (ii + 1 < hdr.item_end) {   // in flight while this item runs
+            const uint32_t *r = P.recs[ii + 1].w;
+            n0 = r[lane], n1 = r[32 + lane], n2 = r[64 + lane], n3 = r[96 + lane];
+        }
+        if (tr && threadIdx.x == 0 && ii == hdr.item_begin) tr[2] = gtime();
+        switch (field(w0, IR_MT)) {
+            case 16: consume_item<16, BF16>(P, S, w0, w1, w2, w3, pipe, qpipe, warp, lane); break;
+            case 32: consume_item<32, BF16>(P, S, w0, w1, w2, w3, pipe, qpipe, warp, lane); break;
+            default: consume_item<64, BF16>(P, S, w0, w1, w2, w3, pipe, qpipe, warp, lane); break;
+        }
+        if (tr && threadIdx.x == 0 && ii == hdr.item_begin) tr[4] = gtime();
+    }
+    if (tr && threadIdx.x == 0) tr[5] = gtime();
     if (abort_flag) {
         // Copies issued before giving up may still be landing in this CTA's shared memory.
         for (int i = 0; i < 64; i++) __nanosleep(1000);
@@ -550,15 +589,21 @@ int launch_attend_mma(yx_ctx *ctx, const AttendArgs &a) {
     P.hkv = a.hkv;
     P.k_arena = a.k_arena;
     P.v_arena = a.v_arena;
-    P.kv_pages = a.kv_pages;
-    P.window = (uint32_t)std::max<int64_t>(a.window, 0);
-    P.pos = ctx->d_pos;
-    P.pages = ctx->d_pages;
-    P.items = a.items;
-    P.cta_begin = a.cta_begin;
+    P.n_blocks = a.kv_pages * (uint32_t)a.hkv;
+    P.cta_hdr = a.cta_hdr;
+    P.tiles = a.tiles;
+    P.recs = a.recs;
+    P.single_use = a.single_use ? 1 : 0;
     P.part_o = a.part_o;
     P.part_ml = a.part_ml;
+    P.counters = a.counters;
+    P.out = a.out;
+    P.out_dtype = a.out_dtype;
+    P.m_out = a.m_out;
+    P.l_out = a.l_out;
+    P.o_out = a.o_out;
     P.status = ctx->dev_status;
+    P.trace = (unsigned long long *)ctx->trace_buf;
     if (bf16) attend_mma_kernel<true><<<a.n_ctas, THREADS, SMEM_BYTES, ctx->stream>>>(P);
     else attend_mma_kernel<false><<<a.n_ctas, THREADS, SMEM_BYTES, ctx->stream>>>(P);
     ctx->launches++;

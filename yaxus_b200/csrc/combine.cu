@@ -115,12 +115,34 @@ __global__ void combine_flat_kernel(int n_parts, const float *__restrict__ m, co
     store_out(out, out_dtype, idx * D + lane * 4, make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv));
 }
 
+__global__ void fill_empty_kernel(size_t n, float *m, float *l, float *o) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n * D) o[i] = 0.0f;
+    if (i < n) {
+        m[i] = -1e30f;
+        l[i] = 0.0f;
+    }
+}
+
 }  // namespace
+
+int launch_fill_empty(yx_ctx *ctx, size_t n, float *m, float *l, float *o) {
+    size_t blocks = (n * D + 255) / 256;
+    fill_empty_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(n, m, l, o);
+    ctx->launches++;
+    return check_cuda(ctx, cudaGetLastError(), "fill_empty kernel");
+}
 
 int launch_combine(yx_ctx *ctx, const Merge *merges, const float *part_o, const float *part_ml, int rows, int hq,
                    int group, void *out, int out_dtype, float *m_out, float *l_out, float *o_out) {
     uint32_t n = (uint32_t)rows * (uint32_t)hq;
     uint32_t blocks = (n * 32 + 127) / 128;
+    if (!ctx->smem_configured[2]) {
+        // Same shared-memory carve-out as the split-key kernel it follows, so that the SMs are
+        // not reconfigured between the two on every attention call.
+        cudaFuncSetAttribute(combine_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        ctx->smem_configured[2] = true;
+    }
     combine_kernel<<<blocks, 128, 0, ctx->stream>>>(merges, part_o, part_ml, n, hq, group, out, out_dtype, m_out,
                                                    l_out, o_out);
     ctx->launches++;
@@ -130,6 +152,10 @@ int launch_combine(yx_ctx *ctx, const Merge *merges, const float *part_o, const 
 int launch_combine_strided(yx_ctx *ctx, int n_parts, const float *m, const float *l, const float *o, size_t sm,
                            size_t sl, size_t so, size_t n, void *out, int out_dtype) {
     size_t blocks = (n * 32 + 127) / 128;
+    if (!ctx->smem_configured[3]) {
+        cudaFuncSetAttribute(combine_flat_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        ctx->smem_configured[3] = true;
+    }
     combine_flat_kernel<<<(unsigned)blocks, 128, 0, ctx->stream>>>(n_parts, m, l, o, sm, sl, so, n, out, out_dtype);
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "combine_flat kernel");

@@ -169,6 +169,12 @@ int launch_append(yx_ctx *ctx, yx_kv *kv, int layer, const void *k_rows, const v
     uint32_t rows = ctx->pass.rows;
     uint32_t total = rows * (uint32_t)kv->hkv * 16u;
     dim3 grid((total + 255) / 256, 2);
+    if (!ctx->smem_configured[4]) {
+        // Keep the carve-out of the attention kernels these run between.
+        cudaFuncSetAttribute(append_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(qk_rope_append_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        ctx->smem_configured[4] = true;
+    }
     append_kernel<<<grid, 256, 0, ctx->stream>>>(k_rows, v_rows, src_dtype, ctx->d_slot, rows, kv->hkv, kv->dtype,
                                                   kv->k(layer), kv->v(layer));
     ctx->launches++;
@@ -180,6 +186,11 @@ int launch_qk_rope_append(yx_ctx *ctx, yx_kv *kv, int layer, const float *qkv, c
     uint32_t rows = ctx->pass.rows;
     uint64_t warps = (uint64_t)rows * (hq + 2 * kv->hkv);
     uint32_t blocks = (uint32_t)((warps * 32 + 255) / 256);
+    if (!ctx->smem_configured[4]) {
+        cudaFuncSetAttribute(append_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(qk_rope_append_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        ctx->smem_configured[4] = true;
+    }
     qk_rope_append_kernel<<<blocks, 256, 0, ctx->stream>>>(qkv, q_norm, k_norm, ctx->d_pos, ctx->d_slot, rows, hq,
                                                           kv->hkv, eps, (const yx_rope *)kv->rope_dev + layer,
                                                           kv->dtype, kv->k(layer), kv->v(layer), q_out);

@@ -11,6 +11,8 @@
 // Rows whose page tables name the same physical pages over a common prefix (what
 // `KvCache::fork` shares, crates/yaxus-model/src/kv.rs:277-295) are put in one item over that
 // prefix, so the shared pages are read once for all of them.
+#include <string.h>
+
 #include <algorithm>
 #include <string>
 #include <unordered_map>
@@ -275,6 +277,49 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
             Merge &m = out.merges[(size_t)it.rows[r] * pp.hkv + it.kv_head];
             it.part[r] = m.first + m.count++;
         }
+    for (const Merge &m : out.merges)
+        if (m.count == 0) out.has_empty_rows = true;
+
+    // 6. The resolved form: page tables walked here, once, instead of by every CTA.
+    if (pp.resolve) {
+        out.cta_hdr.resize(n_ctas);
+        out.recs.resize(out.items.size());
+        out.tiles.reserve((size_t)total_tiles);
+        for (int c = 0; c < n_ctas; c++) {
+            CtaHdr &h = out.cta_hdr[c];
+            h.item_begin = out.cta_begin[c];
+            h.item_end = out.cta_begin[c + 1];
+            h.tile_begin = (uint32_t)out.tiles.size();
+            for (uint32_t i = h.item_begin; i < h.item_end; i++) {
+                const Item &it = out.items[i];
+                for (uint32_t t = it.tile_begin; t < it.tile_end; t++) {
+                    uint32_t a = std::max(it.key_lo, t * TILE_KEYS), b = std::min(it.key_hi, t * TILE_KEYS + TILE_KEYS - 1);
+                    TileDesc d;
+                    d.block = pass.pages[it.pt_off + t * TILE_KEYS / PAGE] * (uint32_t)pp.hkv + it.kv_head;
+                    d.info = (t & 1u) | ((a - t * TILE_KEYS) << 1) | ((b - a + 1) << 8);
+                    out.tiles.push_back(d);
+                }
+                ItemRec &r = out.recs[i];
+                memset(&r, 0, sizeof r);
+                r.w[IR_TILES] = it.tile_end - it.tile_begin;
+                r.w[IR_KEY0] = it.tile_begin * TILE_KEYS;
+                r.w[IR_HEAD_ROWS] = (uint32_t)it.kv_head | ((uint32_t)it.n_rows << 16);
+                r.w[IR_MT] = it.mt;
+                for (int k = 0; k < it.n_rows; k++) {
+                    uint32_t row = it.rows[k], p = pass.pos[row];
+                    const Merge &m = out.merges[(size_t)row * pp.hkv + it.kv_head];
+                    uint32_t *w = r.w + IR_ROW0 + IR_ROW_WORDS * k;
+                    w[IRR_KLO] = std::max(row_lo(p, pp.window), it.key_lo);
+                    w[IRR_KHI] = std::min(p, it.key_hi);
+                    w[IRR_PART] = it.part[k];
+                    w[IRR_ROW] = row;
+                    w[IRR_FIRST] = m.first;
+                    w[IRR_COUNT] = m.count;
+                }
+            }
+            h.tile_end = (uint32_t)out.tiles.size();
+        }
+    }
 
     uint64_t uniq = 0;
     for (auto &kv : seen) uniq += kv.second;
@@ -286,6 +331,12 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
     out.info.unique_kv_bytes = (int64_t)uniq * per_key;
     out.info.logical_kv_bytes = (int64_t)logical * per_key;
     out.info.shared_groups = shared_groups;
+    // Every tile read by one item only: nothing is gained by keeping K/V lines in L2.
+    uint64_t streamed = 0;
+    for (const Item &it : out.items)
+        for (uint32_t t = it.tile_begin; t < it.tile_end; t++)
+            streamed += std::min(it.key_hi, t * TILE_KEYS + TILE_KEYS - 1) - std::max(it.key_lo, t * TILE_KEYS) + 1;
+    out.single_use = streamed * (uint64_t)per_key / pp.hkv <= (uint64_t)out.info.unique_kv_bytes;
 }
 
 }  // namespace yx

@@ -24,7 +24,8 @@ extern "C" int yx_plan_probe(uint32_t rows, const uint32_t *pos, const uint32_t 
     pp.share_prefix = share_prefix != 0;
     pp.esize = esize;
     pp.w32 = cost32 > 0 ? cost32 : 16;
-    pp.w64 = cost64 > 0 ? cost64 : 32;
+    pp.w64 = cost64 > 0 ? cost64 : 16;
+    pp.resolve = true;
     yx::Plan plan;
     try {
         yx::build_split_plan(pass, pp, plan);
@@ -54,4 +55,10 @@ extern "C" int yx_plan_probe(uint32_t rows, const uint32_t *pos, const uint32_t 
         }
     }
     return YX_OK;
+}
+
+// Diagnostics hook (not part of the public header): per-CTA timestamps of the split-key kernel
+// are written to `dev_buf` (8 x u64 per CTA) while it is set.
+extern "C" void yx_debug_set_trace(yx_ctx *ctx, void *dev_buf) {
+    if (ctx) ctx->trace_buf = dev_buf;
 }

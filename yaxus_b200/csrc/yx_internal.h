@@ -69,6 +69,36 @@ struct Merge {
     uint32_t count;  // slots
 };
 
+// ---- the same plan, resolved for the streaming kernel --------------------------------------
+// The tensor split-key kernel never walks a page table: the host, which holds the tables
+// anyway, resolves every 64-key tile to the (page, KV head) block it lives in, so that the
+// kernel's copy engine is fed from one flat array and nothing on the device waits on a
+// dependent lookup.
+
+// What one persistent CTA works through.
+struct CtaHdr {
+    uint32_t item_begin, item_end;   // ItemRec range
+    uint32_t tile_begin, tile_end;   // TileDesc range (the items' tiles, in order)
+};
+
+// One 64-key tile: where it is and which of its rows hold keys of the item.
+struct TileDesc {
+    uint32_t block;   // page * hkv + kv_head: index of the 32 KiB block in the K and V arenas
+    uint32_t info;    // bit 0: which half of the page; bits 1-7: first row; bits 8-15: rows (1..64)
+};
+
+// An item as the kernel reads it: 128 words, fetched by a warp with four coalesced loads.
+struct alignas(16) ItemRec {
+    uint32_t w[128];
+};
+constexpr int IR_TILES = 0;       // tiles of the item
+constexpr int IR_KEY0 = 1;        // logical position of the first tile's first key
+constexpr int IR_HEAD_ROWS = 2;   // kv_head | n_rows << 16
+constexpr int IR_MT = 3;          // padded query rows: 16, 32, 64
+constexpr int IR_ROW0 = 32;       // then six words per pass row:
+constexpr int IR_ROW_WORDS = 6;   //   first key seen, last key seen, partial slot, pass row, first slot, slots
+constexpr int IRR_KLO = 0, IRR_KHI = 1, IRR_PART = 2, IRR_ROW = 3, IRR_FIRST = 4, IRR_COUNT = 5;
+
 struct Plan {
     int path = 0;
     int n_ctas = 0;
@@ -76,6 +106,12 @@ struct Plan {
     std::vector<uint32_t> cta_begin;    // n_ctas + 1 offsets into items
     std::vector<Merge> merges;          // [rows][hkv]
     uint32_t n_parts = 0;
+    // resolved form (filled when PlanParams::resolve is set)
+    std::vector<CtaHdr> cta_hdr;
+    std::vector<TileDesc> tiles;
+    std::vector<ItemRec> recs;
+    bool single_use = false;            // every tile is read by exactly one item
+    bool has_empty_rows = false;        // some (row, kv head) has no item: no live key in the range
     yx_plan_info info{};
 };
 
@@ -93,6 +129,7 @@ struct PlanParams {
     bool share_prefix;
     int esize;               // bytes per stored element
     int w32, w64;            // cost of a tile of an item with 32 / 64 padded rows, in 16ths of a 16-row tile's
+    bool resolve;            // also build the resolved form for the streaming kernel
 };
 
 // Builds the split-key plan.  Throws std::string on a malformed pass.
@@ -133,7 +170,8 @@ struct yx_ctx {
     yx_tuning tuning{};
     yx_plan_info last_plan{};
     int64_t launches = 0;
-    bool smem_configured[8] = {};          // per-kernel opt-in to large dynamic shared memory
+    bool smem_configured[8] = {};
+    void *trace_buf = nullptr;             // device buffer for per-CTA kernel timestamps (diagnostics)          // per-kernel opt-in to large dynamic shared memory
 
     yx_dev_status *dev_status = nullptr;   // pinned, mapped
 
@@ -166,13 +204,16 @@ struct yx_ctx {
         int hkv = 0, group = 0, max_rows = 0, n_ctas = 0, esize = 0, w32 = 0, w64 = 0;
         int64_t window = 0;
         uint64_t key_lo = 0, key_hi = 0;
-        bool share = false;
+        bool share = false, resolve = false;
         yx::Plan plan;
-        char *dev = nullptr;       // items | cta_begin | merges
+        char *dev = nullptr;       // items | cta_begin | merges | cta_hdr | tiles | recs
         size_t dev_cap = 0;
         yx::Item *d_items = nullptr;
         uint32_t *d_cta_begin = nullptr;
         yx::Merge *d_merges = nullptr;
+        yx::CtaHdr *d_cta_hdr = nullptr;
+        yx::TileDesc *d_tiles = nullptr;
+        yx::ItemRec *d_recs = nullptr;
     };
     std::vector<CachedPlan> plans;
 
@@ -182,6 +223,8 @@ struct yx_ctx {
     size_t ws_o_cap = 0, ws_ml_cap = 0;
     float *q_tmp = nullptr;  // normalised, rotated q of yx_attention
     size_t q_tmp_cap = 0;
+    uint32_t *counters = nullptr;   // arrival counters of the fused merge; all zero between launches
+    size_t counters_cap = 0;
 
     // multi-GPU
     ncclComm *comm = nullptr;
@@ -225,9 +268,20 @@ struct AttendArgs {
     int n_ctas;
     float *part_o;
     float *part_ml;
+    // resolved plan and fused merge (tensor kernel)
+    const CtaHdr *cta_hdr;
+    const TileDesc *tiles;
+    const ItemRec *recs;
+    bool single_use;
+    uint32_t *counters;      // one per (pass row, kv head), zero between launches
+    void *out;               // normalised output, or null
+    int out_dtype;
+    float *m_out, *l_out, *o_out;   // merged triple, or null
 };
 int launch_attend_simt(yx_ctx *ctx, const AttendArgs &a);
 int launch_attend_mma(yx_ctx *ctx, const AttendArgs &a);
+// Writes the empty mark (-1e30, 0, 0) for n (row, head) triples.
+int launch_fill_empty(yx_ctx *ctx, size_t n, float *m, float *l, float *o);
 int launch_combine(yx_ctx *ctx, const Merge *merges, const float *part_o, const float *part_ml, int rows,
                    int hq, int group, void *out, int out_dtype, float *m_out, float *l_out, float *o_out);
 // Parts with strides (in floats) sm, sl, so between consecutive parts of m, l and o.
