@@ -289,6 +289,7 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     a.tiles = cp->d_tiles;
     a.recs = cp->d_recs;
     a.single_use = pl.single_use;
+    a.plan = &pl;
     a.counters = ctx->counters;
     a.out = out;
     a.out_dtype = out_dtype;

@@ -66,6 +66,18 @@ struct Pipe {
     }
 };
 
+// What a CTA needs before its first global load returns, passed in kernel-parameter space:
+// its span, its first two tiles and the rows of its first item.  A cold global load at kernel
+// start costs over a microsecond; three of them in a chain (span -> descriptors -> data) were
+// the largest single cost of a 15-microsecond kernel.
+constexpr int MAX_PROLOGUE_CTAS = 160;
+struct CtaPrologue {
+    CtaHdr hdr;
+    TileDesc first[2];
+    uint32_t head_rows, mt;
+    uint16_t rows[MAX_ITEM_ROWS];
+};
+
 struct Params {
     const void *q;
     int q_dtype, hq, group, hkv;
@@ -82,69 +94,90 @@ struct Params {
     float *m_out, *l_out, *o_out;
     yx_dev_status *status;
     unsigned long long *trace;       // optional: 8 timestamps / counters per CTA
+    int has_prologue;
+    CtaPrologue pro[MAX_PROLOGUE_CTAS];
 };
 
 __device__ __forceinline__ uint32_t field(uint32_t w, int idx) { return __shfl_sync(0xffffffffu, w, idx); }
 
 // ---- producer: tile descriptors -> bulk copies ----------------------------------------------
+// One tile: wait for a free stage, zero what a ragged copy leaves alone, start the four copies.
+// Returns false when the CTA has given up.
+__device__ __forceinline__ bool issue_tile(const Params &P, const Shared &S, Pipe &pipe, uint32_t block, uint32_t info,
+                                           uint64_t policy, int lane) {
+    const uint32_t half = info & 1u, r0 = (info >> 1) & 127u, n = (info >> 8) & 255u;
+    int stop = 0;
+    if (lane == 0) {
+        mbar_wait(S.empty + 8 * pipe.stage, pipe.phase ^ 1u, S.abort_flag, P.status, 1);
+        stop = *S.abort_flag;
+    }
+    if (__shfl_sync(0xffffffffu, stop, 0)) return false;
+    const uint32_t sb = S.stages + pipe.stage * STAGE_BYTES;
+    if (n < (uint32_t)TILE_KEYS) {
+        // A ragged tile: the V rows the copy leaves alone meet zero probabilities, so they must
+        // hold finite numbers, whatever the stage held before.
+        for (uint32_t i = lane; i < 2u * TILE_KEYS * 8u; i += 32) {
+            const uint32_t row = (i >> 3) & (TILE_KEYS - 1), sub = i >> 9;
+            if (row < r0 || row >= r0 + n)
+                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(sb + (2 + sub) * SUB_BYTES + row * 128 + (i & 7) * 16), "r"(0u) : "memory");
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        const uint32_t bar = S.full + 8 * pipe.stage;
+        if (block >= P.n_blocks || r0 + n > (uint32_t)TILE_KEYS || n == 0) {
+            // Recorded; the copy is skipped and the consumers see stale data.
+            if (atomicCAS(&P.status->code, 0, 1) == 0) {
+                P.status->where = 200;
+                P.status->a = (int)block;
+                P.status->b = (int)info;
+            }
+            mbar_expect_tx(bar, 0);
+        } else {
+            const uint32_t bytes = n * 128;
+            const size_t off = (size_t)block * (PAGE * D * 2) + (size_t)(half * TILE_KEYS + r0) * 128;
+            const uint32_t dst = sb + r0 * 128;
+            mbar_expect_tx(bar, 4 * bytes);
+            if (P.single_use) {
+                bulk_g2s_hint(dst, P.k_arena + off, bytes, bar, policy);
+                bulk_g2s_hint(dst + SUB_BYTES, P.k_arena + off + PAGE * 128, bytes, bar, policy);
+                bulk_g2s_hint(dst + 2 * SUB_BYTES, P.v_arena + off, bytes, bar, policy);
+                bulk_g2s_hint(dst + 3 * SUB_BYTES, P.v_arena + off + PAGE * 128, bytes, bar, policy);
+            } else {
+                bulk_g2s(dst, P.k_arena + off, bytes, bar);
+                bulk_g2s(dst + SUB_BYTES, P.k_arena + off + PAGE * 128, bytes, bar);
+                bulk_g2s(dst + 2 * SUB_BYTES, P.v_arena + off, bytes, bar);
+                bulk_g2s(dst + 3 * SUB_BYTES, P.v_arena + off + PAGE * 128, bytes, bar);
+            }
+        }
+    }
+    pipe.advance(STAGES);
+    return true;
+}
+
 __device__ void produce(const Params &P, const Shared &S, const CtaHdr hdr, int lane) {
     Pipe pipe{0, 0};
     const uint64_t policy = policy_evict_first();
-    for (uint32_t c = hdr.tile_begin; c < hdr.tile_end; c += 32) {
-        uint2 d = make_uint2(0u, 0u);
-        if (c + lane < hdr.tile_end) d = *(const uint2 *)(P.tiles + c + lane);
+    uint32_t c = hdr.tile_begin;
+    // The descriptors of every later tile are on their way while the first two copies start.
+    uint2 d = make_uint2(0u, 0u);
+    const uint32_t skip = P.has_prologue ? min(2u, hdr.tile_end - hdr.tile_begin) : 0u;
+    if (c + skip + lane < hdr.tile_end) d = *(const uint2 *)(P.tiles + c + skip + lane);
+    for (uint32_t j = 0; j < skip; j++) {
+        const TileDesc t = P.pro[blockIdx.x].first[j];
+        if (!issue_tile(P, S, pipe, t.block, t.info, policy, lane)) return;
+    }
+    c += skip;
+    while (c < hdr.tile_end) {
         const int n_tiles = (int)min(32u, hdr.tile_end - c);
+        uint2 next = make_uint2(0u, 0u);
+        if (c + 32 + lane < hdr.tile_end) next = *(const uint2 *)(P.tiles + c + 32 + lane);
         for (int j = 0; j < n_tiles; j++) {
-            const uint32_t block = __shfl_sync(0xffffffffu, d.x, j);
-            const uint32_t info = __shfl_sync(0xffffffffu, d.y, j);
-            const uint32_t half = info & 1u, r0 = (info >> 1) & 127u, n = (info >> 8) & 255u;
-            int stop = 0;
-            if (lane == 0) {
-                mbar_wait(S.empty + 8 * pipe.stage, pipe.phase ^ 1u, S.abort_flag, P.status, 1);
-                stop = *S.abort_flag;
-            }
-            if (__shfl_sync(0xffffffffu, stop, 0)) return;
-            const uint32_t sb = S.stages + pipe.stage * STAGE_BYTES;
-            if (n < (uint32_t)TILE_KEYS) {
-                // A ragged tile: the V rows the copy leaves alone meet zero probabilities, so
-                // they must hold finite numbers, whatever the stage held before.
-                for (uint32_t i = lane; i < 2u * TILE_KEYS * 8u; i += 32) {
-                    const uint32_t row = (i >> 3) & (TILE_KEYS - 1), sub = i >> 9;
-                    if (row < r0 || row >= r0 + n)
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(sb + (2 + sub) * SUB_BYTES + row * 128 + (i & 7) * 16), "r"(0u) : "memory");
-                }
-                __syncwarp();
-            }
-            if (lane == 0) {
-                const uint32_t bar = S.full + 8 * pipe.stage;
-                if (block >= P.n_blocks || r0 + n > (uint32_t)TILE_KEYS || n == 0) {
-                    // Recorded; the copy is skipped and the consumers see stale data.
-                    if (atomicCAS(&P.status->code, 0, 1) == 0) {
-                        P.status->where = 200;
-                        P.status->a = (int)block;
-                        P.status->b = (int)info;
-                    }
-                    mbar_expect_tx(bar, 0);
-                } else {
-                    const uint32_t bytes = n * 128;
-                    const size_t off = (size_t)block * (PAGE * D * 2) + (size_t)(half * TILE_KEYS + r0) * 128;
-                    const uint32_t dst = sb + r0 * 128;
-                    mbar_expect_tx(bar, 4 * bytes);
-                    if (P.single_use) {
-                        bulk_g2s_hint(dst, P.k_arena + off, bytes, bar, policy);
-                        bulk_g2s_hint(dst + SUB_BYTES, P.k_arena + off + PAGE * 128, bytes, bar, policy);
-                        bulk_g2s_hint(dst + 2 * SUB_BYTES, P.v_arena + off, bytes, bar, policy);
-                        bulk_g2s_hint(dst + 3 * SUB_BYTES, P.v_arena + off + PAGE * 128, bytes, bar, policy);
-                    } else {
-                        bulk_g2s(dst, P.k_arena + off, bytes, bar);
-                        bulk_g2s(dst + SUB_BYTES, P.k_arena + off + PAGE * 128, bytes, bar);
-                        bulk_g2s(dst + 2 * SUB_BYTES, P.v_arena + off, bytes, bar);
-                        bulk_g2s(dst + 3 * SUB_BYTES, P.v_arena + off + PAGE * 128, bytes, bar);
-                    }
-                }
-            }
-            pipe.advance(STAGES);
+            const uint32_t block = __shfl_sync(0xffffffffu, d.x, j), info = __shfl_sync(0xffffffffu, d.y, j);
+            if (!issue_tile(P, S, pipe, block, info, policy, lane)) return;
         }
+        d = next;
+        c += 32;
     }
 }
 
@@ -156,12 +189,25 @@ __device__ __forceinline__ uint32_t q_chunk_off(int row, int chunk) {
 }
 
 template <bool BF16>
-__device__ void stage_queries(const Params &P, const Shared &S, const CtaHdr hdr, int lane) {
+__device__ __noinline__ void stage_queries(const Params &P, const Shared &S, const CtaHdr hdr, int lane) {
     Pipe pipe{0, 0};
     const bool exact = (P.q_dtype == YX_BF16 && BF16) || (P.q_dtype == YX_F16 && !BF16);
+    const int chunk = lane >> 1;
+    const uint32_t sub = (lane & 1) * 8;
     for (uint32_t ii = hdr.item_begin; ii < hdr.item_end; ii++) {
-        const uint32_t *rec = P.recs[ii].w;
-        const uint32_t head_rows = rec[IR_HEAD_ROWS], mt = rec[IR_MT];
+        // Lane r < 16 holds pass row r of the item; the first item's come with the parameters.
+        uint32_t head_rows, mt, my_row = 0;
+        if (ii == hdr.item_begin && P.has_prologue) {
+            const CtaPrologue &pr = P.pro[blockIdx.x];
+            head_rows = pr.head_rows;
+            mt = pr.mt;
+            my_row = pr.rows[lane & (MAX_ITEM_ROWS - 1)];
+        } else {
+            const uint32_t *rec = P.recs[ii].w;
+            my_row = rec[IR_ROW0 + IR_ROW_WORDS * (lane & (MAX_ITEM_ROWS - 1)) + IRR_ROW];
+            head_rows = rec[IR_HEAD_ROWS];
+            mt = rec[IR_MT];
+        }
         const int kvh = (int)(head_rows & 0xffffu), n_rows = (int)(head_rows >> 16);
         const int q_rows = n_rows * P.group;
         int stop = 0;
@@ -172,22 +218,20 @@ __device__ void stage_queries(const Params &P, const Shared &S, const CtaHdr hdr
         if (__shfl_sync(0xffffffffu, stop, 0)) return;
         const uint32_t slot = S.q + pipe.stage * Q_SLOT_BYTES;
         const bool low = mt != 64 && !exact;
-        const int chunk = lane >> 1;
-        const uint32_t sub = (lane & 1) * 8;
-        for (int r0 = 0; r0 < (int)mt; r0 += 8) {
-            float4 v[8];
+        for (int r0 = 0; r0 < (int)mt; r0 += 32) {
+            float4 v[32];
 #pragma unroll
-            for (int k = 0; k < 8; k++) {
+            for (int k = 0; k < 32; k++) {
                 const int qr = r0 + k;
                 v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (qr < q_rows) {
-                    const uint32_t row = rec[IR_ROW0 + IR_ROW_WORDS * (qr / P.group) + IRR_ROW];
+                const uint32_t row = __shfl_sync(0xffffffffu, my_row, min(qr / P.group, MAX_ITEM_ROWS - 1));
+                if (qr < q_rows)
                     v[k] = load4_as_f32(P.q, P.q_dtype, ((size_t)row * P.hq + (size_t)kvh * P.group + qr % P.group) * D + lane * 4);
-                }
             }
 #pragma unroll
-            for (int k = 0; k < 8; k++) {
+            for (int k = 0; k < 32; k++) {
                 const int qr = r0 + k;
+                if (qr >= (int)mt) break;
                 const uint32_t h0 = pack2<BF16>(v[k].x, v[k].y), h1 = pack2<BF16>(v[k].z, v[k].w);
                 const uint32_t addr = slot + q_chunk_off(qr, chunk) + sub;
                 asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(h0), "r"(h1) : "memory");
@@ -210,6 +254,65 @@ __device__ __forceinline__ uint32_t rec_word(uint32_t w1, uint32_t w2, uint32_t 
     const uint32_t a = __shfl_sync(0xffffffffu, w1, idx & 31), b = __shfl_sync(0xffffffffu, w2, idx & 31),
                    c = __shfl_sync(0xffffffffu, w3, idx & 31);
     return idx < 64 ? a : (idx < 96 ? b : c);
+}
+
+// Merges every (row, KV head) of an item that the arrival counters found complete.  The
+// completed (row, head) pairs are dealt to the warps, four at a time per warp, so that their
+// loads overlap: a merge is two dependent round trips to L2, whatever it merges.
+__device__ __noinline__ void merge_completed(const Params &P, const int *flags, uint32_t w1, uint32_t w2, uint32_t w3,
+                                             int n_rows, int kvh, int warp, int lane) {
+    const int group = P.group;
+    int n_done = 0;
+    uint32_t done_mask = 0;
+    for (int r = 0; r < n_rows; r++)
+        if (flags[r]) {
+            done_mask |= 1u << r;
+            n_done++;
+        }
+    if (n_done) {
+        __threadfence();
+        const int n_tasks = n_done * group;
+        for (int t0 = warp * 4; t0 < n_tasks; t0 += CONSUMERS * 4) {
+            uint32_t rows_[4], first_[4], count_[4];
+            int hg_[4];
+            bool on_[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int t = t0 + k;
+                on_[k] = t < n_tasks;
+                const int which = on_[k] ? t / group : 0;   // which completed row
+                hg_[k] = on_[k] ? t % group : 0;
+                // the which-th set bit of done_mask
+                uint32_t mk = done_mask;
+                for (int x = 0; x < which; x++) mk &= mk - 1;
+                const int r = __ffs(mk) - 1;
+                const int base = IR_ROW0 + IR_ROW_WORDS * r;
+                rows_[k] = rec_word(w1, w2, w3, base + IRR_ROW);
+                first_[k] = rec_word(w1, w2, w3, base + IRR_FIRST);
+                count_[k] = rec_word(w1, w2, w3, base + IRR_COUNT);
+            }
+            float mx[4], ls[4];
+            float4 acc[4];
+            merge_parts4(P.part_o, P.part_ml, first_, count_, on_, group, hg_, lane, mx, ls, acc);
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                if (!on_[k]) continue;
+                const size_t idx = (size_t)rows_[k] * P.hq + (size_t)kvh * group + hg_[k];
+                if (P.out) {
+                    const float inv = 1.0f / ls[k];   // a row always sees its own key: > 0 for whole attention
+                    store4(P.out, P.out_dtype, idx * D + lane * 4,
+                           make_float4(acc[k].x * inv, acc[k].y * inv, acc[k].z * inv, acc[k].w * inv));
+                }
+                if (P.o_out) {
+                    *(float4 *)(P.o_out + idx * D + lane * 4) = acc[k];
+                    if (lane == 0) {
+                        P.m_out[idx] = mx[k];
+                        P.l_out[idx] = ls[k];
+                    }
+                }
+            }
+        }
+    }
 }
 
 template <int MT, bool BF16>
@@ -470,30 +573,7 @@ __device__ void consume_item(const Params &P, const Shared &S, uint32_t w0, uint
         }
     }
     asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");
-    for (int r = 0; r < n_rows; r++) {
-        if (!flags[r]) continue;   // uniform across the CTA
-        __threadfence();
-        const int base = IR_ROW0 + IR_ROW_WORDS * r;
-        const uint32_t row = rec_word(w1, w2, w3, base + IRR_ROW), first = rec_word(w1, w2, w3, base + IRR_FIRST),
-                       count = rec_word(w1, w2, w3, base + IRR_COUNT);
-        for (int hg = warp; hg < group; hg += CONSUMERS) {
-            float mx, ls;
-            float4 acc;
-            merge_parts(P.part_o, P.part_ml, first, count, group, hg, lane, mx, ls, acc);
-            const size_t idx = (size_t)row * P.hq + (size_t)kvh * group + hg;
-            if (P.out) {
-                const float inv = 1.0f / ls;   // a row always sees its own key: ls > 0 for whole attention
-                store4(P.out, P.out_dtype, idx * D + lane * 4, make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv));
-            }
-            if (P.o_out) {
-                *(float4 *)(P.o_out + idx * D + lane * 4) = acc;
-                if (lane == 0) {
-                    P.m_out[idx] = mx;
-                    P.l_out[idx] = ls;
-                }
-            }
-        }
-    }
+    merge_completed(P, flags, w1, w2, w3, n_rows, kvh, warp, lane);
     // `flags` and the merge scratch are rewritten only after the next item's barriers.
 }
 
@@ -515,7 +595,7 @@ __global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const __grid_con
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     unsigned long long *tr = P.trace ? P.trace + 8 * blockIdx.x : nullptr;
     if (tr && threadIdx.x == 0) tr[0] = gtime();
-    const CtaHdr hdr = *(const CtaHdr *)(P.cta_hdr + blockIdx.x);   // in flight during the set-up below
+    const CtaHdr hdr = P.has_prologue ? P.pro[blockIdx.x].hdr : *(const CtaHdr *)(P.cta_hdr + blockIdx.x);
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < STAGES; s++) {
@@ -604,6 +684,22 @@ int launch_attend_mma(yx_ctx *ctx, const AttendArgs &a) {
     P.o_out = a.o_out;
     P.status = ctx->dev_status;
     P.trace = (unsigned long long *)ctx->trace_buf;
+    P.has_prologue = 0;
+    if (a.plan && a.n_ctas <= MAX_PROLOGUE_CTAS) {
+        const Plan &pl = *a.plan;
+        P.has_prologue = 1;
+        for (int c = 0; c < a.n_ctas; c++) {
+            CtaPrologue &pr = P.pro[c];
+            pr.hdr = pl.cta_hdr[c];
+            for (uint32_t j = 0; j < 2 && pr.hdr.tile_begin + j < pr.hdr.tile_end; j++) pr.first[j] = pl.tiles[pr.hdr.tile_begin + j];
+            if (pr.hdr.item_begin < pr.hdr.item_end) {
+                const Item &it = pl.items[pr.hdr.item_begin];
+                pr.head_rows = (uint32_t)it.kv_head | ((uint32_t)it.n_rows << 16);
+                pr.mt = it.mt;
+                for (int r = 0; r < MAX_ITEM_ROWS; r++) pr.rows[r] = it.rows[r];
+            }
+        }
+    }
     if (bf16) attend_mma_kernel<true><<<a.n_ctas, THREADS, SMEM_BYTES, ctx->stream>>>(P);
     else attend_mma_kernel<false><<<a.n_ctas, THREADS, SMEM_BYTES, ctx->stream>>>(P);
     ctx->launches++;

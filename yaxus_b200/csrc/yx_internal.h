@@ -273,6 +273,7 @@ struct AttendArgs {
     const TileDesc *tiles;
     const ItemRec *recs;
     bool single_use;
+    const Plan *plan;        // host copy, for what is passed in kernel-parameter space
     uint32_t *counters;      // one per (pass row, kv head), zero between launches
     void *out;               // normalised output, or null
     int out_dtype;
