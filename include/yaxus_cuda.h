@@ -71,7 +71,8 @@ typedef struct yx_tuning {
     int32_t tile_min_rows;   /* rows of one sequence from which the tcgen05 tile kernel is used */
     int32_t cost32;          /* planner cost of a 64-key tile of an item with 32 padded query rows, */
     int32_t cost64;          /* and with 64, in 16ths of the cost of a 16-row item's tile */
-    int32_t reserved[2];
+    int32_t stages;          /* 64-key tiles in flight per SM in the tensor split-key kernel (2..5) */
+    int32_t share_rows;      /* pass rows a shared-prefix item may hold (0: 16 / group, one MMA tile) */
 } yx_tuning;
 
 /* What the last yx_attend / yx_attention call planned; for tests and benchmarks. */
@@ -199,7 +200,8 @@ int yx_attend_allgather(yx_ctx *ctx, yx_kv *kv, int layer, const void *q_dev, in
 /* Runs the split-key planner (the counterpart of `AttentionCase::plan`,
  * crates/yaxus-backend-gpu/src/plan.rs:275-309) on host arrays; needs no device.  Each item is
  * written as YX_PROBE_ITEM_WORDS words: tile_begin, tile_end, key_lo, key_hi, pt_off, kv_head,
- * n_rows, padded rows, CTA, then 16 pass rows and their 16 partial slots. */
+ * n_rows, padded rows, CTA, then 16 pass rows and their 16 partial slots.  share_prefix: 0 off,
+ * 1 on with the default rows per shared item, above 1 that many rows per shared item. */
 #define YX_PROBE_ITEM_WORDS 41
 int yx_plan_probe(uint32_t rows, const uint32_t *pos_host, const uint32_t *pt_off_host, const uint32_t *pages_host,
                   uint32_t n_pages, int hkv, int group, int64_t window, uint64_t key_lo, uint64_t key_hi,

@@ -84,8 +84,10 @@ def check_balance(items, info, cost32=16, cost64=32):
         assert per.max() - per.min() <= 2 * max(w.values())
 
 
-@pytest.mark.parametrize("share", [0, 1])
+@pytest.mark.parametrize("share", [0, 1, 16])
 def test_batched_decode_plan(share):
+    # share: 0 off, 1 the default (a shared item holds 16 / group = 4 one-row sequences, one
+    # 16-row MMA tile), 16: all sixteen sequences in one item of 64 padded rows.
     s = W.batched_decode(fill=False)
     info, items = probe(s.meta, s.hkv, s.hq // s.hkv, share=share)
     check_cover(s.meta, items, s.hkv, None)
@@ -94,11 +96,19 @@ def test_batched_decode_plan(share):
     assert info.n_ctas == 148
     assert info.logical_kv_bytes == s.logical_kv_bytes()
     assert info.unique_kv_bytes == s.unique_kv_bytes()
-    if share:
+    tile_bytes = 64 * 2 * 128 * 2
+    prefix_tiles = 1536 // 64 * s.hkv
+    if share == 16:
         assert info.shared_groups == 1
-        # the shared prefix is streamed once: tiles = unique tokens / 64 per KV head
-        assert info.tiles * 64 * 2 * 128 * 2 < 1.02 * s.unique_kv_bytes() + 16 * 8 * 64 * 512
+        # the shared prefix is streamed once: tiles ~ unique tokens / 64 per KV head
+        assert info.tiles * tile_bytes < 1.02 * s.unique_kv_bytes() + 16 * 8 * tile_bytes
         assert any(int(it[6]) == 16 and int(it[7]) == 64 for it in items)
+    elif share == 1:
+        assert info.shared_groups == 4
+        # ... four times, by items that each fill one 16-row tile
+        assert all(int(it[7]) == 16 for it in items)
+        assert any(int(it[6]) == 4 for it in items)
+        assert info.tiles * tile_bytes < 1.02 * s.unique_kv_bytes() + (16 * 8 + 3 * prefix_tiles) * tile_bytes
     else:
         assert info.shared_groups == 0
         assert all(int(it[6]) == 1 and int(it[7]) == 16 for it in items)

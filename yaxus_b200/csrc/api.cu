@@ -116,7 +116,7 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
         if (cp.pass_serial == ctx->pass_serial && cp.hkv == pp.hkv && cp.group == pp.group &&
             cp.max_rows == pp.max_rows && cp.n_ctas == pp.n_ctas && cp.window == pp.window &&
             cp.key_lo == pp.key_lo && cp.key_hi == pp.key_hi && cp.share == pp.share_prefix && cp.esize == pp.esize &&
-            cp.w32 == pp.w32 && cp.w64 == pp.w64 && cp.resolve == pp.resolve) {
+            cp.w32 == pp.w32 && cp.w64 == pp.w64 && cp.resolve == pp.resolve && cp.share_rows == pp.share_rows) {
             *out = &cp;
             return YX_OK;
         }
@@ -159,6 +159,7 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
     slot->w32 = pp.w32;
     slot->w64 = pp.w64;
     slot->resolve = pp.resolve;
+    slot->share_rows = pp.share_rows;
 
     const Plan &pl = slot->plan;
     auto pad16 = [](size_t n) { return (n + 15) / 16 * 16; };
@@ -241,8 +242,9 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     pp.max_rows = path == 1 ? 1 : std::max(1, std::min(MAX_ITEM_ROWS, 64 / group));
     pp.share_prefix = path != 1 && ctx->tuning.share_prefix != 2;
     pp.w32 = ctx->tuning.cost32 > 0 ? ctx->tuning.cost32 : 16;
-    pp.w64 = ctx->tuning.cost64 > 0 ? ctx->tuning.cost64 : 16;
+    pp.w64 = ctx->tuning.cost64 > 0 ? ctx->tuning.cost64 : 40;
     pp.resolve = path == 2;
+    pp.share_rows = ctx->tuning.share_rows;
     yx_ctx::CachedPlan *cp = nullptr;
     if (int rc = get_plan(ctx, pp, &cp)) return rc;
     const Plan &pl = cp->plan;
@@ -290,6 +292,7 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     a.recs = cp->d_recs;
     a.single_use = pl.single_use;
     a.plan = &pl;
+    a.n_stages = ctx->tuning.stages;
     a.counters = ctx->counters;
     a.out = out;
     a.out_dtype = out_dtype;

@@ -34,24 +34,28 @@ namespace {
 
 using namespace dev;
 
-constexpr int STAGES = 5;
+constexpr int STAGES = 3;
 constexpr int SUB_BYTES = TILE_KEYS * 128;        // one 64-dim half of a 64-key tile
 constexpr int STAGE_BYTES = 4 * SUB_BYTES;        // K lo, K hi, V lo, V hi
 constexpr int CONSUMERS = 4;                      // warps 0..3
 constexpr int PRODUCER = CONSUMERS;               // warp 4
 constexpr int QWARP = CONSUMERS + 1;              // warp 5
-constexpr int THREADS = (CONSUMERS + 2) * 32;
+constexpr int EWARP = CONSUMERS + 2;              // warp 6
+constexpr int THREADS = (CONSUMERS + 3) * 32;
 constexpr int Q_SLOTS = 2;
-constexpr int Q_SLOT_BYTES = 16384;               // 64 rows x 256 B, or 32 rows high + 32 rows low
+constexpr int Q_ROWS_BYTES = 16384;               // 64 rows x 256 B, or 32 rows high + 32 rows low
 constexpr int Q_LOW_OFFSET = 8192;
-constexpr int MERGE_FLOATS = 16 * (D + 2);        // one warp's (m, l, o) for 16 rows
-constexpr int MERGE_BYTES = ((3 * MERGE_FLOATS * 4 + 127) / 128) * 128;
-constexpr int N_BARRIERS = 2 * STAGES + 2 * Q_SLOTS;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + Q_SLOTS * Q_SLOT_BYTES + MERGE_BYTES + 128 + N_BARRIERS * 8;
+constexpr int Q_SLOT_BYTES = Q_ROWS_BYTES + 512;  // then the item's record
+constexpr int MERGE_ROW = D + 4;                  // one row's o, then m and l, padded
+constexpr int MERGE_FLOATS = 16 * MERGE_ROW;      // one warp's 16 rows
+constexpr int MERGE_BYTES = CONSUMERS * MERGE_FLOATS * 4;   // one buffer: every consumer warp's rows
+constexpr int MERGE_BUFS = 2;
+constexpr int N_BARRIERS = 2 * STAGES + 2 * Q_SLOTS + 2 * MERGE_BUFS;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + Q_SLOTS * Q_SLOT_BYTES + MERGE_BUFS * MERGE_BYTES + N_BARRIERS * 8 + 64;
 
 struct Shared {
-    uint32_t stages, q, merge, flags;   // shared-space addresses
-    uint32_t full, empty, qfull, qempty;
+    uint32_t stages, q, merge;          // shared-space addresses
+    uint32_t full, empty, qfull, qempty, efull, eempty;
     volatile int *abort_flag;
 };
 
@@ -94,6 +98,7 @@ struct Params {
     float *m_out, *l_out, *o_out;
     yx_dev_status *status;
     unsigned long long *trace;       // optional: 8 timestamps / counters per CTA
+    int n_stages;                    // stages of the ring in use (2..STAGES): bytes in flight per SM
     int has_prologue;
     CtaPrologue pro[MAX_PROLOGUE_CTAS];
 };
@@ -103,8 +108,17 @@ __device__ __forceinline__ uint32_t field(uint32_t w, int idx) { return __shfl_s
 // ---- producer: tile descriptors -> bulk copies ----------------------------------------------
 // One tile: wait for a free stage, zero what a ragged copy leaves alone, start the four copies.
 // Returns false when the CTA has given up.
-__device__ __forceinline__ bool issue_tile(const Params &P, const Shared &S, Pipe &pipe, uint32_t block, uint32_t info,
-                                           uint64_t policy, int lane) {
+struct Issue {
+    const char *k_arena, *v_arena;
+    yx_dev_status *status;
+    volatile int *abort_flag;
+    uint64_t policy;
+    uint32_t n_blocks, stages, full, empty;
+    int single_use, n_stages;
+};
+__device__ __noinline__ bool issue_tile(const Issue P, Pipe &pipe, uint32_t block, uint32_t info, int lane) {
+    struct { uint32_t stages, full, empty; volatile int *abort_flag; } S = {P.stages, P.full, P.empty, P.abort_flag};
+    const uint64_t policy = P.policy;
     const uint32_t half = info & 1u, r0 = (info >> 1) & 127u, n = (info >> 8) & 255u;
     int stop = 0;
     if (lane == 0) {
@@ -138,7 +152,7 @@ __device__ __forceinline__ bool issue_tile(const Params &P, const Shared &S, Pip
             const size_t off = (size_t)block * (PAGE * D * 2) + (size_t)(half * TILE_KEYS + r0) * 128;
             const uint32_t dst = sb + r0 * 128;
             mbar_expect_tx(bar, 4 * bytes);
-            if (P.single_use) {
+            if (P.single_use && !(info & (1u << 16))) {
                 bulk_g2s_hint(dst, P.k_arena + off, bytes, bar, policy);
                 bulk_g2s_hint(dst + SUB_BYTES, P.k_arena + off + PAGE * 128, bytes, bar, policy);
                 bulk_g2s_hint(dst + 2 * SUB_BYTES, P.v_arena + off, bytes, bar, policy);
@@ -151,13 +165,24 @@ __device__ __forceinline__ bool issue_tile(const Params &P, const Shared &S, Pip
             }
         }
     }
-    pipe.advance(STAGES);
+    pipe.advance(P.n_stages);
     return true;
 }
 
 __device__ void produce(const Params &P, const Shared &S, const CtaHdr hdr, int lane) {
     Pipe pipe{0, 0};
-    const uint64_t policy = policy_evict_first();
+    Issue I;
+    I.k_arena = P.k_arena;
+    I.v_arena = P.v_arena;
+    I.status = P.status;
+    I.abort_flag = S.abort_flag;
+    I.policy = policy_evict_first();
+    I.n_blocks = P.n_blocks;
+    I.stages = S.stages;
+    I.full = S.full;
+    I.empty = S.empty;
+    I.single_use = P.single_use;
+    I.n_stages = P.n_stages;
     uint32_t c = hdr.tile_begin;
     // The descriptors of every later tile are on their way while the first two copies start.
     uint2 d = make_uint2(0u, 0u);
@@ -165,7 +190,8 @@ __device__ void produce(const Params &P, const Shared &S, const CtaHdr hdr, int 
     if (c + skip + lane < hdr.tile_end) d = *(const uint2 *)(P.tiles + c + skip + lane);
     for (uint32_t j = 0; j < skip; j++) {
         const TileDesc t = P.pro[blockIdx.x].first[j];
-        if (!issue_tile(P, S, pipe, t.block, t.info, policy, lane)) return;
+        if (!issue_tile(I, pipe, t.block, t.info, lane)) return;
+        if (P.trace && lane == 0 && j == 0) P.trace[8 * blockIdx.x + 2] = gtime();
     }
     c += skip;
     while (c < hdr.tile_end) {
@@ -174,7 +200,7 @@ __device__ void produce(const Params &P, const Shared &S, const CtaHdr hdr, int 
         if (c + 32 + lane < hdr.tile_end) next = *(const uint2 *)(P.tiles + c + 32 + lane);
         for (int j = 0; j < n_tiles; j++) {
             const uint32_t block = __shfl_sync(0xffffffffu, d.x, j), info = __shfl_sync(0xffffffffu, d.y, j);
-            if (!issue_tile(P, S, pipe, block, info, policy, lane)) return;
+            if (!issue_tile(I, pipe, block, info, lane)) return;
         }
         d = next;
         c += 32;
@@ -188,50 +214,74 @@ __device__ __forceinline__ uint32_t q_chunk_off(int row, int chunk) {
     return (uint32_t)row * 256u + (uint32_t)(((chunk & 8) | ((chunk ^ row) & 7)) << 4);
 }
 
+// Everything this out-of-line routine needs comes by value: a reference to the kernel's
+// parameter block would turn every field access into a load from memory.
+struct QStage {
+    const void *q;
+    const ItemRec *recs;
+    yx_dev_status *status;
+    int q_dtype, hq, group;
+    uint32_t item_begin, item_end;
+    int have_first;                       // the first item's header came with the parameters
+    uint32_t first_head_rows, first_mt, first_row;   // first_row: lane r's pass row
+    uint32_t qbase, qfull, qempty;        // shared-space addresses
+    volatile int *abort_flag;
+};
+
 template <bool BF16>
-__device__ __noinline__ void stage_queries(const Params &P, const Shared &S, const CtaHdr hdr, int lane) {
+__device__ __noinline__ void stage_queries(const QStage A, int lane) {
     Pipe pipe{0, 0};
-    const bool exact = (P.q_dtype == YX_BF16 && BF16) || (P.q_dtype == YX_F16 && !BF16);
+    const bool exact = (A.q_dtype == YX_BF16 && BF16) || (A.q_dtype == YX_F16 && !BF16);
     const int chunk = lane >> 1;
     const uint32_t sub = (lane & 1) * 8;
-    for (uint32_t ii = hdr.item_begin; ii < hdr.item_end; ii++) {
-        // Lane r < 16 holds pass row r of the item; the first item's come with the parameters.
+    for (uint32_t ii = A.item_begin; ii < A.item_end; ii++) {
+        // The item's record goes to shared memory with the queries; lane r < 16 also holds
+        // pass row r of the item.
+        const uint32_t *rec = A.recs[ii].w;
+        const uint4 rec4 = *(const uint4 *)(rec + 4 * lane);
         uint32_t head_rows, mt, my_row = 0;
-        if (ii == hdr.item_begin && P.has_prologue) {
-            const CtaPrologue &pr = P.pro[blockIdx.x];
-            head_rows = pr.head_rows;
-            mt = pr.mt;
-            my_row = pr.rows[lane & (MAX_ITEM_ROWS - 1)];
+        if (ii == A.item_begin && A.have_first) {
+            head_rows = A.first_head_rows;
+            mt = A.first_mt;
+            my_row = A.first_row;
         } else {
-            const uint32_t *rec = P.recs[ii].w;
             my_row = rec[IR_ROW0 + IR_ROW_WORDS * (lane & (MAX_ITEM_ROWS - 1)) + IRR_ROW];
             head_rows = rec[IR_HEAD_ROWS];
             mt = rec[IR_MT];
         }
         const int kvh = (int)(head_rows & 0xffffu), n_rows = (int)(head_rows >> 16);
-        const int q_rows = n_rows * P.group;
+        const int q_rows = n_rows * A.group;
         int stop = 0;
         if (lane == 0) {
-            mbar_wait(S.qempty + 8 * pipe.stage, pipe.phase ^ 1u, S.abort_flag, P.status, 3);
-            stop = *S.abort_flag;
+            mbar_wait(A.qempty + 8 * pipe.stage, pipe.phase ^ 1u, A.abort_flag, A.status, 3);
+            stop = *A.abort_flag;
         }
         if (__shfl_sync(0xffffffffu, stop, 0)) return;
-        const uint32_t slot = S.q + pipe.stage * Q_SLOT_BYTES;
+        const uint32_t slot = A.qbase + pipe.stage * Q_SLOT_BYTES;
         const bool low = mt != 64 && !exact;
-        for (int r0 = 0; r0 < (int)mt; r0 += 32) {
-            float4 v[32];
+        // Lane k works out where query rows k and 32 + k live (one division per lane, not one
+        // per row); the loads then take the addresses by shuffle, eight rows in flight.
+        uint32_t my_elem[2];
 #pragma unroll
-            for (int k = 0; k < 32; k++) {
-                const int qr = r0 + k;
+        for (int h = 0; h < 2; h++) {
+            const int mine = 32 * h + lane;
+            const int pr = mine / A.group;
+            const uint32_t prow = __shfl_sync(0xffffffffu, my_row, min(pr, MAX_ITEM_ROWS - 1));
+            my_elem[h] = mine < q_rows ? (prow * (uint32_t)A.hq + (uint32_t)(kvh * A.group + (mine - pr * A.group))) : 0xffffffffu;
+        }
+#pragma unroll 1
+        for (int r0 = 0; r0 < (int)mt; r0 += 16) {
+            float4 v[16];
+            const uint32_t src = r0 < 32 ? my_elem[0] : my_elem[1];
+#pragma unroll
+            for (int k = 0; k < 16; k++) {
+                const uint32_t e = __shfl_sync(0xffffffffu, src, (r0 + k) & 31);
                 v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-                const uint32_t row = __shfl_sync(0xffffffffu, my_row, min(qr / P.group, MAX_ITEM_ROWS - 1));
-                if (qr < q_rows)
-                    v[k] = load4_as_f32(P.q, P.q_dtype, ((size_t)row * P.hq + (size_t)kvh * P.group + qr % P.group) * D + lane * 4);
+                if (e != 0xffffffffu) v[k] = load4_as_f32(A.q, A.q_dtype, (size_t)e * D + lane * 4);
             }
 #pragma unroll
-            for (int k = 0; k < 32; k++) {
+            for (int k = 0; k < 16; k++) {
                 const int qr = r0 + k;
-                if (qr >= (int)mt) break;
                 const uint32_t h0 = pack2<BF16>(v[k].x, v[k].y), h1 = pack2<BF16>(v[k].z, v[k].w);
                 const uint32_t addr = slot + q_chunk_off(qr, chunk) + sub;
                 asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(h0), "r"(h1) : "memory");
@@ -242,82 +292,178 @@ __device__ __noinline__ void stage_queries(const Params &P, const Shared &S, con
                 }
             }
         }
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(slot + Q_ROWS_BYTES + 16 * lane), "r"(rec4.x),
+                     "r"(rec4.y), "r"(rec4.z), "r"(rec4.w)
+                     : "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(S.qfull + 8 * pipe.stage);
+        if (lane == 0) mbar_arrive(A.qfull + 8 * pipe.stage);
         pipe.advance(Q_SLOTS);
     }
 }
 
 // ---- consumers ---------------------------------------------------------------------------------
-// Word `idx` (32..127) of an item record held as three lane-indexed registers.
-__device__ __forceinline__ uint32_t rec_word(uint32_t w1, uint32_t w2, uint32_t w3, int idx) {
-    const uint32_t a = __shfl_sync(0xffffffffu, w1, idx & 31), b = __shfl_sync(0xffffffffu, w2, idx & 31),
-                   c = __shfl_sync(0xffffffffu, w3, idx & 31);
-    return idx < 64 ? a : (idx < 96 ? b : c);
-}
 
-// Merges every (row, KV head) of an item that the arrival counters found complete.  The
-// completed (row, head) pairs are dealt to the warps, four at a time per warp, so that their
-// loads overlap: a merge is two dependent round trips to L2, whatever it merges.
-__device__ __noinline__ void merge_completed(const Params &P, const int *flags, uint32_t w1, uint32_t w2, uint32_t w3,
-                                             int n_rows, int kvh, int warp, int lane) {
-    const int group = P.group;
-    int n_done = 0;
-    uint32_t done_mask = 0;
-    for (int r = 0; r < n_rows; r++)
-        if (flags[r]) {
-            done_mask |= 1u << r;
-            n_done++;
+// ---- epilogue warp ---------------------------------------------------------------------------
+// The end of an item costs latency, not work: a device-wide fence, an atomic round trip and,
+// for whoever completes a (row, KV head), two dependent reads of other CTAs' triples.  The
+// consumer warps do not wait for any of it.  They leave their rows' (o, m, l) in one of two
+// shared-memory buffers and move on to the next item; this warp
+//  1. merges the key slices of every valid query row and writes the row's triple to the
+//     partial buffer (a lane holds four of the 128 dims, stores coalesced);
+//  2. counts the item in for each of its (row, KV head) with an arrival counter in global
+//     scratch; where it completes one, it merges all of that pair's triples (the reference's
+//     `attn_combine`, crates/yaxus-backend-gpu/src/shaders.rs:1581-1637), writes the output
+//     and resets the counter.
+struct Epilogue {
+    const ItemRec *recs;     // not used for reading rows: the staged slot holds the record
+    float *part_o, *part_ml;
+    uint32_t *counters;
+    void *out;
+    float *m_out, *l_out, *o_out;
+    yx_dev_status *status;
+    volatile int *abort_flag;
+    int out_dtype, hq, hkv, group;
+    uint32_t n_items;
+    uint32_t qbase, qempty, merge, efull, eempty;   // shared-space addresses
+};
+
+// Eight (row, head) pairs at a time, four lanes each: two round trips to L2 per round (the
+// maxima, then weights and vectors with independent loads).  Parts with l <= 0 are dropped by
+// value: their o was never written (shaders.rs:1597-1598).  Loads bypass L1: other SMs wrote
+// these triples during this very kernel.
+__device__ __forceinline__ void merge_completed(const Epilogue &E, const uint32_t *rec, uint32_t done_mask, int kvh,
+                                                int lane) {
+    const int group = E.group;
+    const int n_tasks = __popc(done_mask) * group;
+    const int sub = lane >> 2, l4 = lane & 3;
+    const uint32_t gmask = 0xfu << (sub * 4);
+#pragma unroll 1
+    for (int t0 = 0; t0 < n_tasks; t0 += 8) {
+        const int t = t0 + sub;
+        if (t >= n_tasks) continue;   // a whole four-lane group leaves; shuffles below stay inside a group
+        const int which = t / group, hg = t - which * group;
+        uint32_t mk = done_mask;
+        for (int x = 0; x < which; x++) mk &= mk - 1;
+        const int base = IR_ROW0 + IR_ROW_WORDS * (__ffs(mk) - 1);
+        const uint32_t row = rec[base + IRR_ROW], first = rec[base + IRR_FIRST], count = rec[base + IRR_COUNT];
+        const float *ml = E.part_ml + ((size_t)first * group + hg) * 2;
+        const float *po = E.part_o + ((size_t)first * group + hg) * D + l4 * 32;
+        float mx = -1e30f;
+#pragma unroll 1
+        for (uint32_t c = l4; c < count; c += 4) {
+            const float2 v = __ldcg((const float2 *)(ml + (size_t)c * group * 2));
+            if (v.y > 0.0f) mx = fmaxf(mx, v.x);
         }
-    if (n_done) {
-        __threadfence();
-        const int n_tasks = n_done * group;
-        for (int t0 = warp * 4; t0 < n_tasks; t0 += CONSUMERS * 4) {
-            uint32_t rows_[4], first_[4], count_[4];
-            int hg_[4];
-            bool on_[4];
+        mx = fmaxf(mx, __shfl_xor_sync(gmask, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(gmask, mx, 2));
+        float ls = 0.0f;
+        float4 acc[8];
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-                const int t = t0 + k;
-                on_[k] = t < n_tasks;
-                const int which = on_[k] ? t / group : 0;   // which completed row
-                hg_[k] = on_[k] ? t % group : 0;
-                // the which-th set bit of done_mask
-                uint32_t mk = done_mask;
-                for (int x = 0; x < which; x++) mk &= mk - 1;
-                const int r = __ffs(mk) - 1;
-                const int base = IR_ROW0 + IR_ROW_WORDS * r;
-                rows_[k] = rec_word(w1, w2, w3, base + IRR_ROW);
-                first_[k] = rec_word(w1, w2, w3, base + IRR_FIRST);
-                count_[k] = rec_word(w1, w2, w3, base + IRR_COUNT);
+        for (int k = 0; k < 8; k++) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 2
+        for (uint32_t c = 0; c < count; c++) {
+            const float2 v = __ldcg((const float2 *)(ml + (size_t)c * group * 2));
+            if (!(v.y > 0.0f)) continue;
+            const float w = __expf(v.x - mx);
+            ls += v.y * w;
+            const float4 *src = (const float4 *)(po + (size_t)c * group * D);
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const float4 x = __ldcg(src + k);
+                acc[k].x += x.x * w;
+                acc[k].y += x.y * w;
+                acc[k].z += x.z * w;
+                acc[k].w += x.w * w;
             }
-            float mx[4], ls[4];
-            float4 acc[4];
-            merge_parts4(P.part_o, P.part_ml, first_, count_, on_, group, hg_, lane, mx, ls, acc);
+        }
+        const size_t idx = (size_t)row * E.hq + (size_t)kvh * group + hg;
+        if (E.out) {
+            const float inv = 1.0f / ls;   // a row always sees its own key: > 0 for whole attention
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-                if (!on_[k]) continue;
-                const size_t idx = (size_t)rows_[k] * P.hq + (size_t)kvh * group + hg_[k];
-                if (P.out) {
-                    const float inv = 1.0f / ls[k];   // a row always sees its own key: > 0 for whole attention
-                    store4(P.out, P.out_dtype, idx * D + lane * 4,
-                           make_float4(acc[k].x * inv, acc[k].y * inv, acc[k].z * inv, acc[k].w * inv));
-                }
-                if (P.o_out) {
-                    *(float4 *)(P.o_out + idx * D + lane * 4) = acc[k];
-                    if (lane == 0) {
-                        P.m_out[idx] = mx[k];
-                        P.l_out[idx] = ls[k];
-                    }
-                }
+            for (int k = 0; k < 8; k++)
+                store4(E.out, E.out_dtype, idx * D + l4 * 32 + k * 4,
+                       make_float4(acc[k].x * inv, acc[k].y * inv, acc[k].z * inv, acc[k].w * inv));
+        }
+        if (E.o_out) {
+#pragma unroll
+            for (int k = 0; k < 8; k++) *(float4 *)(E.o_out + idx * D + l4 * 32 + k * 4) = acc[k];
+            if (l4 == 0) {
+                E.m_out[idx] = mx;
+                E.l_out[idx] = ls;
             }
         }
     }
 }
 
+__device__ __noinline__ void epilogue_loop(const Epilogue E, int lane) {
+    const float sl2 = 0.08838834764831845f * 1.4426950408889634f;
+    Pipe ep{0, 0}, qp{0, 0};
+    const int group = E.group;
+#pragma unroll 1
+    for (uint32_t ii = 0; ii < E.n_items; ii++) {
+        mbar_wait(E.efull + 8 * ep.stage, ep.phase, E.abort_flag, E.status, 5);
+        const float *scratch = (const float *)__cvta_shared_to_generic((size_t)(E.merge + ep.stage * MERGE_BYTES));
+        const uint32_t *rec = (const uint32_t *)__cvta_shared_to_generic((size_t)(E.qbase + qp.stage * Q_SLOT_BYTES + Q_ROWS_BYTES));
+        const uint32_t head_rows = rec[IR_HEAD_ROWS];
+        const int kvh = (int)(head_rows & 0xffffu), n_rows = (int)(head_rows >> 16);
+        const int nmt = (int)rec[IR_MT] >> 4, nsl = CONSUMERS / nmt;
+        // 1. the item's triples
+        int qr = 0;
+#pragma unroll 1
+        for (int r = 0; r < n_rows; r++) {
+            const uint32_t part = rec[IR_ROW0 + IR_ROW_WORDS * r + IRR_PART];
+#pragma unroll 1
+            for (int gq = 0; gq < group; gq++, qr++) {
+                const float *base = scratch + (qr >> 4) * MERGE_FLOATS + (qr & 15) * MERGE_ROW;
+                float mx = -INFINITY;
+                for (int x = 0; x < nsl; x++) mx = fmaxf(mx, base[x * nmt * MERGE_FLOATS + D]);
+                const float mu = mx == -INFINITY ? 0.f : mx;
+                float ls = 0.f;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int x = 0; x < nsl; x++) {
+                    const float *w = base + x * nmt * MERGE_FLOATS;
+                    const float f = fast_exp2((w[D] - mu) * sl2);
+                    ls += w[D + 1] * f;
+                    const float4 v = *(const float4 *)(w + 4 * lane);
+                    acc.x += v.x * f;
+                    acc.y += v.y * f;
+                    acc.z += v.z * f;
+                    acc.w += v.w * f;
+                }
+                const size_t slot = (size_t)part * group + gq;
+                __stcg((float4 *)(E.part_o + slot * D + 4 * lane), acc);
+                if (lane == 0) {
+                    const bool none = mx == -INFINITY;
+                    __stcg((float2 *)(E.part_ml + slot * 2), make_float2(none ? -1e30f : mx * 0.08838834764831845f, none ? 0.f : ls));
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(E.eempty + 8 * ep.stage);   // the buffer is the consumers' again
+        // 2. count the item in; merge what it completes
+        __threadfence();   // the triples are visible device-wide before the item is counted
+        bool last = false;
+        if (lane < n_rows) {
+            const int base = IR_ROW0 + IR_ROW_WORDS * lane;
+            uint32_t *ctr = E.counters + (size_t)rec[base + IRR_ROW] * E.hkv + kvh;
+            last = atomicAdd(ctr, 1u) + 1 == rec[base + IRR_COUNT];
+            if (last) *ctr = 0u;   // nobody else touches it in this launch: left clean for the next
+        }
+        const uint32_t done_mask = __ballot_sync(0xffffffffu, last);
+        if (done_mask) {
+            __threadfence();
+            merge_completed(E, rec, done_mask, kvh, lane);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(E.qempty + 8 * qp.stage);   // done with the record too
+        ep.advance(MERGE_BUFS);
+        qp.advance(Q_SLOTS);
+    }
+}
+
 template <int MT, bool BF16>
-__device__ void consume_item(const Params &P, const Shared &S, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3,
-                             Pipe &pipe, Pipe &qpipe, int warp, int lane) {
+__device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe &qpipe, Pipe &epipe, int warp,
+                             int lane) {
     constexpr int NMT = MT / 16;          // 16-row tiles of queries
     constexpr int NSL = CONSUMERS / NMT;  // key slices of a tile
     constexpr int KS = TILE_KEYS / NSL;   // keys per slice
@@ -326,33 +472,34 @@ __device__ void consume_item(const Params &P, const Shared &S, uint32_t w0, uint
     const int mi = warp % NMT, sl = warp / NMT;
     const int g = lane >> 2, t4 = lane & 3;
     const int group = P.group;
-    const uint32_t n_tiles = field(w0, IR_TILES), key_base = field(w0, IR_KEY0);
-    const uint32_t head_rows = field(w0, IR_HEAD_ROWS);
+    const uint32_t slot = S.q + qpipe.stage * Q_SLOT_BYTES;
+    const uint32_t *rec = (const uint32_t *)__cvta_shared_to_generic((size_t)(slot + Q_ROWS_BYTES));
+    const uint32_t n_tiles = rec[IR_TILES], key_base = rec[IR_KEY0];
+    const uint32_t head_rows = rec[IR_HEAD_ROWS];
     const int kvh = (int)(head_rows & 0xffffu), n_rows = (int)(head_rows >> 16);
     const int q_rows = n_rows * group;
     const float sl2 = 0.08838834764831845f * 1.4426950408889634f;   // log2(e) / sqrt(128)
     const bool exact_q = !LOW || (P.q_dtype == YX_BF16 && BF16) || (P.q_dtype == YX_F16 && !BF16);
 
     // The two query rows this thread owns in the accumulator fragments.
-    uint32_t klo[2], khi[2], part[2];
+    uint32_t klo[2], khi[2];
     bool valid[2];
 #pragma unroll
     for (int rs = 0; rs < 2; rs++) {
         const int qr = mi * 16 + g + rs * 8;
         valid[rs] = qr < q_rows;
         const int base = IR_ROW0 + IR_ROW_WORDS * (valid[rs] ? qr / group : 0);
-        const uint32_t a = rec_word(w1, w2, w3, base + IRR_KLO), b = rec_word(w1, w2, w3, base + IRR_KHI);
-        part[rs] = rec_word(w1, w2, w3, base + IRR_PART);
-        klo[rs] = valid[rs] ? a : 0u;            // padded rows: zero queries, nothing masked
-        khi[rs] = valid[rs] ? b : 0xffffffffu;
+        klo[rs] = valid[rs] ? rec[base + IRR_KLO] : 0u;            // padded rows: zero queries, nothing masked
+        khi[rs] = valid[rs] ? rec[base + IRR_KHI] : 0xffffffffu;
     }
 
-    // Query fragments from the staged slot.
-    uint32_t qh[8][4], ql[LOW ? 8 : 1][4];
-    {
-        mbar_wait(S.qfull + 8 * qpipe.stage, qpipe.phase, S.abort_flag, P.status, 4);
-        const uint32_t slot = S.q + qpipe.stage * Q_SLOT_BYTES;
-        const int row = mi * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+    // Query fragments from the staged slot.  Items with 64 rows, short of registers, read
+    // theirs again at every step.
+    constexpr bool HOLD_Q = MT != 64;
+    uint32_t qh[HOLD_Q ? 8 : 1][4], ql[LOW ? 8 : 1][4];
+    const int q_row = mi * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+    if constexpr (HOLD_Q) {
+        const int row = q_row;
 #pragma unroll
         for (int ks = 0; ks < 8; ks++) {
             const uint32_t a = slot + q_chunk_off(row, 2 * ks + (lane >> 4));
@@ -361,9 +508,6 @@ __device__ void consume_item(const Params &P, const Shared &S, uint32_t w0, uint
                 if (!exact_q) ldsm4(a + Q_LOW_OFFSET, ql[ks][0], ql[ks][1], ql[ks][2], ql[ks][3]);
             }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(S.qempty + 8 * qpipe.stage);
-        qpipe.advance(Q_SLOTS);
     }
 
     float o[16][4];
@@ -374,7 +518,7 @@ __device__ void consume_item(const Params &P, const Shared &S, uint32_t w0, uint
     const int lm = lane >> 3, lr = lane & 7;
     for (uint32_t ti = 0; ti < n_tiles; ti++) {
         mbar_wait(S.full + 8 * pipe.stage, pipe.phase, S.abort_flag, P.status, 2);
-        if (P.trace && threadIdx.x == 0 && P.trace[8 * blockIdx.x + 3] == 0) P.trace[8 * blockIdx.x + 3] = gtime();
+        if (P.trace && threadIdx.x == 0 && ti == 0 && P.trace[8 * blockIdx.x + 4] == 0) P.trace[8 * blockIdx.x + 4] = gtime();
         const uint32_t sb = S.stages + pipe.stage * STAGE_BYTES;
 
         // S = Q K^T over this warp's KS keys.  The low parts of the queries accumulate on their
@@ -390,13 +534,19 @@ __device__ void consume_item(const Params &P, const Shared &S, uint32_t w0, uint
         for (int ks = 0; ks < 8; ks++) {
             const uint32_t sub = sb + (ks >> 2) * SUB_BYTES;
             const int c = ((2 * ks) & 7) + (lm & 1);
+            uint32_t qf[4];
+            if constexpr (HOLD_Q) {
+                qf[0] = qh[ks][0], qf[1] = qh[ks][1], qf[2] = qh[ks][2], qf[3] = qh[ks][3];
+            } else {
+                ldsm4(slot + q_chunk_off(q_row, 2 * ks + (lane >> 4)), qf[0], qf[1], qf[2], qf[3]);
+            }
 #pragma unroll
             for (int np = 0; np < NT / 2; np++) {
                 const int key = sl * KS + np * 16 + (lm >> 1) * 8 + lr;
                 uint32_t b0, b1, b2, b3;
                 ldsm4(sub + key * 128 + ((c ^ lr) << 4), b0, b1, b2, b3);
-                mma16816<BF16>(s[2 * np], qh[ks], b0, b1);
-                mma16816<BF16>(s[2 * np + 1], qh[ks], b2, b3);
+                mma16816<BF16>(s[2 * np], qf, b0, b1);
+                mma16816<BF16>(s[2 * np + 1], qf, b2, b3);
                 if constexpr (LOW) {
                     if (!exact_q) {
                         mma16816<BF16>(s2[2 * np], ql[ks], b0, b1);
@@ -431,13 +581,13 @@ __device__ void consume_item(const Params &P, const Shared &S, uint32_t w0, uint
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
             const float mn = fmaxf(m[rs], mx);
             const float mu = mn == -INFINITY ? 0.f : mn;
-            const float alpha = exp2f((m[rs] - mu) * sl2);
+            const float alpha = fast_exp2((m[rs] - mu) * sl2);
             m[rs] = mn;
             float sum = 0.f;
             const float ms = mu * sl2;
 #pragma unroll
             for (int j = 0; j < NT; j++) {
-                const float p0 = exp2f(s[j][2 * rs] * sl2 - ms), p1 = exp2f(s[j][2 * rs + 1] * sl2 - ms);
+                const float p0 = fast_exp2(s[j][2 * rs] * sl2 - ms), p1 = fast_exp2(s[j][2 * rs + 1] * sl2 - ms);
                 s[j][2 * rs] = p0;
                 s[j][2 * rs + 1] = p1;
                 sum += p0 + p1;
@@ -480,101 +630,36 @@ __device__ void consume_item(const Params &P, const Shared &S, uint32_t w0, uint
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(S.empty + 8 * pipe.stage);
-        pipe.advance(STAGES);
+        pipe.advance(P.n_stages);
     }
 
+    if (P.trace && threadIdx.x == 0 && P.trace[8 * blockIdx.x + 7] == 0) P.trace[8 * blockIdx.x + 7] = gtime();
     // Row sums across the quad.
 #pragma unroll
     for (int rs = 0; rs < 2; rs++) {
         l[rs] += __shfl_xor_sync(0xffffffffu, l[rs], 1);
         l[rs] += __shfl_xor_sync(0xffffffffu, l[rs], 2);
     }
-
-    // Merge the key slices of each 16-row tile through shared memory.
-    if constexpr (NSL > 1) {
-        float *scratch = (float *)__cvta_shared_to_generic((size_t)S.merge);
-        if (sl > 0) {
-            float *w = scratch + ((sl - 1) * NMT + mi) * MERGE_FLOATS;
-#pragma unroll
-            for (int rs = 0; rs < 2; rs++) {
-                const int r = g + rs * 8;
-                if (t4 == 0) {
-                    w[r] = m[rs];
-                    w[16 + r] = l[rs];
-                }
-#pragma unroll
-                for (int n = 0; n < 16; n++)
-                    *(float2 *)(w + 32 + r * D + n * 8 + 2 * t4) = make_float2(o[n][2 * rs], o[n][2 * rs + 1]);
-            }
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");
-        if (sl == 0) {
-#pragma unroll
-            for (int rs = 0; rs < 2; rs++) {
-                const int r = g + rs * 8;
-                float mx = m[rs];
-#pragma unroll
-                for (int x = 1; x < NSL; x++) mx = fmaxf(mx, scratch[((x - 1) * NMT + mi) * MERGE_FLOATS + r]);
-                const float mu = mx == -INFINITY ? 0.f : mx;
-                const float f = exp2f((m[rs] - mu) * sl2);
-                l[rs] *= f;
-#pragma unroll
-                for (int n = 0; n < 16; n++) {
-                    o[n][2 * rs] *= f;
-                    o[n][2 * rs + 1] *= f;
-                }
-#pragma unroll
-                for (int x = 1; x < NSL; x++) {
-                    const float *w = scratch + ((x - 1) * NMT + mi) * MERGE_FLOATS;
-                    const float fx = exp2f((w[r] - mu) * sl2);
-                    l[rs] += w[16 + r] * fx;
-#pragma unroll
-                    for (int n = 0; n < 16; n++) {
-                        const float2 v = *(const float2 *)(w + 32 + r * D + n * 8 + 2 * t4);
-                        o[n][2 * rs] += v.x * fx;
-                        o[n][2 * rs + 1] += v.y * fx;
-                    }
-                }
-                m[rs] = mx;
-            }
-        }
-    }
-    if (sl == 0) {
+    // Every warp leaves its 16 rows' (o, m, l) in shared memory for the epilogue warp and goes
+    // on to the next item.
+    {
+        mbar_wait(S.eempty + 8 * epipe.stage, epipe.phase ^ 1u, S.abort_flag, P.status, 6);
+        float *w = (float *)__cvta_shared_to_generic((size_t)(S.merge + epipe.stage * MERGE_BYTES)) + warp * MERGE_FLOATS;
 #pragma unroll
         for (int rs = 0; rs < 2; rs++) {
-            if (!valid[rs]) continue;
-            const int qr = mi * 16 + g + rs * 8;
-            const size_t slot = (size_t)part[rs] * group + (qr % group);
-            float *po = P.part_o + slot * D;
+            float *row = w + (g + rs * 8) * MERGE_ROW;
+            if (t4 == 0) *(float2 *)(row + D) = make_float2(m[rs], l[rs]);
 #pragma unroll
-            for (int n = 0; n < 16; n++) __stcg((float2 *)(po + n * 8 + 2 * t4), make_float2(o[n][2 * rs], o[n][2 * rs + 1]));
-            if (t4 == 0) {
-                const bool none = m[rs] == -INFINITY;
-                __stcg((float2 *)(P.part_ml + slot * 2), make_float2(none ? -1e30f : m[rs] * 0.08838834764831845f, none ? 0.f : l[rs]));
-            }
+            for (int n = 0; n < 16; n++) *(float2 *)(row + n * 8 + 2 * t4) = make_float2(o[n][2 * rs], o[n][2 * rs + 1]);
         }
-        __threadfence();   // the triples are visible device-wide before this item is counted
+        __syncwarp();
+        if (lane == 0) mbar_arrive(S.efull + 8 * epipe.stage);
+        epipe.advance(MERGE_BUFS);
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");
-
-    // Fused merge: count this item in for each of its (row, KV head); whoever completes one
-    // merges all of its triples and writes the result.
-    int *flags = (int *)__cvta_shared_to_generic((size_t)S.flags);
-    if (warp == 0) {
-        // every lane takes part in the shuffles of rec_word; lanes beyond n_rows ignore theirs
-        const int base = IR_ROW0 + IR_ROW_WORDS * min(lane, MAX_ITEM_ROWS - 1);
-        const uint32_t row = rec_word(w1, w2, w3, base + IRR_ROW), count = rec_word(w1, w2, w3, base + IRR_COUNT);
-        if (lane < n_rows) {
-            uint32_t *ctr = P.counters + (size_t)row * P.hkv + kvh;
-            const uint32_t old = atomicAdd(ctr, 1u);
-            const bool last = old + 1 == count;
-            if (last) *ctr = 0u;   // nobody else touches it in this launch: left clean for the next
-            flags[lane] = last ? 1 : 0;
-        }
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");
-    merge_completed(P, flags, w1, w2, w3, n_rows, kvh, warp, lane);
-    // `flags` and the merge scratch are rewritten only after the next item's barriers.
+    // The slot (queries and record) is free once every consumer warp and the epilogue warp are
+    // done with the item.
+    if (lane == 0) mbar_arrive(S.qempty + 8 * qpipe.stage);
+    qpipe.advance(Q_SLOTS);
 }
 
 template <bool BF16>
@@ -585,11 +670,12 @@ __global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const __grid_con
     S.stages = smem_u32(smem);
     S.q = S.stages + STAGES * STAGE_BYTES;
     S.merge = S.q + Q_SLOTS * Q_SLOT_BYTES;
-    S.flags = S.merge + MERGE_BYTES;
-    S.full = S.flags + 128;
+    S.full = S.merge + MERGE_BUFS * MERGE_BYTES;
     S.empty = S.full + 8 * STAGES;
     S.qfull = S.empty + 8 * STAGES;
     S.qempty = S.qfull + 8 * Q_SLOTS;
+    S.efull = S.qempty + 8 * Q_SLOTS;
+    S.eempty = S.efull + 8 * MERGE_BUFS;
     S.abort_flag = &abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -604,47 +690,85 @@ __global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const __grid_con
         }
         for (int s = 0; s < Q_SLOTS; s++) {
             mbar_init(S.qfull + 8 * s, 1);
-            mbar_init(S.qempty + 8 * s, CONSUMERS);
+            mbar_init(S.qempty + 8 * s, CONSUMERS + 1);   // the consumer warps and the epilogue warp
+        }
+        for (int s = 0; s < MERGE_BUFS; s++) {
+            mbar_init(S.efull + 8 * s, CONSUMERS);
+            mbar_init(S.eempty + 8 * s, 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
-    if (tr && threadIdx.x == 0) {
-        tr[1] = gtime();
-        tr[7] = hdr.item_end - hdr.item_begin;
-    }
+    if (tr && threadIdx.x == 0) tr[1] = gtime();
 
     if (warp == PRODUCER) {
         produce(P, S, hdr, lane);
-        if (tr && lane == 0) tr[6] = gtime();
         return;
     }
     if (warp == QWARP) {
-        stage_queries<BF16>(P, S, hdr, lane);
+        QStage A;
+        A.q = P.q;
+        A.recs = P.recs;
+        A.status = P.status;
+        A.q_dtype = P.q_dtype;
+        A.hq = P.hq;
+        A.group = P.group;
+        A.item_begin = hdr.item_begin;
+        A.item_end = hdr.item_end;
+        A.have_first = P.has_prologue;
+        A.first_head_rows = A.first_mt = A.first_row = 0;
+        if (P.has_prologue) {
+            A.first_head_rows = P.pro[blockIdx.x].head_rows;
+            A.first_mt = P.pro[blockIdx.x].mt;
+            A.first_row = P.pro[blockIdx.x].rows[lane & (MAX_ITEM_ROWS - 1)];
+        }
+        A.qbase = S.q;
+        A.qfull = S.qfull;
+        A.qempty = S.qempty;
+        A.abort_flag = S.abort_flag;
+        stage_queries<BF16>(A, lane);
         return;
     }
-    Pipe pipe{0, 0}, qpipe{0, 0};
-    uint32_t n0 = 0, n1 = 0, n2 = 0, n3 = 0;
-    if (hdr.item_begin < hdr.item_end) {
-        const uint32_t *r = P.recs[hdr.item_begin].w;
-        n0 = r[lane], n1 = r[32 + lane], n2 = r[64 + lane], n3 = r[96 + lane];
+    if (warp == EWARP) {
+        Epilogue E;
+        E.recs = P.recs;
+        E.part_o = P.part_o;
+        E.part_ml = P.part_ml;
+        E.counters = P.counters;
+        E.out = P.out;
+        E.m_out = P.m_out;
+        E.l_out = P.l_out;
+        E.o_out = P.o_out;
+        E.status = P.status;
+        E.abort_flag = S.abort_flag;
+        E.out_dtype = P.out_dtype;
+        E.hq = P.hq;
+        E.hkv = P.hkv;
+        E.group = P.group;
+        E.n_items = hdr.item_end - hdr.item_begin;
+        E.qbase = S.q;
+        E.qempty = S.qempty;
+        E.merge = S.merge;
+        E.efull = S.efull;
+        E.eempty = S.eempty;
+        epilogue_loop(E, lane);
+        if (tr && lane == 0) tr[5] = gtime();
+        return;
     }
+    Pipe pipe{0, 0}, qpipe{0, 0}, epipe{0, 0};
     for (uint32_t ii = hdr.item_begin; ii < hdr.item_end; ii++) {
-        const uint32_t w0 = n0, w1 = n1, w2 = n2, w3 = n3;
-        if (ii + 1 < hdr.item_end) {   // in flight while this item runs
-            const uint32_t *r = P.recs[ii + 1].w;
-            n0 = r[lane], n1 = r[32 + lane], n2 = r[64 + lane], n3 = r[96 + lane];
+        // The staged slot holds the item's record and queries.
+        mbar_wait(S.qfull + 8 * qpipe.stage, qpipe.phase, S.abort_flag, P.status, 4);
+        if (tr && threadIdx.x == 0 && ii == hdr.item_begin) tr[3] = gtime();
+        const uint32_t mt = *(const uint32_t *)__cvta_shared_to_generic((size_t)(S.q + qpipe.stage * Q_SLOT_BYTES + Q_ROWS_BYTES + 4 * IR_MT));
+        switch (mt) {
+            case 16: consume_item<16, BF16>(P, S, pipe, qpipe, epipe, warp, lane); break;
+            case 32: consume_item<32, BF16>(P, S, pipe, qpipe, epipe, warp, lane); break;
+            default: consume_item<64, BF16>(P, S, pipe, qpipe, epipe, warp, lane); break;
         }
-        if (tr && threadIdx.x == 0 && ii == hdr.item_begin) tr[2] = gtime();
-        switch (field(w0, IR_MT)) {
-            case 16: consume_item<16, BF16>(P, S, w0, w1, w2, w3, pipe, qpipe, warp, lane); break;
-            case 32: consume_item<32, BF16>(P, S, w0, w1, w2, w3, pipe, qpipe, warp, lane); break;
-            default: consume_item<64, BF16>(P, S, w0, w1, w2, w3, pipe, qpipe, warp, lane); break;
-        }
-        if (tr && threadIdx.x == 0 && ii == hdr.item_begin) tr[4] = gtime();
+        if (tr && threadIdx.x == 0 && ii == hdr.item_begin) tr[6] = gtime();
     }
-    if (tr && threadIdx.x == 0) tr[5] = gtime();
     if (abort_flag) {
         // Copies issued before giving up may still be landing in this CTA's shared memory.
         for (int i = 0; i < 64; i++) __nanosleep(1000);
@@ -685,6 +809,7 @@ int launch_attend_mma(yx_ctx *ctx, const AttendArgs &a) {
     P.status = ctx->dev_status;
     P.trace = (unsigned long long *)ctx->trace_buf;
     P.has_prologue = 0;
+    P.n_stages = a.n_stages >= 2 && a.n_stages <= STAGES ? a.n_stages : 3;
     if (a.plan && a.n_ctas <= MAX_PROLOGUE_CTAS) {
         const Plan &pl = *a.plan;
         P.has_prologue = 1;

@@ -33,6 +33,7 @@ struct Unit {           // rows x one key range, before it is cut across CTAs (a
     std::vector<uint16_t> rows;
     uint32_t pt_off;
     uint32_t lo, hi;    // inclusive
+    bool reused = false;   // other units read the same pages: keep them in L2
 };
 
 inline uint32_t row_lo(uint32_t pos, int64_t window) {
@@ -103,8 +104,12 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
 
     // 3. Shared prefixes.  Cluster whole-group units by their first page; within a cluster
     //    the common run of identical page ids is read once for all member rows.
+    // Rows a shared item may hold.  The default keeps its query rows within one 16-row MMA tile
+    // (16 / group sequences of one row each): such an item costs what a private one costs, its
+    // padding rows become real work, and the other sharers find the pages in L2.
+    const int share_rows = std::max(1, std::min(pp.max_rows, pp.share_rows > 0 ? pp.share_rows : std::max(1, 16 / pp.group)));
     int shared_groups = 0;
-    if (pp.share_prefix && pp.max_rows > 1 && solos.size() > 1) {
+    if (pp.share_prefix && pp.max_rows > 1 && share_rows > 1 && solos.size() > 1) {
         std::unordered_map<uint64_t, std::vector<size_t>> by_first;   // first page id -> solos
         std::vector<uint64_t> order;
         for (size_t si = 0; si < solos.size(); si++) {
@@ -128,7 +133,7 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
             while (at < members.size()) {
                 size_t end = at;
                 size_t rows = 0;
-                while (end < members.size() && rows + units[solos[members[end]].unit].rows.size() <= (size_t)pp.max_rows) {
+                while (end < members.size() && rows + units[solos[members[end]].unit].rows.size() <= (size_t)share_rows) {
                     rows += units[solos[members[end]].unit].rows.size();
                     end++;
                 }
@@ -159,6 +164,7 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
                 if (common > pg0) {
                     Unit su;
                     su.pt_off = u0.pt_off;
+                    su.reused = members.size() > end - at;   // other clusters read these pages too
                     uint32_t lo = UINT32_MAX, hi = 0;
                     for (size_t k = at; k < end; k++) {
                         Unit &u = units[solos[members[k]].unit];
@@ -252,6 +258,7 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
                 it.kv_head = (uint16_t)kh;
                 it.n_rows = (uint16_t)u.rows.size();
                 it.mt = (uint32_t)padded_rows((int)u.rows.size() * pp.group);
+                it.pad_ = u.reused ? 1u : 0u;
                 for (size_t r = 0; r < u.rows.size(); r++) {
                     it.rows[r] = u.rows[r];
                     out.merges[(size_t)u.rows[r] * pp.hkv + kh].count++;
@@ -296,7 +303,7 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
                     uint32_t a = std::max(it.key_lo, t * TILE_KEYS), b = std::min(it.key_hi, t * TILE_KEYS + TILE_KEYS - 1);
                     TileDesc d;
                     d.block = pass.pages[it.pt_off + t * TILE_KEYS / PAGE] * (uint32_t)pp.hkv + it.kv_head;
-                    d.info = (t & 1u) | ((a - t * TILE_KEYS) << 1) | ((b - a + 1) << 8);
+                    d.info = (t & 1u) | ((a - t * TILE_KEYS) << 1) | ((b - a + 1) << 8) | (it.pad_ ? 1u << 16 : 0u);
                     out.tiles.push_back(d);
                 }
                 ItemRec &r = out.recs[i];
@@ -331,12 +338,24 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
     out.info.unique_kv_bytes = (int64_t)uniq * per_key;
     out.info.logical_kv_bytes = (int64_t)logical * per_key;
     out.info.shared_groups = shared_groups;
-    // Every tile read by one item only: nothing is gained by keeping K/V lines in L2.
-    uint64_t streamed = 0;
-    for (const Item &it : out.items)
-        for (uint32_t t = it.tile_begin; t < it.tile_end; t++)
-            streamed += std::min(it.key_hi, t * TILE_KEYS + TILE_KEYS - 1) - std::max(it.key_lo, t * TILE_KEYS) + 1;
-    out.single_use = streamed * (uint64_t)per_key / pp.hkv <= (uint64_t)out.info.unique_kv_bytes;
+    // Tiles not marked as reused are copied with an evict-first hint when each of them is read
+    // by one item only: nothing is gained by keeping those K/V lines in L2.
+    {
+        std::unordered_map<uint64_t, uint32_t> once;   // (physical page, half) -> most keys read by unmarked items
+        uint64_t streamed = 0;
+        for (const Item &it : out.items) {
+            if (it.pad_ || it.kv_head != 0) continue;
+            for (uint32_t t = it.tile_begin; t < it.tile_end; t++) {
+                uint32_t n = std::min(it.key_hi, t * TILE_KEYS + TILE_KEYS - 1) - std::max(it.key_lo, t * TILE_KEYS) + 1;
+                streamed += n;
+                uint32_t &m = once[((uint64_t)pass.pages[it.pt_off + t * TILE_KEYS / PAGE] << 1) | (t & 1)];
+                m = std::max(m, n);
+            }
+        }
+        uint64_t distinct = 0;
+        for (auto &kv : once) distinct += kv.second;
+        out.single_use = streamed <= distinct;
+    }
 }
 
 }  // namespace yx

@@ -26,6 +26,7 @@ extern "C" int yx_plan_probe(uint32_t rows, const uint32_t *pos, const uint32_t 
     pp.w32 = cost32 > 0 ? cost32 : 16;
     pp.w64 = cost64 > 0 ? cost64 : 16;
     pp.resolve = true;
+    pp.share_rows = share_prefix > 1 ? share_prefix : 0;   // values above 1 name the rows a shared item may hold
     yx::Plan plan;
     try {
         yx::build_split_plan(pass, pp, plan);

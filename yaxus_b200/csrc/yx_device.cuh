@@ -36,10 +36,11 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait.  Returns at once when the CTA has given up; on expiry it raises the CTA's
-// abort flag and records where in the context's status word.  Nothing spins forever.
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          yx_dev_status *status, int where) {
-    if (mbar_try(bar, parity)) return;
+// abort flag and records where in the context's status word.  Nothing spins forever.  The
+// spinning part is out of line: it is cold code, and the attention kernels pay for every
+// instruction-cache line they touch.
+__device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                            yx_dev_status *status, int where) {
     if (*abort_flag) return;
     long long t0 = clock64();
     for (uint32_t spins = 1;; spins++) {
@@ -57,6 +58,11 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatil
             }
         }
     }
+}
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          yx_dev_status *status, int where) {
+    if (mbar_try(bar, parity)) return;
+    mbar_wait_slow(bar, parity, abort_flag, status, where);
 }
 
 __device__ __forceinline__ uint64_t policy_evict_first() {
@@ -142,6 +148,13 @@ __device__ __forceinline__ void store4(void *out, int out_dtype, size_t elem, fl
         __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
         *(uint2 *)((uint16_t *)out + elem) = make_uint2(*(uint32_t *)&a, *(uint32_t *)&b);
     }
+}
+
+// 2^x by the special-function unit (two units in the last place; -inf gives 0).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 __device__ __forceinline__ unsigned long long gtime() {

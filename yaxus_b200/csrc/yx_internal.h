@@ -84,7 +84,8 @@ struct CtaHdr {
 // One 64-key tile: where it is and which of its rows hold keys of the item.
 struct TileDesc {
     uint32_t block;   // page * hkv + kv_head: index of the 32 KiB block in the K and V arenas
-    uint32_t info;    // bit 0: which half of the page; bits 1-7: first row; bits 8-15: rows (1..64)
+    uint32_t info;    // bit 0: which half of the page; bits 1-7: first row; bits 8-15: rows (1..64);
+                      // bit 16: other items read the same tile (keep it in L2)
 };
 
 // An item as the kernel reads it: 128 words, fetched by a warp with four coalesced loads.
@@ -110,7 +111,7 @@ struct Plan {
     std::vector<CtaHdr> cta_hdr;
     std::vector<TileDesc> tiles;
     std::vector<ItemRec> recs;
-    bool single_use = false;            // every tile is read by exactly one item
+    bool single_use = false;            // every tile not marked as reused is read by exactly one item
     bool has_empty_rows = false;        // some (row, kv head) has no item: no live key in the range
     yx_plan_info info{};
 };
@@ -130,6 +131,7 @@ struct PlanParams {
     int esize;               // bytes per stored element
     int w32, w64;            // cost of a tile of an item with 32 / 64 padded rows, in 16ths of a 16-row tile's
     bool resolve;            // also build the resolved form for the streaming kernel
+    int share_rows;          // pass rows a shared item may hold (0 = one 16-row MMA tile's worth)
 };
 
 // Builds the split-key plan.  Throws std::string on a malformed pass.
@@ -205,6 +207,7 @@ struct yx_ctx {
         int64_t window = 0;
         uint64_t key_lo = 0, key_hi = 0;
         bool share = false, resolve = false;
+        int share_rows = 0;
         yx::Plan plan;
         char *dev = nullptr;       // items | cta_begin | merges | cta_hdr | tiles | recs
         size_t dev_cap = 0;
@@ -274,6 +277,7 @@ struct AttendArgs {
     const ItemRec *recs;
     bool single_use;
     const Plan *plan;        // host copy, for what is passed in kernel-parameter space
+    int n_stages;            // copy ring depth (0 = default)
     uint32_t *counters;      // one per (pass row, kv head), zero between launches
     void *out;               // normalised output, or null
     int out_dtype;
