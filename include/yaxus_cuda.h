@@ -73,6 +73,8 @@ typedef struct yx_tuning {
     int32_t cost64;          /* and with 64, in 16ths of the cost of a 16-row item's tile */
     int32_t stages;          /* 64-key tiles in flight per SM in the tensor split-key kernel (2..5) */
     int32_t share_rows;      /* pass rows a shared-prefix item may hold (0: 16 / group, one MMA tile) */
+    int32_t item_cost;       /* planner cost of starting an item, in 16ths of a tile, plus one (0: default) */
+    int32_t fused_merge;     /* 1: the split-key kernel merges the triples itself; 0: a combine kernel does */
 } yx_tuning;
 
 /* What the last yx_attend / yx_attention call planned; for tests and benchmarks. */
@@ -205,8 +207,8 @@ int yx_attend_allgather(yx_ctx *ctx, yx_kv *kv, int layer, const void *q_dev, in
 #define YX_PROBE_ITEM_WORDS 41
 int yx_plan_probe(uint32_t rows, const uint32_t *pos_host, const uint32_t *pt_off_host, const uint32_t *pages_host,
                   uint32_t n_pages, int hkv, int group, int64_t window, uint64_t key_lo, uint64_t key_hi,
-                  int max_rows, int n_ctas, int share_prefix, int esize, int cost32, int cost64, yx_plan_info *info,
-                  uint32_t *items_out, uint32_t max_items);
+                  int max_rows, int n_ctas, int share_prefix, int esize, int cost32, int cost64, int item_cost,
+                  int min_piece, yx_plan_info *info, uint32_t *items_out, uint32_t max_items);
 
 #ifdef __cplusplus
 }

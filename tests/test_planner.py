@@ -15,7 +15,7 @@ U64_MAX = (1 << 64) - 1
 
 
 def probe(meta, hkv, group, window=0, key_lo=0, key_hi=U64_MAX, max_rows=16, n_ctas=148, share=1, esize=2, cost32=16,
-          cost64=32):
+          cost64=32, item_cost=0, min_piece=1):
     L = _lib.cuda_lib()
     info = _lib.PlanInfo()
     cap = 200000
@@ -23,7 +23,7 @@ def probe(meta, hkv, group, window=0, key_lo=0, key_hi=U64_MAX, max_rows=16, n_c
     p = lambda a: np.ascontiguousarray(a, np.uint32).ctypes.data_as(ctypes.POINTER(ctypes.c_uint32))
     pos, off, pages = (np.ascontiguousarray(x, np.uint32) for x in (meta.pos, meta.pt_off, meta.pages))
     rc = L.yx_plan_probe(len(pos), p(pos), p(off), p(pages), len(pages), hkv, group, window or 0, key_lo, key_hi,
-                         max_rows, n_ctas, share, esize, cost32, cost64, ctypes.byref(info), p(buf), cap)
+                         max_rows, n_ctas, share, esize, cost32, cost64, item_cost, min_piece, ctypes.byref(info), p(buf), cap)
     assert rc == 0
     items = buf[: info.n_items * _lib.PROBE_ITEM_WORDS].reshape(info.n_items, _lib.PROBE_ITEM_WORDS)
     return info, items
@@ -70,18 +70,22 @@ def check_slots(items, info, group_rows):
     assert len(used) == info.n_parts
 
 
-def check_balance(items, info, cost32=16, cost64=32):
-    """Per-CTA cost (tiles weighted by the item's padded rows) differs by at most ~one tile."""
+def check_balance(items, info, cost32=16, cost64=32, item_cost=0):
+    """Per-CTA cost (tiles weighted by the item's padded rows, plus a fixed cost per item)
+    differs by at most about a tile."""
     w = {16: 16, 32: cost32, 64: cost64}
     per = np.zeros(info.n_ctas, np.int64)
+    per_items = np.zeros(info.n_ctas, np.int64)
     tiles = 0
     for it in items:
         n = int(it[1]) - int(it[0])
         tiles += n
-        per[int(it[8])] += n * w[int(it[7])]
+        per[int(it[8])] += n * w[int(it[7])] + item_cost
+        per_items[int(it[8])] += 1
     assert tiles == info.tiles
     if info.tiles >= info.n_ctas:
-        assert per.max() - per.min() <= 2 * max(w.values())
+        assert per.max() - per.min() <= 2 * max(w.values()) + item_cost * (1 + per_items.max())
+    return per_items
 
 
 @pytest.mark.parametrize("share", [0, 1, 16])
@@ -146,6 +150,26 @@ def test_key_range_restriction():
                 check_balance(items, info)
                 if window and khi <= 8192 - 2048:
                     assert info.n_items == 0 and info.n_parts == 0   # a rank with no live key
+
+
+@pytest.mark.parametrize("item_cost,min_piece", [(48, 4), (0, 8), (200, 1)])
+def test_item_cost_and_minimum_piece(item_cost, min_piece):
+    # The production settings: a fixed cost per item and no pieces of fewer than min_piece
+    # tiles (unless a whole run is that short).  Coverage stays exact; balance is looser.
+    for s in (W.batched_decode(fill=False), W.verify(fill=False)):
+        info, items = probe(s.meta, s.hkv, s.hq // s.hkv, item_cost=item_cost, min_piece=min_piece)
+        check_cover(s.meta, items, s.hkv, None)
+        check_slots(items, info, 1)
+        runs = {}
+        for it in items:
+            runs.setdefault((int(it[4]), int(it[5]), int(it[2])), []).append(int(it[1]) - int(it[0]))
+        for pieces in runs.values():
+            if sum(pieces) >= min_piece:
+                assert min(pieces) >= min_piece
+        per = np.zeros(info.n_ctas, np.int64)
+        for it in items:
+            per[int(it[8])] += int(it[1]) - int(it[0])
+        assert per.max() <= info.tiles / info.n_ctas + 2 * min_piece + item_cost / 16 * 3 + 2
 
 
 def test_decode_is_split_across_keys():

@@ -116,7 +116,7 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
         if (cp.pass_serial == ctx->pass_serial && cp.hkv == pp.hkv && cp.group == pp.group &&
             cp.max_rows == pp.max_rows && cp.n_ctas == pp.n_ctas && cp.window == pp.window &&
             cp.key_lo == pp.key_lo && cp.key_hi == pp.key_hi && cp.share == pp.share_prefix && cp.esize == pp.esize &&
-            cp.w32 == pp.w32 && cp.w64 == pp.w64 && cp.resolve == pp.resolve && cp.share_rows == pp.share_rows) {
+            cp.w32 == pp.w32 && cp.w64 == pp.w64 && cp.resolve == pp.resolve && cp.share_rows == pp.share_rows && cp.item_cost == pp.item_cost) {
             *out = &cp;
             return YX_OK;
         }
@@ -160,6 +160,7 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
     slot->w64 = pp.w64;
     slot->resolve = pp.resolve;
     slot->share_rows = pp.share_rows;
+    slot->item_cost = pp.item_cost;
 
     const Plan &pl = slot->plan;
     auto pad16 = [](size_t n) { return (n + 15) / 16 * 16; };
@@ -245,6 +246,8 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     pp.w64 = ctx->tuning.cost64 > 0 ? ctx->tuning.cost64 : 40;
     pp.resolve = path == 2;
     pp.share_rows = ctx->tuning.share_rows;
+    pp.min_piece = path == 2 ? 4 : 1;
+    pp.item_cost = ctx->tuning.item_cost > 0 ? ctx->tuning.item_cost - 1 : (path == 2 ? 48 : 0);
     yx_ctx::CachedPlan *cp = nullptr;
     if (int rc = get_plan(ctx, pp, &cp)) return rc;
     const Plan &pl = cp->plan;
@@ -293,6 +296,7 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     a.single_use = pl.single_use;
     a.plan = &pl;
     a.n_stages = ctx->tuning.stages;
+    a.fused = ctx->tuning.fused_merge == 1;
     a.counters = ctx->counters;
     a.out = out;
     a.out_dtype = out_dtype;
@@ -302,12 +306,16 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     profile_mark(ctx, 0);
     if (path == 2) {
         // Rows without a live key in the range get no item, so nothing would write them.
-        if (o_out && pl.has_empty_rows)
+        if (a.fused && o_out && pl.has_empty_rows)
             if (int rc = launch_fill_empty(ctx, (size_t)ctx->pass.rows * hq, m_out, l_out, o_out)) return rc;
         if (!pl.items.empty())
             if (int rc = launch_attend_mma(ctx, a)) return rc;
         profile_mark(ctx, 1);
         profile_mark(ctx, 2);
+        if (!a.fused)
+            if (int rc = launch_combine(ctx, cp->d_merges, ctx->ws_o, ctx->ws_ml, (int)ctx->pass.rows, hq, group, out,
+                                        out_dtype, m_out, l_out, o_out))
+                return rc;
         profile_mark(ctx, 3);
     } else {
         if (!pl.items.empty())

@@ -40,8 +40,9 @@ constexpr int STAGE_BYTES = 4 * SUB_BYTES;        // K lo, K hi, V lo, V hi
 constexpr int CONSUMERS = 4;                      // warps 0..3
 constexpr int PRODUCER = CONSUMERS;               // warp 4
 constexpr int QWARP = CONSUMERS + 1;              // warp 5
-constexpr int EWARP = CONSUMERS + 2;              // warp 6
-constexpr int THREADS = (CONSUMERS + 3) * 32;
+constexpr int EWARP = CONSUMERS + 2;              // warps 6 and 7: items alternate between them
+constexpr int EWARPS = 2;
+constexpr int THREADS = (CONSUMERS + 2 + EWARPS) * 32;
 constexpr int Q_SLOTS = 2;
 constexpr int Q_ROWS_BYTES = 16384;               // 64 rows x 256 B, or 32 rows high + 32 rows low
 constexpr int Q_LOW_OFFSET = 8192;
@@ -51,11 +52,12 @@ constexpr int MERGE_FLOATS = 16 * MERGE_ROW;      // one warp's 16 rows
 constexpr int MERGE_BYTES = CONSUMERS * MERGE_FLOATS * 4;   // one buffer: every consumer warp's rows
 constexpr int MERGE_BUFS = 2;
 constexpr int N_BARRIERS = 2 * STAGES + 2 * Q_SLOTS + 2 * MERGE_BUFS;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + Q_SLOTS * Q_SLOT_BYTES + MERGE_BUFS * MERGE_BYTES + N_BARRIERS * 8 + 64;
+constexpr int MLBUF_BYTES = EWARPS * 8 * 32 * 8;  // per epilogue warp: (m, l) of 32 parts for each of 8 merges in flight
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + Q_SLOTS * Q_SLOT_BYTES + MERGE_BUFS * MERGE_BYTES + N_BARRIERS * 8 + MLBUF_BYTES;
 
 struct Shared {
     uint32_t stages, q, merge;          // shared-space addresses
-    uint32_t full, empty, qfull, qempty, efull, eempty;
+    uint32_t full, empty, qfull, qempty, efull, eempty, mlbuf;
     volatile int *abort_flag;
 };
 
@@ -98,6 +100,7 @@ struct Params {
     float *m_out, *l_out, *o_out;
     yx_dev_status *status;
     unsigned long long *trace;       // optional: 8 timestamps / counters per CTA
+    int fused;                       // merge in this kernel (arrival counters) or leave it to the combine kernel
     int n_stages;                    // stages of the ring in use (2..STAGES): bytes in flight per SM
     int has_prologue;
     CtaPrologue pro[MAX_PROLOGUE_CTAS];
@@ -228,18 +231,24 @@ struct QStage {
     volatile int *abort_flag;
 };
 
+// The loads of the next item are issued as soon as the current one is staged, so that by the
+// time its slot is free only the stores to shared memory remain: an item shorter than a round
+// trip to memory does not leave the consumers waiting for their queries.
 template <bool BF16>
 __device__ __noinline__ void stage_queries(const QStage A, int lane) {
     Pipe pipe{0, 0};
     const bool exact = (A.q_dtype == YX_BF16 && BF16) || (A.q_dtype == YX_F16 && !BF16);
     const int chunk = lane >> 1;
     const uint32_t sub = (lane & 1) * 8;
-    for (uint32_t ii = A.item_begin; ii < A.item_end; ii++) {
-        // The item's record goes to shared memory with the queries; lane r < 16 also holds
-        // pass row r of the item.
+
+    // What is held in registers for the item about to be staged.
+    uint4 rec4 = make_uint4(0, 0, 0, 0);
+    uint32_t head_rows = 0, mt = 0, elem[2] = {0xffffffffu, 0xffffffffu};
+    float4 v[16];
+    auto fetch = [&](uint32_t ii) {
         const uint32_t *rec = A.recs[ii].w;
-        const uint4 rec4 = *(const uint4 *)(rec + 4 * lane);
-        uint32_t head_rows, mt, my_row = 0;
+        rec4 = *(const uint4 *)(rec + 4 * lane);
+        uint32_t my_row;   // lane r < 16: pass row r of the item
         if (ii == A.item_begin && A.have_first) {
             head_rows = A.first_head_rows;
             mt = A.first_mt;
@@ -249,8 +258,40 @@ __device__ __noinline__ void stage_queries(const QStage A, int lane) {
             head_rows = rec[IR_HEAD_ROWS];
             mt = rec[IR_MT];
         }
-        const int kvh = (int)(head_rows & 0xffffu), n_rows = (int)(head_rows >> 16);
-        const int q_rows = n_rows * A.group;
+        const int kvh = (int)(head_rows & 0xffffu), q_rows = (int)(head_rows >> 16) * A.group;
+        // Lane k works out where query rows k and 32 + k live (one division per lane, not one
+        // per row); the loads take the addresses by shuffle.
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int mine = 32 * h + lane;
+            const int pr = mine / A.group;
+            const uint32_t prow = __shfl_sync(0xffffffffu, my_row, min(pr, MAX_ITEM_ROWS - 1));
+            elem[h] = mine < q_rows ? (prow * (uint32_t)A.hq + (uint32_t)(kvh * A.group + (mine - pr * A.group))) : 0xffffffffu;
+        }
+#pragma unroll
+        for (int k = 0; k < 16; k++) {
+            const uint32_t e = __shfl_sync(0xffffffffu, elem[0], k);
+            v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (e != 0xffffffffu) v[k] = load4_as_f32(A.q, A.q_dtype, (size_t)e * D + lane * 4);
+        }
+    };
+    auto store16 = [&](uint32_t slot, int r0, bool low) {
+#pragma unroll
+        for (int k = 0; k < 16; k++) {
+            const uint32_t h0 = pack2<BF16>(v[k].x, v[k].y), h1 = pack2<BF16>(v[k].z, v[k].w);
+            const uint32_t addr = slot + q_chunk_off(r0 + k, chunk) + sub;
+            asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(h0), "r"(h1) : "memory");
+            if (low) {
+                const float2 f0 = unpack2<BF16>(h0), f1 = unpack2<BF16>(h1);
+                const uint32_t l0 = pack2<BF16>(v[k].x - f0.x, v[k].y - f0.y), l1 = pack2<BF16>(v[k].z - f1.x, v[k].w - f1.y);
+                asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr + Q_LOW_OFFSET), "r"(l0), "r"(l1) : "memory");
+            }
+        }
+    };
+
+    if (A.item_begin < A.item_end) fetch(A.item_begin);
+#pragma unroll 1
+    for (uint32_t ii = A.item_begin; ii < A.item_end; ii++) {
         int stop = 0;
         if (lane == 0) {
             mbar_wait(A.qempty + 8 * pipe.stage, pipe.phase ^ 1u, A.abort_flag, A.status, 3);
@@ -259,38 +300,18 @@ __device__ __noinline__ void stage_queries(const QStage A, int lane) {
         if (__shfl_sync(0xffffffffu, stop, 0)) return;
         const uint32_t slot = A.qbase + pipe.stage * Q_SLOT_BYTES;
         const bool low = mt != 64 && !exact;
-        // Lane k works out where query rows k and 32 + k live (one division per lane, not one
-        // per row); the loads then take the addresses by shuffle, eight rows in flight.
-        uint32_t my_elem[2];
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const int mine = 32 * h + lane;
-            const int pr = mine / A.group;
-            const uint32_t prow = __shfl_sync(0xffffffffu, my_row, min(pr, MAX_ITEM_ROWS - 1));
-            my_elem[h] = mine < q_rows ? (prow * (uint32_t)A.hq + (uint32_t)(kvh * A.group + (mine - pr * A.group))) : 0xffffffffu;
-        }
+        store16(slot, 0, low);
+        // Items of more than 16 query rows: the rest, sixteen at a time.
 #pragma unroll 1
-        for (int r0 = 0; r0 < (int)mt; r0 += 16) {
-            float4 v[16];
-            const uint32_t src = r0 < 32 ? my_elem[0] : my_elem[1];
+        for (int r0 = 16; r0 < (int)mt; r0 += 16) {
+            const uint32_t src = r0 < 32 ? elem[0] : elem[1];
 #pragma unroll
             for (int k = 0; k < 16; k++) {
                 const uint32_t e = __shfl_sync(0xffffffffu, src, (r0 + k) & 31);
                 v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (e != 0xffffffffu) v[k] = load4_as_f32(A.q, A.q_dtype, (size_t)e * D + lane * 4);
             }
-#pragma unroll
-            for (int k = 0; k < 16; k++) {
-                const int qr = r0 + k;
-                const uint32_t h0 = pack2<BF16>(v[k].x, v[k].y), h1 = pack2<BF16>(v[k].z, v[k].w);
-                const uint32_t addr = slot + q_chunk_off(qr, chunk) + sub;
-                asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(h0), "r"(h1) : "memory");
-                if (low) {
-                    const float2 f0 = unpack2<BF16>(h0), f1 = unpack2<BF16>(h1);
-                    const uint32_t l0 = pack2<BF16>(v[k].x - f0.x, v[k].y - f0.y), l1 = pack2<BF16>(v[k].z - f1.x, v[k].w - f1.y);
-                    asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr + Q_LOW_OFFSET), "r"(l0), "r"(l1) : "memory");
-                }
-            }
+            store16(slot, r0, low);
         }
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(slot + Q_ROWS_BYTES + 16 * lane), "r"(rec4.x),
                      "r"(rec4.y), "r"(rec4.z), "r"(rec4.w)
@@ -298,6 +319,7 @@ __device__ __noinline__ void stage_queries(const QStage A, int lane) {
         __syncwarp();
         if (lane == 0) mbar_arrive(A.qfull + 8 * pipe.stage);
         pipe.advance(Q_SLOTS);
+        if (ii + 1 < A.item_end) fetch(ii + 1);
     }
 }
 
@@ -323,8 +345,9 @@ struct Epilogue {
     yx_dev_status *status;
     volatile int *abort_flag;
     int out_dtype, hq, hkv, group;
-    uint32_t n_items;
-    uint32_t qbase, qempty, merge, efull, eempty;   // shared-space addresses
+    int fused;               // count items in and merge here (else a separate combine kernel merges)
+    uint32_t n_items, first_item;    // this warp takes items first_item, first_item + EWARPS, ...
+    uint32_t qbase, qempty, merge, efull, eempty, mlbuf;   // shared-space addresses
 };
 
 // Eight (row, head) pairs at a time, four lanes each: two round trips to L2 per round (the
@@ -348,33 +371,54 @@ __device__ __forceinline__ void merge_completed(const Epilogue &E, const uint32_
         const uint32_t row = rec[base + IRR_ROW], first = rec[base + IRR_FIRST], count = rec[base + IRR_COUNT];
         const float *ml = E.part_ml + ((size_t)first * group + hg) * 2;
         const float *po = E.part_o + ((size_t)first * group + hg) * D + l4 * 32;
-        float mx = -1e30f;
-#pragma unroll 1
-        for (uint32_t c = l4; c < count; c += 4) {
-            const float2 v = __ldcg((const float2 *)(ml + (size_t)c * group * 2));
-            if (v.y > 0.0f) mx = fmaxf(mx, v.x);
-        }
-        mx = fmaxf(mx, __shfl_xor_sync(gmask, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(gmask, mx, 2));
-        float ls = 0.0f;
+        // Round trip one: every part's (m, l), parked in shared memory.  Round trip two: the
+        // vectors, their loads independent of one another because the weights no longer come
+        // from global memory.  Chunks of 32 parts, a running maximum between chunks.
+        float2 *mls = (float2 *)__cvta_shared_to_generic((size_t)E.mlbuf) + sub * 32;
+        float mx = -1e30f, ls = 0.0f;
         float4 acc[8];
 #pragma unroll
         for (int k = 0; k < 8; k++) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 2
-        for (uint32_t c = 0; c < count; c++) {
-            const float2 v = __ldcg((const float2 *)(ml + (size_t)c * group * 2));
-            if (!(v.y > 0.0f)) continue;
-            const float w = __expf(v.x - mx);
-            ls += v.y * w;
-            const float4 *src = (const float4 *)(po + (size_t)c * group * D);
+#pragma unroll 1
+        for (uint32_t c0 = 0; c0 < count; c0 += 32) {
+            const uint32_t nc = min(32u, count - c0);
+            float cm = -1e30f;
+#pragma unroll 1
+            for (uint32_t c = l4; c < nc; c += 4) {
+                const float2 v = __ldcg((const float2 *)(ml + (size_t)(c0 + c) * group * 2));
+                mls[c] = v;
+                if (v.y > 0.0f) cm = fmaxf(cm, v.x);
+            }
+            cm = fmaxf(cm, __shfl_xor_sync(gmask, cm, 1));
+            cm = fmaxf(cm, __shfl_xor_sync(gmask, cm, 2));
+            __syncwarp(gmask);   // the parked values are visible to the group
+            const float nm = fmaxf(mx, cm), r = __expf(mx - nm);
+            ls *= r;
 #pragma unroll
             for (int k = 0; k < 8; k++) {
-                const float4 x = __ldcg(src + k);
-                acc[k].x += x.x * w;
-                acc[k].y += x.y * w;
-                acc[k].z += x.z * w;
-                acc[k].w += x.w * w;
+                acc[k].x *= r;
+                acc[k].y *= r;
+                acc[k].z *= r;
+                acc[k].w *= r;
             }
+            mx = nm;
+#pragma unroll 2
+            for (uint32_t c = 0; c < nc; c++) {
+                const float2 v = mls[c];
+                if (!(v.y > 0.0f)) continue;
+                const float w = __expf(v.x - mx);
+                ls += v.y * w;
+                const float4 *src = (const float4 *)(po + (size_t)(c0 + c) * group * D);
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    const float4 x = __ldcg(src + k);
+                    acc[k].x += x.x * w;
+                    acc[k].y += x.y * w;
+                    acc[k].z += x.z * w;
+                    acc[k].w += x.w * w;
+                }
+            }
+            __syncwarp(gmask);   // the next chunk reuses the parking space
         }
         const size_t idx = (size_t)row * E.hq + (size_t)kvh * group + hg;
         if (E.out) {
@@ -397,13 +441,16 @@ __device__ __forceinline__ void merge_completed(const Epilogue &E, const uint32_
 
 __device__ __noinline__ void epilogue_loop(const Epilogue E, int lane) {
     const float sl2 = 0.08838834764831845f * 1.4426950408889634f;
-    Pipe ep{0, 0}, qp{0, 0};
+    // Merge buffer b, query slot b and epilogue warp b go together (two of each).
+    static_assert(MERGE_BUFS == EWARPS && Q_SLOTS == EWARPS, "one buffer and one slot per epilogue warp");
+    const uint32_t mine = E.first_item;
+    uint32_t phase = 0;
     const int group = E.group;
 #pragma unroll 1
-    for (uint32_t ii = 0; ii < E.n_items; ii++) {
-        mbar_wait(E.efull + 8 * ep.stage, ep.phase, E.abort_flag, E.status, 5);
-        const float *scratch = (const float *)__cvta_shared_to_generic((size_t)(E.merge + ep.stage * MERGE_BYTES));
-        const uint32_t *rec = (const uint32_t *)__cvta_shared_to_generic((size_t)(E.qbase + qp.stage * Q_SLOT_BYTES + Q_ROWS_BYTES));
+    for (uint32_t ii = mine; ii < E.n_items; ii += EWARPS, phase ^= 1u) {
+        mbar_wait(E.efull + 8 * mine, phase, E.abort_flag, E.status, 5);
+        const float *scratch = (const float *)__cvta_shared_to_generic((size_t)(E.merge + mine * MERGE_BYTES));
+        const uint32_t *rec = (const uint32_t *)__cvta_shared_to_generic((size_t)(E.qbase + mine * Q_SLOT_BYTES + Q_ROWS_BYTES));
         const uint32_t head_rows = rec[IR_HEAD_ROWS];
         const int kvh = (int)(head_rows & 0xffffu), n_rows = (int)(head_rows >> 16);
         const int nmt = (int)rec[IR_MT] >> 4, nsl = CONSUMERS / nmt;
@@ -439,7 +486,11 @@ __device__ __noinline__ void epilogue_loop(const Epilogue E, int lane) {
             }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(E.eempty + 8 * ep.stage);   // the buffer is the consumers' again
+        if (lane == 0) mbar_arrive(E.eempty + 8 * mine);   // the buffer is the consumers' again
+        if (!E.fused) {
+            if (lane == 0) mbar_arrive(E.qempty + 8 * mine);
+            continue;
+        }
         // 2. count the item in; merge what it completes
         __threadfence();   // the triples are visible device-wide before the item is counted
         bool last = false;
@@ -455,9 +506,7 @@ __device__ __noinline__ void epilogue_loop(const Epilogue E, int lane) {
             merge_completed(E, rec, done_mask, kvh, lane);
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(E.qempty + 8 * qp.stage);   // done with the record too
-        ep.advance(MERGE_BUFS);
-        qp.advance(Q_SLOTS);
+        if (lane == 0) mbar_arrive(E.qempty + 8 * mine);   // done with the record too
     }
 }
 
@@ -676,6 +725,7 @@ __global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const __grid_con
     S.qempty = S.qfull + 8 * Q_SLOTS;
     S.efull = S.qempty + 8 * Q_SLOTS;
     S.eempty = S.efull + 8 * MERGE_BUFS;
+    S.mlbuf = S.eempty + 8 * MERGE_BUFS;
     S.abort_flag = &abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -730,7 +780,7 @@ __global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const __grid_con
         stage_queries<BF16>(A, lane);
         return;
     }
-    if (warp == EWARP) {
+    if (warp >= EWARP) {
         Epilogue E;
         E.recs = P.recs;
         E.part_o = P.part_o;
@@ -746,14 +796,17 @@ __global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const __grid_con
         E.hq = P.hq;
         E.hkv = P.hkv;
         E.group = P.group;
+        E.fused = P.fused;
         E.n_items = hdr.item_end - hdr.item_begin;
         E.qbase = S.q;
         E.qempty = S.qempty;
         E.merge = S.merge;
         E.efull = S.efull;
         E.eempty = S.eempty;
+        E.mlbuf = S.mlbuf + (warp - EWARP) * (MLBUF_BYTES / EWARPS);
+        E.first_item = warp - EWARP;
         epilogue_loop(E, lane);
-        if (tr && lane == 0) tr[5] = gtime();
+        if (tr && lane == 0 && (E.n_items < 2 || ((E.n_items - 1) & 1u) == E.first_item)) tr[5] = gtime();
         return;
     }
     Pipe pipe{0, 0}, qpipe{0, 0}, epipe{0, 0};
@@ -809,6 +862,7 @@ int launch_attend_mma(yx_ctx *ctx, const AttendArgs &a) {
     P.status = ctx->dev_status;
     P.trace = (unsigned long long *)ctx->trace_buf;
     P.has_prologue = 0;
+    P.fused = a.fused ? 1 : 0;
     P.n_stages = a.n_stages >= 2 && a.n_stages <= STAGES ? a.n_stages : 3;
     if (a.plan && a.n_ctas <= MAX_PROLOGUE_CTAS) {
         const Plan &pl = *a.plan;

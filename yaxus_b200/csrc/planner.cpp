@@ -214,11 +214,15 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
         int mt = padded_rows((int)u.rows.size() * pp.group);
         return mt == 16 ? 16u : (mt == 32 ? (uint64_t)std::max(pp.w32, 1) : (uint64_t)std::max(pp.w64, 1));
     };
+    // Every item also costs its CTA a fixed amount (queries staged, triples written, an
+    // arrival counted): charged per (unit, KV head) here, and again for each extra piece a
+    // unit is cut into, so that a CTA handed many short items gets fewer tiles.
+    const uint64_t item_cost = (uint64_t)std::max(pp.item_cost, 0);
     uint64_t total_tiles = 0, total_cost = 0;
     for (const Unit &u : units) {
         uint64_t t = (uint64_t)(u.hi / TILE_KEYS - u.lo / TILE_KEYS + 1) * pp.hkv;
         total_tiles += t;
-        total_cost += t * weight(u);
+        total_cost += t * weight(u) + item_cost * pp.hkv;
     }
     int n_ctas = (int)std::min<uint64_t>((uint64_t)std::max(1, pp.n_ctas), std::max<uint64_t>(total_tiles, 1));
     out.n_ctas = n_ctas;
@@ -247,8 +251,15 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
                     cta++;
                     out.cta_begin[cta] = (uint32_t)out.items.size();
                 }
-                uint64_t room = cta == n_ctas - 1 ? UINT64_MAX : (span_end(cta) - done + w / 2) / w;
+                uint64_t left = span_end(cta) > done + item_cost ? span_end(cta) - done - item_cost : 0;
+                uint64_t room = cta == n_ctas - 1 ? UINT64_MAX : (left + w / 2) / w;
                 uint32_t take = (uint32_t)std::min<uint64_t>(std::max<uint64_t>(room, 1), t1 - t);
+                // No crumbs: a piece of fewer than min_piece tiles is not worth an item of its
+                // own.  What little is left of the run joins this piece, and a piece that would
+                // start with little room in this CTA starts in the next one instead.
+                const uint32_t min_piece = (uint32_t)std::max(pp.min_piece, 1);
+                if (take < min_piece) take = std::min(min_piece, t1 - t);
+                if (t1 - t - take < min_piece) take = t1 - t;
                 Item it{};
                 it.tile_begin = t;
                 it.tile_end = t + take;
@@ -264,8 +275,10 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
                     out.merges[(size_t)u.rows[r] * pp.hkv + kh].count++;
                 }
                 out.items.push_back(it);
+                // The first piece of a (unit, head) was charged with the totals; a cut adds a piece.
+                done += take * w + item_cost;
+                if (t != t0) total_cost += item_cost;
                 t += take;
-                done += take * w;
             }
         }
     }

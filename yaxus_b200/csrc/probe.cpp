@@ -6,7 +6,7 @@
 extern "C" int yx_plan_probe(uint32_t rows, const uint32_t *pos, const uint32_t *pt_off, const uint32_t *pages,
                              uint32_t n_pages, int hkv, int group, int64_t window, uint64_t key_lo, uint64_t key_hi,
                              int max_rows, int n_ctas, int share_prefix, int esize, int cost32, int cost64,
-                             yx_plan_info *info, uint32_t *items_out, uint32_t max_items) {
+                             int item_cost, int min_piece, yx_plan_info *info, uint32_t *items_out, uint32_t max_items) {
     if (rows && (!pos || !pt_off)) return YX_ERR_INVALID;
     yx::PassHost pass;
     pass.rows = rows;
@@ -26,6 +26,8 @@ extern "C" int yx_plan_probe(uint32_t rows, const uint32_t *pos, const uint32_t 
     pp.w32 = cost32 > 0 ? cost32 : 16;
     pp.w64 = cost64 > 0 ? cost64 : 16;
     pp.resolve = true;
+    pp.min_piece = min_piece > 0 ? min_piece : 1;
+    pp.item_cost = item_cost > 0 ? item_cost : 0;
     pp.share_rows = share_prefix > 1 ? share_prefix : 0;   // values above 1 name the rows a shared item may hold
     yx::Plan plan;
     try {

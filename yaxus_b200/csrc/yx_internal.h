@@ -132,6 +132,8 @@ struct PlanParams {
     int w32, w64;            // cost of a tile of an item with 32 / 64 padded rows, in 16ths of a 16-row tile's
     bool resolve;            // also build the resolved form for the streaming kernel
     int share_rows;          // pass rows a shared item may hold (0 = one 16-row MMA tile's worth)
+    int item_cost;           // fixed cost of an item, in 16ths of a 16-row tile's
+    int min_piece;           // fewest tiles worth an item of their own
 };
 
 // Builds the split-key plan.  Throws std::string on a malformed pass.
@@ -207,7 +209,7 @@ struct yx_ctx {
         int64_t window = 0;
         uint64_t key_lo = 0, key_hi = 0;
         bool share = false, resolve = false;
-        int share_rows = 0;
+        int share_rows = 0, item_cost = 0;
         yx::Plan plan;
         char *dev = nullptr;       // items | cta_begin | merges | cta_hdr | tiles | recs
         size_t dev_cap = 0;
@@ -278,6 +280,7 @@ struct AttendArgs {
     bool single_use;
     const Plan *plan;        // host copy, for what is passed in kernel-parameter space
     int n_stages;            // copy ring depth (0 = default)
+    bool fused;              // merge inside the split-key kernel
     uint32_t *counters;      // one per (pass row, kv head), zero between launches
     void *out;               // normalised output, or null
     int out_dtype;
