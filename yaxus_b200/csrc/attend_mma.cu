@@ -2,7 +2,8 @@
 // verification and rows over shared prefixes.  Bandwidth-bound: the job of this kernel is to
 // keep every SM's share of HBM busy from the first microsecond to the last.
 //
-//  * Persistent: one CTA per SM walks the span of 64-key tiles the planner cut for it.
+//  * Persistent: one CTA per SM (eight warps: four consumers, a producer, a query stager, two
+//    epilogue warps) walks the span of 64-key tiles the planner cut for it.
 //  * Nothing on the device walks a page table.  The host planner resolves every tile to its
 //    (page, KV head) block; the producer warp reads 32 tile descriptors with one coalesced
 //    load and feeds the copy engine from them, across item boundaries, never draining.
@@ -20,10 +21,12 @@
 //    K or V byte is read once per item however many heads and rows use it.  Scores and
 //    softmax stay in f32 registers; max and sum reduce with quad shuffles.
 //  * Each item ends in an (m, l, o) triple per query row, the format of the reference's
-//    split attention (crates/yaxus-backend-gpu/src/shaders.rs:1466-1579).  The merge of the
-//    triples (the reference's `attn_combine`, shaders.rs:1581-1637) is fused: the CTA that
-//    delivers the last triple of a (row, KV head) merges them and writes the output, found
-//    by an arrival counter in global scratch that the merging CTA resets.
+//    split attention (crates/yaxus-backend-gpu/src/shaders.rs:1466-1579).  Two epilogue warps
+//    write the triples while the consumers are already in the next item.  The merge of the
+//    triples (the reference's `attn_combine`, shaders.rs:1581-1637) is the combine kernel's,
+//    or, when asked for, this kernel's own: the CTA that delivers the last triple of a
+//    (row, KV head) merges them and writes the output, found by an arrival counter in global
+//    scratch that the merging CTA resets.
 //
 // Every wait on an mbarrier is bounded: on expiry the CTA records the failure in the
 // context's status word, stops waiting anywhere, finishes structurally and returns.
@@ -105,8 +108,6 @@ struct Params {
     int has_prologue;
     CtaPrologue pro[MAX_PROLOGUE_CTAS];
 };
-
-__device__ __forceinline__ uint32_t field(uint32_t w, int idx) { return __shfl_sync(0xffffffffu, w, idx); }
 
 // ---- producer: tile descriptors -> bulk copies ----------------------------------------------
 // One tile: wait for a free stage, zero what a ragged copy leaves alone, start the four copies.
