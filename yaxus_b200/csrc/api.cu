@@ -116,7 +116,7 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
         if (cp.pass_serial == ctx->pass_serial && cp.hkv == pp.hkv && cp.group == pp.group &&
             cp.max_rows == pp.max_rows && cp.n_ctas == pp.n_ctas && cp.window == pp.window &&
             cp.key_lo == pp.key_lo && cp.key_hi == pp.key_hi && cp.share == pp.share_prefix && cp.esize == pp.esize &&
-            cp.w32 == pp.w32 && cp.w64 == pp.w64 && cp.resolve == pp.resolve && cp.share_rows == pp.share_rows && cp.item_cost == pp.item_cost) {
+            cp.w32 == pp.w32 && cp.w64 == pp.w64 && cp.resolve == pp.resolve && cp.share_rows == pp.share_rows && cp.item_cost == pp.item_cost && cp.tile_min_rows == pp.tile_min_rows) {
             *out = &cp;
             return YX_OK;
         }
@@ -161,6 +161,7 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
     slot->resolve = pp.resolve;
     slot->share_rows = pp.share_rows;
     slot->item_cost = pp.item_cost;
+    slot->tile_min_rows = pp.tile_min_rows;
 
     const Plan &pl = slot->plan;
     auto pad16 = [](size_t n) { return (n + 15) / 16 * 16; };
@@ -170,7 +171,8 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
     const size_t hdr_b = pad16(pl.cta_hdr.size() * sizeof(CtaHdr));
     const size_t til_b = pad16(pl.tiles.size() * sizeof(TileDesc));
     const size_t rec_b = pl.recs.size() * sizeof(ItemRec);
-    const size_t total = items_b + cta_b + mer_b + hdr_b + til_b + rec_b;
+    const size_t tit_b = pl.tile_items.size() * sizeof(TileItem);
+    const size_t total = items_b + cta_b + mer_b + hdr_b + til_b + rec_b + tit_b;
     if (int rc = ensure_buffer(ctx, (void **)&slot->dev, &slot->dev_cap, total)) {
         slot->pass_serial = 0;
         return rc;
@@ -189,6 +191,7 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
     const size_t o_hdr = put(pl.cta_hdr.data(), pl.cta_hdr.size() * sizeof(CtaHdr), hdr_b);
     const size_t o_til = put(pl.tiles.data(), pl.tiles.size() * sizeof(TileDesc), til_b);
     const size_t o_rec = put(pl.recs.data(), rec_b, rec_b);
+    const size_t o_tit = put(pl.tile_items.data(), tit_b, tit_b);
     if (int rc = upload_ordered(ctx, slot->dev, blob.data(), total)) {
         slot->pass_serial = 0;
         return rc;
@@ -199,6 +202,7 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
     slot->d_cta_hdr = (CtaHdr *)(slot->dev + o_hdr);
     slot->d_tiles = (TileDesc *)(slot->dev + o_til);
     slot->d_recs = (ItemRec *)(slot->dev + o_rec);
+    slot->d_tile_items = (TileItem *)(slot->dev + o_tit);
     *out = slot;
     return YX_OK;
 }
@@ -246,6 +250,11 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     pp.w64 = ctx->tuning.cost64 > 0 ? ctx->tuning.cost64 : 40;
     pp.resolve = path == 2;
     pp.share_rows = ctx->tuning.share_rows;
+    // Prompt-sized runs of rows on a 16-bit cache go to the tcgen05 kernel; it writes final
+    // outputs, so it is not used when triples are asked for.
+    pp.tile_min_rows = 0;
+    if (path == 2 && out && !o_out && ctx->tuning.force_path != 2)
+        pp.tile_min_rows = ctx->tuning.force_path == 3 ? 1 : (ctx->tuning.tile_min_rows > 0 ? ctx->tuning.tile_min_rows : 64);
     pp.min_piece = path == 2 ? 4 : 1;
     pp.item_cost = ctx->tuning.item_cost > 0 ? ctx->tuning.item_cost - 1 : (path == 2 ? 48 : 0);
     yx_ctx::CachedPlan *cp = nullptr;
@@ -304,6 +313,24 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     a.l_out = l_out;
     a.o_out = o_out;
     profile_mark(ctx, 0);
+    if (!pl.tile_items.empty()) {
+        TileArgs t{};
+        t.q = q;
+        t.q_dtype = q_dtype;
+        t.hq = hq;
+        t.group = group;
+        t.hkv = kv->hkv;
+        t.kv_dtype = kv->dtype;
+        t.k_arena = kv->k(layer);
+        t.v_arena = kv->v(layer);
+        t.kv_pages = kv->pages;
+        t.window = pp.window;
+        t.items = cp->d_tile_items;
+        t.n_items = (int)pl.tile_items.size();
+        t.out = out;
+        t.out_dtype = out_dtype;
+        if (int rc = launch_prefill_tc(ctx, t)) return rc;
+    }
     if (path == 2) {
         // Rows without a live key in the range get no item, so nothing would write them.
         if (a.fused && o_out && pl.has_empty_rows)
@@ -328,7 +355,7 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
         profile_mark(ctx, 3);
     }
     ctx->last_plan = pl.info;
-    ctx->last_plan.path = path;
+    ctx->last_plan.path = pl.tile_items.empty() ? path : (pl.items.empty() ? 3 : 5);
     ctx->last_plan.launches = (int)(ctx->launches - launches0);
     return YX_OK;
 }

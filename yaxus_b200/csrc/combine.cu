@@ -37,6 +37,7 @@ __global__ void combine_kernel(const Merge *__restrict__ merges, const float *__
     uint32_t row = idx / (uint32_t)hq;
     int h = (int)(idx % (uint32_t)hq), kvh = h / group, g = h % group;
     Merge mg = merges[(size_t)row * (hq / group) + kvh];
+    if (mg.count == 0 && !o_out) return;   // the row was another kernel's (tiled path)
     float mx = -1e30f, l = 0.0f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (uint32_t c0 = 0; c0 < mg.count; c0 += 32) {

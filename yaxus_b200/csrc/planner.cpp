@@ -70,12 +70,46 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
         }
     }
 
+    // 1b. Long runs of rows (prompt chunks) go to the tiled kernel: 128 consecutive rows of one
+    //     sequence and one query head per item, longest first.  Rows of one sequence have
+    //     consecutive positions (PassMeta's contract, crates/yaxus-model/src/lib.rs:63-65).
+    std::vector<bool> tiled(groups.size(), false);
+    if (pp.tile_min_rows > 0 && pp.key_lo == 0 && pp.key_hi == UINT64_MAX) {
+        for (uint32_t gi = 0; gi < groups.size(); gi++) {
+            const Group &g = groups[gi];
+            if (g.n < (uint32_t)pp.tile_min_rows) continue;
+            bool consecutive = true;
+            for (uint32_t r = 1; r < g.n && consecutive; r++) consecutive = pass.pos[g.row0 + r] == pass.pos[g.row0] + r;
+            if (!consecutive) continue;
+            tiled[gi] = true;
+            for (uint32_t a = 0; a < g.n; a += 128) {
+                const uint32_t n = std::min<uint32_t>(128, g.n - a), pos0 = pass.pos[g.row0 + a];
+                for (int h = 0; h < pp.hkv * pp.group; h++) {
+                    TileItem ti{};
+                    ti.row0 = g.row0 + a;
+                    ti.n_rows = n;
+                    ti.pos0 = pos0;
+                    ti.pt_off = g.pt_off;
+                    ti.head = (uint16_t)h;
+                    ti.kv_head = (uint16_t)(h / pp.group);
+                    ti.page_begin = row_lo(pos0, pp.window) / PAGE;
+                    ti.page_end = (pos0 + n - 1) / PAGE + 1;
+                    out.tile_items.push_back(ti);
+                }
+            }
+        }
+        std::stable_sort(out.tile_items.begin(), out.tile_items.end(), [](const TileItem &a, const TileItem &b) {
+            return a.page_end - a.page_begin > b.page_end - b.page_begin;
+        });
+    }
+
     // 2. Units.  First the per-sequence ones, rows chunked to max_rows.
     std::vector<Unit> units;
     struct Solo { size_t unit; uint32_t group; };
     std::vector<Solo> solos;   // units that hold all rows of one group (candidates for sharing)
     for (uint32_t gi = 0; gi < groups.size(); gi++) {
         const Group &g = groups[gi];
+        if (tiled[gi]) continue;
         for (uint32_t a = 0; a < g.n; a += pp.max_rows) {
             uint32_t b = std::min<uint32_t>(g.n, a + pp.max_rows);
             Unit u;

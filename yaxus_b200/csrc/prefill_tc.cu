@@ -1,0 +1,443 @@
+// Tiled causal attention for many-row passes (prompt chunks) over 16-bit paged KV caches, on
+// the fifth-generation tensor cores: tcgen05.mma with accumulators in tensor memory (TMEM),
+// operands staged in shared memory by bulk asynchronous copies (TMA).  The counterpart of the
+// reference's `attn_tile` (crates/yaxus-backend-gpu/src/shaders.rs:422-630), which is an f32
+// SIMT kernel over 32-row tiles.
+//
+// One CTA works on one item: up to 128 consecutive rows of one sequence (one M = 128 tile of
+// queries) for one query head, against that sequence's pages up to the last row's position.
+// Six warps:
+//   warps 0-3  softmax: thread t owns query row t and TMEM lane t.  It reads the scores of a
+//              128-key tile from TMEM, masks, keeps the running maximum and sum in f32,
+//              writes the probabilities back to TMEM as 16-bit pairs (over the scores), and
+//              rescales the output accumulator when the maximum has grown by more than 2^8
+//              since the last rescale ("lazy" rescaling: until then the probabilities are
+//              simply allowed to exceed 1).
+//   warp 4     producer: page ids fetched 32 at a time, one 32 KiB bulk copy per K page and per
+//              V page (the cache layout is the 128-byte-swizzled operand layout already).
+//   warp 5     MMA issuer: S_j = Q K_j^T (M128 N128 K128, both operands K-major from shared
+//              memory) into one of two TMEM score buffers, then O += P_{j-1} V_{j-1} (P from
+//              TMEM, V MN-major from shared memory).  S_j is issued before P_{j-1}V_{j-1}, so
+//              the softmax of tile j-1 overlaps the tensor work of tile j.
+// TMEM columns: [0,128) S0 / P0, [128,256) S1 / P1, [256,384) O.
+//
+// Every mbarrier wait is bounded; on expiry the CTA records where, stops waiting anywhere,
+// still frees its TMEM and returns.
+#include "yx_device.cuh"
+
+namespace yx {
+namespace {
+
+using namespace dev;
+
+constexpr int BM = 128;                  // query rows per item
+constexpr int BN = 128;                  // keys per tile = one page
+constexpr int K_STAGES = 3, V_STAGES = 2;
+constexpr int PAGE_BYTES = PAGE * D * 2; // one (page, kv head) block of K or of V: 32 KiB
+constexpr int HALF_BYTES = PAGE * 128;   // one 64-dim half
+constexpr int SOFTMAX_WARPS = 4, PRODUCER_WARP = 4, MMA_WARP = 5;
+constexpr int THREADS = 6 * 32;
+constexpr int TMEM_COLS = 512;
+constexpr int COL_S0 = 0, COL_S1 = 128, COL_O = 256;
+// barriers: q_full, k_full[3], k_empty[3], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done
+constexpr int N_BARS = 1 + 2 * K_STAGES + 2 * V_STAGES + 2 + 2 + 1;
+constexpr int SMEM_BYTES = PAGE_BYTES * (1 + K_STAGES + V_STAGES) + N_BARS * 8 + 64;
+
+struct TileParams {
+    const void *q;
+    int q_dtype, hq, group, hkv;
+    const char *k_arena, *v_arena;
+    uint32_t n_blocks;
+    uint32_t window;
+    const uint32_t *pages;
+    const TileItem *items;
+    void *out;
+    int out_dtype;
+    int bf16;            // cache type: 1 bf16, 0 f16
+    yx_dev_status *status;
+};
+
+// Shared-memory matrix descriptor: start address, leading / stride byte offsets (16-byte
+// units), descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3ffff) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor, kind::f16: f32 accumulator, 16-bit A and B of the cache's type.
+__device__ __forceinline__ uint32_t instr_desc(int bf16, int b_mn_major) {
+    const uint32_t fmt = bf16 ? 1u : 0u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(BN >> 3) << 17) |
+           ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+                 "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+                 "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t pack_pair(float x, float y, int bf16) {
+    if (bf16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(x, y);
+        return *(uint32_t *)&v;
+    }
+    __half2 v = __floats2half2_rn(x, y);
+    return *(uint32_t *)&v;
+}
+
+__global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const TileParams P) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t s_q = smem_u32(smem);
+    const uint32_t s_k = s_q + PAGE_BYTES;
+    const uint32_t s_v = s_k + K_STAGES * PAGE_BYTES;
+    const uint32_t bars = s_v + V_STAGES * PAGE_BYTES;
+    const uint32_t b_q_full = bars;
+    const uint32_t b_k_full = bars + 8, b_k_empty = b_k_full + 8 * K_STAGES;
+    const uint32_t b_v_full = b_k_empty + 8 * K_STAGES, b_v_empty = b_v_full + 8 * V_STAGES;
+    const uint32_t b_s_full = b_v_empty + 8 * V_STAGES, b_p_full = b_s_full + 16, b_pv_done = b_p_full + 16;
+    volatile int *abortp = &abort_flag;
+
+    const TileItem it = P.items[blockIdx.x];
+    const uint32_t n_tiles = it.page_end - it.page_begin;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(b_q_full, 1);
+        for (int s = 0; s < K_STAGES; s++) {
+            mbar_init(b_k_full + 8 * s, 1);
+            mbar_init(b_k_empty + 8 * s, 1);
+        }
+        for (int s = 0; s < V_STAGES; s++) {
+            mbar_init(b_v_full + 8 * s, 1);
+            mbar_init(b_v_empty + 8 * s, 1);
+        }
+        for (int s = 0; s < 2; s++) {
+            mbar_init(b_s_full + 8 * s, 1);
+            mbar_init(b_p_full + 8 * s, SOFTMAX_WARPS * 32);
+        }
+        mbar_init(b_pv_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // Stale rows of a ragged V page meet zero probabilities: they must hold finite numbers.
+    for (int i = threadIdx.x; i < V_STAGES * PAGE_BYTES / 16; i += THREADS)
+        ((uint4 *)(smem + (1 + K_STAGES) * PAGE_BYTES))[i] = make_uint4(0, 0, 0, 0);
+    if (warp == MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "n"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_base_s;
+    const float sl2 = 0.08838834764831845f * 1.4426950408889634f;   // log2(e) / sqrt(128)
+
+    if (warp == PRODUCER_WARP) {
+        // ---- producer ------------------------------------------------------------------------
+        const uint32_t kvh = it.kv_head;
+        const uint32_t last_key = it.pos0 + it.n_rows - 1;   // newest key any row sees
+        uint32_t kph = 0, vph = 0;
+        int ks = 0, vs = 0;
+        for (uint32_t c = 0; c < n_tiles; c += 32) {
+            const uint32_t mine = it.page_begin + c + lane;
+            const uint32_t my_page = mine < it.page_end ? P.pages[it.pt_off + mine] : 0u;
+            const uint32_t n = min(32u, n_tiles - c);
+            for (uint32_t j = 0; j < n; j++) {
+                const uint32_t page = __shfl_sync(0xffffffffu, my_page, j);
+                const uint32_t pg = it.page_begin + c + j;
+                const uint32_t rows = min((uint32_t)PAGE, last_key + 1 - pg * PAGE);
+                int stop = 0;
+                if (lane == 0) {
+                    const bool bad = page * (uint32_t)P.hkv + kvh >= P.n_blocks;
+                    if (bad && atomicCAS(&P.status->code, 0, 1) == 0) {
+                        P.status->where = 300;
+                        P.status->a = (int)page;
+                        P.status->b = (int)blockIdx.x;
+                    }
+                    const size_t off = ((size_t)page * P.hkv + kvh) * PAGE_BYTES;
+                    // K
+                    mbar_wait(b_k_empty + 8 * ks, kph ^ 1u, abortp, P.status, 31);
+                    if (!*abortp) {
+                        const uint32_t bar = b_k_full + 8 * ks, dst = s_k + ks * PAGE_BYTES;
+                        if (bad) {
+                            mbar_expect_tx(bar, 0);
+                        } else if (rows == PAGE) {
+                            mbar_expect_tx(bar, PAGE_BYTES);
+                            bulk_g2s(dst, P.k_arena + off, PAGE_BYTES, bar);
+                        } else {
+                            mbar_expect_tx(bar, 2 * rows * 128);
+                            bulk_g2s(dst, P.k_arena + off, rows * 128, bar);
+                            bulk_g2s(dst + HALF_BYTES, P.k_arena + off + HALF_BYTES, rows * 128, bar);
+                        }
+                    }
+                    // V
+                    mbar_wait(b_v_empty + 8 * vs, vph ^ 1u, abortp, P.status, 32);
+                    if (!*abortp) {
+                        const uint32_t bar = b_v_full + 8 * vs, dst = s_v + vs * PAGE_BYTES;
+                        if (bad) {
+                            mbar_expect_tx(bar, 0);
+                        } else if (rows == PAGE) {
+                            mbar_expect_tx(bar, PAGE_BYTES);
+                            bulk_g2s(dst, P.v_arena + off, PAGE_BYTES, bar);
+                        } else {
+                            mbar_expect_tx(bar, 2 * rows * 128);
+                            bulk_g2s(dst, P.v_arena + off, rows * 128, bar);
+                            bulk_g2s(dst + HALF_BYTES, P.v_arena + off + HALF_BYTES, rows * 128, bar);
+                        }
+                    }
+                    stop = *abortp;
+                }
+                if (__shfl_sync(0xffffffffu, stop, 0)) break;
+                if (++ks == K_STAGES) { ks = 0; kph ^= 1u; }
+                if (++vs == V_STAGES) { vs = 0; vph ^= 1u; }
+            }
+            if (*abortp) break;
+        }
+    } else if (warp == MMA_WARP) {
+        // ---- MMA issuer ----------------------------------------------------------------------
+        if (lane == 0) {
+            const uint32_t idesc_qk = instr_desc(P.bf16, 0), idesc_pv = instr_desc(P.bf16, 1);
+            mbar_wait(b_q_full, 0, abortp, P.status, 33);
+            tc_fence_after();
+            uint32_t kph = 0, vph = 0;
+            int ks = 0, vs = 0;
+            auto issue_pv = [&](uint32_t j) {   // O (+)= P_j V_j
+                const uint32_t b = j & 1u;
+                mbar_wait(b_p_full + 8 * b, (j >> 1) & 1u, abortp, P.status, 34);
+                mbar_wait(b_v_full + 8 * vs, vph, abortp, P.status, 35);
+                tc_fence_after();
+                const uint32_t v_base = s_v + vs * PAGE_BYTES;
+#pragma unroll
+                for (int k = 0; k < 8; k++)   // 16 keys per step: two 8-row groups of the MN-major V tile
+                    umma_ts(tmem + COL_O, tmem + (b ? COL_S1 : COL_S0) + k * 8, smem_desc(v_base + k * 16 * 128, HALF_BYTES, 1024),
+                            idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                umma_commit(b_v_empty + 8 * vs);
+                umma_commit(b_pv_done);
+                if (++vs == V_STAGES) { vs = 0; vph ^= 1u; }
+            };
+            for (uint32_t j = 0; j < n_tiles && !*abortp; j++) {
+                const uint32_t b = j & 1u;
+                mbar_wait(b_k_full + 8 * ks, kph, abortp, P.status, 36);
+                tc_fence_after();
+                const uint32_t k_base = s_k + ks * PAGE_BYTES;
+#pragma unroll
+                for (int k = 0; k < 8; k++) {   // 16 dims (32 bytes) per step; dims 64.. in the second half
+                    const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+                    umma_ss(tmem + (b ? COL_S1 : COL_S0), smem_desc(s_q + off, 16, 1024), smem_desc(k_base + off, 16, 1024),
+                            idesc_qk, k > 0 ? 1u : 0u);
+                }
+                umma_commit(b_k_empty + 8 * ks);
+                umma_commit(b_s_full + 8 * b);
+                if (++ks == K_STAGES) { ks = 0; kph ^= 1u; }
+                if (j > 0) issue_pv(j - 1);
+            }
+            if (n_tiles > 0 && !*abortp) issue_pv(n_tiles - 1);
+        }
+    } else {
+        // ---- softmax: thread t owns query row t -----------------------------------------------
+        const int r = threadIdx.x;
+        const bool valid = (uint32_t)r < it.n_rows;
+        const uint32_t pos = it.pos0 + (valid ? r : 0);
+        uint32_t klo = 0;
+        if (P.window > 0 && pos + 1 > P.window) klo = pos + 1 - P.window;
+        const uint32_t khi = pos;
+        const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+
+        // The query tile, converted to the cache's type, into the swizzled operand layout.
+        {
+            const size_t base = ((size_t)(it.row0 + (valid ? r : 0)) * P.hq + it.head) * D;
+#pragma unroll 4
+            for (int c = 0; c < 16; c++) {   // sixteen 16-byte chunks of the row
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+                if (valid) {
+                    a = load4_as_f32(P.q, P.q_dtype, base + c * 8);
+                    b = load4_as_f32(P.q, P.q_dtype, base + c * 8 + 4);
+                }
+                const uint32_t w0 = pack_pair(a.x, a.y, P.bf16), w1 = pack_pair(a.z, a.w, P.bf16),
+                               w2 = pack_pair(b.x, b.y, P.bf16), w3 = pack_pair(b.z, b.w, P.bf16);
+                const uint32_t addr = s_q + (c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_WARPS * 32) : "memory");
+            if (threadIdx.x == 0) mbar_arrive(b_q_full);
+        }
+
+        float m_used = -INFINITY, l = 0.f;
+        for (uint32_t j = 0; j < n_tiles; j++) {
+            const uint32_t b = j & 1u;
+            const uint32_t col_s = b ? COL_S1 : COL_S0;
+            mbar_wait(b_s_full + 8 * b, (j >> 1) & 1u, abortp, P.status, 37);
+            tc_fence_after();
+            uint32_t sr[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; c++) tmem_ld32(lane_addr + col_s + c * 32, sr[c]);
+            tmem_ld_wait();
+            const uint32_t key0 = (it.page_begin + j) * PAGE;
+            const bool need_mask = key0 < klo || key0 + PAGE - 1 > khi;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    float s = __uint_as_float(sr[c][i]);
+                    if (need_mask) {
+                        const uint32_t key = key0 + c * 32 + i;
+                        if (key < klo || key > khi) s = -INFINITY;
+                    }
+                    sr[c][i] = __float_as_uint(s);
+                    mx = fmaxf(mx, s);
+                }
+            // Lazy rescaling: keep the old reference maximum while the new one is within 2^8.
+            float alpha = 1.f;
+            bool rescale = false;
+            if (mx > m_used && (m_used == -INFINITY || (mx - m_used) * sl2 > 8.f)) {
+                alpha = m_used == -INFINITY ? 0.f : fast_exp2((m_used - mx) * sl2);
+                rescale = m_used != -INFINITY;   // nothing accumulated yet otherwise
+                m_used = mx;
+                l *= alpha;
+            }
+            const float ms = (m_used == -INFINITY ? 0.f : m_used) * sl2;
+            // Probabilities over the scores they came from: 128 keys as 64 packed columns.
+            float sum = 0.f;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                uint32_t pr[32];
+#pragma unroll
+                for (int c = 2 * h; c < 2 * h + 2; c++)
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = fast_exp2(__uint_as_float(sr[c][i]) * sl2 - ms);
+                        const float p1 = fast_exp2(__uint_as_float(sr[c][i + 1]) * sl2 - ms);
+                        sum += p0 + p1;
+                        pr[(c & 1) * 16 + (i >> 1)] = pack_pair(p0, p1, P.bf16);
+                    }
+                tmem_st32(lane_addr + col_s + h * 32, pr);
+            }
+            l += sum;
+            tmem_st_wait();
+            // The accumulator is quiet between P_{j-1}V_{j-1} and P_jV_j: rescale it here.
+            if (j > 0) {
+                mbar_wait(b_pv_done, (j - 1) & 1u, abortp, P.status, 38);
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+                    for (int c = 0; c < 4; c++) {
+                        uint32_t orow[32];
+                        tmem_ld32(lane_addr + COL_O + c * 32, orow);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+                        tmem_st32(lane_addr + COL_O + c * 32, orow);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(b_p_full + 8 * b);
+        }
+        // Output: O / l, in the tensor's type.
+        if (n_tiles > 0) {
+            mbar_wait(b_pv_done, (n_tiles - 1) & 1u, abortp, P.status, 39);
+            tc_fence_after();
+            const float inv = 1.0f / l;
+            const size_t obase = ((size_t)(it.row0 + (valid ? r : 0)) * P.hq + it.head) * D;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t orow[32];
+                tmem_ld32(lane_addr + COL_O + c * 32, orow);
+                tmem_ld_wait();
+                if (valid) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        store4(P.out, P.out_dtype, obase + c * 32 + i,
+                               make_float4(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv,
+                                           __uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv));
+                }
+            }
+        }
+    }
+    // Everyone is done with tensor memory before it is given back.
+    tc_fence_before();
+    __syncthreads();
+    if (warp == MMA_WARP) {
+        if (*abortp) {
+            // MMAs and copies issued before giving up may still be running.
+            for (int i = 0; i < 64; i++) __nanosleep(1000);
+        }
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace
+
+int launch_prefill_tc(yx_ctx *ctx, const TileArgs &a) {
+    if (!ctx->smem_configured[6]) {
+        if (int rc = check_cuda(ctx, cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES),
+                                "prefill_tc: shared memory attribute"))
+            return rc;
+        ctx->smem_configured[6] = true;
+    }
+    TileParams P{};
+    P.q = a.q;
+    P.q_dtype = a.q_dtype;
+    P.hq = a.hq;
+    P.group = a.group;
+    P.hkv = a.hkv;
+    P.k_arena = a.k_arena;
+    P.v_arena = a.v_arena;
+    P.n_blocks = a.kv_pages * (uint32_t)a.hkv;
+    P.window = (uint32_t)std::max<int64_t>(a.window, 0);
+    P.pages = ctx->d_pages;
+    P.items = a.items;
+    P.out = a.out;
+    P.out_dtype = a.out_dtype;
+    P.bf16 = a.kv_dtype == YX_BF16 ? 1 : 0;
+    P.status = ctx->dev_status;
+    prefill_tc_kernel<<<a.n_items, THREADS, SMEM_BYTES, ctx->stream>>>(P);
+    ctx->launches++;
+    return check_cuda(ctx, cudaGetLastError(), "prefill_tc kernel");
+}
+
+}  // namespace yx

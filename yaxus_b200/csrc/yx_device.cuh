@@ -39,7 +39,7 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 // abort flag and records where in the context's status word.  Nothing spins forever.  The
 // spinning part is out of line: it is cold code, and the attention kernels pay for every
 // instruction-cache line they touch.
-__device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+static __device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag,
                                             yx_dev_status *status, int where) {
     if (*abort_flag) return;
     long long t0 = clock64();

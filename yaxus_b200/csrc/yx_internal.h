@@ -100,6 +100,20 @@ constexpr int IR_ROW0 = 32;       // then six words per pass row:
 constexpr int IR_ROW_WORDS = 6;   //   first key seen, last key seen, partial slot, pass row, first slot, slots
 constexpr int IRR_KLO = 0, IRR_KHI = 1, IRR_PART = 2, IRR_ROW = 3, IRR_FIRST = 4, IRR_COUNT = 5;
 
+// One item of the tiled (tcgen05) kernel: up to 128 consecutive rows of one sequence for one
+// query head, against pages [page_begin, page_end) of the sequence's table.
+struct TileItem {
+    uint32_t row0;        // first pass row
+    uint32_t n_rows;      // 1..128; row r sits at position pos0 + r
+    uint32_t pos0;
+    uint32_t pt_off;
+    uint16_t head;        // query head
+    uint16_t kv_head;
+    uint32_t page_begin, page_end;
+    uint32_t pad_;
+};
+static_assert(sizeof(TileItem) == 32, "TileItem is 32 bytes");
+
 struct Plan {
     int path = 0;
     int n_ctas = 0;
@@ -108,6 +122,7 @@ struct Plan {
     std::vector<Merge> merges;          // [rows][hkv]
     uint32_t n_parts = 0;
     // resolved form (filled when PlanParams::resolve is set)
+    std::vector<TileItem> tile_items;   // rows handled by the tiled kernel (not in `items`)
     std::vector<CtaHdr> cta_hdr;
     std::vector<TileDesc> tiles;
     std::vector<ItemRec> recs;
@@ -131,6 +146,7 @@ struct PlanParams {
     int esize;               // bytes per stored element
     int w32, w64;            // cost of a tile of an item with 32 / 64 padded rows, in 16ths of a 16-row tile's
     bool resolve;            // also build the resolved form for the streaming kernel
+    int tile_min_rows;       // groups of at least this many rows go to the tiled kernel (0 = none)
     int share_rows;          // pass rows a shared item may hold (0 = one 16-row MMA tile's worth)
     int item_cost;           // fixed cost of an item, in 16ths of a 16-row tile's
     int min_piece;           // fewest tiles worth an item of their own
@@ -219,6 +235,8 @@ struct yx_ctx {
         yx::CtaHdr *d_cta_hdr = nullptr;
         yx::TileDesc *d_tiles = nullptr;
         yx::ItemRec *d_recs = nullptr;
+        yx::TileItem *d_tile_items = nullptr;
+        int tile_min_rows = 0;
     };
     std::vector<CachedPlan> plans;
 
@@ -286,6 +304,18 @@ struct AttendArgs {
     int out_dtype;
     float *m_out, *l_out, *o_out;   // merged triple, or null
 };
+struct TileArgs {
+    const void *q;
+    int q_dtype, hq, group, hkv, kv_dtype;
+    const char *k_arena, *v_arena;
+    uint32_t kv_pages;
+    int64_t window;
+    const TileItem *items;
+    int n_items;
+    void *out;
+    int out_dtype;
+};
+int launch_prefill_tc(yx_ctx *ctx, const TileArgs &a);
 int launch_attend_simt(yx_ctx *ctx, const AttendArgs &a);
 int launch_attend_mma(yx_ctx *ctx, const AttendArgs &a);
 // Writes the empty mark (-1e30, 0, 0) for n (row, head) triples.
