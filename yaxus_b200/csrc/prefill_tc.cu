@@ -41,7 +41,7 @@ constexpr int TMEM_COLS = 512;
 constexpr int COL_S0 = 0, COL_S1 = 128, COL_O = 256;
 // barriers: q_full, k_full[3], k_empty[3], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done
 constexpr int N_BARS = 1 + 2 * K_STAGES + 2 * V_STAGES + 2 + 2 + 1;
-constexpr int SMEM_BYTES = PAGE_BYTES * (1 + K_STAGES + V_STAGES) + N_BARS * 8 + 64;
+constexpr int SMEM_BYTES = PAGE_BYTES * (2 + K_STAGES + V_STAGES) + N_BARS * 8 + 64;   // Q high, Q low, K ring, V ring
 
 struct TileParams {
     const void *q;
@@ -54,6 +54,8 @@ struct TileParams {
     void *out;
     int out_dtype;
     int bf16;            // cache type: 1 bf16, 0 f16
+    int q_lo;            // queries carry a low part (f32 queries on a bf16 cache): S = Qh K^T + Ql K^T
+    int p_lo;            // probabilities carry a low part (bf16 cache): O += Ph V + Pl V
     yx_dev_status *status;
 };
 
@@ -123,13 +125,19 @@ __device__ __forceinline__ uint32_t pack_pair(float x, float y, int bf16) {
     return *(uint32_t *)&v;
 }
 
+__device__ __forceinline__ float2 unpack_pair(uint32_t u, int bf16) {
+    if (bf16) return __bfloat1622float2(*(__nv_bfloat162 *)&u);
+    return __half22float2(*(__half2 *)&u);
+}
+
 __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const TileParams P) {
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t s_q = smem_u32(smem);
-    const uint32_t s_k = s_q + PAGE_BYTES;
+    const uint32_t s_ql = s_q + PAGE_BYTES;
+    const uint32_t s_k = s_ql + PAGE_BYTES;
     const uint32_t s_v = s_k + K_STAGES * PAGE_BYTES;
     const uint32_t bars = s_v + V_STAGES * PAGE_BYTES;
     const uint32_t b_q_full = bars;
@@ -161,7 +169,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const TileParams
     }
     // Stale rows of a ragged V page meet zero probabilities: they must hold finite numbers.
     for (int i = threadIdx.x; i < V_STAGES * PAGE_BYTES / 16; i += THREADS)
-        ((uint4 *)(smem + (1 + K_STAGES) * PAGE_BYTES))[i] = make_uint4(0, 0, 0, 0);
+        ((uint4 *)(smem + (2 + K_STAGES) * PAGE_BYTES))[i] = make_uint4(0, 0, 0, 0);
     if (warp == MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "n"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -249,9 +257,11 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const TileParams
                 tc_fence_after();
                 const uint32_t v_base = s_v + vs * PAGE_BYTES;
 #pragma unroll
-                for (int k = 0; k < 8; k++)   // 16 keys per step: two 8-row groups of the MN-major V tile
-                    umma_ts(tmem + COL_O, tmem + (b ? COL_S1 : COL_S0) + k * 8, smem_desc(v_base + k * 16 * 128, HALF_BYTES, 1024),
-                            idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < 8; k++) {   // 16 keys per step: two 8-row groups of the MN-major V tile
+                    const uint64_t vdesc = smem_desc(v_base + k * 16 * 128, HALF_BYTES, 1024);
+                    umma_ts(tmem + COL_O, tmem + (b ? COL_S1 : COL_S0) + k * 8, vdesc, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                    if (P.p_lo) umma_ts(tmem + COL_O, tmem + (b ? COL_S1 : COL_S0) + 64 + k * 8, vdesc, idesc_pv, 1u);
+                }
                 umma_commit(b_v_empty + 8 * vs);
                 umma_commit(b_pv_done);
                 if (++vs == V_STAGES) { vs = 0; vph ^= 1u; }
@@ -264,8 +274,9 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const TileParams
 #pragma unroll
                 for (int k = 0; k < 8; k++) {   // 16 dims (32 bytes) per step; dims 64.. in the second half
                     const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-                    umma_ss(tmem + (b ? COL_S1 : COL_S0), smem_desc(s_q + off, 16, 1024), smem_desc(k_base + off, 16, 1024),
-                            idesc_qk, k > 0 ? 1u : 0u);
+                    const uint64_t kdesc = smem_desc(k_base + off, 16, 1024);
+                    umma_ss(tmem + (b ? COL_S1 : COL_S0), smem_desc(s_q + off, 16, 1024), kdesc, idesc_qk, k > 0 ? 1u : 0u);
+                    if (P.q_lo) umma_ss(tmem + (b ? COL_S1 : COL_S0), smem_desc(s_ql + off, 16, 1024), kdesc, idesc_qk, 1u);
                 }
                 umma_commit(b_k_empty + 8 * ks);
                 umma_commit(b_s_full + 8 * b);
@@ -298,6 +309,13 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const TileParams
                                w2 = pack_pair(b.x, b.y, P.bf16), w3 = pack_pair(b.z, b.w, P.bf16);
                 const uint32_t addr = s_q + (c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4);
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+                if (P.q_lo) {   // what the 16-bit rounding dropped
+                    const float2 h0 = unpack_pair(w0, P.bf16), h1 = unpack_pair(w1, P.bf16), h2 = unpack_pair(w2, P.bf16),
+                                 h3 = unpack_pair(w3, P.bf16);
+                    const uint32_t l0 = pack_pair(a.x - h0.x, a.y - h0.y, P.bf16), l1 = pack_pair(a.z - h1.x, a.w - h1.y, P.bf16),
+                                   l2 = pack_pair(b.x - h2.x, b.y - h2.y, P.bf16), l3 = pack_pair(b.z - h3.x, b.w - h3.y, P.bf16);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr + PAGE_BYTES), "r"(l0), "r"(l1), "r"(l2), "r"(l3) : "memory");
+                }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_WARPS * 32) : "memory");
@@ -339,11 +357,12 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const TileParams
                 l *= alpha;
             }
             const float ms = (m_used == -INFINITY ? 0.f : m_used) * sl2;
-            // Probabilities over the scores they came from: 128 keys as 64 packed columns.
+            // Probabilities over the scores they came from: 128 keys as 64 packed columns, and
+            // (bf16 caches) what the 8-bit mantissa dropped as 64 more.
             float sum = 0.f;
 #pragma unroll
             for (int h = 0; h < 2; h++) {
-                uint32_t pr[32];
+                uint32_t pr[32], pl[32];
 #pragma unroll
                 for (int c = 2 * h; c < 2 * h + 2; c++)
 #pragma unroll
@@ -351,9 +370,15 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const TileParams
                         const float p0 = fast_exp2(__uint_as_float(sr[c][i]) * sl2 - ms);
                         const float p1 = fast_exp2(__uint_as_float(sr[c][i + 1]) * sl2 - ms);
                         sum += p0 + p1;
-                        pr[(c & 1) * 16 + (i >> 1)] = pack_pair(p0, p1, P.bf16);
+                        const uint32_t w = pack_pair(p0, p1, P.bf16);
+                        pr[(c & 1) * 16 + (i >> 1)] = w;
+                        if (P.p_lo) {
+                            const float2 hf = unpack_pair(w, P.bf16);
+                            pl[(c & 1) * 16 + (i >> 1)] = pack_pair(p0 - hf.x, p1 - hf.y, P.bf16);
+                        }
                     }
                 tmem_st32(lane_addr + col_s + h * 32, pr);
+                if (P.p_lo) tmem_st32(lane_addr + col_s + 64 + h * 32, pl);
             }
             l += sum;
             tmem_st_wait();
@@ -434,6 +459,8 @@ int launch_prefill_tc(yx_ctx *ctx, const TileArgs &a) {
     P.out = a.out;
     P.out_dtype = a.out_dtype;
     P.bf16 = a.kv_dtype == YX_BF16 ? 1 : 0;
+    P.p_lo = P.bf16;
+    P.q_lo = P.bf16 && a.q_dtype == YX_F32;
     P.status = ctx->dev_status;
     prefill_tc_kernel<<<a.n_items, THREADS, SMEM_BYTES, ctx->stream>>>(P);
     ctx->launches++;

@@ -197,6 +197,33 @@ def prefill_chunk(seed: int = SEED0 + 3, n_seq: int = 8, done: int = 0, chunk: i
     return s
 
 
+def prefill_passes(seed: int = SEED0 + 3, n_seq: int = 8, total: int = 4096, chunk: int = 512, kv_dtype: int = BF16,
+                   hq: int = 32, hkv: int = 8, chunks: Optional[range] = None) -> List[Scenario]:
+    """Chunked prefill of `n_seq` sequences of `total` tokens: one Scenario per chunk index, all
+    over the same page tables; chunk c holds rows [c*chunk, (c+1)*chunk) of every sequence.
+    Each scenario carries the chunk's q and the k, v rows it appends; its cached context is
+    left empty (the passes are meant to be run in order on one cache)."""
+    rng = np.random.default_rng(seed)
+    pages_per_seq = (total + PAGE - 1) // PAGE
+    arena_pages = n_seq * pages_per_seq + 3
+    perm = rng.permutation(arena_pages).astype(np.uint32)
+    tables = [perm[s * pages_per_seq:(s + 1) * pages_per_seq].copy() for s in range(n_seq)]
+    kvd = hkv * D
+    out = []
+    empty = np.zeros((0, kvd), np.float32 if kv_dtype == F32 else np.uint16)
+    for c in (chunks if chunks is not None else range(total // chunk)):
+        rows = [(s, c * chunk + j) for s in range(n_seq) for j in range(chunk)]
+        meta = PassMeta.from_rows(rows, tables)
+        T = len(rows)
+        crng = np.random.default_rng(seed * 1000 + c)
+        q = round_through(_normal(crng, (T, hq * D)), kv_dtype)
+        k_new = _normal(crng, (T, kvd))
+        v_new = _normal(crng, (T, kvd))
+        out.append(Scenario(f"prefill_chunk_{c}", hq, hkv, kv_dtype, None, arena_pages, tables, [c * chunk] * n_seq,
+                            [chunk] * n_seq, meta, q, k_new, v_new, empty, empty, seed))
+    return out
+
+
 def long_decode(seed: int = SEED0 + 4, ctx: int = 131072, window: Optional[int] = None, kv_dtype: int = F16,
                 hq: int = 32, hkv: int = 8, fill: bool = True) -> Scenario:
     """One sequence, one query token, `ctx` keys including its own."""
