@@ -75,6 +75,7 @@ typedef struct yx_tuning {
     int32_t share_rows;      /* pass rows a shared-prefix item may hold (0: 16 / group, one MMA tile) */
     int32_t item_cost;       /* planner cost of starting an item, in 16ths of a tile, plus one (0: default) */
     int32_t fused_merge;     /* 1: the split-key kernel merges the triples itself; 0: a combine kernel does */
+    int32_t tile_single;     /* 1: the tcgen05 tile kernel takes one query head per CTA (default: two) */
 } yx_tuning;
 
 /* What the last yx_attend / yx_attention call planned; for tests and benchmarks. */

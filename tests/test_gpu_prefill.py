@@ -41,6 +41,24 @@ def test_ragged_tiles_and_windows(backend, oracle, rows, window):
     kv.close()
 
 
+def test_one_head_per_cta_variant(backend, oracle):
+    # The tile kernel normally takes two query heads of a KV head per CTA; one head per CTA is
+    # used for odd groups and for f32 queries on bf16 caches (they carry a low part).
+    s = W.prefill_chunk(seed=9, n_seq=2, done=300, chunk=200, kv_dtype=BF16, hq=6, hkv=2, total=1024)   # group 3
+    kv = load(backend, s)
+    got = run_step(backend, kv, s, q_dtype=torch.bfloat16)
+    assert backend.last_plan().path == 3
+    assert_close(got, oracle_step(oracle, s, q=q_rounded(s)), what="odd group")
+    kv.close()
+    s = W.prefill_chunk(seed=10, n_seq=1, done=128, chunk=256, kv_dtype=F16, hq=8, hkv=2, total=512)
+    kv = load(backend, s)
+    backend.set_tuning(tile_single=1)
+    got = run_step(backend, kv, s, q_dtype=torch.float16)
+    backend.set_tuning()
+    assert_close(got, oracle_step(oracle, s, q=q_rounded(s)), what="forced single")
+    kv.close()
+
+
 def test_forced_tile_path_on_short_rows(backend, oracle):
     s = W.build("short", 5, 8, 2, F16, [130, 0], [7, 1])
     kv = load(backend, s)

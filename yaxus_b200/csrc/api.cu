@@ -116,7 +116,7 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
         if (cp.pass_serial == ctx->pass_serial && cp.hkv == pp.hkv && cp.group == pp.group &&
             cp.max_rows == pp.max_rows && cp.n_ctas == pp.n_ctas && cp.window == pp.window &&
             cp.key_lo == pp.key_lo && cp.key_hi == pp.key_hi && cp.share == pp.share_prefix && cp.esize == pp.esize &&
-            cp.w32 == pp.w32 && cp.w64 == pp.w64 && cp.resolve == pp.resolve && cp.share_rows == pp.share_rows && cp.item_cost == pp.item_cost && cp.tile_min_rows == pp.tile_min_rows) {
+            cp.w32 == pp.w32 && cp.w64 == pp.w64 && cp.resolve == pp.resolve && cp.share_rows == pp.share_rows && cp.item_cost == pp.item_cost && cp.tile_min_rows == pp.tile_min_rows && cp.tile_pairs == pp.tile_pairs) {
             *out = &cp;
             return YX_OK;
         }
@@ -162,6 +162,7 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
     slot->share_rows = pp.share_rows;
     slot->item_cost = pp.item_cost;
     slot->tile_min_rows = pp.tile_min_rows;
+    slot->tile_pairs = pp.tile_pairs;
 
     const Plan &pl = slot->plan;
     auto pad16 = [](size_t n) { return (n + 15) / 16 * 16; };
@@ -255,6 +256,8 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     pp.tile_min_rows = 0;
     if (path == 2 && out && !o_out && ctx->tuning.force_path != 2)
         pp.tile_min_rows = ctx->tuning.force_path == 3 ? 1 : (ctx->tuning.tile_min_rows > 0 ? ctx->tuning.tile_min_rows : 64);
+    // Two heads per item unless the group is odd or f32 queries need their low part (bf16 caches).
+    pp.tile_pairs = group % 2 == 0 && !(kv->dtype == YX_BF16 && q_dtype == YX_F32) && ctx->tuning.tile_single != 1;
     pp.min_piece = path == 2 ? 4 : 1;
     pp.item_cost = ctx->tuning.item_cost > 0 ? ctx->tuning.item_cost - 1 : (path == 2 ? 48 : 0);
     yx_ctx::CachedPlan *cp = nullptr;
@@ -329,6 +332,7 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
         t.n_items = (int)pl.tile_items.size();
         t.out = out;
         t.out_dtype = out_dtype;
+        t.pairs = pp.tile_pairs;
         if (int rc = launch_prefill_tc(ctx, t)) return rc;
     }
     if (path == 2) {

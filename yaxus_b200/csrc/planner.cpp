@@ -84,7 +84,7 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
             tiled[gi] = true;
             for (uint32_t a = 0; a < g.n; a += 128) {
                 const uint32_t n = std::min<uint32_t>(128, g.n - a), pos0 = pass.pos[g.row0 + a];
-                for (int h = 0; h < pp.hkv * pp.group; h++) {
+                for (int h = 0; h < pp.hkv * pp.group; h += pp.tile_pairs ? 2 : 1) {
                     TileItem ti{};
                     ti.row0 = g.row0 + a;
                     ti.n_rows = n;

@@ -435,6 +435,361 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const TileParams
     }
 }
 
+
+// =============================================================================================
+// Two query tiles per CTA: the same 128 rows for two query heads of one KV head.  Each K and V
+// page is staged once for 256 query rows, two softmax warpgroups work while the tensor core
+// alternates between the tiles, and TMEM is used in full: S/P of tile A [0,128), of tile B
+// [128,256), O of A [256,384), O of B [384,512).  Issue order, per page j:
+//   S_A(j) S_B(j) | P_A(j)V_j  S_A(j+1) | P_B(j)V_j  S_B(j+1) | ...
+// so that a warpgroup's next scores are on their way while the other's probabilities are used.
+// Ten warps: 0-3 softmax of A, 4-7 softmax of B, 8 producer, 9 MMA issuer.
+// =============================================================================================
+constexpr int T2_K_STAGES = 2, T2_V_STAGES = 2;
+constexpr int T2_PRODUCER = 8, T2_MMA = 9;
+constexpr int T2_THREADS = 10 * 32;
+// barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done[2]
+constexpr int T2_BARS = 1 + 2 * T2_K_STAGES + 2 * T2_V_STAGES + 6;
+constexpr int T2_SMEM_BYTES = PAGE_BYTES * (2 + T2_K_STAGES + T2_V_STAGES) + T2_BARS * 8 + 64;
+
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// One 128-key tile of one query row: scores in TMEM at `s_addr` (128 f32 columns, this
+// thread's lane) become probabilities (64 packed columns; a low part in 64 more for bf16
+// caches).  Two passes over the scores, 32 columns at a time, so that little is held in
+// registers and the code stays small: the maximum first, then the exponentials.
+// Returns the factor the accumulated output has to be multiplied by (1 when the reference
+// maximum was kept: lazy rescaling, see the kernel's header).
+__device__ __forceinline__ float softmax_tile(uint32_t s_addr, uint32_t key0, uint32_t klo, uint32_t khi, int bf16,
+                                              int p_lo, float sl2, float &m_used, float &l, bool &rescale) {
+    const bool need_mask = key0 < klo || key0 + PAGE - 1 > khi;
+    float mx = -INFINITY;
+#pragma unroll 1
+    for (int c = 0; c < 4; c++) {
+        uint32_t sr[32];
+        tmem_ld32(s_addr + c * 32, sr);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+                const uint32_t key = key0 + c * 32 + i;
+                if (key >= klo && key <= khi) mx = fmaxf(mx, __uint_as_float(sr[i]));
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) mx = max3(mx, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+        }
+    }
+    float alpha = 1.f;
+    rescale = false;
+    if (mx > m_used && (m_used == -INFINITY || (mx - m_used) * sl2 > 8.f)) {
+        alpha = m_used == -INFINITY ? 0.f : fast_exp2((m_used - mx) * sl2);
+        rescale = m_used != -INFINITY;   // nothing accumulated yet otherwise
+        m_used = mx;
+        l *= alpha;
+    }
+    const float ms = (m_used == -INFINITY ? 0.f : m_used) * sl2;
+    float sum0 = 0.f, sum1 = 0.f;
+    uint32_t lo[64];
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        uint32_t sr[32], hi[16];
+        tmem_ld32(s_addr + c * 32, sr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            float s0 = __uint_as_float(sr[i]), s1 = __uint_as_float(sr[i + 1]);
+            if (need_mask) {
+                const uint32_t key = key0 + c * 32 + i;
+                if (key < klo || key > khi) s0 = -INFINITY;
+                if (key + 1 < klo || key + 1 > khi) s1 = -INFINITY;
+            }
+            const float p0 = fast_exp2(s0 * sl2 - ms), p1 = fast_exp2(s1 * sl2 - ms);
+            sum0 += p0;
+            sum1 += p1;
+            const uint32_t w = pack_pair(p0, p1, bf16);
+            hi[i >> 1] = w;
+            if (p_lo) {
+                // what the 8-bit mantissa dropped: p - float(hi), the halves widened in place
+                const float h0 = __uint_as_float(w << 16), h1 = __uint_as_float(w & 0xffff0000u);
+                lo[c * 16 + (i >> 1)] = pack_pair(p0 - h0, p1 - h1, 1);
+            }
+        }
+        // Columns [16c, 16c+16) of the probabilities sit over scores already read.
+        tmem_st16(s_addr + c * 16, hi);
+    }
+    if (p_lo) {
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            uint32_t part[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) part[i] = lo[c * 16 + i];
+            tmem_st16(s_addr + 64 + c * 16, part);
+        }
+    }
+    l += sum0 + sum1;
+    tmem_st_wait();
+    return alpha;
+}
+
+__global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TileParams P) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t s_qa = smem_u32(smem), s_qb = s_qa + PAGE_BYTES;
+    const uint32_t s_k = s_qb + PAGE_BYTES;
+    const uint32_t s_v = s_k + T2_K_STAGES * PAGE_BYTES;
+    const uint32_t bars = s_v + T2_V_STAGES * PAGE_BYTES;
+    const uint32_t b_q_full = bars;
+    const uint32_t b_k_full = bars + 8, b_k_empty = b_k_full + 8 * T2_K_STAGES;
+    const uint32_t b_v_full = b_k_empty + 8 * T2_K_STAGES, b_v_empty = b_v_full + 8 * T2_V_STAGES;
+    const uint32_t b_s_full = b_v_empty + 8 * T2_V_STAGES, b_p_full = b_s_full + 16, b_pv_done = b_p_full + 16;
+    volatile int *abortp = &abort_flag;
+
+    const TileItem it = P.items[blockIdx.x];   // it.head is the first of the two heads
+    const uint32_t n_tiles = it.page_end - it.page_begin;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(b_q_full, 2);
+        for (int s = 0; s < T2_K_STAGES; s++) {
+            mbar_init(b_k_full + 8 * s, 1);
+            mbar_init(b_k_empty + 8 * s, 1);
+        }
+        for (int s = 0; s < T2_V_STAGES; s++) {
+            mbar_init(b_v_full + 8 * s, 1);
+            mbar_init(b_v_empty + 8 * s, 1);
+        }
+        for (int t = 0; t < 2; t++) {
+            mbar_init(b_s_full + 8 * t, 1);
+            mbar_init(b_p_full + 8 * t, 128);
+            mbar_init(b_pv_done + 8 * t, 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // Stale rows of a ragged V page meet zero probabilities: they must hold finite numbers.
+    for (int i = threadIdx.x; i < T2_V_STAGES * PAGE_BYTES / 16; i += T2_THREADS)
+        ((uint4 *)(smem + (2 + T2_K_STAGES) * PAGE_BYTES))[i] = make_uint4(0, 0, 0, 0);
+    if (warp == T2_MMA) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "n"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_base_s;
+    const float sl2 = 0.08838834764831845f * 1.4426950408889634f;
+
+    if (warp == T2_PRODUCER) {
+        // ---- producer: one K page and one V page per tile, for both query tiles ---------------
+        const uint32_t kvh = it.kv_head;
+        const uint32_t last_key = it.pos0 + it.n_rows - 1;
+        uint32_t kph = 0, vph = 0;
+        int ks = 0, vs = 0;
+        for (uint32_t c = 0; c < n_tiles; c += 32) {
+            const uint32_t mine = it.page_begin + c + lane;
+            const uint32_t my_page = mine < it.page_end ? P.pages[it.pt_off + mine] : 0u;
+            const uint32_t n = min(32u, n_tiles - c);
+            for (uint32_t j = 0; j < n; j++) {
+                const uint32_t page = __shfl_sync(0xffffffffu, my_page, j);
+                const uint32_t pg = it.page_begin + c + j;
+                const uint32_t rows = min((uint32_t)PAGE, last_key + 1 - pg * PAGE);
+                int stop = 0;
+                if (lane == 0) {
+                    const bool bad = page * (uint32_t)P.hkv + kvh >= P.n_blocks;
+                    if (bad && atomicCAS(&P.status->code, 0, 1) == 0) {
+                        P.status->where = 310;
+                        P.status->a = (int)page;
+                        P.status->b = (int)blockIdx.x;
+                    }
+                    const size_t off = ((size_t)page * P.hkv + kvh) * PAGE_BYTES;
+                    for (int kv = 0; kv < 2; kv++) {
+                        const uint32_t empty = kv ? b_v_empty + 8 * vs : b_k_empty + 8 * ks;
+                        const uint32_t bar = kv ? b_v_full + 8 * vs : b_k_full + 8 * ks;
+                        const uint32_t dst = kv ? s_v + vs * PAGE_BYTES : s_k + ks * PAGE_BYTES;
+                        const char *src = (kv ? P.v_arena : P.k_arena) + off;
+                        mbar_wait(empty, (kv ? vph : kph) ^ 1u, abortp, P.status, 41 + kv);
+                        if (*abortp) break;
+                        if (bad) {
+                            mbar_expect_tx(bar, 0);
+                        } else if (rows == PAGE) {
+                            mbar_expect_tx(bar, PAGE_BYTES);
+                            bulk_g2s(dst, src, PAGE_BYTES, bar);
+                        } else {
+                            mbar_expect_tx(bar, 2 * rows * 128);
+                            bulk_g2s(dst, src, rows * 128, bar);
+                            bulk_g2s(dst + HALF_BYTES, src + HALF_BYTES, rows * 128, bar);
+                        }
+                    }
+                    stop = *abortp;
+                }
+                if (__shfl_sync(0xffffffffu, stop, 0)) break;
+                if (++ks == T2_K_STAGES) { ks = 0; kph ^= 1u; }
+                if (++vs == T2_V_STAGES) { vs = 0; vph ^= 1u; }
+            }
+            if (*abortp) break;
+        }
+    } else if (warp == T2_MMA) {
+        // ---- MMA issuer ----------------------------------------------------------------------
+        if (lane == 0 && n_tiles > 0) {
+            const uint32_t idesc_qk = instr_desc(P.bf16, 0), idesc_pv = instr_desc(P.bf16, 1);
+            mbar_wait(b_q_full, 0, abortp, P.status, 43);
+            tc_fence_after();
+            uint32_t kph = 0, vph = 0;
+            int ks = 0, vs = 0;
+            auto issue_s = [&](int t, uint32_t k_base) {   // S_t = Q_t K^T
+                const uint32_t q_base = t ? s_qb : s_qa;
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+                    umma_ss(tmem + t * 128, smem_desc(q_base + off, 16, 1024), smem_desc(k_base + off, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
+                }
+                umma_commit(b_s_full + 8 * t);
+            };
+            auto issue_pv = [&](int t, uint32_t j, uint32_t v_base) {   // O_t (+)= P_t V
+                mbar_wait(b_p_full + 8 * t, j & 1u, abortp, P.status, 44 + t);
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    const uint64_t vdesc = smem_desc(v_base + k * 16 * 128, HALF_BYTES, 1024);
+                    umma_ts(tmem + 256 + t * 128, tmem + t * 128 + k * 8, vdesc, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                    if (P.p_lo) umma_ts(tmem + 256 + t * 128, tmem + t * 128 + 64 + k * 8, vdesc, idesc_pv, 1u);
+                }
+                umma_commit(b_pv_done + 8 * t);
+            };
+            // S_A(0), S_B(0)
+            mbar_wait(b_k_full, 0, abortp, P.status, 46);
+            tc_fence_after();
+            issue_s(0, s_k);
+            issue_s(1, s_k);
+            umma_commit(b_k_empty);
+            ks = 1 % T2_K_STAGES;
+            if (ks == 0) kph ^= 1u;
+            for (uint32_t j = 0; j < n_tiles && !*abortp; j++) {
+                const uint32_t v_base = s_v + vs * PAGE_BYTES;
+                const bool more = j + 1 < n_tiles;
+                const uint32_t k_next = s_k + ks * PAGE_BYTES;
+                mbar_wait(b_v_full + 8 * vs, vph, abortp, P.status, 47);
+                issue_pv(0, j, v_base);
+                if (more) {
+                    mbar_wait(b_k_full + 8 * ks, kph, abortp, P.status, 48);
+                    tc_fence_after();
+                    issue_s(0, k_next);
+                }
+                issue_pv(1, j, v_base);
+                umma_commit(b_v_empty + 8 * vs);
+                if (more) {
+                    issue_s(1, k_next);
+                    umma_commit(b_k_empty + 8 * ks);
+                    if (++ks == T2_K_STAGES) { ks = 0; kph ^= 1u; }
+                }
+                if (++vs == T2_V_STAGES) { vs = 0; vph ^= 1u; }
+            }
+        }
+    } else {
+        // ---- softmax warpgroups: warps 0-3 tile A (head), warps 4-7 tile B (head + 1) -----------
+        const int t = warp >> 2;
+        const int r = threadIdx.x & 127;
+        const bool valid = (uint32_t)r < it.n_rows;
+        const uint32_t head = it.head + t;
+        const uint32_t pos = it.pos0 + (valid ? r : 0);
+        uint32_t klo = 0;
+        if (P.window > 0 && pos + 1 > P.window) klo = pos + 1 - P.window;
+        const uint32_t khi = pos;
+        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t s_addr = lane_addr + t * 128, o_addr = lane_addr + 256 + t * 128;
+        {
+            const uint32_t s_q = t ? s_qb : s_qa;
+            const size_t base = ((size_t)(it.row0 + (valid ? r : 0)) * P.hq + head) * D;
+#pragma unroll 4
+            for (int c = 0; c < 16; c++) {
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+                if (valid) {
+                    a = load4_as_f32(P.q, P.q_dtype, base + c * 8);
+                    b = load4_as_f32(P.q, P.q_dtype, base + c * 8 + 4);
+                }
+                const uint32_t w0 = pack_pair(a.x, a.y, P.bf16), w1 = pack_pair(a.z, a.w, P.bf16),
+                               w2 = pack_pair(b.x, b.y, P.bf16), w3 = pack_pair(b.z, b.w, P.bf16);
+                const uint32_t addr = s_q + (c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // one named barrier per warpgroup
+            if (t == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+            else asm volatile("bar.sync 2, 128;" ::: "memory");
+            if (r == 0) mbar_arrive(b_q_full);
+        }
+        float m_used = -INFINITY, l = 0.f;
+        for (uint32_t j = 0; j < n_tiles; j++) {
+            mbar_wait(b_s_full + 8 * t, j & 1u, abortp, P.status, 49 + t);
+            tc_fence_after();
+            bool rescale;
+            const float alpha = softmax_tile(s_addr, (it.page_begin + j) * PAGE, klo, khi, P.bf16, P.p_lo, sl2, m_used, l, rescale);
+            if (j > 0) {
+                // The accumulator is quiet between P(j-1)V and P(j)V: rescale it here if the
+                // reference maximum moved.
+                mbar_wait(b_pv_done + 8 * t, (j - 1) & 1u, abortp, P.status, 51 + t);
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+                    for (int c = 0; c < 4; c++) {
+                        uint32_t orow[32];
+                        tmem_ld32(o_addr + c * 32, orow);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+                        tmem_st32(o_addr + c * 32, orow);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(b_p_full + 8 * t);
+        }
+        if (n_tiles > 0) {
+            mbar_wait(b_pv_done + 8 * t, (n_tiles - 1) & 1u, abortp, P.status, 53 + t);
+            tc_fence_after();
+            const float inv = 1.0f / l;
+            const size_t obase = ((size_t)(it.row0 + (valid ? r : 0)) * P.hq + head) * D;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t orow[32];
+                tmem_ld32(o_addr + c * 32, orow);
+                tmem_ld_wait();
+                if (valid) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        store4(P.out, P.out_dtype, obase + c * 32 + i,
+                               make_float4(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv,
+                                           __uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv));
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == T2_MMA) {
+        if (*abortp) {
+            for (int i = 0; i < 64; i++) __nanosleep(1000);
+        }
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(TMEM_COLS) : "memory");
+    }
+}
+
 }  // namespace
 
 int launch_prefill_tc(yx_ctx *ctx, const TileArgs &a) {

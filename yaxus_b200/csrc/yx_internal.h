@@ -147,6 +147,7 @@ struct PlanParams {
     int w32, w64;            // cost of a tile of an item with 32 / 64 padded rows, in 16ths of a 16-row tile's
     bool resolve;            // also build the resolved form for the streaming kernel
     int tile_min_rows;       // groups of at least this many rows go to the tiled kernel (0 = none)
+    bool tile_pairs;         // tile items take two query heads of a KV head each (needs an even group)
     int share_rows;          // pass rows a shared item may hold (0 = one 16-row MMA tile's worth)
     int item_cost;           // fixed cost of an item, in 16ths of a 16-row tile's
     int min_piece;           // fewest tiles worth an item of their own
@@ -237,6 +238,7 @@ struct yx_ctx {
         yx::ItemRec *d_recs = nullptr;
         yx::TileItem *d_tile_items = nullptr;
         int tile_min_rows = 0;
+        bool tile_pairs = false;
     };
     std::vector<CachedPlan> plans;
 
@@ -314,6 +316,7 @@ struct TileArgs {
     int n_items;
     void *out;
     int out_dtype;
+    bool pairs;              // items name the first of two query heads of one KV head
 };
 int launch_prefill_tc(yx_ctx *ctx, const TileArgs &a);
 int launch_attend_simt(yx_ctx *ctx, const AttendArgs &a);
