@@ -23,6 +23,7 @@
 //
 // Every mbarrier wait is bounded; on expiry the CTA records where, stops waiting anywhere,
 // still frees its TMEM and returns.
+
 #include "yx_device.cuh"
 
 namespace yx {
@@ -452,7 +453,6 @@ constexpr int T2_THREADS = 10 * 32;
 constexpr int T2_BARS = 1 + 2 * T2_K_STAGES + 2 * T2_V_STAGES + 6;
 constexpr int T2_SMEM_BYTES = PAGE_BYTES * (2 + T2_K_STAGES + T2_V_STAGES) + T2_BARS * 8 + 64;
 
-__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
@@ -543,6 +543,7 @@ __device__ __forceinline__ float softmax_tile(uint32_t s_addr, uint32_t key0, ui
     tmem_st_wait();
     return alpha;
 }
+
 
 __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TileParams P) {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -817,7 +818,18 @@ int launch_prefill_tc(yx_ctx *ctx, const TileArgs &a) {
     P.p_lo = P.bf16;
     P.q_lo = P.bf16 && a.q_dtype == YX_F32;
     P.status = ctx->dev_status;
-    prefill_tc_kernel<<<a.n_items, THREADS, SMEM_BYTES, ctx->stream>>>(P);
+    if (a.pairs) {
+        // Each item names the first of two query heads of one KV head.
+        if (!ctx->smem_configured[7]) {
+            if (int rc = check_cuda(ctx, cudaFuncSetAttribute(prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES),
+                                    "prefill_tc2: shared memory attribute"))
+                return rc;
+            ctx->smem_configured[7] = true;
+        }
+        prefill_tc2_kernel<<<a.n_items, T2_THREADS, T2_SMEM_BYTES, ctx->stream>>>(P);
+    } else {
+        prefill_tc_kernel<<<a.n_items, THREADS, SMEM_BYTES, ctx->stream>>>(P);
+    }
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "prefill_tc kernel");
 }
