@@ -198,6 +198,24 @@ int yx_comm_destroy(yx_ctx *ctx);
 int yx_attend_allgather(yx_ctx *ctx, yx_kv *kv, int layer, const void *q_dev, int q_dtype, int hq,
                         int64_t window, uint64_t key_lo, uint64_t key_hi, void *out_dev, int out_dtype);
 
+/* ---- attention without allocation ----------------------------------------------------------- */
+
+/* No counterpart in the reference.  Same result as yx_attend (cpu lib.rs:389-427) for passes of
+ * at most YX_STATIC_MAX_ROW_HEADS (row, query head) pairs, but the call allocates nothing: the
+ * partial triples of its split-key kernel (YX_STATIC_SPLITS runs of keys per row and KV head) live
+ * in an array built into the library's device image (4 MiB + 64 KiB per device), not in a
+ * workspace from the allocator.  For callers that have handed all free device memory to the KV
+ * page pool, or that cannot take the device-wide stall of an allocation inside their decode loop.
+ * Larger passes are rejected with YX_ERR_INVALID and a message naming the limit.
+ * The context's device must be the current device.  The first call on a device looks the
+ * array's address up; make it before any stream capture begins.  The array is one per device
+ * and process: calls whose kernels may overlap on a device race on it, so order them on one
+ * stream or with events.  Nothing in it needs clearing between calls. */
+#define YX_STATIC_SPLITS 8
+#define YX_STATIC_MAX_ROW_HEADS 1024
+int yx_attend_static(yx_ctx *ctx, yx_kv *kv, int layer, const void *q_dev, int q_dtype, int hq, int64_t window,
+                     void *out_dev, int out_dtype);
+
 /* ---- test hook -------------------------------------------------------------------------- */
 
 /* Runs the split-key planner (the counterpart of `AttentionCase::plan`,

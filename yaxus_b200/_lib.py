@@ -15,6 +15,7 @@ YX_OK, YX_ERR_INVALID, YX_ERR_CUDA, YX_ERR_OOM, YX_ERR_STATE, YX_ERR_DEVICE, YX_
 F32, F16, BF16 = 0, 1, 2
 PAGE = 128
 HEAD_DIM = 128
+STATIC_SPLITS, STATIC_MAX_ROW_HEADS = 8, 1024   # yx_attend_static's built-in scratch
 PROBE_ITEM_WORDS = 41
 
 
@@ -69,6 +70,7 @@ SIGNATURES = {
     "yx_attention": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
     "yx_kv_append": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int]),
     "yx_attend": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int64, c_void_p, c_int]),
+    "yx_attend_static": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int64, c_void_p, c_int]),
     "yx_attend_partial": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int64, c_uint64, c_uint64,
                                   c_void_p, c_void_p, c_void_p]),
     "yx_lse_combine": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_int]),

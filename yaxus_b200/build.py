@@ -7,7 +7,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libyaxus_cuda.so")
 HOST_OUT = os.path.join(HERE, "libyaxus_host.so")
-CUDA_SOURCES = ["api.cu", "kv_ops.cu", "attend_simt.cu", "attend_mma.cu", "prefill_tc.cu", "combine.cu", "dist.cu", "planner.cpp",
+CUDA_SOURCES = ["api.cu", "kv_ops.cu", "attend_simt.cu", "attend_mma.cu", "prefill_tc.cu", "combine.cu", "dist.cu", "attend_static.cu", "planner.cpp",
                 "probe.cpp"]
 HOST_SOURCES = [os.path.join("host", "kv_cache.cpp")]
 NVCC_FLAGS = [
