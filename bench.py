@@ -143,7 +143,7 @@ def run_reference(args):
 
 
 def run_prefill(args):
-    """Chunked causal prefill: 8 sequences x 4096 tokens in 512-row chunks, bf16 Q/K/V, f32
+    """Chunked causal prefill: 8 sequences x 4096 tokens in 512-row chunks, 16-bit Q/K/V (f16 or bf16), f32
     softmax and accumulation.  A step is the whole prefill of the batch (eight passes, each
     appending its 4096 K/V rows and attending); the metric is causal-exact TFLOP/s."""
     import torch
@@ -160,17 +160,20 @@ def run_prefill(args):
     b = CudaBackend(local)
     dev = b.device
     n_seq, total, chunk, hq, hkv = 8, 4096, 512, 32, 8
+    kvt = BF16 if args.kv_dtype == "bf16" else F16
+    tdt = torch.bfloat16 if kvt == BF16 else torch.float16
+    kv_name = "bf16" if kvt == BF16 else "f16"
     n_layers = 2   # 2 x 134 MB of K+V: a step does not find its pages in L2 from the step before
     passes = W.prefill_passes(seed=W.SEED0 + 3 + 1000 * rank, n_seq=n_seq, total=total, chunk=chunk, hq=hq, hkv=hkv)
     s0 = passes[0]
     layers = [LayerMeta(index=i, rope=Rope.default()) for i in range(n_layers)]
-    kv = b.new_kv(hkv, layers, s0.arena_pages, 8192, BF16)
+    kv = b.new_kv(hkv, layers, s0.arena_pages, 8192, kvt)
     g = torch.Generator(device=dev).manual_seed(7 + rank)
     T = s0.meta.rows
-    q = torch.randn(T, hq * 128, device=dev, generator=g).to(torch.bfloat16)
-    k_rows = torch.randn(T, hkv * 128, device=dev, generator=g).to(torch.bfloat16)
-    v_rows = torch.randn(T, hkv * 128, device=dev, generator=g).to(torch.bfloat16)
-    out = torch.empty(T, hq * 128, dtype=torch.bfloat16, device=dev)
+    q = torch.randn(T, hq * 128, device=dev, generator=g).to(tdt)
+    k_rows = torch.randn(T, hkv * 128, device=dev, generator=g).to(tdt)
+    v_rows = torch.randn(T, hkv * 128, device=dev, generator=g).to(tdt)
+    out = torch.empty(T, hq * 128, dtype=tdt, device=dev)
     flops = sum(p.flops() for p in passes)
 
     def step(i):
@@ -192,15 +195,15 @@ def run_prefill(args):
         from tests.oracle import Oracle
         o = Oracle()
         small = W.prefill_passes(seed=5, n_seq=2, total=1024, chunk=512, hq=hq, hkv=hkv)
-        kvs = b.new_kv(hkv, [LayerMeta(index=0, rope=Rope.default())], small[0].arena_pages, 8192, BF16)
+        kvs = b.new_kv(hkv, [LayerMeta(index=0, rope=Rope.default())], small[0].arena_pages, 8192, kvt)
         K = np.zeros((small[0].arena_pages * 128, hkv * 128), np.float32)
         V = np.zeros_like(K)
         t = lambda x, dt: torch.from_numpy(np.ascontiguousarray(x)).to(dev).to(dt)
         for p in small:
             b.begin_pass(p.meta)
             b.kv_append(kvs, 0, t(p.k_new, torch.float32), t(p.v_new, torch.float32))
-            got = b.to_host(b.attend(kvs, 0, t(p.q, torch.bfloat16), hq))
-            o.append_rows(W.round_through(p.k_new, BF16), W.round_through(p.v_new, BF16), p.meta.kv_slot, K, V)
+            got = b.to_host(b.attend(kvs, 0, t(p.q, tdt), hq))
+            o.append_rows(W.round_through(p.k_new, kvt), W.round_through(p.v_new, kvt), p.meta.kv_slot, K, V)
             ref = o.attend(p.q, p.meta.pos, p.meta.pt_off, p.meta.pages, hq, hkv, 128, None, K, V)
             e = assert_close(got, ref, what=p.name)
             max_err = e if max_err is None else max(max_err, e)
@@ -230,11 +233,11 @@ def run_prefill(args):
     split_ms, combine_ms, calls = b.profile_end()
     kernel_ms_per_step = split_ms / max(calls, 1) * len(passes)
 
-    # end to end: metadata, bf16 q/k/v rows from pinned host memory, result read back, per pass
-    qh = torch.empty(T, hq * 128, dtype=torch.bfloat16).pin_memory()
-    kh = torch.empty(T, hkv * 128, dtype=torch.bfloat16).pin_memory()
-    vh = torch.empty(T, hkv * 128, dtype=torch.bfloat16).pin_memory()
-    oh = torch.empty(T, hq * 128, dtype=torch.bfloat16).pin_memory()
+    # end to end: metadata, 16-bit q/k/v rows from pinned host memory, result read back, per pass
+    qh = torch.empty(T, hq * 128, dtype=tdt).pin_memory()
+    kh = torch.empty(T, hkv * 128, dtype=tdt).pin_memory()
+    vh = torch.empty(T, hkv * 128, dtype=tdt).pin_memory()
+    oh = torch.empty(T, hq * 128, dtype=tdt).pin_memory()
     qd, kd, vd = torch.empty_like(qh, device=dev), torch.empty_like(kh, device=dev), torch.empty_like(vh, device=dev)
 
     def e2e_step(i):
@@ -274,14 +277,14 @@ def run_prefill(args):
         line = {
             "metric": "prefill-attn TFLOPS", "value": world * flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": kv_name, "data": "synthetic",
             "config": {"workload": "chunked causal prefill", "sequences": n_seq, "tokens_per_sequence": total,
-                       "chunk": chunk, "hq": hq, "hkv": hkv, "head_dim": 128, "kv_dtype": "bf16",
+                       "chunk": chunk, "hq": hq, "hkv": hkv, "head_dim": 128, "kv_dtype": kv_name,
                        "flops_per_step": flops, "passes_per_step": len(passes),
                        "l2": f"steps alternate over {n_layers} layer arenas of 134 MB",
                        "parallelism": f"by sequence, {world} GPU(s), no collective"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": which, "kernel": "prefill_tc_kernel",
+                         "traffic": None, "peak_source": which, "kernel": "prefill_tc2_kernel",
                          "kernel_ms_per_step": kernel_ms_per_step},
             "clocks": clocks, "gpu_launches": int(launches),
             "plan": {"path": info.path, "tile_items_last_pass": None},
@@ -466,6 +469,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=200)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--workload", default="batched_decode")
+    ap.add_argument("--kv-dtype", default=None, choices=["f16", "bf16"],
+                    help="cache storage type of the prefill workload (default f16, as in the decode workloads)")
     ap.add_argument("--no-check", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

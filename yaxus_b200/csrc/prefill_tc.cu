@@ -58,6 +58,7 @@ struct TileParams {
     int q_lo;            // queries carry a low part (f32 queries on a bf16 cache): S = Qh K^T + Ql K^T
     int p_lo;            // probabilities carry a low part (bf16 cache): O += Ph V + Pl V
     yx_dev_status *status;
+    long long *trace;   // diagnostics: clock stamps of CTA 0's pipeline, or null
 };
 
 // Shared-memory matrix descriptor: start address, leading / stride byte offsets (16-byte
@@ -453,45 +454,54 @@ constexpr int T2_THREADS = 10 * 32;
 constexpr int T2_BARS = 1 + 2 * T2_K_STAGES + 2 * T2_V_STAGES + 6;
 constexpr int T2_SMEM_BYTES = PAGE_BYTES * (2 + T2_K_STAGES + T2_V_STAGES) + T2_BARS * 8 + 64;
 
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
-        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
-}
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
 
-// One 128-key tile of one query row: scores in TMEM at `s_addr` (128 f32 columns, this
-// thread's lane) become probabilities (64 packed columns; a low part in 64 more for bf16
-// caches).  Two passes over the scores, 32 columns at a time, so that little is held in
-// registers and the code stays small: the maximum first, then the exponentials.
-// Returns the factor the accumulated output has to be multiplied by (1 when the reference
-// maximum was kept: lazy rescaling, see the kernel's header).
-__device__ __forceinline__ float softmax_tile(uint32_t s_addr, uint32_t key0, uint32_t klo, uint32_t khi, int bf16,
-                                              int p_lo, float sl2, float &m_used, float &l, bool &rescale) {
-    const bool need_mask = key0 < klo || key0 + PAGE - 1 > khi;
-    float mx = -INFINITY;
+// Scores of keys outside [klo, khi] become -inf, in place in TMEM.  Only ragged tiles (the
+// diagonal, a window's lower edge) come here, so the loop is rolled: small code matters more
+// than speed.
+__device__ __noinline__ void mask_scores(uint32_t s_addr, uint32_t key0, uint32_t klo, uint32_t khi) {
 #pragma unroll 1
     for (int c = 0; c < 4; c++) {
         uint32_t sr[32];
         tmem_ld32(s_addr + c * 32, sr);
         tmem_ld_wait();
-        if (need_mask) {
 #pragma unroll
-            for (int i = 0; i < 32; i++) {
-                const uint32_t key = key0 + c * 32 + i;
-                if (key >= klo && key <= khi) mx = fmaxf(mx, __uint_as_float(sr[i]));
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) mx = max3(mx, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+        for (int i = 0; i < 32; i++) {
+            const uint32_t key = key0 + c * 32 + i;
+            if (key < klo || key > khi) sr[i] = 0xff800000u;
         }
+        tmem_st32(s_addr + c * 32, sr);
     }
+    tmem_st_wait();
+}
+
+// One 128-key tile of one query row: scores in TMEM at `s_addr` (128 f32 columns, this
+// thread's lane) become probabilities (64 packed columns; a low part in 64 more for bf16
+// caches).  The scores are read once and held in registers; the code is straight-line and has
+// no run-time type or mask switches, because the softmax warps are bound by instruction
+// fetch and issue.  Returns the factor the accumulated output has to be multiplied by (1 when
+// the reference maximum was kept: lazy rescaling, see the kernel's header).
+template <bool BF16>
+__device__ __forceinline__ float softmax_tile(uint32_t s_addr, float sl2, float &m_used, float &l, bool &rescale) {
+    uint32_t s0[32], s1[32], s2[32], s3[32];
+    tmem_ld32(s_addr, s0);
+    tmem_ld32(s_addr + 32, s1);
+    tmem_ld32(s_addr + 64, s2);
+    tmem_ld32(s_addr + 96, s3);
+    tmem_ld_wait();
+    float ma = -INFINITY, mb = -INFINITY, mc = -INFINITY, md = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+        ma = max3(ma, __uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
+        mb = max3(mb, __uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
+        mc = max3(mc, __uint_as_float(s2[i]), __uint_as_float(s2[i + 1]));
+        md = max3(md, __uint_as_float(s3[i]), __uint_as_float(s3[i + 1]));
+    }
+    const float mx = fmaxf(fmaxf(ma, mb), fmaxf(mc, md));
     float alpha = 1.f;
     rescale = false;
     if (mx > m_used && (m_used == -INFINITY || (mx - m_used) * sl2 > 8.f)) {
@@ -502,49 +512,71 @@ __device__ __forceinline__ float softmax_tile(uint32_t s_addr, uint32_t key0, ui
     }
     const float ms = (m_used == -INFINITY ? 0.f : m_used) * sl2;
     float sum0 = 0.f, sum1 = 0.f;
-    uint32_t lo[64];
+    // In place: pair i of a chunk (scores 2i, 2i+1) becomes packed probabilities in word i,
+    // which pairs before i no longer need.  For bf16, what the 8-bit mantissa dropped goes to
+    // word 16 + i once the whole chunk is read.
+    auto chunk = [&](uint32_t (&sr)[32]) {
+        uint32_t lo[BF16 ? 16 : 1];
 #pragma unroll
-    for (int c = 0; c < 4; c++) {
-        uint32_t sr[32], hi[16];
-        tmem_ld32(s_addr + c * 32, sr);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-            float s0 = __uint_as_float(sr[i]), s1 = __uint_as_float(sr[i + 1]);
-            if (need_mask) {
-                const uint32_t key = key0 + c * 32 + i;
-                if (key < klo || key > khi) s0 = -INFINITY;
-                if (key + 1 < klo || key + 1 > khi) s1 = -INFINITY;
-            }
-            const float p0 = fast_exp2(s0 * sl2 - ms), p1 = fast_exp2(s1 * sl2 - ms);
+        for (int i = 0; i < 16; i++) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * i]), sl2, -ms));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * i + 1]), sl2, -ms));
             sum0 += p0;
             sum1 += p1;
-            const uint32_t w = pack_pair(p0, p1, bf16);
-            hi[i >> 1] = w;
-            if (p_lo) {
-                // what the 8-bit mantissa dropped: p - float(hi), the halves widened in place
-                const float h0 = __uint_as_float(w << 16), h1 = __uint_as_float(w & 0xffff0000u);
-                lo[c * 16 + (i >> 1)] = pack_pair(p0 - h0, p1 - h1, 1);
+            if (BF16) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+                const uint32_t w = *(uint32_t *)&v;
+                __nv_bfloat162 lv = __floats2bfloat162_rn(p0 - __uint_as_float(w << 16), p1 - __uint_as_float(w & 0xffff0000u));
+                lo[i] = *(uint32_t *)&lv;
+                sr[i] = w;
+            } else {
+                __half2 v = __floats2half2_rn(p0, p1);
+                sr[i] = *(uint32_t *)&v;
             }
         }
-        // Columns [16c, 16c+16) of the probabilities sit over scores already read.
-        tmem_st16(s_addr + c * 16, hi);
-    }
-    if (p_lo) {
+        if (BF16) {
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
-            uint32_t part[16];
-#pragma unroll
-            for (int i = 0; i < 16; i++) part[i] = lo[c * 16 + i];
-            tmem_st16(s_addr + 64 + c * 16, part);
+            for (int i = 0; i < 16; i++) sr[16 + i] = lo[i];
         }
+    };
+    chunk(s0);
+    chunk(s1);
+    chunk(s2);
+    chunk(s3);
+    // words [0,16) of chunk c: probabilities of keys [32c, 32c+32); words [16,32): their low parts
+    uint32_t hi[32];
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        hi[i] = s0[i];
+        hi[16 + i] = s1[i];
+    }
+    tmem_st32(s_addr, hi);
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        hi[i] = s2[i];
+        hi[16 + i] = s3[i];
+    }
+    tmem_st32(s_addr + 32, hi);
+    if (BF16) {
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            hi[i] = s0[16 + i];
+            hi[16 + i] = s1[16 + i];
+        }
+        tmem_st32(s_addr + 64, hi);
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            hi[i] = s2[16 + i];
+            hi[16 + i] = s3[16 + i];
+        }
+        tmem_st32(s_addr + 96, hi);
     }
     l += sum0 + sum1;
     tmem_st_wait();
     return alpha;
 }
 
-
+template <bool BF16>
 __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TileParams P) {
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ uint32_t tmem_base_s;
@@ -647,7 +679,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
     } else if (warp == T2_MMA) {
         // ---- MMA issuer ----------------------------------------------------------------------
         if (lane == 0 && n_tiles > 0) {
-            const uint32_t idesc_qk = instr_desc(P.bf16, 0), idesc_pv = instr_desc(P.bf16, 1);
+            const uint32_t idesc_qk = instr_desc(BF16, 0), idesc_pv = instr_desc(BF16, 1);
             mbar_wait(b_q_full, 0, abortp, P.status, 43);
             tc_fence_after();
             uint32_t kph = 0, vph = 0;
@@ -661,14 +693,18 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
                 }
                 umma_commit(b_s_full + 8 * t);
             };
+            auto stamp = [&](uint32_t j, int e) {
+                if (P.trace && blockIdx.x == 0 && j < 64) P.trace[(2 * 64 + j) * 8 + e] = clock64();
+            };
             auto issue_pv = [&](int t, uint32_t j, uint32_t v_base) {   // O_t (+)= P_t V
                 mbar_wait(b_p_full + 8 * t, j & 1u, abortp, P.status, 44 + t);
+                stamp(j, t ? 5 : 1);
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < 8; k++) {
                     const uint64_t vdesc = smem_desc(v_base + k * 16 * 128, HALF_BYTES, 1024);
                     umma_ts(tmem + 256 + t * 128, tmem + t * 128 + k * 8, vdesc, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-                    if (P.p_lo) umma_ts(tmem + 256 + t * 128, tmem + t * 128 + 64 + k * 8, vdesc, idesc_pv, 1u);
+                    if (BF16) umma_ts(tmem + 256 + t * 128, tmem + t * 128 + 64 + k * 8, vdesc, idesc_pv, 1u);
                 }
                 umma_commit(b_pv_done + 8 * t);
             };
@@ -685,13 +721,18 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
                 const bool more = j + 1 < n_tiles;
                 const uint32_t k_next = s_k + ks * PAGE_BYTES;
                 mbar_wait(b_v_full + 8 * vs, vph, abortp, P.status, 47);
+                stamp(j, 0);
                 issue_pv(0, j, v_base);
+                stamp(j, 2);
                 if (more) {
                     mbar_wait(b_k_full + 8 * ks, kph, abortp, P.status, 48);
+                    stamp(j, 3);
                     tc_fence_after();
                     issue_s(0, k_next);
                 }
+                stamp(j, 4);
                 issue_pv(1, j, v_base);
+                stamp(j, 6);
                 umma_commit(b_v_empty + 8 * vs);
                 if (more) {
                     issue_s(1, k_next);
@@ -723,8 +764,8 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
                     a = load4_as_f32(P.q, P.q_dtype, base + c * 8);
                     b = load4_as_f32(P.q, P.q_dtype, base + c * 8 + 4);
                 }
-                const uint32_t w0 = pack_pair(a.x, a.y, P.bf16), w1 = pack_pair(a.z, a.w, P.bf16),
-                               w2 = pack_pair(b.x, b.y, P.bf16), w3 = pack_pair(b.z, b.w, P.bf16);
+                const uint32_t w0 = pack_pair(a.x, a.y, BF16), w1 = pack_pair(a.z, a.w, BF16),
+                               w2 = pack_pair(b.x, b.y, BF16), w3 = pack_pair(b.z, b.w, BF16);
                 const uint32_t addr = s_q + (c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4);
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
             }
@@ -737,9 +778,16 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
         float m_used = -INFINITY, l = 0.f;
         for (uint32_t j = 0; j < n_tiles; j++) {
             mbar_wait(b_s_full + 8 * t, j & 1u, abortp, P.status, 49 + t);
+            const bool tr = P.trace && blockIdx.x == 0 && r == 0 && j < 64;
+            if (tr) P.trace[(t * 64 + j) * 8 + 0] = clock64();
             tc_fence_after();
             bool rescale;
-            const float alpha = softmax_tile(s_addr, (it.page_begin + j) * PAGE, klo, khi, P.bf16, P.p_lo, sl2, m_used, l, rescale);
+            const uint32_t key0 = (it.page_begin + j) * PAGE;
+            // Warp-uniform decision: the TMEM accesses inside are warp-wide (.sync.aligned) and
+            // must not sit under a per-lane condition.
+            if (__any_sync(0xffffffffu, key0 < klo || key0 + PAGE - 1 > khi)) mask_scores(s_addr, key0, klo, khi);
+            const float alpha = softmax_tile<BF16>(s_addr, sl2, m_used, l, rescale);
+            if (tr) P.trace[(t * 64 + j) * 8 + 1] = clock64();
             if (j > 0) {
                 // The accumulator is quiet between P(j-1)V and P(j)V: rescale it here if the
                 // reference maximum moved.
@@ -759,6 +807,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
                 }
             }
             tc_fence_before();
+            if (tr) P.trace[(t * 64 + j) * 8 + 2] = clock64();
             mbar_arrive(b_p_full + 8 * t);
         }
         if (n_tiles > 0) {
@@ -818,15 +867,20 @@ int launch_prefill_tc(yx_ctx *ctx, const TileArgs &a) {
     P.p_lo = P.bf16;
     P.q_lo = P.bf16 && a.q_dtype == YX_F32;
     P.status = ctx->dev_status;
+    P.trace = (long long *)ctx->trace_buf;
     if (a.pairs) {
         // Each item names the first of two query heads of one KV head.
         if (!ctx->smem_configured[7]) {
-            if (int rc = check_cuda(ctx, cudaFuncSetAttribute(prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES),
+            if (int rc = check_cuda(ctx, cudaFuncSetAttribute(prefill_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES),
+                                    "prefill_tc2: shared memory attribute"))
+                return rc;
+            if (int rc = check_cuda(ctx, cudaFuncSetAttribute(prefill_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES),
                                     "prefill_tc2: shared memory attribute"))
                 return rc;
             ctx->smem_configured[7] = true;
         }
-        prefill_tc2_kernel<<<a.n_items, T2_THREADS, T2_SMEM_BYTES, ctx->stream>>>(P);
+        if (P.bf16) prefill_tc2_kernel<true><<<a.n_items, T2_THREADS, T2_SMEM_BYTES, ctx->stream>>>(P);
+        else prefill_tc2_kernel<false><<<a.n_items, T2_THREADS, T2_SMEM_BYTES, ctx->stream>>>(P);
     } else {
         prefill_tc_kernel<<<a.n_items, THREADS, SMEM_BYTES, ctx->stream>>>(P);
     }
