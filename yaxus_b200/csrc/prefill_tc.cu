@@ -90,6 +90,25 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
                  "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
                  : "memory");
 }
+// The same instructions with the descriptors' constant high words and precomputed low words
+// (start address and leading offset): the issuing thread then spends one add per operand, which
+// matters because a single thread issues every MMA of the CTA.
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+    return ((saddr & 0x3ffff) >> 4) | (((lbo_bytes >> 4) & 0x3fff) << 16);
+}
+constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);   // stride 1024 B, version 1, 128-byte swizzle
+__device__ __forceinline__ void umma_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
+                 "r"(a_lo), "r"(b_lo), "r"(DESC_HI), "r"(idesc), "r"(acc)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 db, {%2, %3};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
+                 "r"(a_tmem), "r"(b_lo), "r"(DESC_HI), "r"(idesc), "r"(acc)
+                 : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -450,8 +469,8 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const TileParams
 constexpr int T2_K_STAGES = 2, T2_V_STAGES = 2;
 constexpr int T2_PRODUCER = 8, T2_MMA = 9;
 constexpr int T2_THREADS = 10 * 32;
-// barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done[2]
-constexpr int T2_BARS = 1 + 2 * T2_K_STAGES + 2 * T2_V_STAGES + 6;
+// barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_half[2][2], pv_done[2]
+constexpr int T2_BARS = 1 + 2 * T2_K_STAGES + 2 * T2_V_STAGES + 8;
 constexpr int T2_SMEM_BYTES = PAGE_BYTES * (2 + T2_K_STAGES + T2_V_STAGES) + T2_BARS * 8 + 64;
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -479,101 +498,57 @@ __device__ __noinline__ void mask_scores(uint32_t s_addr, uint32_t key0, uint32_
     tmem_st_wait();
 }
 
-// One 128-key tile of one query row: scores in TMEM at `s_addr` (128 f32 columns, this
-// thread's lane) become probabilities (64 packed columns; a low part in 64 more for bf16
-// caches).  The scores are read once and held in registers; the code is straight-line and has
-// no run-time type or mask switches, because the softmax warps are bound by instruction
-// fetch and issue.  Returns the factor the accumulated output has to be multiplied by (1 when
-// the reference maximum was kept: lazy rescaling, see the kernel's header).
+// 32 scores of one query row (one chunk of a tile) become probabilities, in place: pair i
+// (scores 2i, 2i+1) becomes a packed 16-bit pair in word i, which the pairs before i no longer
+// need.  For bf16, what the 8-bit mantissa dropped goes to word 16 + i once the whole chunk is
+// read.  Straight-line and free of run-time type switches: the softmax warps are bound by
+// instruction fetch and issue.
 template <bool BF16>
-__device__ __forceinline__ float softmax_tile(uint32_t s_addr, float sl2, float &m_used, float &l, bool &rescale) {
-    uint32_t s0[32], s1[32], s2[32], s3[32];
-    tmem_ld32(s_addr, s0);
-    tmem_ld32(s_addr + 32, s1);
-    tmem_ld32(s_addr + 64, s2);
-    tmem_ld32(s_addr + 96, s3);
-    tmem_ld_wait();
-    float ma = -INFINITY, mb = -INFINITY, mc = -INFINITY, md = -INFINITY;
+__device__ __forceinline__ void exp_chunk(uint32_t (&sr)[32], float sl2, float ms, float &sum0, float &sum1) {
+    uint32_t lo[BF16 ? 16 : 1];
 #pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-        ma = max3(ma, __uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
-        mb = max3(mb, __uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
-        mc = max3(mc, __uint_as_float(s2[i]), __uint_as_float(s2[i + 1]));
-        md = max3(md, __uint_as_float(s3[i]), __uint_as_float(s3[i + 1]));
-    }
-    const float mx = fmaxf(fmaxf(ma, mb), fmaxf(mc, md));
-    float alpha = 1.f;
-    rescale = false;
-    if (mx > m_used && (m_used == -INFINITY || (mx - m_used) * sl2 > 8.f)) {
-        alpha = m_used == -INFINITY ? 0.f : fast_exp2((m_used - mx) * sl2);
-        rescale = m_used != -INFINITY;   // nothing accumulated yet otherwise
-        m_used = mx;
-        l *= alpha;
-    }
-    const float ms = (m_used == -INFINITY ? 0.f : m_used) * sl2;
-    float sum0 = 0.f, sum1 = 0.f;
-    // In place: pair i of a chunk (scores 2i, 2i+1) becomes packed probabilities in word i,
-    // which pairs before i no longer need.  For bf16, what the 8-bit mantissa dropped goes to
-    // word 16 + i once the whole chunk is read.
-    auto chunk = [&](uint32_t (&sr)[32]) {
-        uint32_t lo[BF16 ? 16 : 1];
-#pragma unroll
-        for (int i = 0; i < 16; i++) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * i]), sl2, -ms));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * i + 1]), sl2, -ms));
-            sum0 += p0;
-            sum1 += p1;
-            if (BF16) {
-                __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
-                const uint32_t w = *(uint32_t *)&v;
-                __nv_bfloat162 lv = __floats2bfloat162_rn(p0 - __uint_as_float(w << 16), p1 - __uint_as_float(w & 0xffff0000u));
-                lo[i] = *(uint32_t *)&lv;
-                sr[i] = w;
-            } else {
-                __half2 v = __floats2half2_rn(p0, p1);
-                sr[i] = *(uint32_t *)&v;
-            }
-        }
+    for (int i = 0; i < 16; i++) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * i]), sl2, -ms));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * i + 1]), sl2, -ms));
+        sum0 += p0;
+        sum1 += p1;
         if (BF16) {
-#pragma unroll
-            for (int i = 0; i < 16; i++) sr[16 + i] = lo[i];
+            __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+            const uint32_t w = *(uint32_t *)&v;
+            __nv_bfloat162 lv = __floats2bfloat162_rn(p0 - __uint_as_float(w << 16), p1 - __uint_as_float(w & 0xffff0000u));
+            lo[i] = *(uint32_t *)&lv;
+            sr[i] = w;
+        } else {
+            __half2 v = __floats2half2_rn(p0, p1);
+            sr[i] = *(uint32_t *)&v;
         }
-    };
-    chunk(s0);
-    chunk(s1);
-    chunk(s2);
-    chunk(s3);
-    // words [0,16) of chunk c: probabilities of keys [32c, 32c+32); words [16,32): their low parts
-    uint32_t hi[32];
+    }
+    if (BF16) {
+#pragma unroll
+        for (int i = 0; i < 16; i++) sr[16 + i] = lo[i];
+    }
+}
+
+// Probabilities of 64 keys (two chunks) to TMEM: 32 packed columns at `p_addr`, and for bf16
+// their low parts 64 columns further on.
+template <bool BF16>
+__device__ __forceinline__ void store_half(uint32_t p_addr, const uint32_t (&x)[32], const uint32_t (&y)[32]) {
+    uint32_t w[32];
 #pragma unroll
     for (int i = 0; i < 16; i++) {
-        hi[i] = s0[i];
-        hi[16 + i] = s1[i];
+        w[i] = x[i];
+        w[16 + i] = y[i];
     }
-    tmem_st32(s_addr, hi);
-#pragma unroll
-    for (int i = 0; i < 16; i++) {
-        hi[i] = s2[i];
-        hi[16 + i] = s3[i];
-    }
-    tmem_st32(s_addr + 32, hi);
+    tmem_st32(p_addr, w);
     if (BF16) {
 #pragma unroll
         for (int i = 0; i < 16; i++) {
-            hi[i] = s0[16 + i];
-            hi[16 + i] = s1[16 + i];
+            w[i] = x[16 + i];
+            w[16 + i] = y[16 + i];
         }
-        tmem_st32(s_addr + 64, hi);
-#pragma unroll
-        for (int i = 0; i < 16; i++) {
-            hi[i] = s2[16 + i];
-            hi[16 + i] = s3[16 + i];
-        }
-        tmem_st32(s_addr + 96, hi);
+        tmem_st32(p_addr + 64, w);
     }
-    l += sum0 + sum1;
     tmem_st_wait();
-    return alpha;
 }
 
 template <bool BF16>
@@ -589,11 +564,13 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
     const uint32_t b_q_full = bars;
     const uint32_t b_k_full = bars + 8, b_k_empty = b_k_full + 8 * T2_K_STAGES;
     const uint32_t b_v_full = b_k_empty + 8 * T2_K_STAGES, b_v_empty = b_v_full + 8 * T2_V_STAGES;
-    const uint32_t b_s_full = b_v_empty + 8 * T2_V_STAGES, b_p_full = b_s_full + 16, b_pv_done = b_p_full + 16;
+    const uint32_t b_s_full = b_v_empty + 8 * T2_V_STAGES, b_p_half = b_s_full + 16, b_pv_done = b_p_half + 32;
     volatile int *abortp = &abort_flag;
 
     const TileItem it = P.items[blockIdx.x];   // it.head is the first of the two heads
     const uint32_t n_tiles = it.page_end - it.page_begin;
+    const bool tr0 = P.trace && blockIdx.x == 0 && threadIdx.x == 0;
+    if (tr0) P.trace[1536] = clock64();
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -608,7 +585,8 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
         }
         for (int t = 0; t < 2; t++) {
             mbar_init(b_s_full + 8 * t, 1);
-            mbar_init(b_p_full + 8 * t, 128);
+            mbar_init(b_p_half + 16 * t, 4);       // one arrival per softmax warp,
+            mbar_init(b_p_half + 16 * t + 8, 4);   // for each 64-key half of the tile
             mbar_init(b_pv_done + 8 * t, 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -626,6 +604,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
     tc_fence_after();
     const uint32_t tmem = tmem_base_s;
     const float sl2 = 0.08838834764831845f * 1.4426950408889634f;
+    if (tr0) P.trace[1537] = clock64();
 
     if (warp == T2_PRODUCER) {
         // ---- producer: one K page and one V page per tile, for both query tiles ---------------
@@ -684,61 +663,67 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
             tc_fence_after();
             uint32_t kph = 0, vph = 0;
             int ks = 0, vs = 0;
-            auto issue_s = [&](int t, uint32_t k_base) {   // S_t = Q_t K^T
-                const uint32_t q_base = t ? s_qb : s_qa;
+            // Low descriptor words of the tiles at offset 0; a K-step adds a constant.
+            const uint32_t qa_lo = desc_lo(s_qa, 16), qb_lo = desc_lo(s_qb, 16), k_lo = desc_lo(s_k, 16),
+                           v_lo = desc_lo(s_v, HALF_BYTES);
+            auto issue_s = [&](int t, int stage) {   // S_t = Q_t K^T
+                const uint32_t q_lo = t ? qb_lo : qa_lo, kk_lo = k_lo + stage * (PAGE_BYTES >> 4);
 #pragma unroll
                 for (int k = 0; k < 8; k++) {
-                    const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-                    umma_ss(tmem + t * 128, smem_desc(q_base + off, 16, 1024), smem_desc(k_base + off, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
+                    const uint32_t off = ((k >> 2) * HALF_BYTES + (k & 3) * 32) >> 4;
+                    umma_ss_lo(tmem + t * 128, q_lo + off, kk_lo + off, idesc_qk, k > 0 ? 1u : 0u);
                 }
                 umma_commit(b_s_full + 8 * t);
             };
             auto stamp = [&](uint32_t j, int e) {
                 if (P.trace && blockIdx.x == 0 && j < 64) P.trace[(2 * 64 + j) * 8 + e] = clock64();
             };
-            auto issue_pv = [&](int t, uint32_t j, uint32_t v_base) {   // O_t (+)= P_t V
-                mbar_wait(b_p_full + 8 * t, j & 1u, abortp, P.status, 44 + t);
-                stamp(j, t ? 5 : 1);
-                tc_fence_after();
+            auto issue_pv = [&](int t, uint32_t j, int stage) {   // O_t (+)= P_t V, a 64-key half at a time
+                const uint32_t vv_lo = v_lo + stage * (PAGE_BYTES >> 4);
 #pragma unroll
-                for (int k = 0; k < 8; k++) {
-                    const uint64_t vdesc = smem_desc(v_base + k * 16 * 128, HALF_BYTES, 1024);
-                    umma_ts(tmem + 256 + t * 128, tmem + t * 128 + k * 8, vdesc, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-                    if (BF16) umma_ts(tmem + 256 + t * 128, tmem + t * 128 + 64 + k * 8, vdesc, idesc_pv, 1u);
+                for (int h = 0; h < 2; h++) {
+                    mbar_wait(b_p_half + 16 * t + 8 * h, j & 1u, abortp, P.status, 44 + t);
+                    if (h == 0) stamp(j, t ? 5 : 1);
+                    tc_fence_after();
+#pragma unroll
+                    for (int k = 4 * h; k < 4 * h + 4; k++) {
+                        const uint32_t vk_lo = vv_lo + ((k * 16 * 128) >> 4);
+                        umma_ts_lo(tmem + 256 + t * 128, tmem + t * 128 + k * 8, vk_lo, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                        if (BF16) umma_ts_lo(tmem + 256 + t * 128, tmem + t * 128 + 64 + k * 8, vk_lo, idesc_pv, 1u);
+                    }
                 }
                 umma_commit(b_pv_done + 8 * t);
             };
             // S_A(0), S_B(0)
             mbar_wait(b_k_full, 0, abortp, P.status, 46);
             tc_fence_after();
-            issue_s(0, s_k);
-            issue_s(1, s_k);
+            issue_s(0, 0);
+            issue_s(1, 0);
             umma_commit(b_k_empty);
             ks = 1 % T2_K_STAGES;
             if (ks == 0) kph ^= 1u;
             for (uint32_t j = 0; j < n_tiles && !*abortp; j++) {
-                const uint32_t v_base = s_v + vs * PAGE_BYTES;
                 const bool more = j + 1 < n_tiles;
-                const uint32_t k_next = s_k + ks * PAGE_BYTES;
                 mbar_wait(b_v_full + 8 * vs, vph, abortp, P.status, 47);
                 stamp(j, 0);
-                issue_pv(0, j, v_base);
+                issue_pv(0, j, vs);
                 stamp(j, 2);
                 if (more) {
                     mbar_wait(b_k_full + 8 * ks, kph, abortp, P.status, 48);
                     stamp(j, 3);
                     tc_fence_after();
-                    issue_s(0, k_next);
+                    issue_s(0, ks);
                 }
                 stamp(j, 4);
-                issue_pv(1, j, v_base);
+                issue_pv(1, j, vs);
                 stamp(j, 6);
                 umma_commit(b_v_empty + 8 * vs);
                 if (more) {
-                    issue_s(1, k_next);
+                    issue_s(1, ks);
                     umma_commit(b_k_empty + 8 * ks);
                     if (++ks == T2_K_STAGES) { ks = 0; kph ^= 1u; }
                 }
+                stamp(j, 7);
                 if (++vs == T2_V_STAGES) { vs = 0; vph ^= 1u; }
             }
         }
@@ -755,19 +740,50 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
         const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t s_addr = lane_addr + t * 128, o_addr = lane_addr + 256 + t * 128;
         {
+            // Q tile to shared memory in the operand layout.  Work is dealt by 16-byte chunk, not
+            // by row: 16 consecutive threads read one row's 256 (or 512) contiguous bytes, and
+            // all of a thread's loads are issued before the first store, so the tile costs one
+            // trip to memory.
             const uint32_t s_q = t ? s_qb : s_qa;
-            const size_t base = ((size_t)(it.row0 + (valid ? r : 0)) * P.hq + head) * D;
-#pragma unroll 4
-            for (int c = 0; c < 16; c++) {
-                float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-                if (valid) {
-                    a = load4_as_f32(P.q, P.q_dtype, base + c * 8);
-                    b = load4_as_f32(P.q, P.q_dtype, base + c * 8 + 4);
+            const size_t qbase = ((size_t)it.row0 * P.hq + head) * D;
+            const size_t qrow = (size_t)P.hq * D;
+            auto chunk_addr = [&](int row, int c) {
+                return s_q + (c >> 3) * HALF_BYTES + row * 128 + (((c & 7) ^ (row & 7)) << 4);
+            };
+            if (P.q_dtype == (BF16 ? YX_BF16 : YX_F16)) {
+                uint4 w[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const int idx = i * 128 + r, row = idx >> 4, c = idx & 15;
+                    w[i] = make_uint4(0, 0, 0, 0);
+                    if ((uint32_t)row < it.n_rows) w[i] = *(const uint4 *)((const uint16_t *)P.q + qbase + row * qrow + c * 8);
                 }
-                const uint32_t w0 = pack_pair(a.x, a.y, BF16), w1 = pack_pair(a.z, a.w, BF16),
-                               w2 = pack_pair(b.x, b.y, BF16), w3 = pack_pair(b.z, b.w, BF16);
-                const uint32_t addr = s_q + (c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const int idx = i * 128 + r, row = idx >> 4, c = idx & 15;
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(chunk_addr(row, c)), "r"(w[i].x), "r"(w[i].y), "r"(w[i].z), "r"(w[i].w) : "memory");
+                }
+            } else {
+#pragma unroll 1
+                for (int i0 = 0; i0 < 16; i0 += 4) {
+                    float4 lo4[4], hi4[4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int idx = (i0 + i) * 128 + r, row = idx >> 4, c = idx & 15;
+                        lo4[i] = hi4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if ((uint32_t)row < it.n_rows) {
+                            lo4[i] = load4_as_f32(P.q, P.q_dtype, qbase + row * qrow + c * 8);
+                            hi4[i] = load4_as_f32(P.q, P.q_dtype, qbase + row * qrow + c * 8 + 4);
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int idx = (i0 + i) * 128 + r, row = idx >> 4, c = idx & 15;
+                        const uint32_t w0 = pack_pair(lo4[i].x, lo4[i].y, BF16), w1 = pack_pair(lo4[i].z, lo4[i].w, BF16),
+                                       w2 = pack_pair(hi4[i].x, hi4[i].y, BF16), w3 = pack_pair(hi4[i].z, hi4[i].w, BF16);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(chunk_addr(row, c)), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+                    }
+                }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             // one named barrier per warpgroup
@@ -775,63 +791,145 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
             else asm volatile("bar.sync 2, 128;" ::: "memory");
             if (r == 0) mbar_arrive(b_q_full);
         }
+        if (tr0) P.trace[1538] = clock64();
         float m_used = -INFINITY, l = 0.f;
         for (uint32_t j = 0; j < n_tiles; j++) {
             mbar_wait(b_s_full + 8 * t, j & 1u, abortp, P.status, 49 + t);
             const bool tr = P.trace && blockIdx.x == 0 && r == 0 && j < 64;
             if (tr) P.trace[(t * 64 + j) * 8 + 0] = clock64();
             tc_fence_after();
-            bool rescale;
             const uint32_t key0 = (it.page_begin + j) * PAGE;
             // Warp-uniform decision: the TMEM accesses inside are warp-wide (.sync.aligned) and
             // must not sit under a per-lane condition.
             if (__any_sync(0xffffffffu, key0 < klo || key0 + PAGE - 1 > khi)) mask_scores(s_addr, key0, klo, khi);
-            const float alpha = softmax_tile<BF16>(s_addr, sl2, m_used, l, rescale);
-            if (tr) P.trace[(t * 64 + j) * 8 + 1] = clock64();
-            if (j > 0) {
-                // The accumulator is quiet between P(j-1)V and P(j)V: rescale it here if the
-                // reference maximum moved.
+            // The tile's scores, read once and held in registers.
+            uint32_t s0[32], s1[32], s2[32], s3[32];
+            tmem_ld32(s_addr, s0);
+            tmem_ld32(s_addr + 32, s1);
+            tmem_ld32(s_addr + 64, s2);
+            tmem_ld32(s_addr + 96, s3);
+            tmem_ld_wait();
+            float ma = -INFINITY, mb = -INFINITY, mc = -INFINITY, md = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                ma = max3(ma, __uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
+                mb = max3(mb, __uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
+                mc = max3(mc, __uint_as_float(s2[i]), __uint_as_float(s2[i + 1]));
+                md = max3(md, __uint_as_float(s3[i]), __uint_as_float(s3[i + 1]));
+            }
+            const float mx = fmaxf(fmaxf(ma, mb), fmaxf(mc, md));
+            // Lazy rescaling: the reference maximum moves only when the new one is more than
+            // 2^8 above it, so that most tiles leave the accumulator alone.
+            float alpha = 1.f;
+            bool rescale = false;
+            if (mx > m_used && (m_used == -INFINITY || (mx - m_used) * sl2 > 8.f)) {
+                alpha = m_used == -INFINITY ? 0.f : fast_exp2((m_used - mx) * sl2);
+                rescale = m_used != -INFINITY;   // nothing accumulated yet otherwise
+                m_used = mx;
+                l *= alpha;
+            }
+            if (j > 0 && __any_sync(0xffffffffu, rescale)) {
+                // The accumulator is quiet between P(j-1)V and P(j)V, which waits for this
+                // tile's probabilities.
                 mbar_wait(b_pv_done + 8 * t, (j - 1) & 1u, abortp, P.status, 51 + t);
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
-                    for (int c = 0; c < 4; c++) {
-                        uint32_t orow[32];
-                        tmem_ld32(o_addr + c * 32, orow);
-                        tmem_ld_wait();
+                for (int c = 0; c < 4; c++) {
+                    uint32_t orow[32];
+                    tmem_ld32(o_addr + c * 32, orow);
+                    tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; i++) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
-                        tmem_st32(o_addr + c * 32, orow);
-                    }
-                    tmem_st_wait();
+                    for (int i = 0; i < 32; i++) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+                    tmem_st32(o_addr + c * 32, orow);
                 }
+                tmem_st_wait();
             }
+            const float ms = (m_used == -INFINITY ? 0.f : m_used) * sl2;
+            float sum0 = 0.f, sum1 = 0.f;
+            // Keys [0, 64) first, handed to the tensor core while the other half is computed.
+            exp_chunk<BF16>(s0, sl2, ms, sum0, sum1);
+            exp_chunk<BF16>(s1, sl2, ms, sum0, sum1);
+            store_half<BF16>(s_addr, s0, s1);
             tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(b_p_half + 16 * t);
+            if (tr) P.trace[(t * 64 + j) * 8 + 1] = clock64();
+            exp_chunk<BF16>(s2, sl2, ms, sum0, sum1);
+            exp_chunk<BF16>(s3, sl2, ms, sum0, sum1);
+            store_half<BF16>(s_addr + 32, s2, s3);
+            l += sum0 + sum1;
+            tc_fence_before();
+            __syncwarp();
             if (tr) P.trace[(t * 64 + j) * 8 + 2] = clock64();
-            mbar_arrive(b_p_full + 8 * t);
+            if (lane == 0) mbar_arrive(b_p_half + 16 * t + 8);
         }
         if (n_tiles > 0) {
             mbar_wait(b_pv_done + 8 * t, (n_tiles - 1) & 1u, abortp, P.status, 53 + t);
+            if (tr0) P.trace[1539] = clock64();
             tc_fence_after();
+            // The tile leaves through shared memory (the Q tile's space: its last reader, the
+            // final S MMA, is long done), so that global stores are whole 256-byte row pieces
+            // rather than one row per lane.  16-bit outputs take one round of 128 dims, f32
+            // outputs two rounds of 64.
             const float inv = 1.0f / l;
-            const size_t obase = ((size_t)(it.row0 + (valid ? r : 0)) * P.hq + head) * D;
+            const uint32_t s_o = t ? s_qb : s_qa;
+            const size_t obase = ((size_t)it.row0 * P.hq + head) * D;
+            const size_t orow = (size_t)P.hq * D;
+            const bool wide = P.out_dtype == YX_F32;
+            const int rounds = wide ? 2 : 1;
 #pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                uint32_t orow[32];
-                tmem_ld32(o_addr + c * 32, orow);
-                tmem_ld_wait();
-                if (valid) {
+            for (int rd = 0; rd < rounds; rd++) {
+#pragma unroll 1
+                for (int c = 0; c < (wide ? 2 : 4); c++) {
+                    uint32_t orow_r[32];
+                    const int col0 = wide ? rd * 64 + c * 32 : c * 32;
+                    tmem_ld32(o_addr + col0, orow_r);
+                    tmem_ld_wait();
+                    // this thread's row r, 16-byte chunks of the staging row (256 bytes, swizzled like an operand half)
+                    auto put = [&](int ch, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
+                        const uint32_t addr = s_o + (ch >> 3) * HALF_BYTES + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+                    };
+                    if (wide) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4)
-                        store4(P.out, P.out_dtype, obase + c * 32 + i,
-                               make_float4(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv,
-                                           __uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv));
+                        for (int i = 0; i < 32; i += 4)
+                            put(c * 8 + (i >> 2), __float_as_uint(__uint_as_float(orow_r[i]) * inv),
+                                __float_as_uint(__uint_as_float(orow_r[i + 1]) * inv), __float_as_uint(__uint_as_float(orow_r[i + 2]) * inv),
+                                __float_as_uint(__uint_as_float(orow_r[i + 3]) * inv));
+                    } else {
+                        const bool ob = P.out_dtype == YX_BF16;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8)
+                            put(c * 4 + (i >> 3), pack_pair(__uint_as_float(orow_r[i]) * inv, __uint_as_float(orow_r[i + 1]) * inv, ob),
+                                pack_pair(__uint_as_float(orow_r[i + 2]) * inv, __uint_as_float(orow_r[i + 3]) * inv, ob),
+                                pack_pair(__uint_as_float(orow_r[i + 4]) * inv, __uint_as_float(orow_r[i + 5]) * inv, ob),
+                                pack_pair(__uint_as_float(orow_r[i + 6]) * inv, __uint_as_float(orow_r[i + 7]) * inv, ob));
+                    }
+                }
+                if (t == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+                else asm volatile("bar.sync 2, 128;" ::: "memory");
+#pragma unroll 4
+                for (int i = 0; i < 16; i++) {
+                    const int idx = i * 128 + r, row = idx >> 4, ch = idx & 15;
+                    if ((uint32_t)row < it.n_rows) {
+                        const uint32_t addr = s_o + (ch >> 3) * HALF_BYTES + row * 128 + (((ch & 7) ^ (row & 7)) << 4);
+                        uint4 w;
+                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "r"(addr));
+                        if (wide) *(uint4 *)((float *)P.out + obase + row * orow + rd * 64 + ch * 4) = w;
+                        else *(uint4 *)((uint16_t *)P.out + obase + row * orow + ch * 8) = w;
+                    }
+                }
+                if (rd + 1 < rounds) {
+                    if (t == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+                    else asm volatile("bar.sync 2, 128;" ::: "memory");
                 }
             }
         }
     }
+    if (tr0) P.trace[1540] = clock64();
     tc_fence_before();
     __syncthreads();
+    if (tr0) P.trace[1541] = clock64();
     if (warp == T2_MMA) {
         if (*abortp) {
             for (int i = 0; i < 64; i++) __nanosleep(1000);
