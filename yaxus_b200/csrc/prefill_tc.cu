@@ -466,11 +466,11 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const TileParams
 // so that a warpgroup's next scores are on their way while the other's probabilities are used.
 // Ten warps: 0-3 softmax of A, 4-7 softmax of B, 8 producer, 9 MMA issuer.
 // =============================================================================================
-constexpr int T2_K_STAGES = 2, T2_V_STAGES = 2;
+constexpr int T2_K_STAGES = 2, T2_V_STAGES = 3;
 constexpr int T2_PRODUCER = 8, T2_MMA = 9;
 constexpr int T2_THREADS = 10 * 32;
-// barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_half[2][2], pv_done[2]
-constexpr int T2_BARS = 1 + 2 * T2_K_STAGES + 2 * T2_V_STAGES + 8;
+// barriers: q_full, k_full[2], v_full[3], s_full_a, s_full_b[2], p_half[2][2], pv_done[2]
+constexpr int T2_BARS = 1 + T2_K_STAGES + T2_V_STAGES + 1 + T2_K_STAGES + 4 + 2;
 constexpr int T2_SMEM_BYTES = PAGE_BYTES * (2 + T2_K_STAGES + T2_V_STAGES) + T2_BARS * 8 + 64;
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -562,9 +562,16 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
     const uint32_t s_v = s_k + T2_K_STAGES * PAGE_BYTES;
     const uint32_t bars = s_v + T2_V_STAGES * PAGE_BYTES;
     const uint32_t b_q_full = bars;
-    const uint32_t b_k_full = bars + 8, b_k_empty = b_k_full + 8 * T2_K_STAGES;
-    const uint32_t b_v_full = b_k_empty + 8 * T2_K_STAGES, b_v_empty = b_v_full + 8 * T2_V_STAGES;
-    const uint32_t b_s_full = b_v_empty + 8 * T2_V_STAGES, b_p_half = b_s_full + 16, b_pv_done = b_p_half + 32;
+    // Every tcgen05.commit costs the tensor pipe a bubble, so one completion signal serves
+    // several waiters.  S of tile B for page j (barrier s_full_b[j & 1]) is the last MMA issued
+    // that reads K stage j & 1, and it is issued after P V of both tiles for page j - 1: its
+    // completion tells softmax warpgroup B that scores are ready and the producer that K stage
+    // j & 1 and V stage (j - 1) % 3 are free.  Likewise S of page j + 1 complete means P V of
+    // page j complete, which is all a rescale of the accumulator needs.  Only the last P V of
+    // each tile gets a commit of its own (pv_done).
+    const uint32_t b_k_full = bars + 8, b_v_full = b_k_full + 8 * T2_K_STAGES;
+    const uint32_t b_s_full_a = b_v_full + 8 * T2_V_STAGES, b_s_full_b = b_s_full_a + 8;
+    const uint32_t b_p_half = b_s_full_b + 8 * T2_K_STAGES, b_pv_done = b_p_half + 32;
     volatile int *abortp = &abort_flag;
 
     const TileItem it = P.items[blockIdx.x];   // it.head is the first of the two heads
@@ -577,14 +584,11 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
         mbar_init(b_q_full, 2);
         for (int s = 0; s < T2_K_STAGES; s++) {
             mbar_init(b_k_full + 8 * s, 1);
-            mbar_init(b_k_empty + 8 * s, 1);
+            mbar_init(b_s_full_b + 8 * s, 1);
         }
-        for (int s = 0; s < T2_V_STAGES; s++) {
-            mbar_init(b_v_full + 8 * s, 1);
-            mbar_init(b_v_empty + 8 * s, 1);
-        }
+        for (int s = 0; s < T2_V_STAGES; s++) mbar_init(b_v_full + 8 * s, 1);
+        mbar_init(b_s_full_a, 1);
         for (int t = 0; t < 2; t++) {
-            mbar_init(b_s_full + 8 * t, 1);
             mbar_init(b_p_half + 16 * t, 4);       // one arrival per softmax warp,
             mbar_init(b_p_half + 16 * t + 8, 4);   // for each 64-key half of the tile
             mbar_init(b_pv_done + 8 * t, 1);
@@ -610,15 +614,13 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
         // ---- producer: one K page and one V page per tile, for both query tiles ---------------
         const uint32_t kvh = it.kv_head;
         const uint32_t last_key = it.pos0 + it.n_rows - 1;
-        uint32_t kph = 0, vph = 0;
-        int ks = 0, vs = 0;
         for (uint32_t c = 0; c < n_tiles; c += 32) {
             const uint32_t mine = it.page_begin + c + lane;
             const uint32_t my_page = mine < it.page_end ? P.pages[it.pt_off + mine] : 0u;
             const uint32_t n = min(32u, n_tiles - c);
-            for (uint32_t j = 0; j < n; j++) {
-                const uint32_t page = __shfl_sync(0xffffffffu, my_page, j);
-                const uint32_t pg = it.page_begin + c + j;
+            for (uint32_t jj = 0; jj < n; jj++) {
+                const uint32_t page = __shfl_sync(0xffffffffu, my_page, jj);
+                const uint32_t j = c + jj, pg = it.page_begin + j;
                 const uint32_t rows = min((uint32_t)PAGE, last_key + 1 - pg * PAGE);
                 int stop = 0;
                 if (lane == 0) {
@@ -629,29 +631,28 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
                         P.status->b = (int)blockIdx.x;
                     }
                     const size_t off = ((size_t)page * P.hkv + kvh) * PAGE_BYTES;
-                    for (int kv = 0; kv < 2; kv++) {
-                        const uint32_t empty = kv ? b_v_empty + 8 * vs : b_k_empty + 8 * ks;
-                        const uint32_t bar = kv ? b_v_full + 8 * vs : b_k_full + 8 * ks;
-                        const uint32_t dst = kv ? s_v + vs * PAGE_BYTES : s_k + ks * PAGE_BYTES;
-                        const char *src = (kv ? P.v_arena : P.k_arena) + off;
-                        mbar_wait(empty, (kv ? vph : kph) ^ 1u, abortp, P.status, 41 + kv);
-                        if (*abortp) break;
-                        if (bad) {
-                            mbar_expect_tx(bar, 0);
-                        } else if (rows == PAGE) {
-                            mbar_expect_tx(bar, PAGE_BYTES);
-                            bulk_g2s(dst, src, PAGE_BYTES, bar);
-                        } else {
-                            mbar_expect_tx(bar, 2 * rows * 128);
-                            bulk_g2s(dst, src, rows * 128, bar);
-                            bulk_g2s(dst + HALF_BYTES, src + HALF_BYTES, rows * 128, bar);
+                    // K stage j & 1 and V stage j % 3 are free once S of tile B for page j - 2 is done.
+                    if (j >= 2) mbar_wait(b_s_full_b + 8 * (j & 1), ((j - 2) >> 1) & 1u, abortp, P.status, 41);
+                    if (!*abortp) {
+                        for (int kv = 0; kv < 2; kv++) {
+                            const uint32_t bar = kv ? b_v_full + 8 * (j % 3) : b_k_full + 8 * (j & 1);
+                            const uint32_t dst = kv ? s_v + (j % 3) * PAGE_BYTES : s_k + (j & 1) * PAGE_BYTES;
+                            const char *src = (kv ? P.v_arena : P.k_arena) + off;
+                            if (bad) {
+                                mbar_expect_tx(bar, 0);
+                            } else if (rows == PAGE) {
+                                mbar_expect_tx(bar, PAGE_BYTES);
+                                bulk_g2s(dst, src, PAGE_BYTES, bar);
+                            } else {
+                                mbar_expect_tx(bar, 2 * rows * 128);
+                                bulk_g2s(dst, src, rows * 128, bar);
+                                bulk_g2s(dst + HALF_BYTES, src + HALF_BYTES, rows * 128, bar);
+                            }
                         }
                     }
                     stop = *abortp;
                 }
                 if (__shfl_sync(0xffffffffu, stop, 0)) break;
-                if (++ks == T2_K_STAGES) { ks = 0; kph ^= 1u; }
-                if (++vs == T2_V_STAGES) { vs = 0; vph ^= 1u; }
             }
             if (*abortp) break;
         }
@@ -661,8 +662,6 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
             const uint32_t idesc_qk = instr_desc(BF16, 0), idesc_pv = instr_desc(BF16, 1);
             mbar_wait(b_q_full, 0, abortp, P.status, 43);
             tc_fence_after();
-            uint32_t kph = 0, vph = 0;
-            int ks = 0, vs = 0;
             // Low descriptor words of the tiles at offset 0; a K-step adds a constant.
             const uint32_t qa_lo = desc_lo(s_qa, 16), qb_lo = desc_lo(s_qb, 16), k_lo = desc_lo(s_k, 16),
                            v_lo = desc_lo(s_v, HALF_BYTES);
@@ -673,12 +672,12 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
                     const uint32_t off = ((k >> 2) * HALF_BYTES + (k & 3) * 32) >> 4;
                     umma_ss_lo(tmem + t * 128, q_lo + off, kk_lo + off, idesc_qk, k > 0 ? 1u : 0u);
                 }
-                umma_commit(b_s_full + 8 * t);
+                umma_commit(t ? b_s_full_b + 8 * stage : b_s_full_a);
             };
             auto stamp = [&](uint32_t j, int e) {
                 if (P.trace && blockIdx.x == 0 && j < 64) P.trace[(2 * 64 + j) * 8 + e] = clock64();
             };
-            auto issue_pv = [&](int t, uint32_t j, int stage) {   // O_t (+)= P_t V, a 64-key half at a time
+            auto issue_pv = [&](int t, uint32_t j, uint32_t stage) {   // O_t (+)= P_t V, a 64-key half at a time
                 const uint32_t vv_lo = v_lo + stage * (PAGE_BYTES >> 4);
 #pragma unroll
                 for (int h = 0; h < 2; h++) {
@@ -692,24 +691,22 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
                         if (BF16) umma_ts_lo(tmem + 256 + t * 128, tmem + t * 128 + 64 + k * 8, vk_lo, idesc_pv, 1u);
                     }
                 }
-                umma_commit(b_pv_done + 8 * t);
+                if (j + 1 == n_tiles) umma_commit(b_pv_done + 8 * t);
             };
             // S_A(0), S_B(0)
             mbar_wait(b_k_full, 0, abortp, P.status, 46);
             tc_fence_after();
             issue_s(0, 0);
             issue_s(1, 0);
-            umma_commit(b_k_empty);
-            ks = 1 % T2_K_STAGES;
-            if (ks == 0) kph ^= 1u;
             for (uint32_t j = 0; j < n_tiles && !*abortp; j++) {
                 const bool more = j + 1 < n_tiles;
-                mbar_wait(b_v_full + 8 * vs, vph, abortp, P.status, 47);
+                const uint32_t ks = (j + 1) & 1u, vs = j % 3;
+                mbar_wait(b_v_full + 8 * vs, (j / 3) & 1u, abortp, P.status, 47);
                 stamp(j, 0);
                 issue_pv(0, j, vs);
                 stamp(j, 2);
                 if (more) {
-                    mbar_wait(b_k_full + 8 * ks, kph, abortp, P.status, 48);
+                    mbar_wait(b_k_full + 8 * ks, ((j + 1) >> 1) & 1u, abortp, P.status, 48);
                     stamp(j, 3);
                     tc_fence_after();
                     issue_s(0, ks);
@@ -717,14 +714,8 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
                 stamp(j, 4);
                 issue_pv(1, j, vs);
                 stamp(j, 6);
-                umma_commit(b_v_empty + 8 * vs);
-                if (more) {
-                    issue_s(1, ks);
-                    umma_commit(b_k_empty + 8 * ks);
-                    if (++ks == T2_K_STAGES) { ks = 0; kph ^= 1u; }
-                }
+                if (more) issue_s(1, ks);
                 stamp(j, 7);
-                if (++vs == T2_V_STAGES) { vs = 0; vph ^= 1u; }
             }
         }
     } else {
@@ -794,7 +785,8 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
         if (tr0) P.trace[1538] = clock64();
         float m_used = -INFINITY, l = 0.f;
         for (uint32_t j = 0; j < n_tiles; j++) {
-            mbar_wait(b_s_full + 8 * t, j & 1u, abortp, P.status, 49 + t);
+            if (t == 0) mbar_wait(b_s_full_a, j & 1u, abortp, P.status, 49);
+            else mbar_wait(b_s_full_b + 8 * (j & 1), (j >> 1) & 1u, abortp, P.status, 50);
             const bool tr = P.trace && blockIdx.x == 0 && r == 0 && j < 64;
             if (tr) P.trace[(t * 64 + j) * 8 + 0] = clock64();
             tc_fence_after();
@@ -829,10 +821,8 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
                 l *= alpha;
             }
             if (j > 0 && __any_sync(0xffffffffu, rescale)) {
-                // The accumulator is quiet between P(j-1)V and P(j)V, which waits for this
-                // tile's probabilities.
-                mbar_wait(b_pv_done + 8 * t, (j - 1) & 1u, abortp, P.status, 51 + t);
-                tc_fence_after();
+                // The accumulator is quiet: these scores were computed after P(j-1)V, and P(j)V
+                // waits for this tile's probabilities.
 #pragma unroll 1
                 for (int c = 0; c < 4; c++) {
                     uint32_t orow[32];
@@ -864,7 +854,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
             if (lane == 0) mbar_arrive(b_p_half + 16 * t + 8);
         }
         if (n_tiles > 0) {
-            mbar_wait(b_pv_done + 8 * t, (n_tiles - 1) & 1u, abortp, P.status, 53 + t);
+            mbar_wait(b_pv_done + 8 * t, 0, abortp, P.status, 53 + t);
             if (tr0) P.trace[1539] = clock64();
             tc_fence_after();
             // The tile leaves through shared memory (the Q tile's space: its last reader, the
