@@ -59,6 +59,7 @@ struct TileParams {
     int p_lo;            // probabilities carry a low part (bf16 cache): O += Ph V + Pl V
     yx_dev_status *status;
     long long *trace;   // diagnostics: clock stamps of CTA 0's pipeline, or null
+    uint32_t n_items;
 };
 
 // Shared-memory matrix descriptor: start address, leading / stride byte offsets (16-byte
@@ -563,19 +564,22 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
     const uint32_t bars = s_v + T2_V_STAGES * PAGE_BYTES;
     const uint32_t b_q_full = bars;
     // Every tcgen05.commit costs the tensor pipe a bubble, so one completion signal serves
-    // several waiters.  S of tile B for page j (barrier s_full_b[j & 1]) is the last MMA issued
-    // that reads K stage j & 1, and it is issued after P V of both tiles for page j - 1: its
+    // several waiters.  S of tile B for page g (barrier s_full_b[g & 1]) is the last MMA issued
+    // that reads K stage g & 1, and it is issued after P V of both tiles for page g - 1: its
     // completion tells softmax warpgroup B that scores are ready and the producer that K stage
-    // j & 1 and V stage (j - 1) % 3 are free.  Likewise S of page j + 1 complete means P V of
-    // page j complete, which is all a rescale of the accumulator needs.  Only the last P V of
-    // each tile gets a commit of its own (pv_done).
+    // g & 1 and V stage (g - 1) % 3 are free.  Likewise S of page g + 1 complete means P V of
+    // page g complete, which is all a rescale of the accumulator needs.  Only the last P V of
+    // each item gets a commit of its own (pv_done).
     const uint32_t b_k_full = bars + 8, b_v_full = b_k_full + 8 * T2_K_STAGES;
     const uint32_t b_s_full_a = b_v_full + 8 * T2_V_STAGES, b_s_full_b = b_s_full_a + 8;
     const uint32_t b_p_half = b_s_full_b + 8 * T2_K_STAGES, b_pv_done = b_p_half + 32;
     volatile int *abortp = &abort_flag;
 
-    const TileItem it = P.items[blockIdx.x];   // it.head is the first of the two heads
-    const uint32_t n_tiles = it.page_end - it.page_begin;
+    // The CTA is persistent: it takes items c, 2G-1-c, 2G+c, ... of the list (G CTAs; the list is
+    // sorted longest first, so the serpentine deals similar totals).  `g` counts the CTA's pages
+    // across its items: ring stages and barrier phases follow g, not the page's index in its item.
+    const uint32_t G = gridDim.x;
+    auto item_index = [&](uint32_t n) { return n * G + ((n & 1u) ? G - 1 - blockIdx.x : blockIdx.x); };
     const bool tr0 = P.trace && blockIdx.x == 0 && threadIdx.x == 0;
     if (tr0) P.trace[1536] = clock64();
 
@@ -595,7 +599,8 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    // Stale rows of a ragged V page meet zero probabilities: they must hold finite numbers.
+    // Rows of a V stage that a ragged page leaves unwritten meet zero probabilities: they must
+    // hold finite numbers (afterwards they hold earlier pages' values, which are).
     for (int i = threadIdx.x; i < T2_V_STAGES * PAGE_BYTES / 16; i += T2_THREADS)
         ((uint4 *)(smem + (2 + T2_K_STAGES) * PAGE_BYTES))[i] = make_uint4(0, 0, 0, 0);
     if (warp == T2_MMA) {
@@ -612,60 +617,63 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
 
     if (warp == T2_PRODUCER) {
         // ---- producer: one K page and one V page per tile, for both query tiles ---------------
-        const uint32_t kvh = it.kv_head;
-        const uint32_t last_key = it.pos0 + it.n_rows - 1;
-        for (uint32_t c = 0; c < n_tiles; c += 32) {
-            const uint32_t mine = it.page_begin + c + lane;
-            const uint32_t my_page = mine < it.page_end ? P.pages[it.pt_off + mine] : 0u;
-            const uint32_t n = min(32u, n_tiles - c);
-            for (uint32_t jj = 0; jj < n; jj++) {
-                const uint32_t page = __shfl_sync(0xffffffffu, my_page, jj);
-                const uint32_t j = c + jj, pg = it.page_begin + j;
-                const uint32_t rows = min((uint32_t)PAGE, last_key + 1 - pg * PAGE);
-                int stop = 0;
-                if (lane == 0) {
-                    const bool bad = page * (uint32_t)P.hkv + kvh >= P.n_blocks;
-                    if (bad && atomicCAS(&P.status->code, 0, 1) == 0) {
-                        P.status->where = 310;
-                        P.status->a = (int)page;
-                        P.status->b = (int)blockIdx.x;
-                    }
-                    const size_t off = ((size_t)page * P.hkv + kvh) * PAGE_BYTES;
-                    // K stage j & 1 and V stage j % 3 are free once S of tile B for page j - 2 is done.
-                    if (j >= 2) mbar_wait(b_s_full_b + 8 * (j & 1), ((j - 2) >> 1) & 1u, abortp, P.status, 41);
-                    if (!*abortp) {
-                        for (int kv = 0; kv < 2; kv++) {
-                            const uint32_t bar = kv ? b_v_full + 8 * (j % 3) : b_k_full + 8 * (j & 1);
-                            const uint32_t dst = kv ? s_v + (j % 3) * PAGE_BYTES : s_k + (j & 1) * PAGE_BYTES;
-                            const char *src = (kv ? P.v_arena : P.k_arena) + off;
-                            if (bad) {
-                                mbar_expect_tx(bar, 0);
-                            } else if (rows == PAGE) {
-                                mbar_expect_tx(bar, PAGE_BYTES);
-                                bulk_g2s(dst, src, PAGE_BYTES, bar);
-                            } else {
-                                mbar_expect_tx(bar, 2 * rows * 128);
-                                bulk_g2s(dst, src, rows * 128, bar);
-                                bulk_g2s(dst + HALF_BYTES, src + HALF_BYTES, rows * 128, bar);
+        uint32_t g = 0;
+        for (uint32_t n = 0; item_index(n) < P.n_items && !*abortp; n++) {
+            const TileItem it = P.items[item_index(n)];
+            const uint32_t n_tiles = it.page_end - it.page_begin;
+            const uint32_t kvh = it.kv_head;
+            const uint32_t last_key = it.pos0 + it.n_rows - 1;
+            for (uint32_t c = 0; c < n_tiles; c += 32) {
+                const uint32_t mine = it.page_begin + c + lane;
+                const uint32_t my_page = mine < it.page_end ? P.pages[it.pt_off + mine] : 0u;
+                const uint32_t cnt = min(32u, n_tiles - c);
+                for (uint32_t jj = 0; jj < cnt; jj++, g++) {
+                    const uint32_t page = __shfl_sync(0xffffffffu, my_page, jj);
+                    const uint32_t pg = it.page_begin + c + jj;
+                    const uint32_t rows = min((uint32_t)PAGE, last_key + 1 - pg * PAGE);
+                    int stop = 0;
+                    if (lane == 0) {
+                        const bool bad = page * (uint32_t)P.hkv + kvh >= P.n_blocks;
+                        if (bad && atomicCAS(&P.status->code, 0, 1) == 0) {
+                            P.status->where = 310;
+                            P.status->a = (int)page;
+                            P.status->b = (int)blockIdx.x;
+                        }
+                        const size_t off = ((size_t)page * P.hkv + kvh) * PAGE_BYTES;
+                        // K stage g & 1 and V stage g % 3 are free once S of tile B for page g - 2 is done.
+                        if (g >= 2) mbar_wait(b_s_full_b + 8 * (g & 1), ((g - 2) >> 1) & 1u, abortp, P.status, 41);
+                        if (!*abortp) {
+                            for (int kv = 0; kv < 2; kv++) {
+                                const uint32_t bar = kv ? b_v_full + 8 * (g % 3) : b_k_full + 8 * (g & 1);
+                                const uint32_t dst = kv ? s_v + (g % 3) * PAGE_BYTES : s_k + (g & 1) * PAGE_BYTES;
+                                const char *src = (kv ? P.v_arena : P.k_arena) + off;
+                                if (bad) {
+                                    mbar_expect_tx(bar, 0);
+                                } else if (rows == PAGE) {
+                                    mbar_expect_tx(bar, PAGE_BYTES);
+                                    bulk_g2s(dst, src, PAGE_BYTES, bar);
+                                } else {
+                                    mbar_expect_tx(bar, 2 * rows * 128);
+                                    bulk_g2s(dst, src, rows * 128, bar);
+                                    bulk_g2s(dst + HALF_BYTES, src + HALF_BYTES, rows * 128, bar);
+                                }
                             }
                         }
+                        stop = *abortp;
                     }
-                    stop = *abortp;
+                    if (__shfl_sync(0xffffffffu, stop, 0)) break;
                 }
-                if (__shfl_sync(0xffffffffu, stop, 0)) break;
+                if (*abortp) break;
             }
-            if (*abortp) break;
         }
     } else if (warp == T2_MMA) {
         // ---- MMA issuer ----------------------------------------------------------------------
-        if (lane == 0 && n_tiles > 0) {
+        if (lane == 0) {
             const uint32_t idesc_qk = instr_desc(BF16, 0), idesc_pv = instr_desc(BF16, 1);
-            mbar_wait(b_q_full, 0, abortp, P.status, 43);
-            tc_fence_after();
             // Low descriptor words of the tiles at offset 0; a K-step adds a constant.
             const uint32_t qa_lo = desc_lo(s_qa, 16), qb_lo = desc_lo(s_qb, 16), k_lo = desc_lo(s_k, 16),
                            v_lo = desc_lo(s_v, HALF_BYTES);
-            auto issue_s = [&](int t, int stage) {   // S_t = Q_t K^T
+            auto issue_s = [&](int t, uint32_t stage) {   // S_t = Q_t K^T
                 const uint32_t q_lo = t ? qb_lo : qa_lo, kk_lo = k_lo + stage * (PAGE_BYTES >> 4);
 #pragma unroll
                 for (int k = 0; k < 8; k++) {
@@ -674,249 +682,251 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
                 }
                 umma_commit(t ? b_s_full_b + 8 * stage : b_s_full_a);
             };
-            auto stamp = [&](uint32_t j, int e) {
-                if (P.trace && blockIdx.x == 0 && j < 64) P.trace[(2 * 64 + j) * 8 + e] = clock64();
+            auto stamp = [&](uint32_t g, int e) {
+                if (P.trace && blockIdx.x == 0 && g < 64) P.trace[(2 * 64 + g) * 8 + e] = clock64();
             };
-            auto issue_pv = [&](int t, uint32_t j, uint32_t stage) {   // O_t (+)= P_t V, a 64-key half at a time
-                const uint32_t vv_lo = v_lo + stage * (PAGE_BYTES >> 4);
+            // O_t (+)= P_t V, a 64-key half at a time; `first`: the item's first page
+            auto issue_pv = [&](int t, uint32_t g, bool first, bool last) {
+                const uint32_t vv_lo = v_lo + (g % 3) * (PAGE_BYTES >> 4);
 #pragma unroll
                 for (int h = 0; h < 2; h++) {
-                    mbar_wait(b_p_half + 16 * t + 8 * h, j & 1u, abortp, P.status, 44 + t);
-                    if (h == 0) stamp(j, t ? 5 : 1);
+                    mbar_wait(b_p_half + 16 * t + 8 * h, g & 1u, abortp, P.status, 44 + t);
+                    if (h == 0) stamp(g, t ? 5 : 1);
                     tc_fence_after();
 #pragma unroll
                     for (int k = 4 * h; k < 4 * h + 4; k++) {
                         const uint32_t vk_lo = vv_lo + ((k * 16 * 128) >> 4);
-                        umma_ts_lo(tmem + 256 + t * 128, tmem + t * 128 + k * 8, vk_lo, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                        umma_ts_lo(tmem + 256 + t * 128, tmem + t * 128 + k * 8, vk_lo, idesc_pv, (!first || k > 0) ? 1u : 0u);
                         if (BF16) umma_ts_lo(tmem + 256 + t * 128, tmem + t * 128 + 64 + k * 8, vk_lo, idesc_pv, 1u);
                     }
                 }
-                if (j + 1 == n_tiles) umma_commit(b_pv_done + 8 * t);
+                if (last) umma_commit(b_pv_done + 8 * t);
             };
-            // S_A(0), S_B(0)
-            mbar_wait(b_k_full, 0, abortp, P.status, 46);
-            tc_fence_after();
-            issue_s(0, 0);
-            issue_s(1, 0);
-            for (uint32_t j = 0; j < n_tiles && !*abortp; j++) {
-                const bool more = j + 1 < n_tiles;
-                const uint32_t ks = (j + 1) & 1u, vs = j % 3;
-                mbar_wait(b_v_full + 8 * vs, (j / 3) & 1u, abortp, P.status, 47);
-                stamp(j, 0);
-                issue_pv(0, j, vs);
-                stamp(j, 2);
-                if (more) {
-                    mbar_wait(b_k_full + 8 * ks, ((j + 1) >> 1) & 1u, abortp, P.status, 48);
-                    stamp(j, 3);
-                    tc_fence_after();
-                    issue_s(0, ks);
+            uint32_t g = 0;
+            for (uint32_t n = 0; item_index(n) < P.n_items && !*abortp; n++) {
+                const TileItem it = P.items[item_index(n)];
+                const uint32_t n_tiles = it.page_end - it.page_begin;
+                mbar_wait(b_q_full, n & 1u, abortp, P.status, 43);
+                mbar_wait(b_k_full + 8 * (g & 1), (g >> 1) & 1u, abortp, P.status, 46);
+                tc_fence_after();
+                issue_s(0, g & 1);
+                issue_s(1, g & 1);
+                for (uint32_t j = 0; j < n_tiles && !*abortp; j++, g++) {
+                    const bool more = j + 1 < n_tiles;
+                    mbar_wait(b_v_full + 8 * (g % 3), (g / 3) & 1u, abortp, P.status, 47);
+                    stamp(g, 0);
+                    issue_pv(0, g, j == 0, !more);
+                    stamp(g, 2);
+                    if (more) {
+                        mbar_wait(b_k_full + 8 * ((g + 1) & 1), ((g + 1) >> 1) & 1u, abortp, P.status, 48);
+                        stamp(g, 3);
+                        tc_fence_after();
+                        issue_s(0, (g + 1) & 1);
+                    }
+                    stamp(g, 4);
+                    issue_pv(1, g, j == 0, !more);
+                    stamp(g, 6);
+                    if (more) issue_s(1, (g + 1) & 1);
+                    stamp(g, 7);
                 }
-                stamp(j, 4);
-                issue_pv(1, j, vs);
-                stamp(j, 6);
-                if (more) issue_s(1, ks);
-                stamp(j, 7);
             }
         }
     } else {
         // ---- softmax warpgroups: warps 0-3 tile A (head), warps 4-7 tile B (head + 1) -----------
         const int t = warp >> 2;
         const int r = threadIdx.x & 127;
-        const bool valid = (uint32_t)r < it.n_rows;
-        const uint32_t head = it.head + t;
-        const uint32_t pos = it.pos0 + (valid ? r : 0);
-        uint32_t klo = 0;
-        if (P.window > 0 && pos + 1 > P.window) klo = pos + 1 - P.window;
-        const uint32_t khi = pos;
         const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t s_addr = lane_addr + t * 128, o_addr = lane_addr + 256 + t * 128;
-        {
-            // Q tile to shared memory in the operand layout.  Work is dealt by 16-byte chunk, not
-            // by row: 16 consecutive threads read one row's 256 (or 512) contiguous bytes, and
-            // all of a thread's loads are issued before the first store, so the tile costs one
-            // trip to memory.
-            const uint32_t s_q = t ? s_qb : s_qa;
-            const size_t qbase = ((size_t)it.row0 * P.hq + head) * D;
-            const size_t qrow = (size_t)P.hq * D;
-            auto chunk_addr = [&](int row, int c) {
-                return s_q + (c >> 3) * HALF_BYTES + row * 128 + (((c & 7) ^ (row & 7)) << 4);
-            };
-            if (P.q_dtype == (BF16 ? YX_BF16 : YX_F16)) {
-                uint4 w[16];
-#pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    const int idx = i * 128 + r, row = idx >> 4, c = idx & 15;
-                    w[i] = make_uint4(0, 0, 0, 0);
-                    if ((uint32_t)row < it.n_rows) w[i] = *(const uint4 *)((const uint16_t *)P.q + qbase + row * qrow + c * 8);
-                }
-#pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    const int idx = i * 128 + r, row = idx >> 4, c = idx & 15;
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(chunk_addr(row, c)), "r"(w[i].x), "r"(w[i].y), "r"(w[i].z), "r"(w[i].w) : "memory");
-                }
-            } else {
-#pragma unroll 1
-                for (int i0 = 0; i0 < 16; i0 += 4) {
-                    float4 lo4[4], hi4[4];
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const int idx = (i0 + i) * 128 + r, row = idx >> 4, c = idx & 15;
-                        lo4[i] = hi4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if ((uint32_t)row < it.n_rows) {
-                            lo4[i] = load4_as_f32(P.q, P.q_dtype, qbase + row * qrow + c * 8);
-                            hi4[i] = load4_as_f32(P.q, P.q_dtype, qbase + row * qrow + c * 8 + 4);
-                        }
-                    }
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const int idx = (i0 + i) * 128 + r, row = idx >> 4, c = idx & 15;
-                        const uint32_t w0 = pack_pair(lo4[i].x, lo4[i].y, BF16), w1 = pack_pair(lo4[i].z, lo4[i].w, BF16),
-                                       w2 = pack_pair(hi4[i].x, hi4[i].y, BF16), w3 = pack_pair(hi4[i].z, hi4[i].w, BF16);
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(chunk_addr(row, c)), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
-                    }
-                }
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            // one named barrier per warpgroup
+        const uint32_t s_q = t ? s_qb : s_qa;
+        const size_t qrow = (size_t)P.hq * D;
+        const bool q_direct = P.q_dtype == (BF16 ? YX_BF16 : YX_F16);
+        auto wg_sync = [&]() {   // one named barrier per warpgroup
             if (t == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
             else asm volatile("bar.sync 2, 128;" ::: "memory");
+        };
+        auto chunk_addr = [&](int row, int c) {
+            return s_q + (c >> 3) * HALF_BYTES + row * 128 + (((c & 7) ^ (row & 7)) << 4);
+        };
+        // Q tile in the operand layout.  Work is dealt by 16-byte chunk, not by row: 16 consecutive
+        // threads read one row's 256 contiguous bytes.  A tile of the cache's own type is copied
+        // global -> shared asynchronously (16 bytes per copy, rows past the item's end zero-filled),
+        // so the next item's tile can be fetched while the current item finishes; other types are
+        // converted on the way through registers.
+        auto q_async = [&](const TileItem &ti) {
+            const size_t qbase = ((size_t)ti.row0 * P.hq + ti.head + t) * D;
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const int idx = i * 128 + r, row = idx >> 4, c = idx & 15;
+                const bool ok = (uint32_t)row < ti.n_rows;
+                const uint16_t *src = (const uint16_t *)P.q + qbase + (ok ? row : 0) * qrow + c * 8;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(chunk_addr(row, c)), "l"(src), "r"(ok ? 16 : 0) : "memory");
+            }
+        };
+        auto q_convert = [&](const TileItem &ti) {
+            const size_t qbase = ((size_t)ti.row0 * P.hq + ti.head + t) * D;
+#pragma unroll 1
+            for (int i0 = 0; i0 < 16; i0 += 4) {
+                float4 lo4[4], hi4[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int idx = (i0 + i) * 128 + r, row = idx >> 4, c = idx & 15;
+                    lo4[i] = hi4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if ((uint32_t)row < ti.n_rows) {
+                        lo4[i] = load4_as_f32(P.q, P.q_dtype, qbase + row * qrow + c * 8);
+                        hi4[i] = load4_as_f32(P.q, P.q_dtype, qbase + row * qrow + c * 8 + 4);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int idx = (i0 + i) * 128 + r, row = idx >> 4, c = idx & 15;
+                    const uint32_t w0 = pack_pair(lo4[i].x, lo4[i].y, BF16), w1 = pack_pair(lo4[i].z, lo4[i].w, BF16),
+                                   w2 = pack_pair(hi4[i].x, hi4[i].y, BF16), w3 = pack_pair(hi4[i].z, hi4[i].w, BF16);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(chunk_addr(row, c)), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+                }
+            }
+        };
+        // Makes the staged tile visible to the tensor core and tells the MMA issuer.
+        auto q_publish = [&]() {
+            asm volatile("cp.async.wait_all;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            wg_sync();
             if (r == 0) mbar_arrive(b_q_full);
+        };
+
+        uint32_t g = 0;
+        TileItem it{};
+        if (item_index(0) < P.n_items) {
+            it = P.items[item_index(0)];
+            if (q_direct) q_async(it);
+            else q_convert(it);
+            q_publish();
         }
         if (tr0) P.trace[1538] = clock64();
-        float m_used = -INFINITY, l = 0.f;
-        for (uint32_t j = 0; j < n_tiles; j++) {
-            if (t == 0) mbar_wait(b_s_full_a, j & 1u, abortp, P.status, 49);
-            else mbar_wait(b_s_full_b + 8 * (j & 1), (j >> 1) & 1u, abortp, P.status, 50);
-            const bool tr = P.trace && blockIdx.x == 0 && r == 0 && j < 64;
-            if (tr) P.trace[(t * 64 + j) * 8 + 0] = clock64();
-            tc_fence_after();
-            const uint32_t key0 = (it.page_begin + j) * PAGE;
-            // Warp-uniform decision: the TMEM accesses inside are warp-wide (.sync.aligned) and
-            // must not sit under a per-lane condition.
-            if (__any_sync(0xffffffffu, key0 < klo || key0 + PAGE - 1 > khi)) mask_scores(s_addr, key0, klo, khi);
-            // The tile's scores, read once and held in registers.
-            uint32_t s0[32], s1[32], s2[32], s3[32];
-            tmem_ld32(s_addr, s0);
-            tmem_ld32(s_addr + 32, s1);
-            tmem_ld32(s_addr + 64, s2);
-            tmem_ld32(s_addr + 96, s3);
-            tmem_ld_wait();
-            float ma = -INFINITY, mb = -INFINITY, mc = -INFINITY, md = -INFINITY;
+        for (uint32_t n = 0; item_index(n) < P.n_items && !*abortp; n++) {
+            const uint32_t n_tiles = it.page_end - it.page_begin;
+            const bool valid = (uint32_t)r < it.n_rows;
+            const uint32_t head = it.head + t;
+            const uint32_t pos = it.pos0 + (valid ? r : 0);
+            uint32_t klo = 0;
+            if (P.window > 0 && pos + 1 > P.window) klo = pos + 1 - P.window;
+            const uint32_t khi = pos;
+            const bool have_next = item_index(n + 1) < P.n_items;
+            TileItem next{};
+            if (have_next) next = P.items[item_index(n + 1)];
+            float m_used = -INFINITY, l = 0.f;
+            for (uint32_t j = 0; j < n_tiles; j++, g++) {
+                if (t == 0) mbar_wait(b_s_full_a, g & 1u, abortp, P.status, 49);
+                else mbar_wait(b_s_full_b + 8 * (g & 1), (g >> 1) & 1u, abortp, P.status, 50);
+                const bool tr = P.trace && blockIdx.x == 0 && r == 0 && g < 64;
+                if (tr) P.trace[(t * 64 + g) * 8 + 0] = clock64();
+                tc_fence_after();
+                // The item's last scores are computed: nothing reads its Q tile any more, and the
+                // next item's can start to arrive.
+                if (j + 1 == n_tiles && have_next && q_direct) q_async(next);
+                const uint32_t key0 = (it.page_begin + j) * PAGE;
+                // Warp-uniform decision: the TMEM accesses inside are warp-wide (.sync.aligned) and
+                // must not sit under a per-lane condition.
+                if (__any_sync(0xffffffffu, key0 < klo || key0 + PAGE - 1 > khi)) mask_scores(s_addr, key0, klo, khi);
+                // The tile's scores, read once and held in registers.
+                uint32_t s0[32], s1[32], s2[32], s3[32];
+                tmem_ld32(s_addr, s0);
+                tmem_ld32(s_addr + 32, s1);
+                tmem_ld32(s_addr + 64, s2);
+                tmem_ld32(s_addr + 96, s3);
+                tmem_ld_wait();
+                float ma = -INFINITY, mb = -INFINITY, mc = -INFINITY, md = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                ma = max3(ma, __uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
-                mb = max3(mb, __uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
-                mc = max3(mc, __uint_as_float(s2[i]), __uint_as_float(s2[i + 1]));
-                md = max3(md, __uint_as_float(s3[i]), __uint_as_float(s3[i + 1]));
-            }
-            const float mx = fmaxf(fmaxf(ma, mb), fmaxf(mc, md));
-            // Lazy rescaling: the reference maximum moves only when the new one is more than
-            // 2^8 above it, so that most tiles leave the accumulator alone.
-            float alpha = 1.f;
-            bool rescale = false;
-            if (mx > m_used && (m_used == -INFINITY || (mx - m_used) * sl2 > 8.f)) {
-                alpha = m_used == -INFINITY ? 0.f : fast_exp2((m_used - mx) * sl2);
-                rescale = m_used != -INFINITY;   // nothing accumulated yet otherwise
-                m_used = mx;
-                l *= alpha;
-            }
-            if (j > 0 && __any_sync(0xffffffffu, rescale)) {
-                // The accumulator is quiet: these scores were computed after P(j-1)V, and P(j)V
-                // waits for this tile's probabilities.
-#pragma unroll 1
-                for (int c = 0; c < 4; c++) {
-                    uint32_t orow[32];
-                    tmem_ld32(o_addr + c * 32, orow);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; i++) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
-                    tmem_st32(o_addr + c * 32, orow);
+                for (int i = 0; i < 32; i += 2) {
+                    ma = max3(ma, __uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
+                    mb = max3(mb, __uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
+                    mc = max3(mc, __uint_as_float(s2[i]), __uint_as_float(s2[i + 1]));
+                    md = max3(md, __uint_as_float(s3[i]), __uint_as_float(s3[i + 1]));
                 }
-                tmem_st_wait();
+                const float mx = fmaxf(fmaxf(ma, mb), fmaxf(mc, md));
+                // Lazy rescaling: the reference maximum moves only when the new one is more than
+                // 2^8 above it, so that most tiles leave the accumulator alone.
+                float alpha = 1.f;
+                bool rescale = false;
+                if (mx > m_used && (m_used == -INFINITY || (mx - m_used) * sl2 > 8.f)) {
+                    alpha = m_used == -INFINITY ? 0.f : fast_exp2((m_used - mx) * sl2);
+                    rescale = m_used != -INFINITY;   // nothing accumulated yet otherwise
+                    m_used = mx;
+                    l *= alpha;
+                }
+                if (j > 0 && __any_sync(0xffffffffu, rescale)) {
+                    // The accumulator is quiet: these scores were computed after P(j-1)V, and P(j)V
+                    // waits for this tile's probabilities.
+#pragma unroll 1
+                    for (int c = 0; c < 4; c++) {
+                        uint32_t orow[32];
+                        tmem_ld32(o_addr + c * 32, orow);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+                        tmem_st32(o_addr + c * 32, orow);
+                    }
+                    tmem_st_wait();
+                }
+                const float ms = (m_used == -INFINITY ? 0.f : m_used) * sl2;
+                float sum0 = 0.f, sum1 = 0.f;
+                // Keys [0, 64) first, handed to the tensor core while the other half is computed.
+                exp_chunk<BF16>(s0, sl2, ms, sum0, sum1);
+                exp_chunk<BF16>(s1, sl2, ms, sum0, sum1);
+                store_half<BF16>(s_addr, s0, s1);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(b_p_half + 16 * t);
+                if (tr) P.trace[(t * 64 + g) * 8 + 1] = clock64();
+                exp_chunk<BF16>(s2, sl2, ms, sum0, sum1);
+                exp_chunk<BF16>(s3, sl2, ms, sum0, sum1);
+                store_half<BF16>(s_addr + 32, s2, s3);
+                l += sum0 + sum1;
+                tc_fence_before();
+                __syncwarp();
+                if (tr) P.trace[(t * 64 + g) * 8 + 2] = clock64();
+                if (lane == 0) mbar_arrive(b_p_half + 16 * t + 8);
             }
-            const float ms = (m_used == -INFINITY ? 0.f : m_used) * sl2;
-            float sum0 = 0.f, sum1 = 0.f;
-            // Keys [0, 64) first, handed to the tensor core while the other half is computed.
-            exp_chunk<BF16>(s0, sl2, ms, sum0, sum1);
-            exp_chunk<BF16>(s1, sl2, ms, sum0, sum1);
-            store_half<BF16>(s_addr, s0, s1);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(b_p_half + 16 * t);
-            if (tr) P.trace[(t * 64 + j) * 8 + 1] = clock64();
-            exp_chunk<BF16>(s2, sl2, ms, sum0, sum1);
-            exp_chunk<BF16>(s3, sl2, ms, sum0, sum1);
-            store_half<BF16>(s_addr + 32, s2, s3);
-            l += sum0 + sum1;
-            tc_fence_before();
-            __syncwarp();
-            if (tr) P.trace[(t * 64 + j) * 8 + 2] = clock64();
-            if (lane == 0) mbar_arrive(b_p_half + 16 * t + 8);
-        }
-        if (n_tiles > 0) {
-            mbar_wait(b_pv_done + 8 * t, 0, abortp, P.status, 53 + t);
-            if (tr0) P.trace[1539] = clock64();
+            // The next item's Q tile is published before this item's epilogue: its first scores
+            // are computed meanwhile.  (Its first P V cannot start before this warpgroup has left
+            // the epilogue and delivered probabilities, so the accumulator read below is safe.)
+            if (have_next) {
+                if (!q_direct) q_convert(next);
+                q_publish();
+            }
+            mbar_wait(b_pv_done + 8 * t, n & 1u, abortp, P.status, 53 + t);
+            if (tr0 && n == 0) P.trace[1539] = clock64();
             tc_fence_after();
-            // The tile leaves through shared memory (the Q tile's space: its last reader, the
-            // final S MMA, is long done), so that global stores are whole 256-byte row pieces
-            // rather than one row per lane.  16-bit outputs take one round of 128 dims, f32
-            // outputs two rounds of 64.
+            // Each thread writes its own row, 16 bytes at a time.
             const float inv = 1.0f / l;
-            const uint32_t s_o = t ? s_qb : s_qa;
-            const size_t obase = ((size_t)it.row0 * P.hq + head) * D;
-            const size_t orow = (size_t)P.hq * D;
-            const bool wide = P.out_dtype == YX_F32;
-            const int rounds = wide ? 2 : 1;
+            const size_t obase = ((size_t)(it.row0 + (valid ? r : 0)) * P.hq + head) * D;
 #pragma unroll 1
-            for (int rd = 0; rd < rounds; rd++) {
-#pragma unroll 1
-                for (int c = 0; c < (wide ? 2 : 4); c++) {
-                    uint32_t orow_r[32];
-                    const int col0 = wide ? rd * 64 + c * 32 : c * 32;
-                    tmem_ld32(o_addr + col0, orow_r);
-                    tmem_ld_wait();
-                    // this thread's row r, 16-byte chunks of the staging row (256 bytes, swizzled like an operand half)
-                    auto put = [&](int ch, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
-                        const uint32_t addr = s_o + (ch >> 3) * HALF_BYTES + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
-                    };
-                    if (wide) {
+            for (int c = 0; c < 4; c++) {
+                uint32_t orow_r[32];
+                tmem_ld32(o_addr + c * 32, orow_r);
+                tmem_ld_wait();
+                if (valid) {
+                    if (P.out_dtype == YX_F32) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 4)
-                            put(c * 8 + (i >> 2), __float_as_uint(__uint_as_float(orow_r[i]) * inv),
-                                __float_as_uint(__uint_as_float(orow_r[i + 1]) * inv), __float_as_uint(__uint_as_float(orow_r[i + 2]) * inv),
-                                __float_as_uint(__uint_as_float(orow_r[i + 3]) * inv));
+                            *(float4 *)((float *)P.out + obase + c * 32 + i) =
+                                make_float4(__uint_as_float(orow_r[i]) * inv, __uint_as_float(orow_r[i + 1]) * inv,
+                                            __uint_as_float(orow_r[i + 2]) * inv, __uint_as_float(orow_r[i + 3]) * inv);
                     } else {
                         const bool ob = P.out_dtype == YX_BF16;
 #pragma unroll
                         for (int i = 0; i < 32; i += 8)
-                            put(c * 4 + (i >> 3), pack_pair(__uint_as_float(orow_r[i]) * inv, __uint_as_float(orow_r[i + 1]) * inv, ob),
-                                pack_pair(__uint_as_float(orow_r[i + 2]) * inv, __uint_as_float(orow_r[i + 3]) * inv, ob),
-                                pack_pair(__uint_as_float(orow_r[i + 4]) * inv, __uint_as_float(orow_r[i + 5]) * inv, ob),
-                                pack_pair(__uint_as_float(orow_r[i + 6]) * inv, __uint_as_float(orow_r[i + 7]) * inv, ob));
+                            *(uint4 *)((uint16_t *)P.out + obase + c * 32 + i) =
+                                make_uint4(pack_pair(__uint_as_float(orow_r[i]) * inv, __uint_as_float(orow_r[i + 1]) * inv, ob),
+                                           pack_pair(__uint_as_float(orow_r[i + 2]) * inv, __uint_as_float(orow_r[i + 3]) * inv, ob),
+                                           pack_pair(__uint_as_float(orow_r[i + 4]) * inv, __uint_as_float(orow_r[i + 5]) * inv, ob),
+                                           pack_pair(__uint_as_float(orow_r[i + 6]) * inv, __uint_as_float(orow_r[i + 7]) * inv, ob));
                     }
-                }
-                if (t == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
-                else asm volatile("bar.sync 2, 128;" ::: "memory");
-#pragma unroll 4
-                for (int i = 0; i < 16; i++) {
-                    const int idx = i * 128 + r, row = idx >> 4, ch = idx & 15;
-                    if ((uint32_t)row < it.n_rows) {
-                        const uint32_t addr = s_o + (ch >> 3) * HALF_BYTES + row * 128 + (((ch & 7) ^ (row & 7)) << 4);
-                        uint4 w;
-                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "r"(addr));
-                        if (wide) *(uint4 *)((float *)P.out + obase + row * orow + rd * 64 + ch * 4) = w;
-                        else *(uint4 *)((uint16_t *)P.out + obase + row * orow + ch * 8) = w;
-                    }
-                }
-                if (rd + 1 < rounds) {
-                    if (t == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
-                    else asm volatile("bar.sync 2, 128;" ::: "memory");
                 }
             }
+            if (tr0 && n == 0) P.trace[1540] = clock64();
+            it = next;
         }
     }
-    if (tr0) P.trace[1540] = clock64();
     tc_fence_before();
     __syncthreads();
     if (tr0) P.trace[1541] = clock64();
@@ -967,8 +977,10 @@ int launch_prefill_tc(yx_ctx *ctx, const TileArgs &a) {
                 return rc;
             ctx->smem_configured[7] = true;
         }
-        if (P.bf16) prefill_tc2_kernel<true><<<a.n_items, T2_THREADS, T2_SMEM_BYTES, ctx->stream>>>(P);
-        else prefill_tc2_kernel<false><<<a.n_items, T2_THREADS, T2_SMEM_BYTES, ctx->stream>>>(P);
+        P.n_items = (uint32_t)a.n_items;
+        const int grid = std::min(a.n_items, ctx->sm_count);   // persistent: one CTA per SM
+        if (P.bf16) prefill_tc2_kernel<true><<<grid, T2_THREADS, T2_SMEM_BYTES, ctx->stream>>>(P);
+        else prefill_tc2_kernel<false><<<grid, T2_THREADS, T2_SMEM_BYTES, ctx->stream>>>(P);
     } else {
         prefill_tc_kernel<<<a.n_items, THREADS, SMEM_BYTES, ctx->stream>>>(P);
     }
