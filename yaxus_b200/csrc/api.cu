@@ -173,7 +173,8 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
     const size_t til_b = pad16(pl.tiles.size() * sizeof(TileDesc));
     const size_t rec_b = pl.recs.size() * sizeof(ItemRec);
     const size_t tit_b = pl.tile_items.size() * sizeof(TileItem);
-    const size_t total = items_b + cta_b + mer_b + hdr_b + til_b + rec_b + tit_b;
+    const size_t tcb_b = pad16(pl.tile_cta_begin.size() * sizeof(uint32_t));
+    const size_t total = items_b + cta_b + mer_b + hdr_b + til_b + rec_b + tit_b + tcb_b;
     if (int rc = ensure_buffer(ctx, (void **)&slot->dev, &slot->dev_cap, total)) {
         slot->pass_serial = 0;
         return rc;
@@ -193,6 +194,7 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
     const size_t o_til = put(pl.tiles.data(), pl.tiles.size() * sizeof(TileDesc), til_b);
     const size_t o_rec = put(pl.recs.data(), rec_b, rec_b);
     const size_t o_tit = put(pl.tile_items.data(), tit_b, tit_b);
+    const size_t o_tcb = put(pl.tile_cta_begin.data(), pl.tile_cta_begin.size() * sizeof(uint32_t), tcb_b);
     if (int rc = upload_ordered(ctx, slot->dev, blob.data(), total)) {
         slot->pass_serial = 0;
         return rc;
@@ -204,6 +206,7 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
     slot->d_tiles = (TileDesc *)(slot->dev + o_til);
     slot->d_recs = (ItemRec *)(slot->dev + o_rec);
     slot->d_tile_items = (TileItem *)(slot->dev + o_tit);
+    slot->d_tile_cta_begin = (uint32_t *)(slot->dev + o_tcb);
     *out = slot;
     return YX_OK;
 }
@@ -257,6 +260,7 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     if (path == 2 && out && !o_out && ctx->tuning.force_path != 2)
         pp.tile_min_rows = ctx->tuning.force_path == 3 ? 1 : (ctx->tuning.tile_min_rows > 0 ? ctx->tuning.tile_min_rows : 64);
     // Two heads per item unless the group is odd or f32 queries need their low part (bf16 caches).
+    pp.tile_ctas = ctx->sm_count;
     pp.tile_pairs = group % 2 == 0 && !(kv->dtype == YX_BF16 && q_dtype == YX_F32) && ctx->tuning.tile_single != 1;
     pp.min_piece = path == 2 ? 4 : 1;
     pp.item_cost = ctx->tuning.item_cost > 0 ? ctx->tuning.item_cost - 1 : (path == 2 ? 48 : 0);
@@ -330,6 +334,8 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
         t.window = pp.window;
         t.items = cp->d_tile_items;
         t.n_items = (int)pl.tile_items.size();
+        t.cta_begin = cp->d_tile_cta_begin;
+        t.n_ctas = (int)pl.tile_cta_begin.size() - 1;
         t.out = out;
         t.out_dtype = out_dtype;
         t.pairs = pp.tile_pairs;

@@ -14,6 +14,8 @@
 #include <string.h>
 
 #include <algorithm>
+#include <functional>
+#include <queue>
 #include <string>
 #include <unordered_map>
 
@@ -101,6 +103,29 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
         std::stable_sort(out.tile_items.begin(), out.tile_items.end(), [](const TileItem &a, const TileItem &b) {
             return a.page_end - a.page_begin > b.page_end - b.page_begin;
         });
+        // Deal the items to the persistent CTAs of the tiled kernel: longest first, each to the
+        // CTA with the least work so far.  An item costs its pages plus a fixed part (Q tile in,
+        // output tile out, pipeline fill), about three pages' worth.
+        if (!out.tile_items.empty()) {
+            const int n_items = (int)out.tile_items.size();
+            const int G = std::max(1, std::min(n_items, pp.tile_ctas > 0 ? pp.tile_ctas : n_items));
+            using Load = std::pair<uint64_t, int>;   // (work, CTA)
+            std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
+            for (int c = 0; c < G; c++) heap.push({0, c});
+            std::vector<std::vector<TileItem>> per(G);
+            for (const TileItem &ti : out.tile_items) {
+                Load top = heap.top();
+                heap.pop();
+                per[top.second].push_back(ti);
+                heap.push({top.first + (ti.page_end - ti.page_begin) + 3, top.second});
+            }
+            out.tile_items.clear();
+            out.tile_cta_begin.assign(1, 0);
+            for (int c = 0; c < G; c++) {
+                out.tile_items.insert(out.tile_items.end(), per[c].begin(), per[c].end());
+                out.tile_cta_begin.push_back((uint32_t)out.tile_items.size());
+            }
+        }
     }
 
     // 2. Units.  First the per-sequence ones, rows chunked to max_rows.

@@ -59,7 +59,7 @@ struct TileParams {
     int p_lo;            // probabilities carry a low part (bf16 cache): O += Ph V + Pl V
     yx_dev_status *status;
     long long *trace;   // diagnostics: clock stamps of CTA 0's pipeline, or null
-    uint32_t n_items;
+    const uint32_t *cta_begin;   // items of persistent CTA c: [cta_begin[c], cta_begin[c + 1])
 };
 
 // Shared-memory matrix descriptor: start address, leading / stride byte offsets (16-byte
@@ -575,11 +575,10 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
     const uint32_t b_p_half = b_s_full_b + 8 * T2_K_STAGES, b_pv_done = b_p_half + 32;
     volatile int *abortp = &abort_flag;
 
-    // The CTA is persistent: it takes items c, 2G-1-c, 2G+c, ... of the list (G CTAs; the list is
-    // sorted longest first, so the serpentine deals similar totals).  `g` counts the CTA's pages
-    // across its items: ring stages and barrier phases follow g, not the page's index in its item.
-    const uint32_t G = gridDim.x;
-    auto item_index = [&](uint32_t n) { return n * G + ((n & 1u) ? G - 1 - blockIdx.x : blockIdx.x); };
+    // The CTA is persistent: the host dealt it items [item0, item_end) of the list.  `g` counts
+    // the CTA's pages across its items: ring stages and barrier phases follow g, not the page's
+    // index in its item.
+    const uint32_t item0 = P.cta_begin[blockIdx.x], item_end = P.cta_begin[blockIdx.x + 1];
     const bool tr0 = P.trace && blockIdx.x == 0 && threadIdx.x == 0;
     if (tr0) P.trace[1536] = clock64();
 
@@ -618,8 +617,8 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
     if (warp == T2_PRODUCER) {
         // ---- producer: one K page and one V page per tile, for both query tiles ---------------
         uint32_t g = 0;
-        for (uint32_t n = 0; item_index(n) < P.n_items && !*abortp; n++) {
-            const TileItem it = P.items[item_index(n)];
+        for (uint32_t n = 0; item0 + n < item_end && !*abortp; n++) {
+            const TileItem it = P.items[item0 + n];
             const uint32_t n_tiles = it.page_end - it.page_begin;
             const uint32_t kvh = it.kv_head;
             const uint32_t last_key = it.pos0 + it.n_rows - 1;
@@ -703,8 +702,8 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
                 if (last) umma_commit(b_pv_done + 8 * t);
             };
             uint32_t g = 0;
-            for (uint32_t n = 0; item_index(n) < P.n_items && !*abortp; n++) {
-                const TileItem it = P.items[item_index(n)];
+            for (uint32_t n = 0; item0 + n < item_end && !*abortp; n++) {
+                const TileItem it = P.items[item0 + n];
                 const uint32_t n_tiles = it.page_end - it.page_begin;
                 mbar_wait(b_q_full, n & 1u, abortp, P.status, 43);
                 mbar_wait(b_k_full + 8 * (g & 1), (g >> 1) & 1u, abortp, P.status, 46);
@@ -795,14 +794,14 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
 
         uint32_t g = 0;
         TileItem it{};
-        if (item_index(0) < P.n_items) {
-            it = P.items[item_index(0)];
+        if (item0 < item_end) {
+            it = P.items[item0];
             if (q_direct) q_async(it);
             else q_convert(it);
             q_publish();
         }
         if (tr0) P.trace[1538] = clock64();
-        for (uint32_t n = 0; item_index(n) < P.n_items && !*abortp; n++) {
+        for (uint32_t n = 0; item0 + n < item_end && !*abortp; n++) {
             const uint32_t n_tiles = it.page_end - it.page_begin;
             const bool valid = (uint32_t)r < it.n_rows;
             const uint32_t head = it.head + t;
@@ -810,9 +809,9 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
             uint32_t klo = 0;
             if (P.window > 0 && pos + 1 > P.window) klo = pos + 1 - P.window;
             const uint32_t khi = pos;
-            const bool have_next = item_index(n + 1) < P.n_items;
+            const bool have_next = item0 + n + 1 < item_end;
             TileItem next{};
-            if (have_next) next = P.items[item_index(n + 1)];
+            if (have_next) next = P.items[item0 + n + 1];
             float m_used = -INFINITY, l = 0.f;
             for (uint32_t j = 0; j < n_tiles; j++, g++) {
                 if (t == 0) mbar_wait(b_s_full_a, g & 1u, abortp, P.status, 49);
@@ -977,8 +976,8 @@ int launch_prefill_tc(yx_ctx *ctx, const TileArgs &a) {
                 return rc;
             ctx->smem_configured[7] = true;
         }
-        P.n_items = (uint32_t)a.n_items;
-        const int grid = std::min(a.n_items, ctx->sm_count);   // persistent: one CTA per SM
+        P.cta_begin = a.cta_begin;
+        const int grid = a.n_ctas;   // persistent: at most one CTA per SM
         if (P.bf16) prefill_tc2_kernel<true><<<grid, T2_THREADS, T2_SMEM_BYTES, ctx->stream>>>(P);
         else prefill_tc2_kernel<false><<<grid, T2_THREADS, T2_SMEM_BYTES, ctx->stream>>>(P);
     } else {

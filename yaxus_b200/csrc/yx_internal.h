@@ -122,7 +122,8 @@ struct Plan {
     std::vector<Merge> merges;          // [rows][hkv]
     uint32_t n_parts = 0;
     // resolved form (filled when PlanParams::resolve is set)
-    std::vector<TileItem> tile_items;   // rows handled by the tiled kernel (not in `items`)
+    std::vector<TileItem> tile_items;   // rows handled by the tiled kernel (not in `items`), grouped by CTA
+    std::vector<uint32_t> tile_cta_begin;   // offsets into tile_items per persistent CTA, plus the end
     std::vector<CtaHdr> cta_hdr;
     std::vector<TileDesc> tiles;
     std::vector<ItemRec> recs;
@@ -148,6 +149,7 @@ struct PlanParams {
     bool resolve;            // also build the resolved form for the streaming kernel
     int tile_min_rows;       // groups of at least this many rows go to the tiled kernel (0 = none)
     bool tile_pairs;         // tile items take two query heads of a KV head each (needs an even group)
+    int tile_ctas;           // persistent CTAs of the tiled kernel (0: one per item)
     int share_rows;          // pass rows a shared item may hold (0 = one 16-row MMA tile's worth)
     int item_cost;           // fixed cost of an item, in 16ths of a 16-row tile's
     int min_piece;           // fewest tiles worth an item of their own
@@ -237,6 +239,7 @@ struct yx_ctx {
         yx::TileDesc *d_tiles = nullptr;
         yx::ItemRec *d_recs = nullptr;
         yx::TileItem *d_tile_items = nullptr;
+        uint32_t *d_tile_cta_begin = nullptr;
         int tile_min_rows = 0;
         bool tile_pairs = false;
     };
@@ -314,6 +317,8 @@ struct TileArgs {
     int64_t window;
     const TileItem *items;
     int n_items;
+    const uint32_t *cta_begin;   // n_ctas + 1 offsets into items (persistent kernel)
+    int n_ctas;
     void *out;
     int out_dtype;
     bool pairs;              // items name the first of two query heads of one KV head
