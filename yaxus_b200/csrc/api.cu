@@ -341,6 +341,9 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
         t.pairs = pp.tile_pairs;
         if (int rc = launch_prefill_tc(ctx, t)) return rc;
     }
+    // With every row in the tiled kernel's hands and no partial triples asked for, the merge
+    // has nothing to do.
+    const bool need_combine = !pl.items.empty() || o_out != nullptr;
     if (path == 2) {
         // Rows without a live key in the range get no item, so nothing would write them.
         if (a.fused && o_out && pl.has_empty_rows)
@@ -349,7 +352,7 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
             if (int rc = launch_attend_mma(ctx, a)) return rc;
         profile_mark(ctx, 1);
         profile_mark(ctx, 2);
-        if (!a.fused)
+        if (!a.fused && need_combine)
             if (int rc = launch_combine(ctx, cp->d_merges, ctx->ws_o, ctx->ws_ml, (int)ctx->pass.rows, hq, group, out,
                                         out_dtype, m_out, l_out, o_out))
                 return rc;
@@ -359,9 +362,10 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
             if (int rc = launch_attend_simt(ctx, a)) return rc;
         profile_mark(ctx, 1);
         profile_mark(ctx, 2);
-        if (int rc = launch_combine(ctx, cp->d_merges, ctx->ws_o, ctx->ws_ml, (int)ctx->pass.rows, hq, group, out,
-                                    out_dtype, m_out, l_out, o_out))
-            return rc;
+        if (need_combine)
+            if (int rc = launch_combine(ctx, cp->d_merges, ctx->ws_o, ctx->ws_ml, (int)ctx->pass.rows, hq, group, out,
+                                        out_dtype, m_out, l_out, o_out))
+                return rc;
         profile_mark(ctx, 3);
     }
     ctx->last_plan = pl.info;
