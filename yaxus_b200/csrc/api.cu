@@ -116,7 +116,7 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
         if (cp.pass_serial == ctx->pass_serial && cp.hkv == pp.hkv && cp.group == pp.group &&
             cp.max_rows == pp.max_rows && cp.n_ctas == pp.n_ctas && cp.window == pp.window &&
             cp.key_lo == pp.key_lo && cp.key_hi == pp.key_hi && cp.share == pp.share_prefix && cp.esize == pp.esize &&
-            cp.w32 == pp.w32 && cp.w64 == pp.w64 && cp.resolve == pp.resolve && cp.share_rows == pp.share_rows && cp.item_cost == pp.item_cost && cp.tile_min_rows == pp.tile_min_rows && cp.tile_pairs == pp.tile_pairs) {
+            cp.w32 == pp.w32 && cp.w64 == pp.w64 && cp.resolve == pp.resolve && cp.share_rows == pp.share_rows && cp.item_cost == pp.item_cost && cp.min_piece == pp.min_piece && cp.tile_min_rows == pp.tile_min_rows && cp.tile_pairs == pp.tile_pairs) {
             *out = &cp;
             return YX_OK;
         }
@@ -161,6 +161,7 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
     slot->resolve = pp.resolve;
     slot->share_rows = pp.share_rows;
     slot->item_cost = pp.item_cost;
+    slot->min_piece = pp.min_piece;
     slot->tile_min_rows = pp.tile_min_rows;
     slot->tile_pairs = pp.tile_pairs;
 
@@ -262,8 +263,8 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     // Two heads per item unless the group is odd or f32 queries need their low part (bf16 caches).
     pp.tile_ctas = ctx->sm_count;
     pp.tile_pairs = group % 2 == 0 && !(kv->dtype == YX_BF16 && q_dtype == YX_F32) && ctx->tuning.tile_single != 1;
-    pp.min_piece = path == 2 ? 4 : 1;
-    pp.item_cost = ctx->tuning.item_cost > 0 ? ctx->tuning.item_cost - 1 : (path == 2 ? 48 : 0);
+    pp.min_piece = ctx->tuning.min_piece > 0 ? ctx->tuning.min_piece : (path == 2 ? 2 : 1);
+    pp.item_cost = ctx->tuning.item_cost > 0 ? ctx->tuning.item_cost - 1 : (path == 2 ? 16 : 0);
     yx_ctx::CachedPlan *cp = nullptr;
     if (int rc = get_plan(ctx, pp, &cp)) return rc;
     const Plan &pl = cp->plan;

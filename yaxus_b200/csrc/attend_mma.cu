@@ -40,10 +40,10 @@ using namespace dev;
 constexpr int STAGES = 3;
 constexpr int SUB_BYTES = TILE_KEYS * 128;        // one 64-dim half of a 64-key tile
 constexpr int STAGE_BYTES = 4 * SUB_BYTES;        // K lo, K hi, V lo, V hi
-constexpr int CONSUMERS = 4;                      // warps 0..3
-constexpr int PRODUCER = CONSUMERS;               // warp 4
-constexpr int QWARP = CONSUMERS + 1;              // warp 5
-constexpr int EWARP = CONSUMERS + 2;              // warps 6 and 7: items alternate between them
+constexpr int CONSUMERS = 8;                      // warps 0..7, two per scheduler
+constexpr int PRODUCER = CONSUMERS;               // warp 8
+constexpr int QWARP = CONSUMERS + 1;              // warp 9
+constexpr int EWARP = CONSUMERS + 2;              // warps 10 and 11: items alternate between them
 constexpr int EWARPS = 2;
 constexpr int THREADS = (CONSUMERS + 2 + EWARPS) * 32;
 constexpr int Q_SLOTS = 2;
@@ -51,7 +51,7 @@ constexpr int Q_ROWS_BYTES = 16384;               // 64 rows x 256 B, or 32 rows
 constexpr int Q_LOW_OFFSET = 8192;
 constexpr int Q_SLOT_BYTES = Q_ROWS_BYTES + 512;  // then the item's record
 constexpr int MERGE_ROW = D + 4;                  // one row's o, then m and l, padded
-constexpr int MERGE_FLOATS = 16 * MERGE_ROW;      // one warp's 16 rows
+constexpr int MERGE_FLOATS = 8 * MERGE_ROW;       // one warp's 8 queries
 constexpr int MERGE_BYTES = CONSUMERS * MERGE_FLOATS * 4;   // one buffer: every consumer warp's rows
 constexpr int MERGE_BUFS = 2;
 constexpr int N_BARRIERS = 2 * STAGES + 2 * Q_SLOTS + 2 * MERGE_BUFS;
@@ -440,8 +440,63 @@ __device__ __forceinline__ void merge_completed(const Epilogue &E, const uint32_
     }
 }
 
-__device__ __noinline__ void epilogue_loop(const Epilogue E, int lane) {
+// The item's triples: for each of its queries first_q, first_q + q_step, ... the slices its
+// consumer warps left in shared memory are merged and written to the partial buffer (a lane
+// holds four of the 128 dims, stores coalesced).  Which warps hold slices of column tile jq
+// follows the kernel's dispatch table: warp w0 + x * wstep, x < nsl.
+__device__ __forceinline__ void merge_queries(const float *scratch, const uint32_t *rec, float *part_o, float *part_ml,
+                                              int group, int first_q, int q_step, int lane) {
     const float sl2 = 0.08838834764831845f * 1.4426950408889634f;
+    const int n_rows = (int)(rec[IR_HEAD_ROWS] >> 16);
+    const int mt = (int)rec[IR_MT];
+    const int q_rows = n_rows * group;
+    const bool narrow = mt == 16 && q_rows <= 8;
+    const int nsl = narrow ? 8 : (mt == 16 ? 4 : (mt == 32 ? 2 : 1));
+#pragma unroll 1
+    for (int qr = first_q; qr < q_rows; qr += q_step) {
+        const int r = qr / group, gq = qr - r * group;
+        const uint32_t part = rec[IR_ROW0 + IR_ROW_WORDS * r + IRR_PART];
+        const int jq = qr >> 3;
+        const int w0 = narrow ? 0 : (mt == 16 ? jq * 4 : jq), wstep = (narrow || mt == 16) ? 1 : 4;
+        const float *base = scratch + w0 * MERGE_FLOATS + (qr & 7) * MERGE_ROW;
+        // all slices' loads are independent of one another
+        float2 ml[8];
+        float4 v[8];
+#pragma unroll
+        for (int x = 0; x < 8; x++) {
+            ml[x] = make_float2(-INFINITY, 0.f);
+            v[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (x < nsl) {
+                const float *w = base + x * wstep * MERGE_FLOATS;
+                ml[x] = *(const float2 *)(w + D);
+                v[x] = *(const float4 *)(w + 4 * lane);
+            }
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int x = 0; x < 8; x++) mx = fmaxf(mx, ml[x].x);
+        const float mu = mx == -INFINITY ? 0.f : mx;
+        float ls = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int x = 0; x < 8; x++) {
+            const float f = fast_exp2((ml[x].x - mu) * sl2);   // 0 for a slice that saw no key (and for x >= nsl)
+            ls += ml[x].y * f;
+            acc.x += v[x].x * f;
+            acc.y += v[x].y * f;
+            acc.z += v[x].z * f;
+            acc.w += v[x].w * f;
+        }
+        const size_t slot = (size_t)part * group + gq;
+        __stcg((float4 *)(part_o + slot * D + 4 * lane), acc);
+        if (lane == 0) {
+            const bool none = mx == -INFINITY;
+            __stcg((float2 *)(part_ml + slot * 2), make_float2(none ? -1e30f : mx * 0.08838834764831845f, none ? 0.f : ls));
+        }
+    }
+}
+
+__device__ __noinline__ void epilogue_loop(const Epilogue E, int lane) {
     // Merge buffer b, query slot b and epilogue warp b go together (two of each).
     static_assert(MERGE_BUFS == EWARPS && Q_SLOTS == EWARPS, "one buffer and one slot per epilogue warp");
     const uint32_t mine = E.first_item;
@@ -454,38 +509,8 @@ __device__ __noinline__ void epilogue_loop(const Epilogue E, int lane) {
         const uint32_t *rec = (const uint32_t *)__cvta_shared_to_generic((size_t)(E.qbase + mine * Q_SLOT_BYTES + Q_ROWS_BYTES));
         const uint32_t head_rows = rec[IR_HEAD_ROWS];
         const int kvh = (int)(head_rows & 0xffffu), n_rows = (int)(head_rows >> 16);
-        const int nmt = (int)rec[IR_MT] >> 4, nsl = CONSUMERS / nmt;
         // 1. the item's triples
-        int qr = 0;
-#pragma unroll 1
-        for (int r = 0; r < n_rows; r++) {
-            const uint32_t part = rec[IR_ROW0 + IR_ROW_WORDS * r + IRR_PART];
-#pragma unroll 1
-            for (int gq = 0; gq < group; gq++, qr++) {
-                const float *base = scratch + (qr >> 4) * MERGE_FLOATS + (qr & 15) * MERGE_ROW;
-                float mx = -INFINITY;
-                for (int x = 0; x < nsl; x++) mx = fmaxf(mx, base[x * nmt * MERGE_FLOATS + D]);
-                const float mu = mx == -INFINITY ? 0.f : mx;
-                float ls = 0.f;
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int x = 0; x < nsl; x++) {
-                    const float *w = base + x * nmt * MERGE_FLOATS;
-                    const float f = fast_exp2((w[D] - mu) * sl2);
-                    ls += w[D + 1] * f;
-                    const float4 v = *(const float4 *)(w + 4 * lane);
-                    acc.x += v.x * f;
-                    acc.y += v.y * f;
-                    acc.z += v.z * f;
-                    acc.w += v.w * f;
-                }
-                const size_t slot = (size_t)part * group + gq;
-                __stcg((float4 *)(E.part_o + slot * D + 4 * lane), acc);
-                if (lane == 0) {
-                    const bool none = mx == -INFINITY;
-                    __stcg((float2 *)(E.part_ml + slot * 2), make_float2(none ? -1e30f : mx * 0.08838834764831845f, none ? 0.f : ls));
-                }
-            }
-        }
+        merge_queries(scratch, rec, E.part_o, E.part_ml, group, 0, 1, lane);
         __syncwarp();
         if (lane == 0) mbar_arrive(E.eempty + 8 * mine);   // the buffer is the consumers' again
         if (!E.fused) {
@@ -511,171 +536,169 @@ __device__ __noinline__ void epilogue_loop(const Epilogue E, int lane) {
     }
 }
 
-template <int MT, bool BF16>
+// One item on one consumer warp.  The product is taken transposed, S^T = K Q^T and
+// O^T = V^T P^T: the 16-row side of the MMA holds keys (or dims), which are always full, and
+// the 8-column side holds queries, of which a decode row has only its group's few.  A warp owns
+// one column tile (8 queries, index j) and KBW 16-key blocks of a tile starting at key k0; with
+// `turn` >= 0 it takes every other tile only (two tiles are then in work at a time).  Eight such
+// warps, two per scheduler, keep the issue slots busy where one warp per scheduler left them
+// waiting on its own dependent instructions.
+template <int KBW, bool BF16>
 __device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe &qpipe, Pipe &epipe, int warp,
-                             int lane) {
-    constexpr int NMT = MT / 16;          // 16-row tiles of queries
-    constexpr int NSL = CONSUMERS / NMT;  // key slices of a tile
-    constexpr int KS = TILE_KEYS / NSL;   // keys per slice
-    constexpr int NT = KS / 8;            // 8-key score tiles per warp
-    constexpr bool LOW = MT != 64;        // f32 queries carry a low part (not for 64-row items)
-    const int mi = warp % NMT, sl = warp / NMT;
+                             int lane, int j, int k0, int turn, bool low_ok, bool last) {
+    constexpr int PARTS = KBW == 1 ? 4 : (KBW == 2 ? 2 : 1);   // partial sums per key block: short MMA chains
     const int g = lane >> 2, t4 = lane & 3;
     const int group = P.group;
     const uint32_t slot = S.q + qpipe.stage * Q_SLOT_BYTES;
     const uint32_t *rec = (const uint32_t *)__cvta_shared_to_generic((size_t)(slot + Q_ROWS_BYTES));
     const uint32_t n_tiles = rec[IR_TILES], key_base = rec[IR_KEY0];
-    const uint32_t head_rows = rec[IR_HEAD_ROWS];
-    const int kvh = (int)(head_rows & 0xffffu), n_rows = (int)(head_rows >> 16);
+    const int n_rows = (int)(rec[IR_HEAD_ROWS] >> 16);
     const int q_rows = n_rows * group;
     const float sl2 = 0.08838834764831845f * 1.4426950408889634f;   // log2(e) / sqrt(128)
-    const bool exact_q = !LOW || (P.q_dtype == YX_BF16 && BF16) || (P.q_dtype == YX_F16 && !BF16);
+    const bool exact_q = (P.q_dtype == YX_BF16 && BF16) || (P.q_dtype == YX_F16 && !BF16);
+    const bool low = low_ok && !exact_q;   // f32 queries carry a low part
 
-    // The two query rows this thread owns in the accumulator fragments.
+    // The two queries this thread meets in the accumulator fragments: columns 2 t4 and 2 t4 + 1.
     uint32_t klo[2], khi[2];
-    bool valid[2];
 #pragma unroll
-    for (int rs = 0; rs < 2; rs++) {
-        const int qr = mi * 16 + g + rs * 8;
-        valid[rs] = qr < q_rows;
-        const int base = IR_ROW0 + IR_ROW_WORDS * (valid[rs] ? qr / group : 0);
-        klo[rs] = valid[rs] ? rec[base + IRR_KLO] : 0u;            // padded rows: zero queries, nothing masked
-        khi[rs] = valid[rs] ? rec[base + IRR_KHI] : 0xffffffffu;
+    for (int c = 0; c < 2; c++) {
+        const int qr = j * 8 + 2 * t4 + c;
+        const bool valid = qr < q_rows;
+        const int base = IR_ROW0 + IR_ROW_WORDS * (valid ? qr / group : 0);
+        klo[c] = valid ? rec[base + IRR_KLO] : 0u;            // padded queries are zero: nothing to mask
+        khi[c] = valid ? rec[base + IRR_KHI] : 0xffffffffu;
+    }
+    // Query fragments (the column operand), held for the whole item.
+    const int lm = lane >> 3, lr = lane & 7;
+    uint32_t qh[8][2], ql[8][2];
+#pragma unroll
+    for (int ks = 0; ks < 8; ks++) {
+        const uint32_t a = slot + q_chunk_off(j * 8 + lr, 2 * ks + (lm & 1));
+        ldsm2(a, qh[ks][0], qh[ks][1]);
+        ql[ks][0] = ql[ks][1] = 0u;
+        if (low) ldsm2(a + Q_LOW_OFFSET, ql[ks][0], ql[ks][1]);
     }
 
-    // Query fragments from the staged slot.  Items with 64 rows, short of registers, read
-    // theirs again at every step.
-    constexpr bool HOLD_Q = MT != 64;
-    uint32_t qh[HOLD_Q ? 8 : 1][4], ql[LOW ? 8 : 1][4];
-    const int q_row = mi * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
-    if constexpr (HOLD_Q) {
-        const int row = q_row;
+    float o[8][4];   // O^T: dims 16 n + g (+8), queries 2 t4 (+1)
 #pragma unroll
-        for (int ks = 0; ks < 8; ks++) {
-            const uint32_t a = slot + q_chunk_off(row, 2 * ks + (lane >> 4));
-            ldsm4(a, qh[ks][0], qh[ks][1], qh[ks][2], qh[ks][3]);
-            if constexpr (LOW) {
-                if (!exact_q) ldsm4(a + Q_LOW_OFFSET, ql[ks][0], ql[ks][1], ql[ks][2], ql[ks][3]);
-            }
-        }
-    }
-
-    float o[16][4];
-#pragma unroll
-    for (int n = 0; n < 16; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    for (int n = 0; n < 8; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-    const int lm = lane >> 3, lr = lane & 7;
     for (uint32_t ti = 0; ti < n_tiles; ti++) {
+        const long long w0 = (P.trace && threadIdx.x == 0) ? clock64() : 0;
         mbar_wait(S.full + 8 * pipe.stage, pipe.phase, S.abort_flag, P.status, 2);
+        if (turn >= 0 && (int)(ti & 1u) != turn) {
+            // The other warps' tile.  It is still waited for and released: a warp that skipped
+            // ahead without looking could meet a barrier two phases on, which a parity wait
+            // cannot tell from the phase it expects.
+            if (lane == 0) mbar_arrive(S.empty + 8 * pipe.stage);
+            pipe.advance(P.n_stages);
+            continue;
+        }
+        if (P.trace && threadIdx.x == 0) P.trace[8 * blockIdx.x + 7] += (unsigned long long)(clock64() - w0);
         if (P.trace && threadIdx.x == 0 && ti == 0 && P.trace[8 * blockIdx.x + 4] == 0) P.trace[8 * blockIdx.x + 4] = gtime();
         const uint32_t sb = S.stages + pipe.stage * STAGE_BYTES;
 
-        // S = Q K^T over this warp's KS keys.  The low parts of the queries accumulate on their
-        // own, so that no MMA waits on more than the eight before it in its chain.
-        float s[NT][4], s2[LOW ? NT : 1][4];
+        // S^T = K Q^T over this warp's keys.
+        float sp[KBW][PARTS][4];
 #pragma unroll
-        for (int j = 0; j < NT; j++) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-        if constexpr (LOW) {
+        for (int kb = 0; kb < KBW; kb++)
 #pragma unroll
-            for (int j = 0; j < NT; j++) s2[j][0] = s2[j][1] = s2[j][2] = s2[j][3] = 0.f;
-        }
+            for (int p = 0; p < PARTS; p++) sp[kb][p][0] = sp[kb][p][1] = sp[kb][p][2] = sp[kb][p][3] = 0.f;
 #pragma unroll
         for (int ks = 0; ks < 8; ks++) {
             const uint32_t sub = sb + (ks >> 2) * SUB_BYTES;
-            const int c = ((2 * ks) & 7) + (lm & 1);
-            uint32_t qf[4];
-            if constexpr (HOLD_Q) {
-                qf[0] = qh[ks][0], qf[1] = qh[ks][1], qf[2] = qh[ks][2], qf[3] = qh[ks][3];
-            } else {
-                ldsm4(slot + q_chunk_off(q_row, 2 * ks + (lane >> 4)), qf[0], qf[1], qf[2], qf[3]);
-            }
+            const int c = ((2 * ks) & 7) + (lane >> 4);
 #pragma unroll
-            for (int np = 0; np < NT / 2; np++) {
-                const int key = sl * KS + np * 16 + (lm >> 1) * 8 + lr;
-                uint32_t b0, b1, b2, b3;
-                ldsm4(sub + key * 128 + ((c ^ lr) << 4), b0, b1, b2, b3);
-                mma16816<BF16>(s[2 * np], qf, b0, b1);
-                mma16816<BF16>(s[2 * np + 1], qf, b2, b3);
-                if constexpr (LOW) {
-                    if (!exact_q) {
-                        mma16816<BF16>(s2[2 * np], ql[ks], b0, b1);
-                        mma16816<BF16>(s2[2 * np + 1], ql[ks], b2, b3);
-                    }
-                }
+            for (int kb = 0; kb < KBW; kb++) {
+                const int key = k0 + kb * 16 + (lm & 1) * 8 + lr;
+                uint32_t a[4];   // keys as the row operand
+                ldsm4(sub + key * 128 + ((c ^ lr) << 4), a[0], a[1], a[2], a[3]);
+                // hi and lo parts, even and odd steps in different sums where there is room for them
+                mma16816<BF16>(sp[kb][PARTS == 4 ? (ks & 1) * 2 : 0], a, qh[ks][0], qh[ks][1]);
+                if (low) mma16816<BF16>(sp[kb][PARTS == 4 ? (ks & 1) * 2 + 1 : (PARTS == 2 ? 1 : 0)], a, ql[ks][0], ql[ks][1]);
             }
         }
-        if constexpr (LOW) {
+        float s[KBW][4];
 #pragma unroll
-            for (int j = 0; j < NT; j++)
-#pragma unroll
-                for (int e = 0; e < 4; e++) s[j][e] += s2[j][e];
-        }
-        // Mask keys outside each row's [klo, khi].
-        const uint32_t key0 = key_base + ti * TILE_KEYS + sl * KS + 2 * t4;
-#pragma unroll
-        for (int j = 0; j < NT; j++)
+        for (int kb = 0; kb < KBW; kb++)
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                const uint32_t key = key0 + j * 8 + (e & 1);
-                const int rs = e >> 1;
-                if (key < klo[rs] || key > khi[rs]) s[j][e] = -INFINITY;
-            }
-        // Online softmax, per owned row.
+                float v = sp[kb][0][e];
 #pragma unroll
-        for (int rs = 0; rs < 2; rs++) {
+                for (int p = 1; p < PARTS; p++) v += sp[kb][p][e];
+                s[kb][e] = v;
+            }
+        // Mask keys outside each query's [klo, khi]: element e sits at key g + 8 (e >> 1), query 2 t4 + (e & 1).
+        const uint32_t key0 = key_base + ti * TILE_KEYS + k0 + g;
+#pragma unroll
+        for (int kb = 0; kb < KBW; kb++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const uint32_t key = key0 + kb * 16 + (e >> 1) * 8;
+                if (key < klo[e & 1] || key > khi[e & 1]) s[kb][e] = -INFINITY;
+            }
+        // Online softmax per query: the maximum runs over this thread's keys, then over the
+        // eight lanes that hold the other keys of the same queries.
+        float alpha[2];
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
             float mx = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < NT; j++) mx = fmaxf(mx, fmaxf(s[j][2 * rs], s[j][2 * rs + 1]));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float mn = fmaxf(m[rs], mx);
+            for (int kb = 0; kb < KBW; kb++) mx = fmaxf(mx, fmaxf(s[kb][c], s[kb][2 + c]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float mn = fmaxf(m[c], mx);
             const float mu = mn == -INFINITY ? 0.f : mn;
-            const float alpha = fast_exp2((m[rs] - mu) * sl2);
-            m[rs] = mn;
-            float sum = 0.f;
+            alpha[c] = fast_exp2((m[c] - mu) * sl2);
+            m[c] = mn;
             const float ms = mu * sl2;
+            float sum = 0.f;
 #pragma unroll
-            for (int j = 0; j < NT; j++) {
-                const float p0 = fast_exp2(s[j][2 * rs] * sl2 - ms), p1 = fast_exp2(s[j][2 * rs + 1] * sl2 - ms);
-                s[j][2 * rs] = p0;
-                s[j][2 * rs + 1] = p1;
+            for (int kb = 0; kb < KBW; kb++) {
+                const float p0 = fast_exp2(s[kb][c] * sl2 - ms), p1 = fast_exp2(s[kb][2 + c] * sl2 - ms);
+                s[kb][c] = p0;
+                s[kb][2 + c] = p1;
                 sum += p0 + p1;
             }
-            l[rs] = l[rs] * alpha + sum;
+            l[c] = l[c] * alpha[c] + sum;   // this thread's keys only: lanes are summed at the end
+        }
+        // The accumulator is rescaled only when some query's maximum moved (warp-uniform).
+        if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
-            for (int n = 0; n < 16; n++) {
-                o[n][2 * rs] *= alpha;
-                o[n][2 * rs + 1] *= alpha;
+            for (int n = 0; n < 8; n++) {
+                o[n][0] *= alpha[0];
+                o[n][1] *= alpha[1];
+                o[n][2] *= alpha[0];
+                o[n][3] *= alpha[1];
             }
         }
-        // O += P V.
+        // O^T += V^T P^T, 16 keys at a time.  The probabilities sit as (key row, query pair); a
+        // matrix transpose across the warp turns them into the column operand (key pair, query).
 #pragma unroll
-        for (int kk = 0; kk < KS / 16; kk++) {
-            uint32_t a[4], al[4];
+        for (int kb = 0; kb < KBW; kb++) {
+            uint32_t pb[2], pl[2];
 #pragma unroll
-            for (int r = 0; r < 4; r++) {
-                const float p0 = s[2 * kk + (r >> 1)][(r & 1) * 2], p1 = s[2 * kk + (r >> 1)][(r & 1) * 2 + 1];
-                a[r] = pack2<BF16>(p0, p1);
+            for (int h = 0; h < 2; h++) {
+                const float p0 = s[kb][2 * h], p1 = s[kb][2 * h + 1];
+                const uint32_t w = pack2<BF16>(p0, p1);
+                pb[h] = movmatrix_trans(w);
                 if constexpr (BF16) {
                     // bf16 keeps 8 bits of a probability; its remainder goes in a second MMA.
-                    const float2 hf = unpack2<BF16>(a[r]);
-                    al[r] = pack2<BF16>(p0 - hf.x, p1 - hf.y);
+                    const float2 hf = unpack2<BF16>(w);
+                    pl[h] = movmatrix_trans(pack2<BF16>(p0 - hf.x, p1 - hf.y));
                 }
             }
-            const int key = sl * KS + kk * 16 + (lm & 1) * 8 + lr;
+            const int key = k0 + kb * 16 + (lm >> 1) * 8 + lr;
 #pragma unroll
-            for (int np = 0; np < 8; np++) {
-                const uint32_t sub = sb + 2 * SUB_BYTES + (np >> 2) * SUB_BYTES;
-                const int c = ((2 * np) & 7) + (lm >> 1);
-                uint32_t b0, b1, b2, b3;
-                ldsm4t(sub + key * 128 + ((c ^ lr) << 4), b0, b1, b2, b3);
-                mma16816<BF16>(o[2 * np], a, b0, b1);
-                mma16816<BF16>(o[2 * np + 1], a, b2, b3);
-                if constexpr (BF16) {
-                    mma16816<BF16>(o[2 * np], al, b0, b1);
-                    mma16816<BF16>(o[2 * np + 1], al, b2, b3);
-                }
+            for (int n = 0; n < 8; n++) {
+                const uint32_t sub = sb + 2 * SUB_BYTES + (n >> 2) * SUB_BYTES;
+                const int c = ((2 * n) & 7) + (lm & 1);
+                uint32_t a[4];   // dims as the row operand: V read transposed
+                ldsm4t(sub + key * 128 + ((c ^ lr) << 4), a[0], a[1], a[2], a[3]);
+                mma16816<BF16>(o[n], a, pb[0], pb[1]);
+                if constexpr (BF16) mma16816<BF16>(o[n], a, pl[0], pl[1]);
             }
         }
         __syncwarp();
@@ -683,24 +706,36 @@ __device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe 
         pipe.advance(P.n_stages);
     }
 
-    if (P.trace && threadIdx.x == 0 && P.trace[8 * blockIdx.x + 7] == 0) P.trace[8 * blockIdx.x + 7] = gtime();
-    // Row sums across the quad.
+    // Sums of exponentials across the lanes that share a query.
 #pragma unroll
-    for (int rs = 0; rs < 2; rs++) {
-        l[rs] += __shfl_xor_sync(0xffffffffu, l[rs], 1);
-        l[rs] += __shfl_xor_sync(0xffffffffu, l[rs], 2);
+    for (int c = 0; c < 2; c++) {
+        l[c] += __shfl_xor_sync(0xffffffffu, l[c], 4);
+        l[c] += __shfl_xor_sync(0xffffffffu, l[c], 8);
+        l[c] += __shfl_xor_sync(0xffffffffu, l[c], 16);
     }
-    // Every warp leaves its 16 rows' (o, m, l) in shared memory for the epilogue warp and goes
+    // Every warp leaves its 8 queries' (o, m, l) in shared memory for the epilogue warp and goes
     // on to the next item.
     {
         mbar_wait(S.eempty + 8 * epipe.stage, epipe.phase ^ 1u, S.abort_flag, P.status, 6);
         float *w = (float *)__cvta_shared_to_generic((size_t)(S.merge + epipe.stage * MERGE_BYTES)) + warp * MERGE_FLOATS;
 #pragma unroll
-        for (int rs = 0; rs < 2; rs++) {
-            float *row = w + (g + rs * 8) * MERGE_ROW;
-            if (t4 == 0) *(float2 *)(row + D) = make_float2(m[rs], l[rs]);
+        for (int c = 0; c < 2; c++) {
+            float *row = w + (2 * t4 + c) * MERGE_ROW;
+            if (g == 0) *(float2 *)(row + D) = make_float2(m[c], l[c]);
 #pragma unroll
-            for (int n = 0; n < 16; n++) *(float2 *)(row + n * 8 + 2 * t4) = make_float2(o[n][2 * rs], o[n][2 * rs + 1]);
+            for (int n = 0; n < 8; n++) {
+                row[n * 16 + g] = o[n][c];
+                row[n * 16 + g + 8] = o[n][2 + c];
+            }
+        }
+        if (last) {
+            // The CTA's last item: nothing is left to stream, so the consumer warps merge it
+            // themselves, a share of the queries each, instead of queueing it behind one
+            // epilogue warp at the very end of the kernel.
+            asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");
+            const float *scratch = (const float *)__cvta_shared_to_generic((size_t)(S.merge + epipe.stage * MERGE_BYTES));
+            merge_queries(scratch, rec, P.part_o, P.part_ml, group, warp, CONSUMERS, lane);
+            return;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(S.efull + 8 * epipe.stage);
@@ -799,6 +834,7 @@ __global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const __grid_con
         E.group = P.group;
         E.fused = P.fused;
         E.n_items = hdr.item_end - hdr.item_begin;
+        if (!P.fused && E.n_items > 0) E.n_items--;   // the last item is the consumer warps' own
         E.qbase = S.q;
         E.qempty = S.qempty;
         E.merge = S.merge;
@@ -807,7 +843,6 @@ __global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const __grid_con
         E.mlbuf = S.mlbuf + (warp - EWARP) * (MLBUF_BYTES / EWARPS);
         E.first_item = warp - EWARP;
         epilogue_loop(E, lane);
-        if (tr && lane == 0 && (E.n_items < 2 || ((E.n_items - 1) & 1u) == E.first_item)) tr[5] = gtime();
         return;
     }
     Pipe pipe{0, 0}, qpipe{0, 0}, epipe{0, 0};
@@ -816,13 +851,20 @@ __global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const __grid_con
         mbar_wait(S.qfull + 8 * qpipe.stage, qpipe.phase, S.abort_flag, P.status, 4);
         if (tr && threadIdx.x == 0 && ii == hdr.item_begin) tr[3] = gtime();
         const uint32_t mt = *(const uint32_t *)__cvta_shared_to_generic((size_t)(S.q + qpipe.stage * Q_SLOT_BYTES + Q_ROWS_BYTES + 4 * IR_MT));
-        switch (mt) {
-            case 16: consume_item<16, BF16>(P, S, pipe, qpipe, epipe, warp, lane); break;
-            case 32: consume_item<32, BF16>(P, S, pipe, qpipe, epipe, warp, lane); break;
-            default: consume_item<64, BF16>(P, S, pipe, qpipe, epipe, warp, lane); break;
-        }
+        const bool last = !P.fused && ii + 1 == hdr.item_end;   // merged by the consumer warps themselves
+        const uint32_t hr = *(const uint32_t *)__cvta_shared_to_generic((size_t)(S.q + qpipe.stage * Q_SLOT_BYTES + Q_ROWS_BYTES + 4 * IR_HEAD_ROWS));
+        const int q_rows = (int)(hr >> 16) * P.group;
+        // Who takes what of a 64-key tile (the epilogue warp's merge knows the same table):
+        //   up to 8 queries: column tile 0 everywhere, a 16-key block each, warps 0-3 even tiles and 4-7 odd ones;
+        //   up to 16: column tile warp / 4, a 16-key block each;  up to 32: column tile warp % 4, 32 keys each;
+        //   up to 64: column tile warp, the whole tile.
+        if (mt == 16 && q_rows <= 8) consume_item<1, BF16>(P, S, pipe, qpipe, epipe, warp, lane, 0, (warp & 3) * 16, warp >> 2, true, last);
+        else if (mt == 16) consume_item<1, BF16>(P, S, pipe, qpipe, epipe, warp, lane, warp >> 2, (warp & 3) * 16, -1, true, last);
+        else if (mt == 32) consume_item<2, BF16>(P, S, pipe, qpipe, epipe, warp, lane, warp & 3, (warp >> 2) * 32, -1, true, last);
+        else consume_item<4, BF16>(P, S, pipe, qpipe, epipe, warp, lane, warp, 0, -1, false, last);
         if (tr && threadIdx.x == 0 && ii == hdr.item_begin) tr[6] = gtime();
     }
+    if (tr && threadIdx.x == 0) tr[5] = gtime();
     if (abort_flag) {
         // Copies issued before giving up may still be landing in this CTA's shared memory.
         for (int i = 0; i < 64; i++) __nanosleep(1000);
@@ -864,7 +906,7 @@ int launch_attend_mma(yx_ctx *ctx, const AttendArgs &a) {
     P.trace = (unsigned long long *)ctx->trace_buf;
     P.has_prologue = 0;
     P.fused = a.fused ? 1 : 0;
-    P.n_stages = a.n_stages >= 2 && a.n_stages <= STAGES ? a.n_stages : 3;
+    P.n_stages = a.n_stages >= 2 && a.n_stages <= STAGES ? a.n_stages : STAGES;
     if (a.plan && a.n_ctas <= MAX_PROLOGUE_CTAS) {
         const Plan &pl = *a.plan;
         P.has_prologue = 1;

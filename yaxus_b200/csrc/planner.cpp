@@ -285,6 +285,9 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
     }
     int n_ctas = (int)std::min<uint64_t>((uint64_t)std::max(1, pp.n_ctas), std::max<uint64_t>(total_tiles, 1));
     out.n_ctas = n_ctas;
+    // About one run is cut at every CTA boundary; the extra pieces are charged up front so that
+    // the CTAs' spans do not grow as the cutting goes on.
+    total_cost += item_cost * (uint64_t)(n_ctas - 1);
     out.cta_begin.assign(n_ctas + 1, 0);
     out.merges.assign((size_t)T * pp.hkv, Merge{0, 0});
 
@@ -336,7 +339,6 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
                 out.items.push_back(it);
                 // The first piece of a (unit, head) was charged with the totals; a cut adds a piece.
                 done += take * w + item_cost;
-                if (t != t0) total_cost += item_cost;
                 t += take;
             }
         }

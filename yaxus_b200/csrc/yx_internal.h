@@ -228,7 +228,7 @@ struct yx_ctx {
         int64_t window = 0;
         uint64_t key_lo = 0, key_hi = 0;
         bool share = false, resolve = false;
-        int share_rows = 0, item_cost = 0;
+        int share_rows = 0, item_cost = 0, min_piece = 0;
         yx::Plan plan;
         char *dev = nullptr;       // items | cta_begin | merges | cta_hdr | tiles | recs
         size_t dev_cap = 0;
