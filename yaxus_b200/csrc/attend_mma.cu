@@ -786,6 +786,12 @@ __global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const __grid_con
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
+    // The merge kernel that follows may be set up from here on (it waits for this grid to
+    // complete before it reads a triple).  This kernel in turn may have been started before the
+    // kernel ahead of it finished: nothing written by earlier kernels (K/V rows, queries, the
+    // partial buffers' previous readers) is touched before this wait.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (tr && threadIdx.x == 0) tr[1] = gtime();
 
     if (warp == PRODUCER) {
@@ -922,8 +928,18 @@ int launch_attend_mma(yx_ctx *ctx, const AttendArgs &a) {
             }
         }
     }
-    if (bf16) attend_mma_kernel<true><<<a.n_ctas, THREADS, SMEM_BYTES, ctx->stream>>>(P);
-    else attend_mma_kernel<false><<<a.n_ctas, THREADS, SMEM_BYTES, ctx->stream>>>(P);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)a.n_ctas);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t le = bf16 ? cudaLaunchKernelEx(&cfg, attend_mma_kernel<true>, P) : cudaLaunchKernelEx(&cfg, attend_mma_kernel<false>, P);
+    if (int rc = check_cuda(ctx, le, "attend_mma kernel launch")) return rc;
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "attend_mma kernel");
 }

@@ -36,7 +36,11 @@ __global__ void combine_kernel(const Merge *__restrict__ merges, const float *__
     if (idx >= n) return;
     uint32_t row = idx / (uint32_t)hq;
     int h = (int)(idx % (uint32_t)hq), kvh = h / group, g = h % group;
-    Merge mg = merges[(size_t)row * (hq / group) + kvh];
+    Merge mg = merges[(size_t)row * (hq / group) + kvh];   // host-written: not the split-key kernel's output
+    // Launched as a programmatic dependent of the split-key kernel: it may start while that
+    // kernel's last CTAs run.  The triples are read only after the whole grid before it is
+    // complete and its writes are visible.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (mg.count == 0 && !o_out) return;   // the row was another kernel's (tiled path)
     float mx = -1e30f, l = 0.0f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -144,8 +148,21 @@ int launch_combine(yx_ctx *ctx, const Merge *merges, const float *part_o, const 
         cudaFuncSetAttribute(combine_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         ctx->smem_configured[2] = true;
     }
-    combine_kernel<<<blocks, 128, 0, ctx->stream>>>(merges, part_o, part_ml, n, hq, group, out, out_dtype, m_out,
-                                                   l_out, o_out);
+    // Programmatic stream serialisation: the launch is set up while the kernel before it still
+    // runs, which hides a launch latency that is a tenth of a decode step.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (int rc = check_cuda(ctx, cudaLaunchKernelEx(&cfg, combine_kernel, merges, part_o, part_ml, n, hq, group, out, out_dtype, m_out, l_out, o_out),
+                            "combine kernel launch"))
+        return rc;
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "combine kernel");
 }
