@@ -72,7 +72,7 @@ def check_slots(items, info, group_rows):
 
 def check_balance(items, info, cost32=16, cost64=32, item_cost=0):
     """Per-CTA cost (tiles weighted by the item's padded rows, plus a fixed cost per item)
-    differs by at most about a tile."""
+    differs by a few tiles at most."""
     w = {16: 16, 32: cost32, 64: cost64}
     per = np.zeros(info.n_ctas, np.int64)
     per_items = np.zeros(info.n_ctas, np.int64)
@@ -84,7 +84,9 @@ def check_balance(items, info, cost32=16, cost64=32, item_cost=0):
         per_items[int(it[8])] += 1
     assert tiles == info.tiles
     if info.tiles >= info.n_ctas:
-        assert per.max() - per.min() <= 2 * max(w.values()) + item_cost * (1 + per_items.max())
+        # a CTA may close up to six tiles early rather than end on a short piece of a new run;
+        # what it leaves is shared by the CTAs after it
+        assert per.max() - per.min() <= (2 + 6) * max(w.values()) + item_cost * (1 + per_items.max())
     return per_items
 
 

@@ -285,15 +285,28 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
     }
     int n_ctas = (int)std::min<uint64_t>((uint64_t)std::max(1, pp.n_ctas), std::max<uint64_t>(total_tiles, 1));
     out.n_ctas = n_ctas;
-    // About one run is cut at every CTA boundary; the extra pieces are charged up front so that
-    // the CTAs' spans do not grow as the cutting goes on.
-    total_cost += item_cost * (uint64_t)(n_ctas - 1);
     out.cta_begin.assign(n_ctas + 1, 0);
     out.merges.assign((size_t)T * pp.hkv, Merge{0, 0});
 
-    uint64_t done = 0;   // cost handed out so far
+    // Each CTA's target is set when it is opened: an equal share of what is still unassigned
+    // (`rem`: tiles and one item per run not yet begun) plus the cuts still to come, about one per
+    // CTA boundary.  How many cuts there will be is not known beforehand (a CTA may end on a run
+    // boundary), so a division fixed at the start would starve or overload the last CTAs; this
+    // one corrects itself at every boundary.
+    uint64_t rem = total_cost;
+    uint64_t done = 0;      // cost handed out so far
+    uint64_t cta_end = 0;   // `done` at which the open CTA is full
     int cta = 0;
-    auto span_end = [&](int c) { return total_cost * (uint64_t)(c + 1) / (uint64_t)n_ctas; };
+    auto open_cta = [&](bool mid_run) {
+        const uint64_t ahead = (uint64_t)(n_ctas - cta - 1);
+        const uint64_t cuts = item_cost * ahead * 3 / 4 + (mid_run ? item_cost : 0);
+        cta_end = done + (rem + cuts) / (ahead + 1);
+    };
+    open_cta(false);
+    // A CTA's last item is the one whose latency nothing hides (queries in, a few tiles, merge,
+    // triples out: about four tiles' time however short it is).  A run is therefore not begun
+    // in a CTA that has room for only a few of its tiles left.
+    const uint64_t min_last = 4;
     std::unordered_map<uint64_t, uint32_t> seen;   // (physical page, half) -> most keys read
     for (const Unit &u : units) {
         const uint64_t w = weight(u);
@@ -307,13 +320,22 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
         }
         for (int kh = 0; kh < pp.hkv; kh++) {
             uint32_t t = t0;
-            while (t < t1) {
-                // Move on when less than half a tile's cost is left in this CTA's span.
-                while (cta < n_ctas - 1 && done + w / 2 >= span_end(cta)) {
+            if (pp.resolve && cta < n_ctas - 1 && (uint32_t)out.cta_begin[cta] < out.items.size()) {
+                const uint64_t room = cta_end > done + item_cost ? (cta_end - done - item_cost) / w : 0;
+                if (room < min_last && room < (uint64_t)(t1 - t0)) {
                     cta++;
                     out.cta_begin[cta] = (uint32_t)out.items.size();
+                    open_cta(false);
                 }
-                uint64_t left = span_end(cta) > done + item_cost ? span_end(cta) - done - item_cost : 0;
+            }
+            while (t < t1) {
+                // Move on when less than half a tile's cost is left in this CTA's span.
+                while (cta < n_ctas - 1 && done + w / 2 >= cta_end) {
+                    cta++;
+                    out.cta_begin[cta] = (uint32_t)out.items.size();
+                    open_cta(t != t0);
+                }
+                uint64_t left = cta_end > done + item_cost ? cta_end - done - item_cost : 0;
                 uint64_t room = cta == n_ctas - 1 ? UINT64_MAX : (left + w / 2) / w;
                 uint32_t take = (uint32_t)std::min<uint64_t>(std::max<uint64_t>(room, 1), t1 - t);
                 // No crumbs: a piece of fewer than min_piece tiles is not worth an item of its
@@ -337,8 +359,9 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
                     out.merges[(size_t)u.rows[r] * pp.hkv + kh].count++;
                 }
                 out.items.push_back(it);
-                // The first piece of a (unit, head) was charged with the totals; a cut adds a piece.
+                // `rem` holds one item per run; a cut's extra item is charged to the CTA only.
                 done += take * w + item_cost;
+                rem -= take * w + (t == t0 ? item_cost : 0);
                 t += take;
             }
         }
