@@ -56,6 +56,21 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
     if (T > 65535) throw std::string("a pass holds at most 65535 rows");
     out = Plan();
 
+    // Dense ids of the physical pages named in this pass (page-table entry -> id), so that
+    // per-page bookkeeping below is a flat array rather than a hash map.
+    std::vector<uint32_t> dense(pass.pages.size());
+    uint32_t n_dense = 0;
+    {
+        std::vector<uint32_t> order(pass.pages.size());
+        for (uint32_t i = 0; i < order.size(); i++) order[i] = i;
+        std::sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) { return pass.pages[a] < pass.pages[b]; });
+        for (size_t k = 0; k < order.size(); k++) {
+            if (k > 0 && pass.pages[order[k]] != pass.pages[order[k - 1]]) n_dense++;
+            dense[order[k]] = n_dense;
+        }
+        if (!order.empty()) n_dense++;
+    }
+
     // 1. Row groups: runs of rows with the same page table.
     std::vector<Group> groups;
     for (uint32_t i = 0; i < T;) {
@@ -307,15 +322,14 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
     // triples out: about four tiles' time however short it is).  A run is therefore not begun
     // in a CTA that has room for only a few of its tiles left.
     const uint64_t min_last = 4;
-    std::unordered_map<uint64_t, uint32_t> seen;   // (physical page, half) -> most keys read
+    std::vector<uint32_t> seen(2 * (size_t)n_dense, 0);   // (physical page, half) -> most keys read
     for (const Unit &u : units) {
         const uint64_t w = weight(u);
         uint32_t t0 = u.lo / TILE_KEYS, t1 = u.hi / TILE_KEYS + 1;
         for (uint32_t t = t0; t < t1; t++) {
             uint32_t a = std::max(u.lo, t * TILE_KEYS), b = std::min(u.hi, t * TILE_KEYS + TILE_KEYS - 1);
             uint32_t n = b - a + 1;
-            uint64_t key = ((uint64_t)pass.pages[u.pt_off + t * TILE_KEYS / PAGE] << 1) | (t & 1);
-            uint32_t &s = seen[key];
+            uint32_t &s = seen[((size_t)dense[u.pt_off + t * TILE_KEYS / PAGE] << 1) | (t & 1)];
             s = std::max(s, n);
         }
         for (int kh = 0; kh < pp.hkv; kh++) {
@@ -426,7 +440,7 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
     }
 
     uint64_t uniq = 0;
-    for (auto &kv : seen) uniq += kv.second;
+    for (uint32_t v : seen) uniq += v;
     out.info.n_ctas = n_ctas;
     out.info.n_items = (int)out.items.size();
     out.info.n_parts = (int)out.n_parts;
@@ -438,19 +452,19 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
     // Tiles not marked as reused are copied with an evict-first hint when each of them is read
     // by one item only: nothing is gained by keeping those K/V lines in L2.
     {
-        std::unordered_map<uint64_t, uint32_t> once;   // (physical page, half) -> most keys read by unmarked items
+        std::vector<uint32_t> once(2 * (size_t)n_dense, 0);   // (physical page, half) -> most keys read by unmarked items
         uint64_t streamed = 0;
         for (const Item &it : out.items) {
             if (it.pad_ || it.kv_head != 0) continue;
             for (uint32_t t = it.tile_begin; t < it.tile_end; t++) {
                 uint32_t n = std::min(it.key_hi, t * TILE_KEYS + TILE_KEYS - 1) - std::max(it.key_lo, t * TILE_KEYS) + 1;
                 streamed += n;
-                uint32_t &m = once[((uint64_t)pass.pages[it.pt_off + t * TILE_KEYS / PAGE] << 1) | (t & 1)];
+                uint32_t &m = once[((size_t)dense[it.pt_off + t * TILE_KEYS / PAGE] << 1) | (t & 1)];
                 m = std::max(m, n);
             }
         }
         uint64_t distinct = 0;
-        for (auto &kv : once) distinct += kv.second;
+        for (uint32_t v : once) distinct += v;
         out.single_use = streamed <= distinct;
     }
 }
