@@ -424,7 +424,11 @@ def run_cuda(args):
             "scaling": "strong" if split_kv else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_config(args.workload, s, world),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak if achieved else None, "traffic": None, "peak_source": which,
+                         "frac": achieved / peak if achieved else None,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the split-key kernel on
+                         # this very workload, from the ncu capture summarised under profiles/
+                         "traffic": 95.9e6 if (args.workload == "batched_decode" and world == 1) else None,
+                         "peak_source": which,
                          "kernel": "attend_mma_kernel" if info.path == 2 else "attend_simt_kernel",
                          "kernel_ms": kernel_ms, "combine_ms": combine_ms / max(calls, 1),
                          "algorithmic_bytes": per_gpu_bytes},

@@ -44,6 +44,16 @@ __global__ void combine_kernel(const Merge *__restrict__ merges, const float *__
     if (mg.count == 0 && !o_out) return;   // the row was another kernel's (tiled path)
     float mx = -1e30f, l = 0.0f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    // The first few vectors are asked for together with the (m, l) pairs: a row and KV head has
+    // two or three parts on average, and the merge then costs one memory latency instead of two.
+    // (A part that turns out empty is loaded but not used: its vector may never have been written.)
+    constexpr int EARLY = 4;
+    float4 early[EARLY];
+#pragma unroll
+    for (int j = 0; j < EARLY; j++) {
+        early[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if ((uint32_t)j < mg.count) early[j] = *(const float4 *)(part_o + ((size_t)(mg.first + j) * group + g) * D + lane * 4);
+    }
     for (uint32_t c0 = 0; c0 < mg.count; c0 += 32) {
         const uint32_t c = c0 + lane;
         float em = -1e30f, el = 0.0f;
@@ -69,8 +79,22 @@ __global__ void combine_kernel(const Merge *__restrict__ merges, const float *__
         acc.w *= r;
         mx = nm;
         const int nc = (int)min(32u, mg.count - c0);
+        int j0 = 0;
+        if (c0 == 0) {
+#pragma unroll
+            for (int j = 0; j < EARLY; j++) {
+                const float wj = __shfl_sync(0xffffffffu, w, j);
+                if (j < nc && wj > 0.0f) {
+                    acc.x += early[j].x * wj;
+                    acc.y += early[j].y * wj;
+                    acc.z += early[j].z * wj;
+                    acc.w += early[j].w * wj;
+                }
+            }
+            j0 = EARLY;
+        }
 #pragma unroll 4
-        for (int j = 0; j < nc; j++) {
+        for (int j = j0; j < nc; j++) {
             const float wj = __shfl_sync(0xffffffffu, w, j);
             if (wj > 0.0f) {   // an empty part's o was never written
                 float4 po = *(const float4 *)(part_o + ((size_t)(mg.first + c0 + j) * group + g) * D + lane * 4);

@@ -172,118 +172,5 @@ __device__ __forceinline__ unsigned long long gtime() {
     return t;
 }
 
-// Merge of `count` partial triples (slots first..first+count of one (row, kv head), head g of
-// `group`) by one warp: lane c reads the (m, l) of part c, the warp agrees on the maximum and
-// the weights, then the o vectors are read with independent loads.  Parts with l <= 0 are
-// dropped by value: their o was never written
-// (crates/yaxus-backend-gpu/src/shaders.rs:1597-1598).  Loads bypass L1 (.cg): the parts may
-// have been written by other SMs during this very kernel.
-__device__ __forceinline__ void merge_parts(const float *part_o, const float *part_ml, uint32_t first, uint32_t count,
-                                            int group, int g, int lane, float &mx, float &l, float4 &acc) {
-    mx = -1e30f;
-    l = 0.0f;
-    acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (uint32_t c0 = 0; c0 < count; c0 += 32) {
-        const uint32_t c = c0 + lane;
-        float em = -1e30f, el = 0.0f;
-        if (c < count) {
-            float2 v = __ldcg((const float2 *)(part_ml + ((size_t)(first + c) * group + g) * 2));
-            em = v.x;
-            el = v.y;
-        }
-        const bool live = el > 0.0f;
-        float cm = live ? em : -1e30f;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, o));
-        const float nm = fmaxf(mx, cm);
-        const float r = __expf(mx - nm);
-        const float w = live ? __expf(em - nm) : 0.0f;
-        float ls = el * w;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
-        l = l * r + ls;
-        acc.x *= r;
-        acc.y *= r;
-        acc.z *= r;
-        acc.w *= r;
-        mx = nm;
-        const int nc = (int)min(32u, count - c0);
-#pragma unroll 4
-        for (int j = 0; j < nc; j++) {
-            const float wj = __shfl_sync(0xffffffffu, w, j);
-            if (wj > 0.0f) {
-                float4 po = __ldcg((const float4 *)(part_o + ((size_t)(first + c0 + j) * group + g) * D + lane * 4));
-                acc.x += po.x * wj;
-                acc.y += po.y * wj;
-                acc.z += po.z * wj;
-                acc.w += po.w * wj;
-            }
-        }
-    }
-}
-
-// Four merges at once by one warp (tasks with on[k] false are skipped): all (m, l) loads are
-// issued before any is used, then all o loads, so the four cost two round trips together.
-// Parts beyond 32 per task fall back to the one-at-a-time routine.
-__device__ __forceinline__ void merge_parts4(const float *part_o, const float *part_ml, const uint32_t (&first)[4],
-                                             const uint32_t (&count)[4], const bool (&on)[4], int group,
-                                             const int (&g)[4], int lane, float (&mx)[4], float (&l)[4],
-                                             float4 (&acc)[4]) {
-    bool small = true;
-#pragma unroll
-    for (int k = 0; k < 4; k++) small = small && (!on[k] || count[k] <= 32);
-    if (!small) {
-#pragma unroll
-        for (int k = 0; k < 4; k++)
-            if (on[k]) merge_parts(part_o, part_ml, first[k], count[k], group, g[k], lane, mx[k], l[k], acc[k]);
-        return;
-    }
-    float2 ml[4];
-#pragma unroll
-    for (int k = 0; k < 4; k++) {
-        ml[k] = make_float2(-1e30f, 0.0f);
-        if (on[k] && (uint32_t)lane < count[k])
-            ml[k] = __ldcg((const float2 *)(part_ml + ((size_t)(first[k] + lane) * group + g[k]) * 2));
-    }
-    float w[4];
-#pragma unroll
-    for (int k = 0; k < 4; k++) {
-        const bool live = ml[k].y > 0.0f;
-        float cm = live ? ml[k].x : -1e30f;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, o));
-        w[k] = live ? __expf(ml[k].x - cm) : 0.0f;
-        float ls = ml[k].y * w[k];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
-        mx[k] = cm;
-        l[k] = ls;
-        acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    uint32_t most = 0;
-#pragma unroll
-    for (int k = 0; k < 4; k++) most = max(most, on[k] ? count[k] : 0u);
-    for (uint32_t j = 0; j < most; j++) {
-        float4 po[4];
-        float wj[4];
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            wj[k] = __shfl_sync(0xffffffffu, w[k], j & 31);
-            po[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (on[k] && j < count[k] && wj[k] > 0.0f)
-                po[k] = __ldcg((const float4 *)(part_o + ((size_t)(first[k] + j) * group + g[k]) * D + lane * 4));
-            else
-                wj[k] = 0.0f;
-        }
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            acc[k].x += po[k].x * wj[k];
-            acc[k].y += po[k].y * wj[k];
-            acc[k].z += po[k].z * wj[k];
-            acc[k].w += po[k].w * wj[k];
-        }
-    }
-}
-
 }  // namespace dev
 }  // namespace yx
