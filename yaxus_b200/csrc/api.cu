@@ -53,11 +53,10 @@ int ensure_buffer(yx_ctx *ctx, void **buf, size_t *cap, size_t bytes) {
 // kernels of earlier passes (crates/yaxus-backend-gpu/src/dev/wgpu/mod.rs:284-294).  Here a
 // ring of pinned buffers does the same: the caller's arrays are copied at once, the
 // host-to-device copy is ordered on the stream, and a buffer is reused only after its copy.
-int upload_ordered(yx_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes) {
-    if (bytes == 0) return YX_OK;
+// A pinned staging buffer of at least `bytes`, free to write (its previous upload has left it).
+int stage_acquire(yx_ctx *ctx, size_t bytes, void **host) {
     if (ctx->ring.empty()) ctx->ring.resize(8);
     yx_ctx::Stage &st = ctx->ring[ctx->ring_next];
-    ctx->ring_next = (ctx->ring_next + 1) % ctx->ring.size();
     if (st.busy) {
         if (int rc = check_cuda(ctx, cudaEventSynchronize(st.done), "wait for a staging buffer")) return rc;
         st.busy = false;
@@ -72,12 +71,27 @@ int upload_ordered(yx_ctx *ctx, void *dst_dev, const void *src_host, size_t byte
     }
     if (!st.done)
         if (int rc = check_cuda(ctx, cudaEventCreateWithFlags(&st.done, cudaEventDisableTiming), "cudaEventCreate")) return rc;
-    memcpy(st.host, src_host, bytes);
+    *host = st.host;
+    return YX_OK;
+}
+
+// Sends the buffer stage_acquire last returned, stream-ordered, and moves on to the next one.
+int stage_commit(yx_ctx *ctx, void *dst_dev, size_t bytes) {
+    yx_ctx::Stage &st = ctx->ring[ctx->ring_next];
+    ctx->ring_next = (ctx->ring_next + 1) % ctx->ring.size();
     if (int rc = check_cuda(ctx, cudaMemcpyAsync(dst_dev, st.host, bytes, cudaMemcpyHostToDevice, ctx->stream), "upload"))
         return rc;
     if (int rc = check_cuda(ctx, cudaEventRecord(st.done, ctx->stream), "cudaEventRecord")) return rc;
     st.busy = true;
     return YX_OK;
+}
+
+int upload_ordered(yx_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes) {
+    if (bytes == 0) return YX_OK;
+    void *host = nullptr;
+    if (int rc = stage_acquire(ctx, bytes, &host)) return rc;
+    memcpy(host, src_host, bytes);
+    return stage_commit(ctx, dst_dev, bytes);
 }
 
 namespace {
@@ -180,10 +194,16 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
         slot->pass_serial = 0;
         return rc;
     }
-    std::vector<char> blob(total);
+    // The parts are laid out straight in a pinned staging buffer (padding bytes are never read).
+    char *blob = nullptr;
+    if (total > 0)
+        if (int rc = stage_acquire(ctx, total, (void **)&blob)) {
+            slot->pass_serial = 0;
+            return rc;
+        }
     size_t at = 0;
     auto put = [&](const void *src, size_t bytes, size_t padded) {
-        if (bytes) memcpy(blob.data() + at, src, bytes);
+        if (bytes) memcpy(blob + at, src, bytes);
         size_t here = at;
         at += padded;
         return here;
@@ -196,7 +216,7 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
     const size_t o_rec = put(pl.recs.data(), rec_b, rec_b);
     const size_t o_tit = put(pl.tile_items.data(), tit_b, tit_b);
     const size_t o_tcb = put(pl.tile_cta_begin.data(), pl.tile_cta_begin.size() * sizeof(uint32_t), tcb_b);
-    if (int rc = upload_ordered(ctx, slot->dev, blob.data(), total)) {
+    if (int rc = total > 0 ? stage_commit(ctx, slot->dev, total) : YX_OK) {
         slot->pass_serial = 0;
         return rc;
     }

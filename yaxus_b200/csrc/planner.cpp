@@ -54,7 +54,21 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
     if (pp.hkv <= 0 || pp.group <= 0) throw std::string("bad head counts");
     if (pp.max_rows < 1 || pp.max_rows > MAX_ITEM_ROWS) throw std::string("bad rows per item");
     if (T > 65535) throw std::string("a pass holds at most 65535 rows");
-    out = Plan();
+    // The plan object is reused from call to call: its arrays keep their capacity.
+    out.path = 0;
+    out.n_ctas = 0;
+    out.items.clear();
+    out.cta_begin.clear();
+    out.merges.clear();
+    out.n_parts = 0;
+    out.tile_items.clear();
+    out.tile_cta_begin.clear();
+    out.cta_hdr.clear();
+    out.tiles.clear();
+    out.recs.clear();
+    out.single_use = false;
+    out.has_empty_rows = false;
+    out.info = yx_plan_info{};
 
     // Dense ids of the physical pages named in this pass (page-table entry -> id), so that
     // per-page bookkeeping below is a flat array rather than a hash map.
@@ -417,8 +431,7 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
                     d.info = (t & 1u) | ((a - t * TILE_KEYS) << 1) | ((b - a + 1) << 8) | (it.pad_ ? 1u << 16 : 0u);
                     out.tiles.push_back(d);
                 }
-                ItemRec &r = out.recs[i];
-                memset(&r, 0, sizeof r);
+                ItemRec &r = out.recs[i];   // zero from resize(): the array was cleared
                 r.w[IR_TILES] = it.tile_end - it.tile_begin;
                 r.w[IR_KEY0] = it.tile_begin * TILE_KEYS;
                 r.w[IR_HEAD_ROWS] = (uint32_t)it.kv_head | ((uint32_t)it.n_rows << 16);
