@@ -376,6 +376,25 @@ def run_cuda(args):
         step(i)
     split_ms, combine_ms, calls = b.profile_end()
     kernel_ms = split_ms / max(calls, 1)
+    if not split_kv:
+        # The dominant kernel by itself, as it runs in the stream: back-to-back launches between
+        # two events (events around every single launch add the launch latency that chained
+        # launches hide, and read higher than the whole step).
+        b.set_tuning(skip_merge=1)
+        b.begin_pass(s.meta)
+        for i in range(20):
+            step(i)
+        n_k = min(args.steps, 4096)
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        k0.record()
+        for i in range(n_k):
+            step(i)
+        k1.record()
+        torch.cuda.synchronize()
+        kernel_ms = k0.elapsed_time(k1) / n_k
+        b.set_tuning()
+        b.begin_pass(s.meta)
 
     # end to end through the boundary call: pass metadata and qkv rows from pinned host
     # memory, fused norm + RoPE + append + attention, result read back to the host.

@@ -77,6 +77,7 @@ typedef struct yx_tuning {
     int32_t fused_merge;     /* 1: the split-key kernel merges the triples itself; 0: a combine kernel does */
     int32_t tile_single;     /* 1: the tcgen05 tile kernel takes one query head per CTA (default: two) */
     int32_t min_piece;       /* fewest 64-key tiles the planner makes an item of when it cuts a run (0: default) */
+    int32_t skip_merge;      /* 1: measurement only - the split-key kernel runs, its triples are not merged (no output) */
 } yx_tuning;
 
 /* What the last yx_attend / yx_attention call planned; for tests and benchmarks. */

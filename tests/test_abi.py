@@ -30,7 +30,7 @@ def test_bindings_match_the_header():
 def test_struct_sizes():
     assert ctypes.sizeof(_lib.Rope) == 65 * 4
     assert ctypes.sizeof(_lib.Layer) == 66 * 4
-    assert ctypes.sizeof(_lib.Tuning) == 48
+    assert ctypes.sizeof(_lib.Tuning) == 52
     assert ctypes.sizeof(_lib.PlanInfo) == 48
 
 

@@ -364,7 +364,7 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     }
     // With every row in the tiled kernel's hands and no partial triples asked for, the merge
     // has nothing to do.
-    const bool need_combine = !pl.items.empty() || o_out != nullptr;
+    const bool need_combine = (!pl.items.empty() || o_out != nullptr) && ctx->tuning.skip_merge != 1;
     if (path == 2) {
         // Rows without a live key in the range get no item, so nothing would write them.
         if (a.fused && o_out && pl.has_empty_rows)
