@@ -14,7 +14,7 @@
  *    (crates/yaxus-model/src/lib.rs:187-197).  Nothing here aborts the process.
  *  - All work is enqueued on the context's stream; only yx_sync and yx_download with
  *    `wait != 0` wait for the device.  A context is not thread-safe (the reference drives a
- *    backend from one inference thread, docs/DESIGN.md:131).
+ *    backend from one inference thread: its design notes, section on the engine thread).
  *  - Pointers named *_dev are device pointers; *_host are host pointers.
  *  - head_dim must be 128 and the page is 128 tokens, as in the reference's GPU backend
  *    (crates/yaxus-backend-gpu/src/lib.rs:72, crates/yaxus-model/src/kv.rs:17).
