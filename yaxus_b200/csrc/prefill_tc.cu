@@ -530,26 +530,25 @@ __device__ __forceinline__ void exp_chunk(uint32_t (&sr)[32], float sl2, float m
     }
 }
 
+// 32 columns to TMEM: words [o, o + 16) of x, then of y (no copy through a third array).
+__device__ __forceinline__ void tmem_st32_pair(uint32_t taddr, const uint32_t (&x)[32], const uint32_t (&y)[32], int o) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+        "r"(x[o + 0]), "r"(x[o + 1]), "r"(x[o + 2]), "r"(x[o + 3]), "r"(x[o + 4]), "r"(x[o + 5]), "r"(x[o + 6]), "r"(x[o + 7]),
+        "r"(x[o + 8]), "r"(x[o + 9]), "r"(x[o + 10]), "r"(x[o + 11]), "r"(x[o + 12]), "r"(x[o + 13]), "r"(x[o + 14]), "r"(x[o + 15]),
+        "r"(y[o + 0]), "r"(y[o + 1]), "r"(y[o + 2]), "r"(y[o + 3]), "r"(y[o + 4]), "r"(y[o + 5]), "r"(y[o + 6]), "r"(y[o + 7]),
+        "r"(y[o + 8]), "r"(y[o + 9]), "r"(y[o + 10]), "r"(y[o + 11]), "r"(y[o + 12]), "r"(y[o + 13]), "r"(y[o + 14]), "r"(y[o + 15])
+        : "memory");
+}
+
 // Probabilities of 64 keys (two chunks) to TMEM: 32 packed columns at `p_addr`, and for bf16
-// their low parts 64 columns further on.
+// their low parts 64 columns further on.  The stores are only issued: the caller waits for them
+// (tcgen05.wait::st) before it tells the tensor core.
 template <bool BF16>
 __device__ __forceinline__ void store_half(uint32_t p_addr, const uint32_t (&x)[32], const uint32_t (&y)[32]) {
-    uint32_t w[32];
-#pragma unroll
-    for (int i = 0; i < 16; i++) {
-        w[i] = x[i];
-        w[16 + i] = y[i];
-    }
-    tmem_st32(p_addr, w);
-    if (BF16) {
-#pragma unroll
-        for (int i = 0; i < 16; i++) {
-            w[i] = x[16 + i];
-            w[16 + i] = y[16 + i];
-        }
-        tmem_st32(p_addr + 64, w);
-    }
-    tmem_st_wait();
+    tmem_st32_pair(p_addr, x, y, 0);
+    if (BF16) tmem_st32_pair(p_addr + 64, x, y, 16);
 }
 
 template <bool BF16>
@@ -872,13 +871,16 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
                 exp_chunk<BF16>(s0, sl2, ms, sum0, sum1);
                 exp_chunk<BF16>(s1, sl2, ms, sum0, sum1);
                 store_half<BF16>(s_addr, s0, s1);
+                // the stores' latency passes under the next chunk's exponentials
+                exp_chunk<BF16>(s2, sl2, ms, sum0, sum1);
+                tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(b_p_half + 16 * t);
                 if (tr) P.trace[(t * 64 + g) * 8 + 1] = clock64();
-                exp_chunk<BF16>(s2, sl2, ms, sum0, sum1);
                 exp_chunk<BF16>(s3, sl2, ms, sum0, sum1);
                 store_half<BF16>(s_addr + 32, s2, s3);
+                tmem_st_wait();
                 l += sum0 + sum1;
                 tc_fence_before();
                 __syncwarp();
