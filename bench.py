@@ -125,14 +125,21 @@ def run_reference(args):
     def step():
         return o.attend(s.q, s.meta.pos, s.meta.pt_off, s.meta.pages, s.hq, s.hkv, 128, s.window, K, V, threads=cores)
 
-    for _ in range(args.warmup):
+    # Bounded: the CPU takes tens of milliseconds per step, and K may be a GPU-sized count.  At most
+    # about a minute of timed CPU work; the per-step time is what is reported.
+    t0 = time.perf_counter()
+    step()
+    est = time.perf_counter() - t0
+    n_warm = max(0, min(args.warmup, int(10.0 / est)) - 1)
+    n_timed = max(1, min(args.steps, int(60.0 / est)))
+    for _ in range(n_warm):
         step()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(n_timed):
         step()
-    dt = (time.perf_counter() - t0) / args.steps
+    dt = (time.perf_counter() - t0) / n_timed
     value = s.unique_kv_bytes() / dt / 1e9
-    sample = f"the whole step ({s.meta.rows} rows x {s.hq} heads), {args.steps} times"
+    sample = f"the whole step ({s.meta.rows} rows x {s.hq} heads), {n_timed} of the {args.steps} steps timed"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
