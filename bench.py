@@ -245,18 +245,45 @@ def run_prefill(args):
     kh = torch.empty(T, hkv * 128, dtype=tdt).pin_memory()
     vh = torch.empty(T, hkv * 128, dtype=tdt).pin_memory()
     oh = torch.empty(T, hq * 128, dtype=tdt).pin_memory()
-    qd, kd, vd = torch.empty_like(qh, device=dev), torch.empty_like(kh, device=dev), torch.empty_like(vh, device=dev)
+    # Two sets of device buffers and two copy streams: the rows of pass p + 1 go up and the
+    # result of pass p - 1 comes down while pass p computes (what a serving loop does with host
+    # buffers); every buffer's reuse is ordered by events.
+    qd = [torch.empty_like(qh, device=dev) for _ in range(2)]
+    kd = [torch.empty_like(kh, device=dev) for _ in range(2)]
+    vd = [torch.empty_like(vh, device=dev) for _ in range(2)]
+    od = [torch.empty(T, hq * 128, dtype=tdt, device=dev) for _ in range(2)]
+    up, down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    main = torch.cuda.current_stream(dev)
+    in_ready = [torch.cuda.Event() for _ in range(2)]
+    in_free = [torch.cuda.Event() for _ in range(2)]
+    out_ready = [torch.cuda.Event() for _ in range(2)]
+    out_free = [torch.cuda.Event() for _ in range(2)]
 
     def e2e_step(i):
-        for p in passes:
+        for n, p in enumerate(passes):
+            x = n & 1
+            with torch.cuda.stream(up):
+                up.wait_event(in_free[x])            # the pass that last read this set is done
+                qd[x].copy_(qh, non_blocking=True)
+                kd[x].copy_(kh, non_blocking=True)
+                vd[x].copy_(vh, non_blocking=True)
+                in_ready[x].record(up)
             b.begin_pass(p.meta)
-            qd.copy_(qh, non_blocking=True)
-            kd.copy_(kh, non_blocking=True)
-            vd.copy_(vh, non_blocking=True)
-            b.kv_append(kv, i % n_layers, kd, vd)
-            b.attend(kv, i % n_layers, qd, hq, out=out)
-            oh.copy_(out, non_blocking=True)
-            b.sync()
+            main.wait_event(in_ready[x])
+            main.wait_event(out_free[x])             # the download that last read this output is done
+            b.kv_append(kv, i % n_layers, kd[x], vd[x])
+            b.attend(kv, i % n_layers, qd[x], hq, out=od[x])
+            in_free[x].record(main)
+            out_ready[x].record(main)
+            with torch.cuda.stream(down):
+                down.wait_event(out_ready[x])
+                oh.copy_(od[x], non_blocking=True)
+                out_free[x].record(down)
+        main.wait_stream(down)
+        b.sync()
+    for x in range(2):
+        in_free[x].record(main)
+        out_free[x].record(main)
     e2e_step(0)
     barrier()
     e2e_n = max(1, min(args.steps, 10))
