@@ -77,7 +77,6 @@ typedef struct yx_tuning {
     int32_t fused_merge;     /* 1: the split-key kernel merges the triples itself; 0: a combine kernel does */
     int32_t tile_single;     /* 1: the tcgen05 tile kernel takes one query head per CTA (default: two) */
     int32_t min_piece;       /* fewest 64-key tiles the planner makes an item of when it cuts a run (0: default) */
-    int32_t skip_merge;      /* 1: measurement only - the split-key kernel runs, its triples are not merged (no output) */
 } yx_tuning;
 
 /* What the last yx_attend / yx_attention call planned; for tests and benchmarks. */
@@ -210,26 +209,16 @@ int yx_attend_allgather(yx_ctx *ctx, yx_kv *kv, int layer, const void *q_dev, in
  * page pool, or that cannot take the device-wide stall of an allocation inside their decode loop.
  * Larger passes are rejected with YX_ERR_INVALID and a message naming the limit.
  * The context's device must be the current device.  The first call on a device looks the
- * array's address up; make it before any stream capture begins.  The array is one per device
- * and process: calls whose kernels may overlap on a device race on it, so order them on one
- * stream or with events.  Nothing in it needs clearing between calls. */
+ * array's address up; make it before any stream capture begins.  Where the CUDA runtime loads
+ * modules lazily, that first call is also where the driver commits the 4 MiB of the array: free
+ * device memory drops once, there, and not again.  The array is one per device context (one per
+ * device for a process that only uses the runtime API): calls whose kernels may overlap on a
+ * device race on it, so order them on one stream or with events.  Nothing in it needs clearing
+ * between calls. */
 #define YX_STATIC_SPLITS 8
 #define YX_STATIC_MAX_ROW_HEADS 1024
 int yx_attend_static(yx_ctx *ctx, yx_kv *kv, int layer, const void *q_dev, int q_dtype, int hq, int64_t window,
                      void *out_dev, int out_dtype);
-
-/* ---- test hook -------------------------------------------------------------------------- */
-
-/* Runs the split-key planner (the counterpart of `AttentionCase::plan`,
- * crates/yaxus-backend-gpu/src/plan.rs:275-309) on host arrays; needs no device.  Each item is
- * written as YX_PROBE_ITEM_WORDS words: tile_begin, tile_end, key_lo, key_hi, pt_off, kv_head,
- * n_rows, padded rows, CTA, then 16 pass rows and their 16 partial slots.  share_prefix: 0 off,
- * 1 on with the default rows per shared item, above 1 that many rows per shared item. */
-#define YX_PROBE_ITEM_WORDS 41
-int yx_plan_probe(uint32_t rows, const uint32_t *pos_host, const uint32_t *pt_off_host, const uint32_t *pages_host,
-                  uint32_t n_pages, int hkv, int group, int64_t window, uint64_t key_lo, uint64_t key_hi,
-                  int max_rows, int n_ctas, int share_prefix, int esize, int cost32, int cost64, int item_cost,
-                  int min_piece, yx_plan_info *info, uint32_t *items_out, uint32_t max_items);
 
 #ifdef __cplusplus
 }

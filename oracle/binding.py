@@ -1,5 +1,6 @@
-"""ctypes face of the CPU oracle (oracle/yx_ref.cpp).  Test infrastructure: only tests,
-the smoke check and the benchmark's CPU baseline may use it."""
+"""ctypes face of the CPU oracle (yx_ref.cpp beside this file).  Test infrastructure: only the
+tests, the smoke check and the benchmark's CPU-baseline and reference legs may use it; the
+CUDA library never does."""
 import ctypes
 import os
 from ctypes import POINTER, c_double, c_float, c_int, c_int64, c_size_t, c_uint16, c_uint32, c_uint64
@@ -32,7 +33,7 @@ def _u32(a):
 class Oracle:
     def __init__(self):
         if not os.path.exists(LIB):
-            from oracle import build
+            from . import build
             build.build()
         L = ctypes.CDLL(LIB)
         L.yxref_selftest.restype = c_double

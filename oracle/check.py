@@ -1,5 +1,7 @@
-"""Helpers shared by the GPU parity tests: load a workload into the CUDA backend, run the
-same step through the CPU oracle, compare within the path's tolerance."""
+"""The checker side of a parity comparison: load a workload into the CUDA backend, run the
+same step through the CPU oracle, compare within the path's tolerance.  Test infrastructure,
+like everything in this directory: used by the tests, the smoke check and the benchmark's
+parity and CPU-baseline legs, never by the CUDA library."""
 import numpy as np
 import torch
 

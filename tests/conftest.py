@@ -10,7 +10,7 @@ if ROOT not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200)")
-    # Build what is missing (the GPU box receives prebuilt libraries with the snapshot).
+    # Build whatever is missing or older than its sources.
     from oracle import build as oracle_build
     oracle_build.build()
     from yaxus_b200 import build as lib_build
@@ -19,7 +19,7 @@ def pytest_configure(config):
 
 @pytest.fixture(scope="session")
 def oracle():
-    from tests.oracle import Oracle
+    from oracle.binding import Oracle
     return Oracle()
 
 

@@ -15,7 +15,9 @@ import numpy as np
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
 
-from tests.oracle import Oracle  # noqa: E402
+from oracle.binding import Oracle  # noqa: E402
+from yaxus_b200 import workloads as W  # noqa: E402
+from yaxus_b200._lib import BF16, F16  # noqa: E402
 from yaxus_b200.kvcache import PassMeta  # noqa: E402
 
 
@@ -51,6 +53,13 @@ def main():
         q = o.write_rows(qkv, meta.pos, meta.kv_slot, q_norm, k_norm, hq, hkv, d, eps, inv_freq, conc, K, V)
         out[f"out_{tag}"] = o.attend(q, meta.pos, meta.pt_off, meta.pages, hq, hkv, d, w, K, V, threads=1)
         out["q_rot"] = q
+        # 16-bit caches: the cached context and the rows write_rows stores are rounded to the
+        # storage type (round to nearest even), everything else is the f32 algorithm.
+        for name, dt in (("f16", F16), ("bf16", BF16)):
+            K, V = W.round_through(K0, dt), W.round_through(V0, dt)
+            q = o.write_rows(qkv, meta.pos, meta.kv_slot, q_norm, k_norm, hq, hkv, d, eps, inv_freq, conc, K, V,
+                             store_dtype=dt)
+            out[f"out_{tag}_{name}"] = o.attend(q, meta.pos, meta.pt_off, meta.pages, hq, hkv, d, w, K, V, threads=1)
     np.savez_compressed(
         os.path.join(os.path.dirname(os.path.abspath(__file__)), "attention_small.npz"), hq=hq, hkv=hkv, eps=eps,
         window=window, conc=conc, inv_freq=inv_freq, qkv=qkv, q_norm=q_norm, k_norm=k_norm, pos=meta.pos,

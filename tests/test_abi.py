@@ -8,8 +8,8 @@ from yaxus_b200 import _lib
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def declared_functions():
-    text = open(os.path.join(ROOT, "include", "yaxus_cuda.h")).read()
+def declared_functions(path=os.path.join("include", "yaxus_cuda.h")):
+    text = open(os.path.join(ROOT, path)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(yx_[a-z0-9_]+)\s*\(", text)))
 
@@ -24,13 +24,14 @@ def test_every_declared_symbol_is_exported():
 
 def test_bindings_match_the_header():
     assert sorted(_lib.SIGNATURES) == declared_functions()
+    assert sorted(_lib.HOOK_SIGNATURES) == declared_functions(os.path.join("yaxus_b200", "csrc", "yx_hooks.h"))
     _lib.cuda_lib()   # binds every signature; raises on a missing symbol
 
 
 def test_struct_sizes():
     assert ctypes.sizeof(_lib.Rope) == 65 * 4
     assert ctypes.sizeof(_lib.Layer) == 66 * 4
-    assert ctypes.sizeof(_lib.Tuning) == 52
+    assert ctypes.sizeof(_lib.Tuning) == 48
     assert ctypes.sizeof(_lib.PlanInfo) == 48
 
 

@@ -28,7 +28,7 @@ def _free_port():
 
 def _worker(rank, world, port, case, results):
     sys.path.insert(0, ROOT)
-    from tests.oracle import Oracle
+    from oracle.binding import Oracle
     from yaxus_b200 import workloads as W
     from yaxus_b200._lib import F16
     os.environ["MASTER_ADDR"] = "127.0.0.1"

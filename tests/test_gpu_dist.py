@@ -4,6 +4,7 @@ exchanges nothing.  Needs two devices; skipped on one."""
 import os
 import socket
 import sys
+import time
 
 import numpy as np
 import pytest
@@ -26,8 +27,8 @@ def _worker(rank, world, port, results):
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     import torch.distributed as dist
-    from tests.gpu_util import assert_close, dev, load, oracle_step
-    from tests.oracle import Oracle
+    from oracle.check import assert_close, dev, load, oracle_step
+    from oracle.binding import Oracle
     from yaxus_b200 import CudaBackend
     from yaxus_b200 import workloads as W
     torch.cuda.set_device(rank)
@@ -37,6 +38,9 @@ def _worker(rank, world, port, results):
         b = CudaBackend(rank)
         o = Oracle()
         b.comm_create(world, rank)
+        # Every collective first, every comparison afterwards: a rank whose check fails must not
+        # leave its peer alone inside the next all-gather, which has no bound of its own.
+        pending = []
         for window in (None, 3000):
             # every rank holds the whole cache here (the test is about the exchange); it reads its pages only
             s = W.long_decode(ctx=8192 + 33, window=window, hq=8, hkv=2)
@@ -45,8 +49,11 @@ def _worker(rank, world, port, results):
             b.kv_append(kv, 0, dev(b, s.k_new), dev(b, s.v_new))
             _, _, klo, khi = W.partition_pages(s.arena_pages, world, rank)
             out = b.attend_allgather(kv, 0, dev(b, s.q), s.hq, -1, klo, khi)
-            assert_close(b.to_host(out), oracle_step(o, s), what=f"rank {rank} window {window}")
+            pending.append((b.to_host(out), s, f"rank {rank} window {window}"))
             kv.close()
+        dist.barrier()    # the last collective of this test: nothing below waits for a peer
+        for got, s, what in pending:
+            assert_close(got, oracle_step(o, s), what=what)
         # by sequence: each rank its own sequences, no exchange
         whole = W.build("seq", 21, 8, 2, 1, [300, 5, 127, 1000], [1] * 4)
         ref = oracle_step(o, whole)
@@ -63,7 +70,8 @@ def _worker(rank, world, port, results):
         ok = True
     finally:
         results[rank] = ok
-        dist.destroy_process_group()
+        # No destroy_process_group here: it is a collective, and a rank that failed must not make
+        # its peer wait.  The process ends right after this.
 
 
 def test_two_gpus_split_keys_and_sequences():
@@ -77,7 +85,19 @@ def test_two_gpus_split_keys_and_sequences():
         procs = [ctx.Process(target=_worker, args=(r, world, port, results)) for r in range(world)]
         for p in procs:
             p.start()
-        for p in procs:
-            p.join(300)
-            assert p.exitcode == 0, f"rank exited with {p.exitcode}"
+        try:
+            deadline = time.time() + 300
+            for p in procs:
+                p.join(max(1.0, deadline - time.time()))
+        finally:
+            # A rank still alive here is stuck (its peer died inside a collective): it is ended, not
+            # left spinning on a GPU.
+            for p in procs:
+                if p.is_alive():
+                    p.terminate()
+                    p.join(10)
+                if p.is_alive():
+                    p.kill()
+                    p.join(10)
+        assert [p.exitcode for p in procs] == [0] * world, [p.exitcode for p in procs]
         assert dict(results) == {0: True, 1: True}

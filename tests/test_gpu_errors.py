@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from tests.gpu_util import dev, load
+from oracle.check import dev, load
 from yaxus_b200 import _lib
 from yaxus_b200 import workloads as W
 from yaxus_b200._lib import F16, F32
@@ -84,7 +84,7 @@ def test_several_passes_queue_without_a_sync(backend, oracle):
     # Pass metadata is copied at begin_pass and uploaded in stream order, so many passes can
     # be queued before any read-back (the reference's command-stream writes,
     # crates/yaxus-backend-gpu/src/dev/wgpu/mod.rs:284-294).
-    from tests.gpu_util import assert_close, oracle_step
+    from oracle.check import assert_close, oracle_step
     scen = [W.build("q", 40 + i, 8, 2, F16, [50 + 37 * i, 3 * i], [1 + i % 3, 2]) for i in range(12)]
     kvs = [load(backend, s) for s in scen]
     outs = []
@@ -97,3 +97,21 @@ def test_several_passes_queue_without_a_sync(backend, oracle):
         assert_close(o.cpu().numpy(), oracle_step(oracle, s), what=s.name)
     for kv in kvs:
         kv.close()
+
+
+def test_a_device_wait_that_runs_out_is_an_error_not_a_hang(backend, oracle):
+    # Every wait inside the kernels is bounded; when one runs out the kernel records it in the
+    # context's status word and returns, and the next read-back reports YX_ERR_DEVICE.  Here a
+    # one-CTA kernel waits on an mbarrier nobody arrives on, with a limit of about a millisecond
+    # (no attention kernel is starved to provoke it).  The context stays usable afterwards.
+    from oracle.check import assert_close, oracle_step, run_step
+    rc = backend._L.yx_hook_expire_wait(backend._ctx, 2_000_000)
+    assert rc == _lib.YX_OK
+    with pytest.raises(BackendError) as e:
+        backend.sync()
+    assert e.value.code == _lib.YX_ERR_DEVICE and "code 2 at 900" in str(e.value)
+    backend.clear_error()
+    s = W.build("after", 5, 8, 2, F16, [300, 40], [1, 3])
+    kv = load(backend, s)
+    assert_close(run_step(backend, kv, s), oracle_step(oracle, s), what="after an expired wait")
+    kv.close()

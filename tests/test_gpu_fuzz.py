@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-from tests.gpu_util import ABS_TOL, assert_close, dev, load, oracle_step
+from oracle.check import ABS_TOL, assert_close, dev, load, oracle_step
 from yaxus_b200 import workloads as W
 from yaxus_b200._lib import BF16, F16, F32
 

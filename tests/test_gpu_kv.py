@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from tests.gpu_util import dev, layers_for, load
+from oracle.check import dev, layers_for, load
 from yaxus_b200 import workloads as W
 from yaxus_b200._lib import BF16, F16, F32, PAGE
 from yaxus_b200.backend import LayerMeta
@@ -101,7 +101,7 @@ def test_fork_copy_on_write_through_the_host_cache(backend, oracle):
         out = backend.to_host(backend.attend(kv, 0, dev(backend, q), hq))
         oracle.append_rows(W.round_through(k, F16), W.round_through(v, F16), meta.kv_slot, K, V)
         ref = oracle.attend(q, meta.pos, meta.pt_off, meta.pages, hq, hkv, 128, None, K, V)
-        from tests.gpu_util import assert_close
+        from oracle.check import assert_close
         assert_close(out, ref, what="fork step")
 
     a = cache.new_seq()

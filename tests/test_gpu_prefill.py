@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from tests.gpu_util import assert_close, dev, load, oracle_step, run_step
+from oracle.check import assert_close, dev, load, oracle_step, run_step
 from yaxus_b200 import workloads as W
 from yaxus_b200._lib import BF16, F16
 
@@ -77,7 +77,30 @@ def test_output_dtypes_and_f32_queries(backend, oracle):
     for qt, ot, tol in ((torch.bfloat16, torch.bfloat16, 2e-2), (torch.bfloat16, torch.float32, 2e-3)):
         got = run_step(backend, kv, s, q_dtype=qt, out_dtype=ot)
         assert_close(got, ref, abs_tol=tol, what=f"{qt} -> {ot}")
-    # f32 queries are rounded to the cache's type by the kernel: same reference
+    # f32 queries keep their low part on a bf16 cache: the reference is fed the unrounded queries
     got = run_step(backend, kv, s, q_dtype=torch.float32)
-    assert_close(got, ref, abs_tol=4e-3, what="f32 q")
+    assert_close(got, oracle_step(oracle, s), what="f32 q")
+    kv.close()
+
+
+def test_last_chunk_of_the_full_configuration(backend, oracle):
+    # Chunked prefill at its benchmark shape: 8 sequences x 4096 tokens, 32 query / 8 KV heads,
+    # bf16 Q/K/V.  The cache holds the first seven chunks (3584 tokens per sequence); the pass is
+    # the eighth chunk, 512 rows per sequence: the most pages per item, 512 items dealt over the
+    # persistent CTAs.  The appended rows are checked byte-exact at their slots, the output
+    # against the oracle on every eighth row of every sequence.
+    s = W.prefill_chunk(seed=W.SEED0 + 3, n_seq=8, done=3584, chunk=512, kv_dtype=BF16, hq=32, hkv=8, total=4096)
+    assert s.meta.rows == 4096
+    kv = load(backend, s)
+    got = run_step(backend, kv, s, q_dtype=torch.bfloat16, src_dtype=torch.float32)
+    assert backend.last_plan().path == 3
+    K = s.k_f32()
+    V = s.v_f32()
+    oracle.append_rows(W.round_through(s.k_new, BF16), W.round_through(s.v_new, BF16), s.meta.kv_slot, K, V)
+    k_dev, v_dev = backend.read_pages(kv, 0, 0, s.arena_pages)
+    assert np.array_equal(W.from_bits(k_dev, BF16), K) and np.array_equal(W.from_bits(v_dev, BF16), V)
+    sample = np.concatenate([np.arange(sq * 512, (sq + 1) * 512)[::8] for sq in range(8)])
+    ref = oracle.attend(q_rounded(s)[sample], s.meta.pos[sample], s.meta.pt_off[sample], s.meta.pages, s.hq, s.hkv, 128,
+                        None, K, V)
+    assert_close(got[sample], ref, what="chunk 7 of 8 x 4096")
     kv.close()

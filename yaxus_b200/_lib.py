@@ -8,7 +8,8 @@ import os
 from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint32, c_uint64, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-CUDA_LIB = os.path.join(HERE, "libyaxus_cuda.so")
+# YAXUS_CUDA_LIB names another build of the same library (the diagnostic build with time stamps).
+CUDA_LIB = os.environ.get("YAXUS_CUDA_LIB") or os.path.join(HERE, "libyaxus_cuda.so")
 HOST_LIB = os.path.join(HERE, "libyaxus_host.so")
 
 YX_OK, YX_ERR_INVALID, YX_ERR_CUDA, YX_ERR_OOM, YX_ERR_STATE, YX_ERR_DEVICE, YX_ERR_NCCL, YX_ERR_UNSUPPORTED = range(8)
@@ -29,7 +30,7 @@ class Layer(ctypes.Structure):
 
 class Tuning(ctypes.Structure):
     _fields_ = [("force_path", c_int32), ("ctas_per_sm", c_int32), ("share_prefix", c_int32),
-                ("tile_min_rows", c_int32), ("cost32", c_int32), ("cost64", c_int32), ("stages", c_int32), ("share_rows", c_int32), ("item_cost", c_int32), ("fused_merge", c_int32), ("tile_single", c_int32), ("min_piece", c_int32), ("skip_merge", c_int32)]
+                ("tile_min_rows", c_int32), ("cost32", c_int32), ("cost64", c_int32), ("stages", c_int32), ("share_rows", c_int32), ("item_cost", c_int32), ("fused_merge", c_int32), ("tile_single", c_int32), ("min_piece", c_int32)]
 
 
 class PlanInfo(ctypes.Structure):
@@ -79,8 +80,15 @@ SIGNATURES = {
     "yx_comm_destroy": (c_int, [c_void_p]),
     "yx_attend_allgather": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int64, c_uint64, c_uint64,
                                     c_void_p, c_int]),
+}
+
+# The library's own test and measurement hooks (csrc/yx_hooks.h); not part of the C ABI.
+HOOK_SIGNATURES = {
     "yx_plan_probe": (c_int, [c_uint32, _U32P, _U32P, _U32P, c_uint32, c_int, c_int, c_int64, c_uint64, c_uint64,
                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, POINTER(PlanInfo), _U32P, c_uint32]),
+    "yx_hook_skip_merge": (c_int, [c_void_p, c_int]),
+    "yx_hook_expire_wait": (c_int, [c_void_p, c_uint64]),
+    "yx_hook_set_trace": (c_int, [c_void_p, c_void_p]),
 }
 
 HOST_SIGNATURES = {
@@ -128,7 +136,7 @@ def cuda_lib():
             raise RuntimeError(
                 f"{CUDA_LIB} is missing: build it with `python -m yaxus_b200.build` "
                 "(needs nvcc; targets sm_100a). yaxus_b200 has no CPU or PyTorch fallback.")
-        _cuda = _bind(ctypes.CDLL(CUDA_LIB), SIGNATURES)
+        _cuda = _bind(_bind(ctypes.CDLL(CUDA_LIB), SIGNATURES), HOOK_SIGNATURES)
     return _cuda
 
 

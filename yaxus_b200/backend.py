@@ -148,10 +148,14 @@ class CudaBackend:
 
     def set_tuning(self, force_path: int = 0, ctas_per_sm: int = 0, share_prefix: int = 0, tile_min_rows: int = 0,
                    cost32: int = 0, cost64: int = 0, stages: int = 0, share_rows: int = 0,
-                   item_cost: int = 0, fused_merge: int = 0, tile_single: int = 0, min_piece: int = 0, skip_merge: int = 0):
+                   item_cost: int = 0, fused_merge: int = 0, tile_single: int = 0, min_piece: int = 0):
         t = _lib.Tuning(force_path, ctas_per_sm, share_prefix, tile_min_rows, cost32, cost64, stages, share_rows, item_cost,
-                        fused_merge, tile_single, min_piece, skip_merge)
+                        fused_merge, tile_single, min_piece)
         self._L.yx_set_tuning(self._ctx, ctypes.byref(t))
+
+    def hook_skip_merge(self, on: bool) -> None:
+        """Measurement hook (csrc/yx_hooks.h): attention calls leave the merge out."""
+        self._L.yx_hook_skip_merge(self._ctx, 1 if on else 0)
 
     def last_plan(self) -> _lib.PlanInfo:
         info = _lib.PlanInfo()

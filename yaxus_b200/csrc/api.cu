@@ -1,5 +1,6 @@
 // The C ABI of libyaxus_cuda: contexts, KV storage, pass metadata and the attention entry
-// points.  Kernels live in kv_ops.cu, attend_simt.cu, attend_mma.cu and combine.cu.
+// points.  Kernels live in kv_ops.cu, attend_simt.cu, attend_mma.cu (split-key, 16-bit caches),
+// prefill_tc.cu (tcgen05 tiles for prompt chunks) and combine.cu.
 #include <string.h>
 
 #include <algorithm>
@@ -254,8 +255,7 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     if (ctx->pass.rows == 0) return YX_OK;
     if (!q || (!out && !o_out)) return fail(ctx, YX_ERR_INVALID, "null tensor");
     if (window < 0) window = kv->layers[layer].window;
-    for (uint32_t r = 0; r < ctx->pass.rows; r++)
-        if (ctx->pass.pos[r] >= kv->max_pos) return fail(ctx, YX_ERR_INVALID, "a row's position exceeds max_pos");
+    if (ctx->pass.max_pos_seen >= kv->max_pos) return fail(ctx, YX_ERR_INVALID, "a row's position exceeds max_pos");
     DeviceGuard guard(ctx->device);
 
     const int path = pick_path(ctx, kv);
@@ -289,10 +289,10 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     if (int rc = get_plan(ctx, pp, &cp)) return rc;
     const Plan &pl = cp->plan;
 
-    // Every page id the plan will read must be inside the arena.
-    for (uint32_t p : ctx->pass.pages)
-        if (p >= kv->pages && key_lo == 0 && key_hi == UINT64_MAX)
-            return fail(ctx, YX_ERR_INVALID, "page id outside the KV arena");
+    // Every page id the plan will read must be inside the arena.  (With a key range, entries of
+    // pages outside the range may be placeholders: the kernels' own check covers what is read.)
+    if (ctx->pass.max_page_seen >= kv->pages && !ctx->pass.pages.empty() && key_lo == 0 && key_hi == UINT64_MAX)
+        return fail(ctx, YX_ERR_INVALID, "page id outside the KV arena");
 
     size_t o_bytes = (size_t)std::max<uint32_t>(pl.n_parts, 1) * group * D * sizeof(float);
     size_t ml_bytes = (size_t)std::max<uint32_t>(pl.n_parts, 1) * group * 2 * sizeof(float);
@@ -364,7 +364,7 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     }
     // With every row in the tiled kernel's hands and no partial triples asked for, the merge
     // has nothing to do.
-    const bool need_combine = (!pl.items.empty() || o_out != nullptr) && ctx->tuning.skip_merge != 1;
+    const bool need_combine = (!pl.items.empty() || o_out != nullptr) && !ctx->skip_merge;
     if (path == 2) {
         // Rows without a live key in the range get no item, so nothing would write them.
         if (a.fused && o_out && pl.has_empty_rows)
@@ -667,37 +667,47 @@ int yx_begin_pass(yx_ctx *ctx, uint32_t rows, const uint32_t *pos, const uint32_
     if (rows && (!pos || !kv_slot || !pt_off)) return fail(ctx, YX_ERR_INVALID, "begin_pass: null array");
     if (n_pages && !pages) return fail(ctx, YX_ERR_INVALID, "begin_pass: null page table");
     if (rows > 65535) return fail(ctx, YX_ERR_UNSUPPORTED, "begin_pass: more than 65535 rows");
+    uint32_t max_pos = 0, max_slot = 0, max_page = 0;
     for (uint32_t r = 0; r < rows; r++) {
         if ((uint64_t)pt_off[r] + pos[r] / PAGE >= n_pages)
             return fail(ctx, YX_ERR_INVALID, "begin_pass: a row's page table runs past `pages`");
         // kv_slot must be the slot of the row's own position (PassMeta, lib.rs:69-70).
         if (kv_slot[r] != pages[pt_off[r] + pos[r] / PAGE] * (uint32_t)PAGE + pos[r] % PAGE)
             return fail(ctx, YX_ERR_INVALID, "begin_pass: kv_slot is not slot(pages, pos)");
+        max_pos = std::max(max_pos, pos[r]);
+        max_slot = std::max(max_slot, kv_slot[r]);
     }
+    for (uint32_t i = 0; i < n_pages; i++) max_page = std::max(max_page, pages[i]);
     DeviceGuard guard(ctx->device);
     PassHost &p = ctx->pass;
     p.rows = rows;
-    p.pos.assign(pos, pos + rows);
+    p.pos.assign(pos, pos + rows);          // the vectors keep their capacity from pass to pass
     p.kv_slot.assign(kv_slot, kv_slot + rows);
     p.pt_off.assign(pt_off, pt_off + rows);
     p.pages.assign(pages, pages + n_pages);
+    p.max_pos_seen = max_pos;
+    p.max_slot_seen = max_slot;
+    p.max_page_seen = max_page;
     ctx->pass_serial++;
     ctx->have_pass = true;
 
-    size_t words = (size_t)3 * rows + n_pages;
+    const size_t words = (size_t)3 * rows + n_pages;
     if (int rc = ensure_buffer(ctx, (void **)&ctx->d_meta, &ctx->d_meta_cap, std::max<size_t>(words, 4) * 4)) return rc;
-    std::vector<uint32_t> blob(words);
-    if (rows) {
-        memcpy(blob.data(), pos, rows * 4);
-        memcpy(blob.data() + rows, kv_slot, rows * 4);
-        memcpy(blob.data() + 2 * (size_t)rows, pt_off, rows * 4);
-    }
-    if (n_pages) memcpy(blob.data() + 3 * (size_t)rows, pages, (size_t)n_pages * 4);
     ctx->d_pos = ctx->d_meta;
     ctx->d_slot = ctx->d_meta + rows;
     ctx->d_ptoff = ctx->d_meta + 2 * (size_t)rows;
     ctx->d_pages = ctx->d_meta + 3 * (size_t)rows;
-    return upload_ordered(ctx, ctx->d_meta, blob.data(), words * 4);
+    if (words == 0) return YX_OK;
+    // The arrays go straight into a pinned staging buffer: one copy, one upload, no allocation.
+    uint32_t *blob = nullptr;
+    if (int rc = stage_acquire(ctx, words * 4, (void **)&blob)) return rc;
+    if (rows) {
+        memcpy(blob, pos, rows * 4);
+        memcpy(blob + rows, kv_slot, rows * 4);
+        memcpy(blob + 2 * (size_t)rows, pt_off, rows * 4);
+    }
+    if (n_pages) memcpy(blob + 3 * (size_t)rows, pages, (size_t)n_pages * 4);
+    return stage_commit(ctx, ctx->d_meta, words * 4);
 }
 
 int yx_kv_append(yx_ctx *ctx, yx_kv *kv, int layer, const void *k_rows, const void *v_rows, int src_dtype) {
@@ -709,8 +719,7 @@ int yx_kv_append(yx_ctx *ctx, yx_kv *kv, int layer, const void *k_rows, const vo
         return fail(ctx, YX_ERR_INVALID, "kv_append: rows must be f32 or of the cache's type");
     if (ctx->pass.rows == 0) return YX_OK;
     if (!k_rows || !v_rows) return fail(ctx, YX_ERR_INVALID, "null tensor");
-    for (uint32_t s : ctx->pass.kv_slot)
-        if (s / PAGE >= kv->pages) return fail(ctx, YX_ERR_INVALID, "kv_slot outside the KV arena");
+    if (ctx->pass.max_slot_seen / PAGE >= kv->pages) return fail(ctx, YX_ERR_INVALID, "kv_slot outside the KV arena");
     DeviceGuard guard(ctx->device);
     return launch_append(ctx, kv, layer, k_rows, v_rows, src_dtype);
 }
@@ -735,8 +744,7 @@ int yx_attention(yx_ctx *ctx, yx_kv *kv, int layer, const float *qkv, const floa
     if (hq <= 0 || hq % kv->hkv != 0) return fail(ctx, YX_ERR_INVALID, "hq must be a positive multiple of hkv");
     if (ctx->pass.rows == 0) return YX_OK;
     if (!qkv || !q_norm || !k_norm || !out) return fail(ctx, YX_ERR_INVALID, "null tensor");
-    for (uint32_t s : ctx->pass.kv_slot)
-        if (s / PAGE >= kv->pages) return fail(ctx, YX_ERR_INVALID, "kv_slot outside the KV arena");
+    if (ctx->pass.max_slot_seen / PAGE >= kv->pages) return fail(ctx, YX_ERR_INVALID, "kv_slot outside the KV arena");
     DeviceGuard guard(ctx->device);
     size_t q_bytes = (size_t)ctx->pass.rows * hq * D * sizeof(float);
     if (int rc = ensure_buffer(ctx, (void **)&ctx->q_tmp, &ctx->q_tmp_cap, q_bytes)) return rc;

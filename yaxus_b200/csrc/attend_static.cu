@@ -16,14 +16,19 @@
 // Set-up: the first call on a device looks the scratch array's address up.  Make that first
 // call before any stream capture begins.  Later calls only launch the two kernels.
 //
-// Concurrency: the scratch array is one per device and process.  Two calls whose kernels may
-// overlap on the same device (different streams, different contexts, different threads) race
-// on it and give wrong results; order them on one stream or with events.
+// Concurrency: the scratch array is one per device context (a process that only uses the
+// runtime API has one context per device).  Two calls whose kernels may overlap in the same
+// context (different streams, different yx_ctx objects, different threads) race on it and give
+// wrong results; order them on one stream or with events.  The address is looked up again when
+// the calling thread's current CUDA context is not the one it was looked up in (after a device
+// reset, or under a driver-API context): a symbol's address belongs to a context.
 //
 // Nothing in the scratch has to start at zero: every triple a merge reads was written by the
 // first kernel of the same call (a run without a live key writes the empty mark -1e30, 0).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+
+#include <dlfcn.h>
 
 #include <mutex>
 #include <string>
@@ -50,15 +55,33 @@ static __device__ __align__(256) StaticScratch g_static_scratch;
 
 std::mutex g_lookup_lock;
 StaticScratch *g_scratch_addr[MAX_DEVICES] = {};
+void *g_scratch_ctx[MAX_DEVICES] = {};   // the CUDA context each address was looked up in
 
-// The array's address on `device`, which must be the current device.
+// The calling thread's current CUDA context, or null if the driver library cannot be asked (the
+// runtime has it loaded already; nothing is linked against it).
+void *current_cuda_context() {
+    using Fn = int (*)(void **);
+    static Fn fn = [] {
+        void *h = dlopen("libcuda.so.1", RTLD_LAZY | RTLD_NOLOAD);
+        return h ? (Fn)dlsym(h, "cuCtxGetCurrent") : (Fn) nullptr;
+    }();
+    void *c = nullptr;
+    if (fn && fn(&c) == 0) return c;
+    return nullptr;
+}
+
+// The array's address on `device`, which must be the current device.  Looked up once per device
+// and context; a changed context means a different copy of the array at a different address.
 cudaError_t scratch_on(int device, StaticScratch **out) {
     std::lock_guard<std::mutex> hold(g_lookup_lock);
-    if (!g_scratch_addr[device]) {
+    void *now = current_cuda_context();
+    if (!g_scratch_addr[device] || g_scratch_ctx[device] != now) {
         StaticScratch *p = nullptr;
         cudaError_t e = cudaGetSymbolAddress((void **)&p, g_static_scratch);
         if (e != cudaSuccess) return e;
         g_scratch_addr[device] = p;
+        // the runtime may have made the context current only inside the call above
+        g_scratch_ctx[device] = now ? now : current_cuda_context();
     }
     *out = g_scratch_addr[device];
     return cudaSuccess;
@@ -232,9 +255,14 @@ extern "C" int yx_attend_static(yx_ctx *ctx, yx_kv *kv, int layer, const void *q
     if (int rc = check_cuda(ctx, cudaGetDevice(&current), "yx_attend_static: current device")) return rc;
     if (current != ctx->device)
         return fail(ctx, YX_ERR_STATE, "yx_attend_static: the context's device must be the current device");
+    // The same host-side checks as yx_attend (the kernel's own record-and-skip is the second line).
+    if (ctx->pass.max_pos_seen >= kv->max_pos) return fail(ctx, YX_ERR_INVALID, "a row's position exceeds max_pos");
+    if (ctx->pass.max_page_seen >= kv->pages && !ctx->pass.pages.empty())
+        return fail(ctx, YX_ERR_INVALID, "page id outside the KV arena");
     StaticScratch *scratch = nullptr;
     if (int rc = check_cuda(ctx, scratch_on(ctx->device, &scratch), "yx_attend_static: scratch address")) return rc;
-    const int64_t w = window < 0 ? (int64_t)kv->layers[layer].window : window;
+    int64_t w = window < 0 ? (int64_t)kv->layers[layer].window : window;
+    if (w > (int64_t)UINT32_MAX) w = (int64_t)UINT32_MAX;   // wider than any position: the same as none
     const int group = hq / kv->hkv;
     attend_static_split_kernel<<<dim3(rows * (uint32_t)kv->hkv, SPLITS), WARPS * 32, 0, ctx->stream>>>(
         q, q_dtype, hq, group, kv->k(layer), kv->v(layer), kv->hkv, kv->dtype, kv->pages, (uint32_t)(w > 0 ? w : 0),

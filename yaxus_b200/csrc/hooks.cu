@@ -1,7 +1,10 @@
-// Test hook: the split-key planner on host arrays, without a device.
+// Hooks for the library's own tests and benchmark (yx_hooks.h): the planner on host arrays, a
+// switch that leaves the merge out of an attention call, a kernel whose bounded wait runs out,
+// and the time-stamp buffer of a diagnostic build.
 #include <string.h>
 
-#include "yx_internal.h"
+#include "yx_device.cuh"
+#include "yx_hooks.h"
 
 extern "C" int yx_plan_probe(uint32_t rows, const uint32_t *pos, const uint32_t *pt_off, const uint32_t *pages,
                              uint32_t n_pages, int hkv, int group, int64_t window, uint64_t key_lo, uint64_t key_hi,
@@ -60,8 +63,54 @@ extern "C" int yx_plan_probe(uint32_t rows, const uint32_t *pos, const uint32_t 
     return YX_OK;
 }
 
-// Diagnostics hook (not part of the public header): per-CTA timestamps of the split-key kernel
-// are written to `dev_buf` (8 x u64 per CTA) while it is set.
-extern "C" void yx_debug_set_trace(yx_ctx *ctx, void *dev_buf) {
-    if (ctx) ctx->trace_buf = dev_buf;
+extern "C" int yx_hook_skip_merge(yx_ctx *ctx, int on) {
+    if (!ctx) return YX_ERR_INVALID;
+    ctx->skip_merge = on != 0;
+    return YX_OK;
+}
+
+namespace {
+
+// One CTA, one mbarrier that nobody arrives on, the same bounded wait the attention kernels use
+// with a caller-chosen limit.  No memory traffic, nothing to drain: when the wait gives up the
+// failure is in the status word and the kernel returns normally.
+__global__ void expire_wait_kernel(yx_dev_status *status, long long limit) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    const uint32_t b = yx::dev::smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        yx::dev::mbar_init(b, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) yx::dev::mbar_wait_slow(b, 0, &abort_flag, status, 900, limit);
+}
+
+}  // namespace
+
+extern "C" int yx_hook_expire_wait(yx_ctx *ctx, uint64_t limit_cycles) {
+    if (!ctx) return YX_ERR_INVALID;
+    if (ctx->status != YX_OK) return ctx->status;
+    // Never more than about a second, whatever is asked for.
+    const long long limit = (long long)(limit_cycles > 2000000000ull ? 2000000000ull : limit_cycles);
+    int prev = -1;
+    cudaGetDevice(&prev);
+    if (prev != ctx->device) cudaSetDevice(ctx->device);
+    expire_wait_kernel<<<1, 32, 0, ctx->stream>>>(ctx->dev_status, limit);
+    int rc = yx::check_cuda(ctx, cudaGetLastError(), "expire_wait kernel");
+    if (prev != ctx->device) cudaSetDevice(prev);
+    if (!rc) ctx->launches++;
+    return rc;
+}
+
+extern "C" int yx_hook_set_trace(yx_ctx *ctx, void *dev_buf) {
+    if (!ctx) return YX_ERR_INVALID;
+#ifdef YX_TRACE
+    ctx->trace_buf = dev_buf;
+    return YX_OK;
+#else
+    (void)dev_buf;
+    return YX_ERR_UNSUPPORTED;
+#endif
 }

@@ -618,7 +618,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
     // the CTA's pages across its items: ring stages and barrier phases follow g, not the page's
     // index in its item.
     const uint32_t item0 = P.cta_begin[blockIdx.x], item_end = P.cta_begin[blockIdx.x + 1];
-    const bool tr0 = P.trace && blockIdx.x == 0 && threadIdx.x == 0;
+    const bool tr0 = YX_TR(P.trace != nullptr) && blockIdx.x == 0 && threadIdx.x == 0;
     if (tr0) P.trace[1536] = clock64();
 
     if (threadIdx.x == 0) {
@@ -721,7 +721,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
                 umma_commit(t ? b_s_full_b + 8 * stage : b_s_full_a);
             };
             auto stamp = [&](uint32_t g, int e) {
-                if (P.trace && blockIdx.x == 0 && g < 64) P.trace[(2 * 64 + g) * 8 + e] = clock64();
+                if (YX_TR(P.trace != nullptr) && blockIdx.x == 0 && g < 64) P.trace[(2 * 64 + g) * 8 + e] = clock64();
             };
             // O_t (+)= P_t V, a 64-key half at a time; `first`: the item's first page
             auto issue_pv = [&](int t, uint32_t g, bool first, bool last) {
@@ -855,7 +855,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
             for (uint32_t j = 0; j < n_tiles; j++, g++) {
                 if (t == 0) mbar_wait(b_s_full_a, g & 1u, abortp, P.status, 49);
                 else mbar_wait(b_s_full_b + 8 * (g & 1), (g >> 1) & 1u, abortp, P.status, 50);
-                const bool tr = P.trace && blockIdx.x == 0 && r == 0 && g < 64;
+                const bool tr = YX_TR(P.trace != nullptr) && blockIdx.x == 0 && r == 0 && g < 64;
                 if (tr) P.trace[(t * 64 + g) * 8 + 0] = clock64();
                 tc_fence_after();
                 // The item's last scores are computed: nothing reads its Q tile any more, and the

@@ -7,6 +7,14 @@
 
 #include "yx_internal.h"
 
+// Time stamps inside the kernels exist only in a diagnostic build (-DYX_TRACE); in the shipped
+// library the condition is a compile-time false and the stamping code is dropped.
+#ifdef YX_TRACE
+#define YX_TR(cond) (cond)
+#else
+#define YX_TR(cond) false
+#endif
+
 namespace yx {
 namespace dev {
 
@@ -41,19 +49,19 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait.  Returns at once when the CTA has given up; on expiry it raises the CTA's
-// abort flag and records where in the context's status word.  Nothing spins forever.  The
+// Bounded wait (`limit` SM cycles).  Returns at once when the CTA has given up; on expiry it raises
+// the CTA's abort flag and records where in the context's status word.  Nothing spins forever.  The
 // spinning part is out of line: it is cold code, and the attention kernels pay for every
 // instruction-cache line they touch.
 static __device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                            yx_dev_status *status, int where) {
+                                            yx_dev_status *status, int where, long long limit = WAIT_CYCLES) {
     if (*abort_flag) return;
     long long t0 = clock64();
     for (uint32_t spins = 1;; spins++) {
         if (mbar_try(bar, parity)) return;
         if ((spins & 255u) == 0) {
             if (*abort_flag) return;
-            if (clock64() - t0 > WAIT_CYCLES) {
+            if (clock64() - t0 > limit) {
                 *abort_flag = 1;
                 if (atomicCAS(&status->code, 0, 2) == 0) {
                     status->where = where;

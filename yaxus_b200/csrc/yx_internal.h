@@ -135,6 +135,10 @@ struct Plan {
 struct PassHost {
     uint32_t rows = 0;
     std::vector<uint32_t> pos, kv_slot, pt_off, pages;
+    // taken once at begin_pass, so that every attention call of the pass checks them in O(1)
+    uint32_t max_pos_seen = 0;    // largest position of a row
+    uint32_t max_page_seen = 0;   // largest page id in `pages`
+    uint32_t max_slot_seen = 0;   // largest kv_slot of a row
 };
 
 struct PlanParams {
@@ -193,8 +197,9 @@ struct yx_ctx {
     yx_tuning tuning{};
     yx_plan_info last_plan{};
     int64_t launches = 0;
-    bool smem_configured[8] = {};
-    void *trace_buf = nullptr;             // device buffer for per-CTA kernel timestamps (diagnostics)          // per-kernel opt-in to large dynamic shared memory
+    bool smem_configured[8] = {};          // per-kernel opt-in to large dynamic shared memory
+    void *trace_buf = nullptr;             // device buffer for per-CTA kernel timestamps (builds with -DYX_TRACE)
+    bool skip_merge = false;               // measurement hook: leave the merge of the triples out
 
     yx_dev_status *dev_status = nullptr;   // pinned, mapped
 
