@@ -84,6 +84,7 @@ int stage_commit(yx_ctx *ctx, void *dst_dev, size_t bytes) {
         return rc;
     if (int rc = check_cuda(ctx, cudaEventRecord(st.done, ctx->stream), "cudaEventRecord")) return rc;
     st.busy = true;
+    ctx->last_launch = yx_ctx::LAST_OTHER;
     return YX_OK;
 }
 
@@ -269,7 +270,8 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     pp.esize = kv->esize;
     const int per_sm = ctx->tuning.ctas_per_sm > 0 ? ctx->tuning.ctas_per_sm : (path == 1 ? 4 : 1);
     pp.n_ctas = ctx->sm_count * per_sm;
-    pp.max_rows = path == 1 ? 1 : std::max(1, std::min(MAX_ITEM_ROWS, 64 / group));
+    // (a slot of the split-key kernel holds 32 query rows of f32 or 64 of a 16-bit type)
+    pp.max_rows = path == 1 ? 1 : std::max(1, std::min(MAX_ITEM_ROWS, (q_dtype == YX_F32 ? 32 : 64) / group));
     pp.share_prefix = path != 1 && ctx->tuning.share_prefix != 2;
     pp.w32 = ctx->tuning.cost32 > 0 ? ctx->tuning.cost32 : 16;
     pp.w64 = ctx->tuning.cost64 > 0 ? ctx->tuning.cost64 : 40;
@@ -333,6 +335,8 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     a.single_use = pl.single_use;
     a.plan = &pl;
     a.n_stages = ctx->tuning.stages;
+    a.early_kv = ctx->last_launch == yx_ctx::LAST_ATTEND ||
+                 (ctx->last_launch == yx_ctx::LAST_APPEND && ctx->last_append_serial == ctx->pass_serial);
     a.fused = ctx->tuning.fused_merge == 1;
     a.counters = ctx->counters;
     a.out = out;
@@ -389,6 +393,7 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
                 return rc;
         profile_mark(ctx, 3);
     }
+    if (ctx->launches != launches0) ctx->last_launch = yx_ctx::LAST_ATTEND;
     ctx->last_plan = pl.info;
     ctx->last_plan.path = pl.tile_items.empty() ? path : (pl.items.empty() ? 3 : 5);
     ctx->last_plan.launches = (int)(ctx->launches - launches0);
@@ -541,12 +546,14 @@ int yx_tensor_free(yx_ctx *ctx, void *dev) {
 int yx_upload(yx_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes) {
     if (!ctx || (bytes && (!dst_dev || !src_host))) return YX_ERR_INVALID;
     DeviceGuard guard(ctx->device);
+    ctx->last_launch = yx_ctx::LAST_OTHER;
     return check_cuda(ctx, cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream), "upload");
 }
 
 int yx_download(yx_ctx *ctx, void *dst_host, const void *src_dev, size_t bytes, int wait) {
     if (!ctx || (bytes && (!dst_host || !src_dev))) return YX_ERR_INVALID;
     DeviceGuard guard(ctx->device);
+    ctx->last_launch = yx_ctx::LAST_OTHER;
     if (int rc = check_cuda(ctx, cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, ctx->stream), "download"))
         return rc;
     return wait ? yx_sync(ctx) : YX_OK;
@@ -621,6 +628,7 @@ int yx_kv_copy_page(yx_ctx *ctx, yx_kv *kv, uint32_t src, uint32_t dst) {
     if (src >= kv->pages || dst >= kv->pages) return fail(ctx, YX_ERR_INVALID, "copy_page: page outside the arena");
     if (src == dst) return YX_OK;
     DeviceGuard guard(ctx->device);
+    ctx->last_launch = yx_ctx::LAST_KV_WRITE;
     return launch_copy_page(ctx, kv, src, dst);
 }
 
@@ -630,6 +638,7 @@ static int page_io(yx_ctx *ctx, yx_kv *kv, int layer, uint32_t first, uint32_t n
     if (layer < 0 || layer >= kv->n_layers || n_pages == 0 || (uint64_t)first + n_pages > kv->pages)
         return fail(ctx, YX_ERR_INVALID, "page io: out of range");
     DeviceGuard guard(ctx->device);
+    ctx->last_launch = yx_ctx::LAST_KV_WRITE;
     size_t bytes = (size_t)n_pages * PAGE * kv->hkv * D * kv->esize;
     void *lin = nullptr;
     if (int rc = check_cuda(ctx, cudaMalloc(&lin, 2 * bytes), "page io: cudaMalloc")) return rc;
@@ -721,6 +730,8 @@ int yx_kv_append(yx_ctx *ctx, yx_kv *kv, int layer, const void *k_rows, const vo
     if (!k_rows || !v_rows) return fail(ctx, YX_ERR_INVALID, "null tensor");
     if (ctx->pass.max_slot_seen / PAGE >= kv->pages) return fail(ctx, YX_ERR_INVALID, "kv_slot outside the KV arena");
     DeviceGuard guard(ctx->device);
+    ctx->last_launch = yx_ctx::LAST_APPEND;
+    ctx->last_append_serial = ctx->pass_serial;
     return launch_append(ctx, kv, layer, k_rows, v_rows, src_dtype);
 }
 
@@ -750,6 +761,8 @@ int yx_attention(yx_ctx *ctx, yx_kv *kv, int layer, const float *qkv, const floa
     if (int rc = ensure_buffer(ctx, (void **)&ctx->q_tmp, &ctx->q_tmp_cap, q_bytes)) return rc;
     // write_rows, then attend (cpu lib.rs:526-529): all rows' K/V land before any row attends.
     if (int rc = launch_qk_rope_append(ctx, kv, layer, qkv, q_norm, k_norm, hq, eps, ctx->q_tmp)) return rc;
+    ctx->last_launch = yx_ctx::LAST_APPEND;
+    ctx->last_append_serial = ctx->pass_serial;
     int64_t launches0 = ctx->launches - 1;
     int rc = attend_impl(ctx, kv, layer, ctx->q_tmp, YX_F32, hq, -1, 0, UINT64_MAX, out, YX_F32, nullptr, nullptr, nullptr);
     ctx->last_plan.launches = (int)(ctx->launches - launches0);

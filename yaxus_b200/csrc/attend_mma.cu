@@ -2,8 +2,8 @@
 // verification and rows over shared prefixes.  Bandwidth-bound: the job of this kernel is to
 // keep every SM's share of HBM busy from the first microsecond to the last.
 //
-//  * Persistent: one CTA per SM (eight warps: four consumers, a producer, a query stager, two
-//    epilogue warps) walks the span of 64-key tiles the planner cut for it.
+//  * Persistent: one CTA per SM, twelve warps (eight consumers, a producer, a query stager, two
+//    epilogue warps), walks the span of 64-key tiles the planner cut for it.
 //  * Nothing on the device walks a page table.  The host planner resolves every tile to its
 //    (page, KV head) block; the producer warp reads 32 tile descriptors with one coalesced
 //    load and feeds the copy engine from them, across item boundaries, never draining.
@@ -13,13 +13,20 @@
 //    the copy of a ragged tile is simply shorter.  Tiles that no other item reads are copied
 //    with an L2 evict-first hint, so that the stream does not push the plan, the queries and
 //    the partial results out of L2.
-//  * A helper warp stages the queries of the next item in shared memory (converted to the
-//    cache's 16-bit type, f32 queries as a high and a low part), so that consumers never wait
-//    on global memory at an item boundary.
-//  * Four consumer warps share each tile.  All query heads of the KV head's group, and all
-//    rows of an item, are the M rows of one `mma.sync` tile (16, 32 or 64 padded rows), so a
-//    K or V byte is read once per item however many heads and rows use it.  Scores and
-//    softmax stay in f32 registers; max and sum reduce with quad shuffles.
+//  * The CTA's first tiles and the rows of its first item ride in kernel-parameter space, and the
+//    producer warp sets up the barriers and starts those copies before the CTA's first
+//    __syncthreads: nothing on the way to the first byte waits on a global load.
+//  * The kernel is launched as a programmatic dependent of the kernel before it.  K/V tiles
+//    that kernel cannot have written (everything but the tiles holding this pass's new rows,
+//    which the planner marks) are copied before the grid dependency is waited for, so a CTA
+//    that starts while the previous kernel's last CTAs still run has its ring full when the
+//    wait returns.  Queries, partial results and marked tiles are touched only after the wait.
+//  * Queries come in by bulk copies too: the stager warp issues one copy per query row of the
+//    next item (raw, in the caller's type) plus one for the item's record; the consumer warps
+//    build their MMA fragments from the raw rows (f32 queries as a high and a low 16-bit part).
+//  * Eight consumer warps share each tile.  All query heads of the KV head's group, and all
+//    rows of an item, are columns of `mma.sync` tiles, so a K or V byte is read once per item
+//    however many heads and rows use it.  Scores and softmax stay in f32 registers.
 //  * Each item ends in an (m, l, o) triple per query row, the format of the reference's
 //    split attention (crates/yaxus-backend-gpu/src/shaders.rs:1466-1579).  Two epilogue warps
 //    write the triples while the consumers are already in the next item.  The merge of the
@@ -27,9 +34,16 @@
 //    or, when asked for, this kernel's own: the CTA that delivers the last triple of a
 //    (row, KV head) merges them and writes the output, found by an arrival counter in global
 //    scratch that the merging CTA resets.
+//  * 152 registers per thread, not the 168 the compiler would take: 384 x 152 leaves room in the
+//    register file for a CTA of the merge kernel beside this one, which is what lets the merge
+//    kernel and, behind it, the next attention call be resident before this call has finished.
 //
 // Every wait on an mbarrier is bounded: on expiry the CTA records the failure in the
-// context's status word, stops waiting anywhere, finishes structurally and returns.
+// context's status word, stops waiting anywhere, waits (bounded) for the copies it has in
+// flight, and returns.
+#include <stddef.h>
+#include <string.h>
+
 #include "yx_device.cuh"
 
 namespace yx {
@@ -47,8 +61,13 @@ constexpr int EWARP = CONSUMERS + 2;              // warps 10 and 11: items alte
 constexpr int EWARPS = 2;
 constexpr int THREADS = (CONSUMERS + 2 + EWARPS) * 32;
 constexpr int Q_SLOTS = 2;
-constexpr int Q_ROWS_BYTES = 16384;               // 64 rows x 256 B, or 32 rows high + 32 rows low
-constexpr int Q_LOW_OFFSET = 8192;
+// A slot holds the item's query rows as they are in global memory, one bulk copy per row, each
+// row padded so that the fragment loads of a warp fall in different banks: 32 rows of 128 f32
+// (512 + 32 bytes) or 64 rows of 128 16-bit elements (256 + 16 bytes).
+constexpr int Q_STRIDE_F32 = 512 + 32;
+constexpr int Q_STRIDE_16 = 256 + 16;
+constexpr int Q_ROWS_BYTES = 32 * Q_STRIDE_F32;
+static_assert(Q_ROWS_BYTES == 64 * Q_STRIDE_16, "both query forms fill the slot");
 constexpr int Q_SLOT_BYTES = Q_ROWS_BYTES + 512;  // then the item's record
 constexpr int MERGE_ROW = D + 4;                  // one row's o, then m and l, padded
 constexpr int MERGE_FLOATS = 8 * MERGE_ROW;       // one warp's 8 queries
@@ -75,17 +94,7 @@ struct Pipe {
     }
 };
 
-// What a CTA needs before its first global load returns, passed in kernel-parameter space:
-// its span, its first two tiles and the rows of its first item.  A cold global load at kernel
-// start costs over a microsecond; three of them in a chain (span -> descriptors -> data) were
-// the largest single cost of a 15-microsecond kernel.
 constexpr int MAX_PROLOGUE_CTAS = 160;
-struct CtaPrologue {
-    CtaHdr hdr;
-    TileDesc first[2];
-    uint32_t head_rows, mt;
-    uint16_t rows[MAX_ITEM_ROWS];
-};
 
 struct Params {
     const void *q;
@@ -105,11 +114,27 @@ struct Params {
     unsigned long long *trace;       // optional: 8 timestamps / counters per CTA
     int fused;                       // merge in this kernel (arrival counters) or leave it to the combine kernel
     int n_stages;                    // stages of the ring in use (2..STAGES): bytes in flight per SM
+    int early_kv;                    // tiles not marked TILE_FRESH may be copied before the grid dependency wait
     int has_prologue;
     CtaPrologue pro[MAX_PROLOGUE_CTAS];
 };
 
 // ---- producer: tile descriptors -> bulk copies ----------------------------------------------
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// After a wait has run out: the copies already issued into this CTA's shared memory must have
+// landed before the CTA may leave.  `full` are the barriers they complete on; the stages before
+// `pipe.stage` were last issued in phase `pipe.phase`, the others one phase earlier.
+__device__ __noinline__ void drain_copies(uint32_t full, int n, Pipe pipe) {
+    for (int s = 0; s < n; s++) {
+        // (a barrier never used reads as complete for the phase before its first)
+        const uint32_t parity = s < pipe.stage ? pipe.phase : (pipe.phase ^ 1u);
+        const long long t0 = clock64();
+        while (!mbar_try(full + 8 * s, parity) && clock64() - t0 < 4000000ll) {
+        }
+    }
+}
+
 // One tile: wait for a free stage, zero what a ragged copy leaves alone, start the four copies.
 // Returns false when the CTA has given up.
 struct Issue {
@@ -120,17 +145,16 @@ struct Issue {
     uint32_t n_blocks, stages, full, empty;
     int single_use, n_stages;
 };
+// (By value: a reference would turn every field access of this out-of-line routine into a load.)
 __device__ __noinline__ bool issue_tile(const Issue P, Pipe &pipe, uint32_t block, uint32_t info, int lane) {
-    struct { uint32_t stages, full, empty; volatile int *abort_flag; } S = {P.stages, P.full, P.empty, P.abort_flag};
-    const uint64_t policy = P.policy;
     const uint32_t half = info & 1u, r0 = (info >> 1) & 127u, n = (info >> 8) & 255u;
     int stop = 0;
     if (lane == 0) {
-        mbar_wait(S.empty + 8 * pipe.stage, pipe.phase ^ 1u, S.abort_flag, P.status, 1);
-        stop = *S.abort_flag;
+        mbar_wait(P.empty + 8 * pipe.stage, pipe.phase ^ 1u, P.abort_flag, P.status, 1);
+        stop = *P.abort_flag;
     }
     if (__shfl_sync(0xffffffffu, stop, 0)) return false;
-    const uint32_t sb = S.stages + pipe.stage * STAGE_BYTES;
+    const uint32_t sb = P.stages + pipe.stage * STAGE_BYTES;
     if (n < (uint32_t)TILE_KEYS) {
         // A ragged tile: the V rows the copy leaves alone meet zero probabilities, so they must
         // hold finite numbers, whatever the stage held before.
@@ -139,10 +163,11 @@ __device__ __noinline__ bool issue_tile(const Issue P, Pipe &pipe, uint32_t bloc
             if (row < r0 || row >= r0 + n)
                 asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(sb + (2 + sub) * SUB_BYTES + row * 128 + (i & 7) * 16), "r"(0u) : "memory");
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
     }
     if (lane == 0) {
-        const uint32_t bar = S.full + 8 * pipe.stage;
+        const uint32_t bar = P.full + 8 * pipe.stage;
         if (block >= P.n_blocks || r0 + n > (uint32_t)TILE_KEYS || n == 0) {
             // Recorded; the copy is skipped and the consumers see stale data.
             if (atomicCAS(&P.status->code, 0, 1) == 0) {
@@ -156,11 +181,11 @@ __device__ __noinline__ bool issue_tile(const Issue P, Pipe &pipe, uint32_t bloc
             const size_t off = (size_t)block * (PAGE * D * 2) + (size_t)(half * TILE_KEYS + r0) * 128;
             const uint32_t dst = sb + r0 * 128;
             mbar_expect_tx(bar, 4 * bytes);
-            if (P.single_use && !(info & (1u << 16))) {
-                bulk_g2s_hint(dst, P.k_arena + off, bytes, bar, policy);
-                bulk_g2s_hint(dst + SUB_BYTES, P.k_arena + off + PAGE * 128, bytes, bar, policy);
-                bulk_g2s_hint(dst + 2 * SUB_BYTES, P.v_arena + off, bytes, bar, policy);
-                bulk_g2s_hint(dst + 3 * SUB_BYTES, P.v_arena + off + PAGE * 128, bytes, bar, policy);
+            if (P.single_use && !(info & TILE_REUSED)) {
+                bulk_g2s_hint(dst, P.k_arena + off, bytes, bar, P.policy);
+                bulk_g2s_hint(dst + SUB_BYTES, P.k_arena + off + PAGE * 128, bytes, bar, P.policy);
+                bulk_g2s_hint(dst + 2 * SUB_BYTES, P.v_arena + off, bytes, bar, P.policy);
+                bulk_g2s_hint(dst + 3 * SUB_BYTES, P.v_arena + off + PAGE * 128, bytes, bar, P.policy);
             } else {
                 bulk_g2s(dst, P.k_arena + off, bytes, bar);
                 bulk_g2s(dst + SUB_BYTES, P.k_arena + off + PAGE * 128, bytes, bar);
@@ -173,6 +198,9 @@ __device__ __noinline__ bool issue_tile(const Issue P, Pipe &pipe, uint32_t bloc
     return true;
 }
 
+// The producer warp's whole life.  It runs from the top of the kernel: barrier set-up, the first
+// tiles out of parameter space, the CTA-wide barrier that publishes the set-up, then the rest of
+// the span from the descriptor array.
 __device__ void produce(const Params &P, const Shared &S, const CtaHdr hdr, int lane) {
     Pipe pipe{0, 0};
     Issue I;
@@ -187,110 +215,88 @@ __device__ void produce(const Params &P, const Shared &S, const CtaHdr hdr, int 
     I.empty = S.empty;
     I.single_use = P.single_use;
     I.n_stages = P.n_stages;
+    // Until the grid dependency has been waited for, only tiles that the kernel ahead of this one
+    // cannot have written are copied; the first marked tile makes the warp wait.
+    bool waited = false;
+    if (!P.early_kv) {
+        grid_dependency_wait();
+        waited = true;
+    }
+    auto gate = [&](uint32_t info) {
+        if (!waited && (info & TILE_FRESH)) {
+            grid_dependency_wait();
+            waited = true;
+        }
+    };
+    bool alive = true;
     uint32_t c = hdr.tile_begin;
-    // The descriptors of every later tile are on their way while the first two copies start.
-    uint2 d = make_uint2(0u, 0u);
-    const uint32_t skip = P.has_prologue ? min(2u, hdr.tile_end - hdr.tile_begin) : 0u;
-    if (c + skip + lane < hdr.tile_end) d = *(const uint2 *)(P.tiles + c + skip + lane);
-    for (uint32_t j = 0; j < skip; j++) {
+    const uint32_t skip = P.has_prologue ? min(min((uint32_t)PROLOGUE_TILES, (uint32_t)P.n_stages), hdr.tile_end - hdr.tile_begin) : 0u;
+    for (uint32_t j = 0; j < skip && alive; j++) {
         const TileDesc t = P.pro[blockIdx.x].first[j];
-        if (!issue_tile(I, pipe, t.block, t.info, lane)) return;
-        if (P.trace && lane == 0 && j == 0) P.trace[8 * blockIdx.x + 2] = gtime();
+        gate(t.info);
+        alive = issue_tile(I, pipe, t.block, t.info, lane);
+        if (YX_TR(P.trace != nullptr) && lane == 0 && j == 0) P.trace[8 * blockIdx.x + 2] = gtime();
     }
     c += skip;
-    while (c < hdr.tile_end) {
+    asm volatile("bar.sync 0;" ::: "memory");   // the CTA-wide barrier after set-up (every other warp is at its own)
+    // The descriptors of every later tile.
+    uint2 d = make_uint2(0u, 0u);
+    if (alive && c + lane < hdr.tile_end) d = *(const uint2 *)(P.tiles + c + lane);
+    while (alive && c < hdr.tile_end) {
         const int n_tiles = (int)min(32u, hdr.tile_end - c);
         uint2 next = make_uint2(0u, 0u);
         if (c + 32 + lane < hdr.tile_end) next = *(const uint2 *)(P.tiles + c + 32 + lane);
-        for (int j = 0; j < n_tiles; j++) {
+        for (int j = 0; j < n_tiles && alive; j++) {
             const uint32_t block = __shfl_sync(0xffffffffu, d.x, j), info = __shfl_sync(0xffffffffu, d.y, j);
-            if (!issue_tile(I, pipe, block, info, lane)) return;
+            gate(info);
+            alive = issue_tile(I, pipe, block, info, lane);
         }
         d = next;
         c += 32;
     }
+    if (!alive && lane == 0) drain_copies(S.full, P.n_stages, pipe);
 }
 
 // ---- query staging ---------------------------------------------------------------------------
-// Row r of a slot is 256 bytes (128 16-bit elements); its sixteen 16-byte chunks are stored at
-// (chunk & 8) | ((chunk ^ r) & 7), which lets ldmatrix read A fragments without bank conflicts.
-__device__ __forceinline__ uint32_t q_chunk_off(int row, int chunk) {
-    return (uint32_t)row * 256u + (uint32_t)(((chunk & 8) | ((chunk ^ row) & 7)) << 4);
-}
-
 // Everything this out-of-line routine needs comes by value: a reference to the kernel's
 // parameter block would turn every field access into a load from memory.
 struct QStage {
-    const void *q;
+    const char *q;
     const ItemRec *recs;
     yx_dev_status *status;
-    int q_dtype, hq, group;
+    int hq, group;
+    uint32_t row_bytes, stride;           // of one query row in global and in shared memory
     uint32_t item_begin, item_end;
     int have_first;                       // the first item's header came with the parameters
-    uint32_t first_head_rows, first_mt, first_row;   // first_row: lane r's pass row
+    uint32_t first_head_rows, first_row[2];   // first_row[h]: the pass row of query row 32 h + lane
     uint32_t qbase, qfull, qempty;        // shared-space addresses
     volatile int *abort_flag;
 };
 
-// The loads of the next item are issued as soon as the current one is staged, so that by the
-// time its slot is free only the stores to shared memory remain: an item shorter than a round
-// trip to memory does not leave the consumers waiting for their queries.
-template <bool BF16>
+// One bulk copy per query row, issued by the lane of the same index (and the lane again for
+// rows 32..63), plus one for the item's record.  The rows and the head of the next item are
+// fetched into registers as soon as the current item's copies are on their way, so that when
+// its slot comes free only the copies remain to be started.
 __device__ __noinline__ void stage_queries(const QStage A, int lane) {
     Pipe pipe{0, 0};
-    const bool exact = (A.q_dtype == YX_BF16 && BF16) || (A.q_dtype == YX_F16 && !BF16);
-    const int chunk = lane >> 1;
-    const uint32_t sub = (lane & 1) * 8;
-
-    // What is held in registers for the item about to be staged.
-    uint4 rec4 = make_uint4(0, 0, 0, 0);
-    uint32_t head_rows = 0, mt = 0, elem[2] = {0xffffffffu, 0xffffffffu};
-    float4 v[16];
+    uint32_t head_rows = 0, prow[2] = {0, 0};
     auto fetch = [&](uint32_t ii) {
-        const uint32_t *rec = A.recs[ii].w;
-        rec4 = *(const uint4 *)(rec + 4 * lane);
-        uint32_t my_row;   // lane r < 16: pass row r of the item
         if (ii == A.item_begin && A.have_first) {
             head_rows = A.first_head_rows;
-            mt = A.first_mt;
-            my_row = A.first_row;
-        } else {
-            my_row = rec[IR_ROW0 + IR_ROW_WORDS * (lane & (MAX_ITEM_ROWS - 1)) + IRR_ROW];
-            head_rows = rec[IR_HEAD_ROWS];
-            mt = rec[IR_MT];
+            prow[0] = A.first_row[0];
+            prow[1] = A.first_row[1];
+            return;
         }
-        const int kvh = (int)(head_rows & 0xffffu), q_rows = (int)(head_rows >> 16) * A.group;
-        // Lane k works out where query rows k and 32 + k live (one division per lane, not one
-        // per row); the loads take the addresses by shuffle.
+        const uint32_t *rec = A.recs[ii].w;
+        head_rows = __ldg(rec + IR_HEAD_ROWS);
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            const int mine = 32 * h + lane;
-            const int pr = mine / A.group;
-            const uint32_t prow = __shfl_sync(0xffffffffu, my_row, min(pr, MAX_ITEM_ROWS - 1));
-            elem[h] = mine < q_rows ? (prow * (uint32_t)A.hq + (uint32_t)(kvh * A.group + (mine - pr * A.group))) : 0xffffffffu;
-        }
-#pragma unroll
-        for (int k = 0; k < 16; k++) {
-            const uint32_t e = __shfl_sync(0xffffffffu, elem[0], k);
-            v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (e != 0xffffffffu) v[k] = load4_as_f32(A.q, A.q_dtype, (size_t)e * D + lane * 4);
+            const int r = min((32 * h + lane) / A.group, MAX_ITEM_ROWS - 1);
+            prow[h] = __ldg(rec + IR_ROW0 + IR_ROW_WORDS * r + IRR_ROW);
         }
     };
-    auto store16 = [&](uint32_t slot, int r0, bool low) {
-#pragma unroll
-        for (int k = 0; k < 16; k++) {
-            const uint32_t h0 = pack2<BF16>(v[k].x, v[k].y), h1 = pack2<BF16>(v[k].z, v[k].w);
-            const uint32_t addr = slot + q_chunk_off(r0 + k, chunk) + sub;
-            asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(h0), "r"(h1) : "memory");
-            if (low) {
-                const float2 f0 = unpack2<BF16>(h0), f1 = unpack2<BF16>(h1);
-                const uint32_t l0 = pack2<BF16>(v[k].x - f0.x, v[k].y - f0.y), l1 = pack2<BF16>(v[k].z - f1.x, v[k].w - f1.y);
-                asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr + Q_LOW_OFFSET), "r"(l0), "r"(l1) : "memory");
-            }
-        }
-    };
-
     if (A.item_begin < A.item_end) fetch(A.item_begin);
+    bool alive = true;
 #pragma unroll 1
     for (uint32_t ii = A.item_begin; ii < A.item_end; ii++) {
         int stop = 0;
@@ -298,30 +304,28 @@ __device__ __noinline__ void stage_queries(const QStage A, int lane) {
             mbar_wait(A.qempty + 8 * pipe.stage, pipe.phase ^ 1u, A.abort_flag, A.status, 3);
             stop = *A.abort_flag;
         }
-        if (__shfl_sync(0xffffffffu, stop, 0)) return;
-        const uint32_t slot = A.qbase + pipe.stage * Q_SLOT_BYTES;
-        const bool low = mt != 64 && !exact;
-        store16(slot, 0, low);
-        // Items of more than 16 query rows: the rest, sixteen at a time.
-#pragma unroll 1
-        for (int r0 = 16; r0 < (int)mt; r0 += 16) {
-            const uint32_t src = r0 < 32 ? elem[0] : elem[1];
-#pragma unroll
-            for (int k = 0; k < 16; k++) {
-                const uint32_t e = __shfl_sync(0xffffffffu, src, (r0 + k) & 31);
-                v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (e != 0xffffffffu) v[k] = load4_as_f32(A.q, A.q_dtype, (size_t)e * D + lane * 4);
-            }
-            store16(slot, r0, low);
+        if (__shfl_sync(0xffffffffu, stop, 0)) {
+            alive = false;
+            break;
         }
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(slot + Q_ROWS_BYTES + 16 * lane), "r"(rec4.x),
-                     "r"(rec4.y), "r"(rec4.z), "r"(rec4.w)
-                     : "memory");
+        const uint32_t slot = A.qbase + pipe.stage * Q_SLOT_BYTES, bar = A.qfull + 8 * pipe.stage;
+        const int kvh = (int)(head_rows & 0xffffu), q_rows = (int)(head_rows >> 16) * A.group;
+        if (lane == 0) mbar_expect_tx(bar, (uint32_t)q_rows * A.row_bytes + (uint32_t)sizeof(ItemRec));
         __syncwarp();
-        if (lane == 0) mbar_arrive(A.qfull + 8 * pipe.stage);
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int qr = 32 * h + lane;
+            if (qr < q_rows) {
+                const int r = qr / A.group, g = qr - r * A.group;
+                const size_t elem = (size_t)prow[h] * (size_t)A.hq + (size_t)(kvh * A.group + g);
+                bulk_g2s(slot + (uint32_t)qr * A.stride, A.q + elem * A.row_bytes, A.row_bytes, bar);
+            }
+        }
+        if (lane == 0) bulk_g2s(slot + Q_ROWS_BYTES, A.recs + ii, (uint32_t)sizeof(ItemRec), bar);
         pipe.advance(Q_SLOTS);
         if (ii + 1 < A.item_end) fetch(ii + 1);
     }
+    if (!alive && lane == 0) drain_copies(A.qfull, Q_SLOTS, pipe);
 }
 
 // ---- consumers ---------------------------------------------------------------------------------
@@ -568,15 +572,54 @@ __device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe 
         klo[c] = valid ? rec[base + IRR_KLO] : 0u;            // padded queries are zero: nothing to mask
         khi[c] = valid ? rec[base + IRR_KHI] : 0xffffffffu;
     }
-    // Query fragments (the column operand), held for the whole item.
     const int lm = lane >> 3, lr = lane & 7;
+    // Query fragments (the column operand), held for the whole item, built from the raw rows the
+    // stager's copies left in the slot: this thread holds dims 16 ks + 2 t4 (+1) and + 8 of query
+    // j * 8 + g.  f32 queries (and 16-bit ones of the other type) become a high part in the cache's
+    // type and, where there is room for it, a low part.
     uint32_t qh[8][2], ql[8][2];
+    {
+        const int qr = j * 8 + g;
+        const bool valid = qr < q_rows;   // rows past the item's queries were not copied: zeros instead
+        if (P.q_dtype == YX_F32) {
+            const uint32_t a = slot + (uint32_t)qr * Q_STRIDE_F32 + 8u * t4;
 #pragma unroll
-    for (int ks = 0; ks < 8; ks++) {
-        const uint32_t a = slot + q_chunk_off(j * 8 + lr, 2 * ks + (lm & 1));
-        ldsm2(a, qh[ks][0], qh[ks][1]);
-        ql[ks][0] = ql[ks][1] = 0u;
-        if (low) ldsm2(a + Q_LOW_OFFSET, ql[ks][0], ql[ks][1]);
+            for (int ks = 0; ks < 8; ks++) {
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    float2 v = make_float2(0.f, 0.f);
+                    if (valid) asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a + 64u * ks + 32u * h));
+                    const uint32_t hi = pack2<BF16>(v.x, v.y);
+                    qh[ks][h] = hi;
+                    ql[ks][h] = 0u;
+                    if (low) {
+                        const float2 f = unpack2<BF16>(hi);
+                        ql[ks][h] = pack2<BF16>(v.x - f.x, v.y - f.y);
+                    }
+                }
+            }
+        } else {
+            const uint32_t a = slot + (uint32_t)qr * Q_STRIDE_16 + 4u * t4;
+#pragma unroll
+            for (int ks = 0; ks < 8; ks++) {
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    uint32_t raw = 0u;
+                    if (valid) asm volatile("ld.shared.b32 %0, [%1];" : "=r"(raw) : "r"(a + 32u * ks + 16u * h));
+                    qh[ks][h] = raw;
+                    ql[ks][h] = 0u;
+                    if (!exact_q) {
+                        const float2 v = P.q_dtype == YX_BF16 ? unpack2<true>(raw) : unpack2<false>(raw);
+                        const uint32_t hi = pack2<BF16>(v.x, v.y);
+                        qh[ks][h] = hi;
+                        if (low) {
+                            const float2 f = unpack2<BF16>(hi);
+                            ql[ks][h] = pack2<BF16>(v.x - f.x, v.y - f.y);
+                        }
+                    }
+                }
+            }
+        }
     }
 
     float o[8][4];   // O^T: dims 16 n + g (+8), queries 2 t4 (+1)
@@ -585,7 +628,7 @@ __device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
     for (uint32_t ti = 0; ti < n_tiles; ti++) {
-        const long long w0 = (P.trace && threadIdx.x == 0) ? clock64() : 0;
+        const long long w0 = (YX_TR(P.trace != nullptr) && threadIdx.x == 0) ? clock64() : 0;
         mbar_wait(S.full + 8 * pipe.stage, pipe.phase, S.abort_flag, P.status, 2);
         if (turn >= 0 && (int)(ti & 1u) != turn) {
             // The other warps' tile.  It is still waited for and released: a warp that skipped
@@ -595,8 +638,8 @@ __device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe 
             pipe.advance(P.n_stages);
             continue;
         }
-        if (P.trace && threadIdx.x == 0) P.trace[8 * blockIdx.x + 7] += (unsigned long long)(clock64() - w0);
-        if (P.trace && threadIdx.x == 0 && ti == 0 && P.trace[8 * blockIdx.x + 4] == 0) P.trace[8 * blockIdx.x + 4] = gtime();
+        if (YX_TR(P.trace != nullptr) && threadIdx.x == 0) P.trace[8 * blockIdx.x + 7] += (unsigned long long)(clock64() - w0);
+        if (YX_TR(P.trace != nullptr) && threadIdx.x == 0 && ti == 0 && P.trace[8 * blockIdx.x + 4] == 0) P.trace[8 * blockIdx.x + 4] = gtime();
         const uint32_t sb = S.stages + pipe.stage * STAGE_BYTES;
 
         // S^T = K Q^T over this warp's keys.
@@ -748,7 +791,7 @@ __device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe 
 }
 
 template <bool BF16>
-__global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const __grid_constant__ Params P) {
+__global__ void __maxnreg__(152) attend_mma_kernel(const __grid_constant__ Params P) {
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ int abort_flag;
     Shared S;
@@ -765,61 +808,67 @@ __global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const __grid_con
     S.abort_flag = &abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    unsigned long long *tr = P.trace ? P.trace + 8 * blockIdx.x : nullptr;
+    // The kernels behind this one in the stream (the merge, then the next attention call) may be
+    // made resident from here on; each waits for its own grid dependency before it reads or
+    // writes anything this kernel touches.
+    if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    unsigned long long *tr = YX_TR(P.trace != nullptr) ? P.trace + 8 * blockIdx.x : nullptr;
     if (tr && threadIdx.x == 0) tr[0] = gtime();
     const CtaHdr hdr = P.has_prologue ? P.pro[blockIdx.x].hdr : *(const CtaHdr *)(P.cta_hdr + blockIdx.x);
-    if (threadIdx.x == 0) {
-        abort_flag = 0;
-        for (int s = 0; s < STAGES; s++) {
-            mbar_init(S.full + 8 * s, 1);
-            mbar_init(S.empty + 8 * s, CONSUMERS);
-        }
-        for (int s = 0; s < Q_SLOTS; s++) {
-            mbar_init(S.qfull + 8 * s, 1);
-            mbar_init(S.qempty + 8 * s, CONSUMERS + 1);   // the consumer warps and the epilogue warp
-        }
-        for (int s = 0; s < MERGE_BUFS; s++) {
-            mbar_init(S.efull + 8 * s, CONSUMERS);
-            mbar_init(S.eempty + 8 * s, 1);
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
-    // The merge kernel that follows may be set up from here on (it waits for this grid to
-    // complete before it reads a triple).  This kernel in turn may have been started before the
-    // kernel ahead of it finished: nothing written by earlier kernels (K/V rows, queries, the
-    // partial buffers' previous readers) is touched before this wait.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (tr && threadIdx.x == 0) tr[1] = gtime();
 
     if (warp == PRODUCER) {
+        // The producer sets the barriers up itself and starts the first copies at once; the
+        // CTA-wide barrier inside produce() publishes the set-up to the other warps.
+        if (lane == 0) {
+            abort_flag = 0;
+            for (int s = 0; s < STAGES; s++) {
+                mbar_init(S.full + 8 * s, 1);
+                mbar_init(S.empty + 8 * s, CONSUMERS);
+            }
+            for (int s = 0; s < Q_SLOTS; s++) {
+                mbar_init(S.qfull + 8 * s, 1);
+                mbar_init(S.qempty + 8 * s, CONSUMERS + 1);   // the consumer warps and the epilogue warp
+            }
+            for (int s = 0; s < MERGE_BUFS; s++) {
+                mbar_init(S.efull + 8 * s, CONSUMERS);
+                mbar_init(S.eempty + 8 * s, 1);
+            }
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __syncwarp();
         produce(P, S, hdr, lane);
         return;
     }
+    asm volatile("bar.sync 0;" ::: "memory");
+    // Nothing written by earlier kernels (queries, the partial buffers' previous readers) is
+    // touched by these warps before this wait.
+    grid_dependency_wait();
+    if (tr && threadIdx.x == 0) tr[1] = gtime();
+
     if (warp == QWARP) {
         QStage A;
-        A.q = P.q;
+        A.q = (const char *)P.q;
         A.recs = P.recs;
         A.status = P.status;
-        A.q_dtype = P.q_dtype;
         A.hq = P.hq;
         A.group = P.group;
+        A.row_bytes = P.q_dtype == YX_F32 ? 512u : 256u;
+        A.stride = P.q_dtype == YX_F32 ? (uint32_t)Q_STRIDE_F32 : (uint32_t)Q_STRIDE_16;
         A.item_begin = hdr.item_begin;
         A.item_end = hdr.item_end;
         A.have_first = P.has_prologue;
-        A.first_head_rows = A.first_mt = A.first_row = 0;
+        A.first_head_rows = A.first_row[0] = A.first_row[1] = 0;
         if (P.has_prologue) {
             A.first_head_rows = P.pro[blockIdx.x].head_rows;
-            A.first_mt = P.pro[blockIdx.x].mt;
-            A.first_row = P.pro[blockIdx.x].rows[lane & (MAX_ITEM_ROWS - 1)];
+            A.first_row[0] = P.pro[blockIdx.x].rows[min(lane / P.group, MAX_ITEM_ROWS - 1)];
+            A.first_row[1] = P.pro[blockIdx.x].rows[min((32 + lane) / P.group, MAX_ITEM_ROWS - 1)];
         }
         A.qbase = S.q;
         A.qfull = S.qfull;
         A.qempty = S.qempty;
         A.abort_flag = S.abort_flag;
-        stage_queries<BF16>(A, lane);
+        stage_queries(A, lane);
         return;
     }
     if (warp >= EWARP) {
@@ -863,7 +912,7 @@ __global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const __grid_con
         // Who takes what of a 64-key tile (the epilogue warp's merge knows the same table):
         //   up to 8 queries: column tile 0 everywhere, a 16-key block each, warps 0-3 even tiles and 4-7 odd ones;
         //   up to 16: column tile warp / 4, a 16-key block each;  up to 32: column tile warp % 4, 32 keys each;
-        //   up to 64: column tile warp, the whole tile.
+        //   up to 64: column tile warp, the whole tile (16-bit queries only: 64 f32 rows do not fit a slot).
         if (mt == 16 && q_rows <= 8) consume_item<1, BF16>(P, S, pipe, qpipe, epipe, warp, lane, 0, (warp & 3) * 16, warp >> 2, true, last);
         else if (mt == 16) consume_item<1, BF16>(P, S, pipe, qpipe, epipe, warp, lane, warp >> 2, (warp & 3) * 16, -1, true, last);
         else if (mt == 32) consume_item<2, BF16>(P, S, pipe, qpipe, epipe, warp, lane, warp & 3, (warp >> 2) * 32, -1, true, last);
@@ -871,10 +920,6 @@ __global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const __grid_con
         if (tr && threadIdx.x == 0 && ii == hdr.item_begin) tr[6] = gtime();
     }
     if (tr && threadIdx.x == 0) tr[5] = gtime();
-    if (abort_flag) {
-        // Copies issued before giving up may still be landing in this CTA's shared memory.
-        for (int i = 0; i < 64; i++) __nanosleep(1000);
-    }
 }
 
 }  // namespace
@@ -887,7 +932,14 @@ int launch_attend_mma(yx_ctx *ctx, const AttendArgs &a) {
         if (int rc = check_cuda(ctx, e, "attend_mma: shared memory attribute")) return rc;
         ctx->smem_configured[bf16] = true;
     }
-    Params P{};
+    // The bulk copies of the query rows need 16-byte aligned sources.
+    if (((uintptr_t)a.q & 15u) != 0) return fail(ctx, YX_ERR_INVALID, "attention: the query tensor must be 16-byte aligned");
+    if (a.q_dtype == YX_F32 && a.plan) {
+        for (const Item &it : a.plan->items)
+            if (it.mt > 32) return fail(ctx, YX_ERR_INVALID, "attention: an item of more than 32 f32 query rows (planner bug)");
+    }
+    static thread_local Params P;   // 13 KB: kept off the stack
+    memset(&P, 0, offsetof(Params, pro));
     P.q = a.q;
     P.q_dtype = a.q_dtype;
     P.hq = a.hq;
@@ -913,20 +965,10 @@ int launch_attend_mma(yx_ctx *ctx, const AttendArgs &a) {
     P.has_prologue = 0;
     P.fused = a.fused ? 1 : 0;
     P.n_stages = a.n_stages >= 2 && a.n_stages <= STAGES ? a.n_stages : STAGES;
-    if (a.plan && a.n_ctas <= MAX_PROLOGUE_CTAS) {
-        const Plan &pl = *a.plan;
+    P.early_kv = a.early_kv ? 1 : 0;
+    if (a.plan && a.n_ctas <= MAX_PROLOGUE_CTAS && (int)a.plan->prologue.size() == a.n_ctas) {
         P.has_prologue = 1;
-        for (int c = 0; c < a.n_ctas; c++) {
-            CtaPrologue &pr = P.pro[c];
-            pr.hdr = pl.cta_hdr[c];
-            for (uint32_t j = 0; j < 2 && pr.hdr.tile_begin + j < pr.hdr.tile_end; j++) pr.first[j] = pl.tiles[pr.hdr.tile_begin + j];
-            if (pr.hdr.item_begin < pr.hdr.item_end) {
-                const Item &it = pl.items[pr.hdr.item_begin];
-                pr.head_rows = (uint32_t)it.kv_head | ((uint32_t)it.n_rows << 16);
-                pr.mt = it.mt;
-                for (int r = 0; r < MAX_ITEM_ROWS; r++) pr.rows[r] = it.rows[r];
-            }
-        }
+        memcpy(P.pro, a.plan->prologue.data(), sizeof(CtaPrologue) * (size_t)a.n_ctas);
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)a.n_ctas);

@@ -28,7 +28,7 @@ __device__ __forceinline__ void store_out(void *out, int out_dtype, size_t elem,
 // slot s and head-in-group g sits at index s * group + g.  Lane c reads the (m, l) of part c,
 // the warp agrees on the maximum and the weights, and only then are the o vectors read, all
 // loads independent of one another: the merge costs two memory latencies, not two per part.
-__global__ void combine_kernel(const Merge *__restrict__ merges, const float *__restrict__ part_o,
+__global__ void __launch_bounds__(128) combine_kernel(const Merge *__restrict__ merges, const float *__restrict__ part_o,
                                const float *__restrict__ part_ml, uint32_t n, int hq, int group, void *out,
                                int out_dtype, float *m_out, float *l_out, float *o_out) {
     uint32_t idx = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -37,9 +37,12 @@ __global__ void combine_kernel(const Merge *__restrict__ merges, const float *__
     uint32_t row = idx / (uint32_t)hq;
     int h = (int)(idx % (uint32_t)hq), kvh = h / group, g = h % group;
     Merge mg = merges[(size_t)row * (hq / group) + kvh];   // host-written: not the split-key kernel's output
-    // Launched as a programmatic dependent of the split-key kernel: it may start while that
-    // kernel's last CTAs run.  The triples are read only after the whole grid before it is
-    // complete and its writes are visible.
+    // Launched as a programmatic dependent of the split-key kernel: it is resident beside that
+    // kernel's CTAs (48 registers a thread: a CTA fits in what the split-key kernel leaves of
+    // the register file) long before they finish.  The kernel behind this one, usually the next
+    // attention call, may be made resident in turn.  The triples are read only after the whole
+    // grid before this one is complete and its writes are visible.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (mg.count == 0 && !o_out) return;   // the row was another kernel's (tiled path)
     float mx = -1e30f, l = 0.0f;

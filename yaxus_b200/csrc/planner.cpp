@@ -36,6 +36,7 @@ struct Unit {           // rows x one key range, before it is cut across CTAs (a
     uint32_t pt_off;
     uint32_t lo, hi;    // inclusive
     bool reused = false;   // other units read the same pages: keep them in L2
+    uint32_t fresh_from = 0;   // first position its sequence(s) append in this pass: keys from here on may be new
 };
 
 inline uint32_t row_lo(uint32_t pos, int64_t window) {
@@ -66,6 +67,7 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
     out.cta_hdr.clear();
     out.tiles.clear();
     out.recs.clear();
+    out.prologue.clear();
     out.single_use = false;
     out.has_empty_rows = false;
     out.info = yx_plan_info{};
@@ -168,6 +170,7 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
             uint32_t b = std::min<uint32_t>(g.n, a + pp.max_rows);
             Unit u;
             u.pt_off = g.pt_off;
+            u.fresh_from = pass.pos[g.row0];   // rows of a sequence are consecutive: its first row's position
             uint64_t lo = UINT64_MAX, hi = 0;
             for (uint32_t r = g.row0 + a; r < g.row0 + b; r++) {
                 u.rows.push_back((uint16_t)r);
@@ -252,6 +255,8 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
                 if (common > pg0) {
                     Unit su;
                     su.pt_off = u0.pt_off;
+                    su.fresh_from = UINT32_MAX;
+                    for (size_t k = at; k < end; k++) su.fresh_from = std::min(su.fresh_from, units[solos[members[k]].unit].fresh_from);
                     su.reused = members.size() > end - at;   // other clusters read these pages too
                     uint32_t lo = UINT32_MAX, hi = 0;
                     for (size_t k = at; k < end; k++) {
@@ -381,7 +386,7 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
                 it.kv_head = (uint16_t)kh;
                 it.n_rows = (uint16_t)u.rows.size();
                 it.mt = (uint32_t)padded_rows((int)u.rows.size() * pp.group);
-                it.pad_ = u.reused ? 1u : 0u;
+                it.flags = (u.reused ? 1u : 0u) | (u.fresh_from << 1);   // bit 0: reused; the rest: fresh_from (positions < 2^31)
                 for (size_t r = 0; r < u.rows.size(); r++) {
                     it.rows[r] = u.rows[r];
                     out.merges[(size_t)u.rows[r] * pp.hkv + kh].count++;
@@ -428,7 +433,8 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
                     uint32_t a = std::max(it.key_lo, t * TILE_KEYS), b = std::min(it.key_hi, t * TILE_KEYS + TILE_KEYS - 1);
                     TileDesc d;
                     d.block = pass.pages[it.pt_off + t * TILE_KEYS / PAGE] * (uint32_t)pp.hkv + it.kv_head;
-                    d.info = (t & 1u) | ((a - t * TILE_KEYS) << 1) | ((b - a + 1) << 8) | (it.pad_ ? 1u << 16 : 0u);
+                    d.info = (t & 1u) | ((a - t * TILE_KEYS) << 1) | ((b - a + 1) << 8) | ((it.flags & 1u) ? TILE_REUSED : 0u) |
+                             (b >= (it.flags >> 1) ? TILE_FRESH : 0u);
                     out.tiles.push_back(d);
                 }
                 ItemRec &r = out.recs[i];   // zero from resize(): the array was cleared
@@ -450,6 +456,19 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
             }
             h.tile_end = (uint32_t)out.tiles.size();
         }
+        out.prologue.assign(n_ctas, CtaPrologue{});
+        for (int c = 0; c < n_ctas; c++) {
+            CtaPrologue &pr = out.prologue[c];
+            pr.hdr = out.cta_hdr[c];
+            for (uint32_t j = 0; j < (uint32_t)PROLOGUE_TILES && pr.hdr.tile_begin + j < pr.hdr.tile_end; j++)
+                pr.first[j] = out.tiles[pr.hdr.tile_begin + j];
+            if (pr.hdr.item_begin < pr.hdr.item_end) {
+                const Item &it = out.items[pr.hdr.item_begin];
+                pr.head_rows = (uint32_t)it.kv_head | ((uint32_t)it.n_rows << 16);
+                pr.mt = it.mt;
+                for (int r = 0; r < MAX_ITEM_ROWS; r++) pr.rows[r] = it.rows[r];
+            }
+        }
     }
 
     uint64_t uniq = 0;
@@ -468,7 +487,7 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
         std::vector<uint32_t> once(2 * (size_t)n_dense, 0);   // (physical page, half) -> most keys read by unmarked items
         uint64_t streamed = 0;
         for (const Item &it : out.items) {
-            if (it.pad_ || it.kv_head != 0) continue;
+            if ((it.flags & 1u) || it.kv_head != 0) continue;
             for (uint32_t t = it.tile_begin; t < it.tile_end; t++) {
                 uint32_t n = std::min(it.key_hi, t * TILE_KEYS + TILE_KEYS - 1) - std::max(it.key_lo, t * TILE_KEYS) + 1;
                 streamed += n;

@@ -59,7 +59,8 @@ struct alignas(16) Item {
     uint16_t rows[MAX_ITEM_ROWS];        // pass rows
     uint32_t part[MAX_ITEM_ROWS];        // partial slot of each row for this KV head
     uint32_t mt;                         // padded query rows (n_rows * group rounded up): 16, 32 or 64
-    uint32_t pad_;
+    uint32_t flags;                      // bit 0: other items read the same pages; bits 1..31: the first position
+                                         // the item's sequences append in this pass (keys from there on may be new)
 };
 static_assert(sizeof(Item) == 128, "Item is 128 bytes");
 
@@ -85,8 +86,15 @@ struct CtaHdr {
 struct TileDesc {
     uint32_t block;   // page * hkv + kv_head: index of the 32 KiB block in the K and V arenas
     uint32_t info;    // bit 0: which half of the page; bits 1-7: first row; bits 8-15: rows (1..64);
-                      // bit 16: other items read the same tile (keep it in L2)
+                      // bit 16: other items read the same tile (keep it in L2);
+                      // bit 17: the tile may hold rows that this pass appends (see TILE_FRESH)
 };
+// A tile is "fresh" when it covers positions at or after the first row its sequence has in this
+// pass: the kernel that ran just before the attention kernel (the append) may have written it.
+// Every other tile was complete before that kernel started, so the attention kernel may copy it
+// before it waits for its grid dependency.
+constexpr uint32_t TILE_REUSED = 1u << 16;
+constexpr uint32_t TILE_FRESH = 1u << 17;
 
 // An item as the kernel reads it: 128 words, fetched by a warp with four coalesced loads.
 struct alignas(16) ItemRec {
@@ -99,6 +107,18 @@ constexpr int IR_MT = 3;          // padded query rows: 16, 32, 64
 constexpr int IR_ROW0 = 32;       // then six words per pass row:
 constexpr int IR_ROW_WORDS = 6;   //   first key seen, last key seen, partial slot, pass row, first slot, slots
 constexpr int IRR_KLO = 0, IRR_KHI = 1, IRR_PART = 2, IRR_ROW = 3, IRR_FIRST = 4, IRR_COUNT = 5;
+
+// What a persistent CTA of the split-key kernel needs before its first global load returns; it
+// travels in kernel-parameter space: the CTA's span, its first tiles and the rows of its first
+// item.  A cold global load at kernel start costs over a microsecond, and three of them in a
+// chain (span -> descriptors -> data) were once the largest single cost of the kernel.
+constexpr int PROLOGUE_TILES = 3;
+struct CtaPrologue {
+    CtaHdr hdr;
+    TileDesc first[PROLOGUE_TILES];
+    uint32_t head_rows, mt;            // of the first item: kv_head | n_rows << 16, padded query rows
+    uint16_t rows[MAX_ITEM_ROWS];      // its pass rows
+};
 
 // One item of the tiled (tcgen05) kernel: up to 128 consecutive rows of one sequence for one
 // query head, against pages [page_begin, page_end) of the sequence's table.
@@ -127,6 +147,7 @@ struct Plan {
     std::vector<CtaHdr> cta_hdr;
     std::vector<TileDesc> tiles;
     std::vector<ItemRec> recs;
+    std::vector<CtaPrologue> prologue;  // one per CTA (resolved form)
     bool single_use = false;            // every tile not marked as reused is read by exactly one item
     bool has_empty_rows = false;        // some (row, kv head) has no item: no live key in the range
     yx_plan_info info{};
@@ -200,6 +221,12 @@ struct yx_ctx {
     bool smem_configured[8] = {};          // per-kernel opt-in to large dynamic shared memory
     void *trace_buf = nullptr;             // device buffer for per-CTA kernel timestamps (builds with -DYX_TRACE)
     bool skip_merge = false;               // measurement hook: leave the merge of the triples out
+    // What this context last put on its stream, for the split-key kernel's early K/V copies: it may
+    // copy tiles before waiting for the kernel ahead of it only if that kernel cannot have written
+    // them (an append of the current pass writes the marked tiles only; attention kernels write none).
+    enum { LAST_OTHER = 0, LAST_APPEND, LAST_ATTEND, LAST_KV_WRITE };
+    int last_launch = LAST_OTHER;
+    uint64_t last_append_serial = 0;
 
     yx_dev_status *dev_status = nullptr;   // pinned, mapped
 
@@ -308,6 +335,7 @@ struct AttendArgs {
     bool single_use;
     const Plan *plan;        // host copy, for what is passed in kernel-parameter space
     int n_stages;            // copy ring depth (0 = default)
+    bool early_kv;           // unmarked tiles may be copied before the grid dependency wait
     bool fused;              // merge inside the split-key kernel
     uint32_t *counters;      // one per (pass row, kv head), zero between launches
     void *out;               // normalised output, or null
