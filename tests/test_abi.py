@@ -28,6 +28,35 @@ def test_bindings_match_the_header():
     _lib.cuda_lib()   # binds every signature; raises on a missing symbol
 
 
+def header_arity(path=os.path.join("include", "yaxus_cuda.h")):
+    """name -> number of parameters, for every function the header declares."""
+    text = open(os.path.join(ROOT, path)).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    out = {}
+    for m in re.finditer(r"\b(yx_[a-z0-9_]+)\s*\(([^;{]*?)\)\s*;", text):
+        args = m.group(2).strip()
+        out[m.group(1)] = 0 if args in ("", "void") else args.count(",") + 1
+    return out
+
+
+def test_rust_ffi_block_matches_the_header():
+    # crates/yaxus-backend-cuda/src/ffi.rs (uncompiled: no rustc here) must declare every header
+    # entry, with the same number of parameters, and nothing the header lacks.
+    text = open(os.path.join(ROOT, "crates", "yaxus-backend-cuda", "src", "ffi.rs")).read()
+    text = re.sub(r"//.*", "", text)
+    block = text[text.index('extern "C"'):]
+    rust = {}
+    for m in re.finditer(r"pub fn (yx_[a-z0-9_]+)\s*\(([^;]*?)\)\s*(?:->\s*[^;]+)?;", block, flags=re.S):
+        args = m.group(2).strip()
+        rust[m.group(1)] = 0 if not args else len([a for a in args.split(",") if a.strip()])
+    assert rust == header_arity()
+    # the structs passed by pointer have the header's fields, in order
+    for c_name, fields in (("yx_tuning", _lib.Tuning._fields_), ("yx_plan_info", _lib.PlanInfo._fields_)):
+        body = text[text.index(f"pub struct {c_name}"):]
+        body = body[:body.index("}")]
+        assert re.findall(r"pub (\w+):", body) == [f[0] for f in fields], c_name
+
+
 def test_struct_sizes():
     assert ctypes.sizeof(_lib.Rope) == 65 * 4
     assert ctypes.sizeof(_lib.Layer) == 66 * 4

@@ -188,7 +188,7 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
     const size_t mer_b = pad16(pl.merges.size() * sizeof(Merge));
     const size_t hdr_b = pad16(pl.cta_hdr.size() * sizeof(CtaHdr));
     const size_t til_b = pad16(pl.tiles.size() * sizeof(TileDesc));
-    const size_t rec_b = pl.recs.size() * sizeof(ItemRec);
+    const size_t rec_b = pp.resolve ? pl.items.size() * sizeof(ItemRec) : 0;   // (the array may be longer: capacity kept)
     const size_t tit_b = pl.tile_items.size() * sizeof(TileItem);
     const size_t tcb_b = pad16(pl.tile_cta_begin.size() * sizeof(uint32_t));
     const size_t total = items_b + cta_b + mer_b + hdr_b + til_b + rec_b + tit_b + tcb_b;

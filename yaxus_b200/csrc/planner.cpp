@@ -66,25 +66,29 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
     out.tile_cta_begin.clear();
     out.cta_hdr.clear();
     out.tiles.clear();
-    out.recs.clear();
-    out.prologue.clear();
+    out.prologue.clear();   // (recs keeps its records: every word that is read is rewritten below)
     out.single_use = false;
     out.has_empty_rows = false;
     out.info = yx_plan_info{};
 
     // Dense ids of the physical pages named in this pass (page-table entry -> id), so that
-    // per-page bookkeeping below is a flat array rather than a hash map.
-    std::vector<uint32_t> dense(pass.pages.size());
+    // per-page bookkeeping below is a flat array.  Found with a small open-addressing table:
+    // sorting the entries cost more than the rest of the plan of a decode pass.
+    std::vector<uint32_t> &dense = out.scratch_dense;
+    dense.resize(pass.pages.size());
     uint32_t n_dense = 0;
     {
-        std::vector<uint32_t> order(pass.pages.size());
-        for (uint32_t i = 0; i < order.size(); i++) order[i] = i;
-        std::sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) { return pass.pages[a] < pass.pages[b]; });
-        for (size_t k = 0; k < order.size(); k++) {
-            if (k > 0 && pass.pages[order[k]] != pass.pages[order[k - 1]]) n_dense++;
-            dense[order[k]] = n_dense;
+        size_t cap = 64;
+        while (cap < 2 * pass.pages.size()) cap <<= 1;
+        std::vector<uint64_t> &table = out.scratch_table;   // (page + 1) << 32 | id; 0 = empty
+        table.assign(cap, 0);
+        for (size_t i = 0; i < pass.pages.size(); i++) {
+            const uint64_t key = (uint64_t)pass.pages[i] + 1;
+            size_t h = (size_t)((key * 0x9E3779B97F4A7C15ull) >> 32) & (cap - 1);
+            while (table[h] != 0 && (table[h] >> 32) != key) h = (h + 1) & (cap - 1);
+            if (table[h] == 0) table[h] = (key << 32) | n_dense++;
+            dense[i] = (uint32_t)table[h];
         }
-        if (!order.empty()) n_dense++;
     }
 
     // 1. Row groups: runs of rows with the same page table.
@@ -417,45 +421,56 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
     for (const Merge &m : out.merges)
         if (m.count == 0) out.has_empty_rows = true;
 
-    // 6. The resolved form: page tables walked here, once, instead of by every CTA.
+    // 6. The resolved form: page tables walked here, once, instead of by every CTA.  (Plain
+    //    pointers into arrays sized up front: this loop is most of the cost of planning a decode
+    //    pass, and it runs on the critical path of every pass.)
     if (pp.resolve) {
         out.cta_hdr.resize(n_ctas);
-        out.recs.resize(out.items.size());
-        out.tiles.reserve((size_t)total_tiles);
+        if (out.recs.size() < out.items.size()) out.recs.resize(out.items.size());   // words a record does not use keep old values
+        out.tiles.resize((size_t)total_tiles);
+        TileDesc *td = out.tiles.data();
+        const uint32_t *pages = pass.pages.data(), *pos = pass.pos.data();
+        const Item *items = out.items.data();
+        const Merge *merges = out.merges.data();
+        ItemRec *recs = out.recs.data();
+        const uint32_t hkv = (uint32_t)pp.hkv;
+        size_t n_tiles = 0;
         for (int c = 0; c < n_ctas; c++) {
             CtaHdr &h = out.cta_hdr[c];
             h.item_begin = out.cta_begin[c];
             h.item_end = out.cta_begin[c + 1];
-            h.tile_begin = (uint32_t)out.tiles.size();
+            h.tile_begin = (uint32_t)n_tiles;
             for (uint32_t i = h.item_begin; i < h.item_end; i++) {
-                const Item &it = out.items[i];
+                const Item &it = items[i];
+                const uint32_t *pt = pages + it.pt_off;
+                const uint32_t flags = (it.flags & 1u) ? TILE_REUSED : 0u, fresh_from = it.flags >> 1;
                 for (uint32_t t = it.tile_begin; t < it.tile_end; t++) {
-                    uint32_t a = std::max(it.key_lo, t * TILE_KEYS), b = std::min(it.key_hi, t * TILE_KEYS + TILE_KEYS - 1);
-                    TileDesc d;
-                    d.block = pass.pages[it.pt_off + t * TILE_KEYS / PAGE] * (uint32_t)pp.hkv + it.kv_head;
-                    d.info = (t & 1u) | ((a - t * TILE_KEYS) << 1) | ((b - a + 1) << 8) | ((it.flags & 1u) ? TILE_REUSED : 0u) |
-                             (b >= (it.flags >> 1) ? TILE_FRESH : 0u);
-                    out.tiles.push_back(d);
+                    const uint32_t k0 = t * TILE_KEYS;
+                    const uint32_t a = std::max(it.key_lo, k0), b = std::min(it.key_hi, k0 + TILE_KEYS - 1);
+                    TileDesc &d = td[n_tiles++];
+                    d.block = pt[t >> 1] * hkv + it.kv_head;
+                    d.info = (t & 1u) | ((a - k0) << 1) | ((b - a + 1) << 8) | flags | (b >= fresh_from ? TILE_FRESH : 0u);
                 }
-                ItemRec &r = out.recs[i];   // zero from resize(): the array was cleared
-                r.w[IR_TILES] = it.tile_end - it.tile_begin;
-                r.w[IR_KEY0] = it.tile_begin * TILE_KEYS;
-                r.w[IR_HEAD_ROWS] = (uint32_t)it.kv_head | ((uint32_t)it.n_rows << 16);
-                r.w[IR_MT] = it.mt;
+                uint32_t *w = recs[i].w;
+                w[IR_TILES] = it.tile_end - it.tile_begin;
+                w[IR_KEY0] = it.tile_begin * TILE_KEYS;
+                w[IR_HEAD_ROWS] = (uint32_t)it.kv_head | ((uint32_t)it.n_rows << 16);
+                w[IR_MT] = it.mt;
                 for (int k = 0; k < it.n_rows; k++) {
-                    uint32_t row = it.rows[k], p = pass.pos[row];
-                    const Merge &m = out.merges[(size_t)row * pp.hkv + it.kv_head];
-                    uint32_t *w = r.w + IR_ROW0 + IR_ROW_WORDS * k;
-                    w[IRR_KLO] = std::max(row_lo(p, pp.window), it.key_lo);
-                    w[IRR_KHI] = std::min(p, it.key_hi);
-                    w[IRR_PART] = it.part[k];
-                    w[IRR_ROW] = row;
-                    w[IRR_FIRST] = m.first;
-                    w[IRR_COUNT] = m.count;
+                    const uint32_t row = it.rows[k], p = pos[row];
+                    const Merge &m = merges[(size_t)row * hkv + it.kv_head];
+                    uint32_t *rw = w + IR_ROW0 + IR_ROW_WORDS * k;
+                    rw[IRR_KLO] = std::max(row_lo(p, pp.window), it.key_lo);
+                    rw[IRR_KHI] = std::min(p, it.key_hi);
+                    rw[IRR_PART] = it.part[k];
+                    rw[IRR_ROW] = row;
+                    rw[IRR_FIRST] = m.first;
+                    rw[IRR_COUNT] = m.count;
                 }
             }
-            h.tile_end = (uint32_t)out.tiles.size();
+            h.tile_end = (uint32_t)n_tiles;
         }
+        out.tiles.resize(n_tiles);
         out.prologue.assign(n_ctas, CtaPrologue{});
         for (int c = 0; c < n_ctas; c++) {
             CtaPrologue &pr = out.prologue[c];

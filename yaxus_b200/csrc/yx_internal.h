@@ -148,6 +148,8 @@ struct Plan {
     std::vector<TileDesc> tiles;
     std::vector<ItemRec> recs;
     std::vector<CtaPrologue> prologue;  // one per CTA (resolved form)
+    std::vector<uint32_t> scratch_dense, scratch_seen, scratch_once;   // planner scratch, kept for its capacity
+    std::vector<uint64_t> scratch_table;
     bool single_use = false;            // every tile not marked as reused is read by exactly one item
     bool has_empty_rows = false;        // some (row, kv head) has no item: no live key in the range
     yx_plan_info info{};
