@@ -82,21 +82,25 @@ def test_single_sequence_decode_f32(backend, oracle):
     kv.close()
 
 
-@pytest.mark.parametrize("share,share_rows,groups", [(1, 0, 4), (1, 16, 1), (1, 8, 2), (2, 0, 0)])
+@pytest.mark.parametrize("share,share_rows,groups,q16", [(1, 0, 4, False), (1, 16, 2, False), (1, 16, 1, True),
+                                                       (1, 8, 2, False), (2, 0, 0, False)])
 @pytest.mark.parametrize("kv_dtype", [F16, BF16])
-def test_batched_decode_shared_prefix(backend, oracle, share, share_rows, groups, kv_dtype):
+def test_batched_decode_shared_prefix(backend, oracle, share, share_rows, groups, q16, kv_dtype):
     # 16 sequences over a shared 1536-token prefix (same physical pages) with private
     # suffixes of 0..2560 tokens; 32 query / 8 KV heads.  The prefix is read by items of 4
-    # sequences (the default), of all 16, of 8, or by every sequence on its own.
+    # sequences (the default), of 8 (the most f32 query rows an item holds: 32), of all 16
+    # (16-bit queries: 64 rows), or by every sequence on its own.
     s = W.batched_decode(kv_dtype=kv_dtype)
     kv = load(backend, s)
     backend.set_tuning(share_prefix=share, share_rows=share_rows)
-    got = run_step(backend, kv, s)
+    qt = (torch.float16 if kv_dtype == F16 else torch.bfloat16) if q16 else torch.float32
+    got = run_step(backend, kv, s, q_dtype=qt)
     info = backend.last_plan()
     backend.set_tuning()
     assert info.path == 2 and info.shared_groups == groups
     assert info.unique_kv_bytes == s.unique_kv_bytes()
-    assert_close(got, oracle_step(oracle, s), what=f"batched decode share={share}")
+    q = W.round_through(s.q, kv_dtype) if q16 else None
+    assert_close(got, oracle_step(oracle, s, q=q), what=f"batched decode share={share}")
     kv.close()
 
 

@@ -116,11 +116,13 @@ int fold_device_status(yx_ctx *ctx) {
     if (ctx->dev_status && ctx->dev_status->code != 0) {
         yx_dev_status s = *ctx->dev_status;
         ctx->dev_status->code = 0;
+        ctx->dev_status->expired = 0;
         // A kernel that gave up may have left arrival counters of the fused merge non-zero.
         if (ctx->counters) cudaMemsetAsync(ctx->counters, 0, ctx->counters_cap, ctx->stream);
         return fail(ctx, YX_ERR_DEVICE,
                     "a kernel reported a failed check: code " + std::to_string(s.code) + " at " +
-                        std::to_string(s.where) + " (" + std::to_string(s.a) + ", " + std::to_string(s.b) + ")");
+                        std::to_string(s.where) + " (" + std::to_string(s.a) + ", " + std::to_string(s.b) + ")" +
+                        (s.expired ? ", waits that ran out: mask " + std::to_string(s.expired) : std::string()));
     }
     return YX_OK;
 }
@@ -287,6 +289,10 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     pp.tile_pairs = group % 2 == 0 && !(kv->dtype == YX_BF16 && q_dtype == YX_F32) && ctx->tuning.tile_single != 1;
     pp.min_piece = ctx->tuning.min_piece > 0 ? ctx->tuning.min_piece : (path == 2 ? 2 : 1);
     pp.item_cost = ctx->tuning.item_cost > 0 ? ctx->tuning.item_cost - 1 : (path == 2 ? 40 : 0);
+    // (taken before get_plan, whose upload of a new plan is itself an ordering point on the stream)
+    const bool predecessor_wrote_marked_tiles_only =
+        ctx->last_launch == yx_ctx::LAST_ATTEND ||
+        (ctx->last_launch == yx_ctx::LAST_APPEND && ctx->last_append_serial == ctx->pass_serial);
     yx_ctx::CachedPlan *cp = nullptr;
     if (int rc = get_plan(ctx, pp, &cp)) return rc;
     const Plan &pl = cp->plan;
@@ -312,6 +318,7 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     }
 
     AttendArgs a{};
+    a.rows = ctx->pass.rows;
     a.q = q;
     a.q_dtype = q_dtype;
     a.hq = hq;
@@ -335,8 +342,7 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     a.single_use = pl.single_use;
     a.plan = &pl;
     a.n_stages = ctx->tuning.stages;
-    a.early_kv = ctx->last_launch == yx_ctx::LAST_ATTEND ||
-                 (ctx->last_launch == yx_ctx::LAST_APPEND && ctx->last_append_serial == ctx->pass_serial);
+    a.early_kv = predecessor_wrote_marked_tiles_only;
     a.fused = ctx->tuning.fused_merge == 1;
     a.counters = ctx->counters;
     a.out = out;

@@ -60,6 +60,8 @@ constexpr int QWARP = CONSUMERS + 1;              // warp 9
 constexpr int EWARP = CONSUMERS + 2;              // warps 10 and 11: items alternate between them
 constexpr int EWARPS = 2;
 constexpr int THREADS = (CONSUMERS + 2 + EWARPS) * 32;
+constexpr int CONSUMER_BARRIER = 1;               // named barriers (0 is __syncthreads')
+constexpr int SETUP_BARRIER = 2;
 constexpr int Q_SLOTS = 2;
 // A slot holds the item's query rows as they are in global memory, one bulk copy per row, each
 // row padded so that the fragment loads of a warp fall in different banks: 32 rows of 128 f32
@@ -111,15 +113,26 @@ struct Params {
     int out_dtype;
     float *m_out, *l_out, *o_out;
     yx_dev_status *status;
-    unsigned long long *trace;       // optional: 8 timestamps / counters per CTA
+    unsigned long long *trace;       // optional: 16 timestamps / counters per CTA
     int fused;                       // merge in this kernel (arrival counters) or leave it to the combine kernel
     int n_stages;                    // stages of the ring in use (2..STAGES): bytes in flight per SM
     int early_kv;                    // tiles not marked TILE_FRESH may be copied before the grid dependency wait
+    uint32_t n_items, n_tiles, n_parts;   // sizes of the plan's arrays and of the partial buffers, for the kernel's own checks
+    unsigned long long q_bytes;      // size of the query tensor
     int has_prologue;
     CtaPrologue pro[MAX_PROLOGUE_CTAS];
 };
 
 // ---- producer: tile descriptors -> bulk copies ----------------------------------------------
+// A failed check of the kernel's own index arithmetic: recorded (first one wins), the access skipped.
+__device__ __noinline__ void record_bad_index(yx_dev_status *status, int where, unsigned long long a, unsigned long long b) {
+    if (atomicCAS(&status->code, 0, 3) == 0) {
+        status->where = where;
+        status->a = (int)a;
+        status->b = (int)b;
+    }
+}
+
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // After a wait has run out: the copies already issued into this CTA's shared memory must have
@@ -198,9 +211,8 @@ __device__ __noinline__ bool issue_tile(const Issue P, Pipe &pipe, uint32_t bloc
     return true;
 }
 
-// The producer warp's whole life.  It runs from the top of the kernel: barrier set-up, the first
-// tiles out of parameter space, the CTA-wide barrier that publishes the set-up, then the rest of
-// the span from the descriptor array.
+// The producer warp's life after it has set the barriers up: the first tiles out of parameter
+// space, then the rest of the span from the descriptor array.
 __device__ void produce(const Params &P, const Shared &S, const CtaHdr hdr, int lane) {
     Pipe pipe{0, 0};
     Issue I;
@@ -235,12 +247,15 @@ __device__ void produce(const Params &P, const Shared &S, const CtaHdr hdr, int 
         const TileDesc t = P.pro[blockIdx.x].first[j];
         gate(t.info);
         alive = issue_tile(I, pipe, t.block, t.info, lane);
-        if (YX_TR(P.trace != nullptr) && lane == 0 && j == 0) P.trace[8 * blockIdx.x + 2] = gtime();
+        if (YX_TR(P.trace != nullptr) && lane == 0 && j == 0) P.trace[16 * blockIdx.x + 2] = gtime();
     }
     c += skip;
-    asm volatile("bar.sync 0;" ::: "memory");   // the CTA-wide barrier after set-up (every other warp is at its own)
     // The descriptors of every later tile.
     uint2 d = make_uint2(0u, 0u);
+    if (hdr.tile_end > P.n_tiles) {   // the kernel's own check of its span
+        if (lane == 0) record_bad_index(P.status, 305, hdr.tile_end, P.n_tiles);
+        alive = false;
+    }
     if (alive && c + lane < hdr.tile_end) d = *(const uint2 *)(P.tiles + c + lane);
     while (alive && c < hdr.tile_end) {
         const int n_tiles = (int)min(32u, hdr.tile_end - c);
@@ -258,8 +273,10 @@ __device__ void produce(const Params &P, const Shared &S, const CtaHdr hdr, int 
 }
 
 // ---- query staging ---------------------------------------------------------------------------
-// Everything this out-of-line routine needs comes by value: a reference to the kernel's
-// parameter block would turn every field access into a load from memory.
+// (Inlined into the kernel.  As an out-of-line routine that took this structure by value, the way
+// issue_tile and epilogue_loop take theirs, it was never entered by the stager warp on sm_100a
+// with CUDA 12.9 - the time stamps of a diagnostic build showed the warp reach the call and
+// nothing after it - and the consumers waited for their queries until the wait ran out.)
 struct QStage {
     const char *q;
     const ItemRec *recs;
@@ -268,23 +285,30 @@ struct QStage {
     uint32_t row_bytes, stride;           // of one query row in global and in shared memory
     uint32_t item_begin, item_end;
     int have_first;                       // the first item's header came with the parameters
-    uint32_t first_head_rows, first_row[2];   // first_row[h]: the pass row of query row 32 h + lane
+    uint32_t first_head_rows, first_row0, first_row1;   // first_row<h>: the pass row of query row 32 h + lane
     uint32_t qbase, qfull, qempty;        // shared-space addresses
     volatile int *abort_flag;
+    uint32_t n_items;                     // records in `recs`
+    unsigned long long q_bytes;           // bytes in `q`
+    unsigned long long *trace;            // this CTA's time stamps (diagnostic build), or null
 };
 
 // One bulk copy per query row, issued by the lane of the same index (and the lane again for
 // rows 32..63), plus one for the item's record.  The rows and the head of the next item are
 // fetched into registers as soon as the current item's copies are on their way, so that when
 // its slot comes free only the copies remain to be started.
-__device__ __noinline__ void stage_queries(const QStage A, int lane) {
+__device__ __forceinline__ void stage_queries(const QStage &A, int lane) {
     Pipe pipe{0, 0};
     uint32_t head_rows = 0, prow[2] = {0, 0};
     auto fetch = [&](uint32_t ii) {
         if (ii == A.item_begin && A.have_first) {
             head_rows = A.first_head_rows;
-            prow[0] = A.first_row[0];
-            prow[1] = A.first_row[1];
+            prow[0] = A.first_row0;
+            prow[1] = A.first_row1;
+            return;
+        }
+        if (ii >= A.n_items) {
+            head_rows = 0;
             return;
         }
         const uint32_t *rec = A.recs[ii].w;
@@ -296,6 +320,7 @@ __device__ __noinline__ void stage_queries(const QStage A, int lane) {
         }
     };
     if (A.item_begin < A.item_end) fetch(A.item_begin);
+    if (YX_TR(A.trace != nullptr) && lane == 0) A.trace[8] = gtime();
     bool alive = true;
 #pragma unroll 1
     for (uint32_t ii = A.item_begin; ii < A.item_end; ii++) {
@@ -308,20 +333,43 @@ __device__ __noinline__ void stage_queries(const QStage A, int lane) {
             alive = false;
             break;
         }
+        if (YX_TR(A.trace != nullptr) && lane == 0 && ii == A.item_begin) A.trace[9] = gtime();
         const uint32_t slot = A.qbase + pipe.stage * Q_SLOT_BYTES, bar = A.qfull + 8 * pipe.stage;
-        const int kvh = (int)(head_rows & 0xffffu), q_rows = (int)(head_rows >> 16) * A.group;
-        if (lane == 0) mbar_expect_tx(bar, (uint32_t)q_rows * A.row_bytes + (uint32_t)sizeof(ItemRec));
-        __syncwarp();
+        const int kvh = (int)(head_rows & 0xffffu);
+        int q_rows = (int)(head_rows >> 16) * A.group;
+        // The kernel's own checks: a record outside the array, more query rows than a slot holds, a
+        // query row outside the tensor.  Recorded; the copy is left out (the barrier still completes).
+        const bool rec_ok = ii < A.n_items;
+        if (q_rows > 64 || (A.row_bytes == 512u && q_rows > 32)) {
+            if (lane == 0) record_bad_index(A.status, 301, (unsigned long long)q_rows, ii);
+            q_rows = 0;
+        }
+        size_t elem[2] = {0, 0};
+        bool ok[2] = {false, false};
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const int qr = 32 * h + lane;
             if (qr < q_rows) {
                 const int r = qr / A.group, g = qr - r * A.group;
-                const size_t elem = (size_t)prow[h] * (size_t)A.hq + (size_t)(kvh * A.group + g);
-                bulk_g2s(slot + (uint32_t)qr * A.stride, A.q + elem * A.row_bytes, A.row_bytes, bar);
+                elem[h] = (size_t)prow[h] * (size_t)A.hq + (size_t)(kvh * A.group + g);
+                ok[h] = (elem[h] + 1) * A.row_bytes <= A.q_bytes;
+                if (!ok[h]) record_bad_index(A.status, 302, elem[h], ii);
             }
         }
-        if (lane == 0) bulk_g2s(slot + Q_ROWS_BYTES, A.recs + ii, (uint32_t)sizeof(ItemRec), bar);
+        const uint32_t n_ok = __popc(__ballot_sync(0xffffffffu, ok[0])) + __popc(__ballot_sync(0xffffffffu, ok[1]));
+        if (!rec_ok && lane == 0) record_bad_index(A.status, 303, ii, A.n_items);
+        if (lane == 0) mbar_expect_tx(bar, n_ok * A.row_bytes + (rec_ok ? (uint32_t)sizeof(ItemRec) : 0u));
+        __syncwarp();
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+            if (ok[h]) bulk_g2s(slot + (uint32_t)(32 * h + lane) * A.stride, A.q + elem[h] * A.row_bytes, A.row_bytes, bar);
+        if (lane == 0 && rec_ok) bulk_g2s(slot + Q_ROWS_BYTES, A.recs + ii, (uint32_t)sizeof(ItemRec), bar);
+        if (YX_TR(A.trace != nullptr) && lane == 0 && ii == A.item_begin) {
+            A.trace[10] = gtime();
+            A.trace[11] = ((unsigned long long)n_ok << 32) | (unsigned long long)(n_ok * A.row_bytes + (rec_ok ? 512u : 0u));
+            A.trace[12] = ((unsigned long long)head_rows << 32) | bar;
+            A.trace[13] = (unsigned long long)(uintptr_t)(A.q + elem[0] * A.row_bytes);
+        }
         pipe.advance(Q_SLOTS);
         if (ii + 1 < A.item_end) fetch(ii + 1);
     }
@@ -351,6 +399,7 @@ struct Epilogue {
     volatile int *abort_flag;
     int out_dtype, hq, hkv, group;
     int fused;               // count items in and merge here (else a separate combine kernel merges)
+    uint32_t n_parts;        // slots in the partial buffers
     uint32_t n_items, first_item;    // this warp takes items first_item, first_item + EWARPS, ...
     uint32_t qbase, qempty, merge, efull, eempty, mlbuf;   // shared-space addresses
 };
@@ -449,7 +498,8 @@ __device__ __forceinline__ void merge_completed(const Epilogue &E, const uint32_
 // holds four of the 128 dims, stores coalesced).  Which warps hold slices of column tile jq
 // follows the kernel's dispatch table: warp w0 + x * wstep, x < nsl.
 __device__ __forceinline__ void merge_queries(const float *scratch, const uint32_t *rec, float *part_o, float *part_ml,
-                                              int group, int first_q, int q_step, int lane) {
+                                              int group, int first_q, int q_step, int lane, uint32_t n_parts,
+                                              yx_dev_status *status) {
     const float sl2 = 0.08838834764831845f * 1.4426950408889634f;
     const int n_rows = (int)(rec[IR_HEAD_ROWS] >> 16);
     const int mt = (int)rec[IR_MT];
@@ -491,6 +541,10 @@ __device__ __forceinline__ void merge_queries(const float *scratch, const uint32
             acc.z += v[x].z * f;
             acc.w += v[x].w * f;
         }
+        if (part >= n_parts) {   // the kernel's own check: recorded, the store left out
+            if (lane == 0) record_bad_index(status, 304, part, n_parts);
+            continue;
+        }
         const size_t slot = (size_t)part * group + gq;
         __stcg((float4 *)(part_o + slot * D + 4 * lane), acc);
         if (lane == 0) {
@@ -514,7 +568,7 @@ __device__ __noinline__ void epilogue_loop(const Epilogue E, int lane) {
         const uint32_t head_rows = rec[IR_HEAD_ROWS];
         const int kvh = (int)(head_rows & 0xffffu), n_rows = (int)(head_rows >> 16);
         // 1. the item's triples
-        merge_queries(scratch, rec, E.part_o, E.part_ml, group, 0, 1, lane);
+        merge_queries(scratch, rec, E.part_o, E.part_ml, group, 0, 1, lane, E.n_parts, E.status);
         __syncwarp();
         if (lane == 0) mbar_arrive(E.eempty + 8 * mine);   // the buffer is the consumers' again
         if (!E.fused) {
@@ -638,8 +692,8 @@ __device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe 
             pipe.advance(P.n_stages);
             continue;
         }
-        if (YX_TR(P.trace != nullptr) && threadIdx.x == 0) P.trace[8 * blockIdx.x + 7] += (unsigned long long)(clock64() - w0);
-        if (YX_TR(P.trace != nullptr) && threadIdx.x == 0 && ti == 0 && P.trace[8 * blockIdx.x + 4] == 0) P.trace[8 * blockIdx.x + 4] = gtime();
+        if (YX_TR(P.trace != nullptr) && threadIdx.x == 0) P.trace[16 * blockIdx.x + 7] += (unsigned long long)(clock64() - w0);
+        if (YX_TR(P.trace != nullptr) && threadIdx.x == 0 && ti == 0 && P.trace[16 * blockIdx.x + 4] == 0) P.trace[16 * blockIdx.x + 4] = gtime();
         const uint32_t sb = S.stages + pipe.stage * STAGE_BYTES;
 
         // S^T = K Q^T over this warp's keys.
@@ -775,9 +829,9 @@ __device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe 
             // The CTA's last item: nothing is left to stream, so the consumer warps merge it
             // themselves, a share of the queries each, instead of queueing it behind one
             // epilogue warp at the very end of the kernel.
-            asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");
+            asm volatile("bar.sync %0, %1;" ::"n"(CONSUMER_BARRIER), "n"(CONSUMERS * 32) : "memory");
             const float *scratch = (const float *)__cvta_shared_to_generic((size_t)(S.merge + epipe.stage * MERGE_BYTES));
-            merge_queries(scratch, rec, P.part_o, P.part_ml, group, warp, CONSUMERS, lane);
+            merge_queries(scratch, rec, P.part_o, P.part_ml, group, warp, CONSUMERS, lane, P.n_parts, P.status);
             return;
         }
         __syncwarp();
@@ -791,7 +845,7 @@ __device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe 
 }
 
 template <bool BF16>
-__global__ void __maxnreg__(152) attend_mma_kernel(const __grid_constant__ Params P) {
+__global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const __grid_constant__ Params P) {
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ int abort_flag;
     Shared S;
@@ -812,13 +866,12 @@ __global__ void __maxnreg__(152) attend_mma_kernel(const __grid_constant__ Param
     // made resident from here on; each waits for its own grid dependency before it reads or
     // writes anything this kernel touches.
     if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    unsigned long long *tr = YX_TR(P.trace != nullptr) ? P.trace + 8 * blockIdx.x : nullptr;
+    unsigned long long *tr = YX_TR(P.trace != nullptr) ? P.trace + 16 * blockIdx.x : nullptr;
     if (tr && threadIdx.x == 0) tr[0] = gtime();
     const CtaHdr hdr = P.has_prologue ? P.pro[blockIdx.x].hdr : *(const CtaHdr *)(P.cta_hdr + blockIdx.x);
 
     if (warp == PRODUCER) {
-        // The producer sets the barriers up itself and starts the first copies at once; the
-        // CTA-wide barrier inside produce() publishes the set-up to the other warps.
+        // The producer sets the barriers up itself and starts the first copies at once.
         if (lane == 0) {
             abort_flag = 0;
             for (int s = 0; s < STAGES; s++) {
@@ -837,10 +890,17 @@ __global__ void __maxnreg__(152) attend_mma_kernel(const __grid_constant__ Param
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         }
         __syncwarp();
+        // The set-up is published through a named barrier that this warp only arrives at (it has
+        // nothing to wait for) and the eleven other warps wait on; they then fetch queries while
+        // this warp starts the first K/V copies.  (Barrier 0, the __syncthreads barrier, reached
+        // from two places in the code did not hold the other warps back: they went on to use
+        // mbarriers that were not yet initialised.)
+        __threadfence_block();
+        asm volatile("bar.arrive %0, %1;" ::"n"(SETUP_BARRIER), "n"(THREADS) : "memory");
         produce(P, S, hdr, lane);
         return;
     }
-    asm volatile("bar.sync 0;" ::: "memory");
+    asm volatile("bar.sync %0, %1;" ::"n"(SETUP_BARRIER), "n"(THREADS) : "memory");
     // Nothing written by earlier kernels (queries, the partial buffers' previous readers) is
     // touched by these warps before this wait.
     grid_dependency_wait();
@@ -858,16 +918,19 @@ __global__ void __maxnreg__(152) attend_mma_kernel(const __grid_constant__ Param
         A.item_begin = hdr.item_begin;
         A.item_end = hdr.item_end;
         A.have_first = P.has_prologue;
-        A.first_head_rows = A.first_row[0] = A.first_row[1] = 0;
+        A.first_head_rows = A.first_row0 = A.first_row1 = 0;
         if (P.has_prologue) {
             A.first_head_rows = P.pro[blockIdx.x].head_rows;
-            A.first_row[0] = P.pro[blockIdx.x].rows[min(lane / P.group, MAX_ITEM_ROWS - 1)];
-            A.first_row[1] = P.pro[blockIdx.x].rows[min((32 + lane) / P.group, MAX_ITEM_ROWS - 1)];
+            A.first_row0 = P.pro[blockIdx.x].rows[min(lane / P.group, MAX_ITEM_ROWS - 1)];
+            A.first_row1 = P.pro[blockIdx.x].rows[min((32 + lane) / P.group, MAX_ITEM_ROWS - 1)];
         }
         A.qbase = S.q;
         A.qfull = S.qfull;
         A.qempty = S.qempty;
         A.abort_flag = S.abort_flag;
+        A.n_items = P.n_items;
+        A.q_bytes = P.q_bytes;
+        A.trace = tr;
         stage_queries(A, lane);
         return;
     }
@@ -888,6 +951,7 @@ __global__ void __maxnreg__(152) attend_mma_kernel(const __grid_constant__ Param
         E.hkv = P.hkv;
         E.group = P.group;
         E.fused = P.fused;
+        E.n_parts = P.n_parts;
         E.n_items = hdr.item_end - hdr.item_begin;
         if (!P.fused && E.n_items > 0) E.n_items--;   // the last item is the consumer warps' own
         E.qbase = S.q;
@@ -966,6 +1030,10 @@ int launch_attend_mma(yx_ctx *ctx, const AttendArgs &a) {
     P.fused = a.fused ? 1 : 0;
     P.n_stages = a.n_stages >= 2 && a.n_stages <= STAGES ? a.n_stages : STAGES;
     P.early_kv = a.early_kv ? 1 : 0;
+    P.n_items = a.plan ? (uint32_t)a.plan->items.size() : 0u;
+    P.n_tiles = a.plan ? (uint32_t)a.plan->tiles.size() : 0u;
+    P.n_parts = a.plan ? a.plan->n_parts : 0u;
+    P.q_bytes = (unsigned long long)a.rows * (unsigned long long)a.hq * D * (a.q_dtype == YX_F32 ? 4u : 2u);
     if (a.plan && a.n_ctas <= MAX_PROLOGUE_CTAS && (int)a.plan->prologue.size() == a.n_ctas) {
         P.has_prologue = 1;
         memcpy(P.pro, a.plan->prologue.data(), sizeof(CtaPrologue) * (size_t)a.n_ctas);

@@ -63,6 +63,7 @@ static __device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity
             if (*abort_flag) return;
             if (clock64() - t0 > limit) {
                 *abort_flag = 1;
+                atomicOr(&status->expired, 1u << (where & 31));
                 if (atomicCAS(&status->code, 0, 2) == 0) {
                     status->where = where;
                     status->a = (int)blockIdx.x;

@@ -206,6 +206,7 @@ struct yx_dev_status {
     int code;      // first failed device check (0 = none)
     int where;     // kernel-specific location
     int a, b;
+    unsigned int expired;   // one bit per `where` (mod 32) of every wait that ran out, not just the first
 };
 
 struct ncclComm;
@@ -314,6 +315,7 @@ int launch_page_io(yx_ctx *ctx, yx_kv *kv, int layer, uint32_t first_page, uint3
                    bool write);
 
 struct AttendArgs {
+    uint32_t rows;           // rows of the pass (of q and out)
     const void *q;
     int q_dtype;
     int hq;
