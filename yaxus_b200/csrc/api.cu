@@ -288,7 +288,7 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     pp.tile_ctas = ctx->sm_count;
     pp.tile_pairs = group % 2 == 0 && !(kv->dtype == YX_BF16 && q_dtype == YX_F32) && ctx->tuning.tile_single != 1;
     pp.min_piece = ctx->tuning.min_piece > 0 ? ctx->tuning.min_piece : (path == 2 ? 2 : 1);
-    pp.item_cost = ctx->tuning.item_cost > 0 ? ctx->tuning.item_cost - 1 : (path == 2 ? 40 : 0);
+    pp.item_cost = ctx->tuning.item_cost > 0 ? ctx->tuning.item_cost - 1 : (path == 2 ? 14 : 0);
     // (taken before get_plan, whose upload of a new plan is itself an ordering point on the stream)
     const bool predecessor_wrote_marked_tiles_only =
         ctx->last_launch == yx_ctx::LAST_ATTEND ||

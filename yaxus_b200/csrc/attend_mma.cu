@@ -2,8 +2,8 @@
 // verification and rows over shared prefixes.  Bandwidth-bound: the job of this kernel is to
 // keep every SM's share of HBM busy from the first microsecond to the last.
 //
-//  * Persistent: one CTA per SM, twelve warps (eight consumers, a producer, a query stager, two
-//    epilogue warps), walks the span of 64-key tiles the planner cut for it.
+//  * Persistent: one CTA per SM, eleven warps (eight consumers, a producer, a query stager, an
+//    epilogue warp), walks the span of 64-key tiles the planner cut for it.
 //  * Nothing on the device walks a page table.  The host planner resolves every tile to its
 //    (page, KV head) block; the producer warp reads 32 tile descriptors with one coalesced
 //    load and feeds the copy engine from them, across item boundaries, never draining.
@@ -28,14 +28,14 @@
 //    rows of an item, are columns of `mma.sync` tiles, so a K or V byte is read once per item
 //    however many heads and rows use it.  Scores and softmax stay in f32 registers.
 //  * Each item ends in an (m, l, o) triple per query row, the format of the reference's
-//    split attention (crates/yaxus-backend-gpu/src/shaders.rs:1466-1579).  Two epilogue warps
-//    write the triples while the consumers are already in the next item.  The merge of the
+//    split attention (crates/yaxus-backend-gpu/src/shaders.rs:1466-1579).  The epilogue warp
+//    writes the triples while the consumers are already in the next item.  The merge of the
 //    triples (the reference's `attn_combine`, shaders.rs:1581-1637) is the combine kernel's,
 //    or, when asked for, this kernel's own: the CTA that delivers the last triple of a
 //    (row, KV head) merges them and writes the output, found by an arrival counter in global
 //    scratch that the merging CTA resets.
-//  * 152 registers per thread, not the 168 the compiler would take: 384 x 152 leaves room in the
-//    register file for a CTA of the merge kernel beside this one, which is what lets the merge
+//  * 168 registers per thread and eleven warps: 352 x 168 leaves room in the register file for a
+//    CTA of the merge kernel (128 threads x 48) beside this one, which is what lets the merge
 //    kernel and, behind it, the next attention call be resident before this call has finished.
 //
 // Every wait on an mbarrier is bounded: on expiry the CTA records the failure in the
@@ -51,14 +51,14 @@ namespace {
 
 using namespace dev;
 
-constexpr int STAGES = 3;
+constexpr int STAGES = 4;
 constexpr int SUB_BYTES = TILE_KEYS * 128;        // one 64-dim half of a 64-key tile
 constexpr int STAGE_BYTES = 4 * SUB_BYTES;        // K lo, K hi, V lo, V hi
 constexpr int CONSUMERS = 8;                      // warps 0..7, two per scheduler
 constexpr int PRODUCER = CONSUMERS;               // warp 8
 constexpr int QWARP = CONSUMERS + 1;              // warp 9
-constexpr int EWARP = CONSUMERS + 2;              // warps 10 and 11: items alternate between them
-constexpr int EWARPS = 2;
+constexpr int EWARP = CONSUMERS + 2;              // warp 10
+constexpr int EWARPS = 1;
 constexpr int THREADS = (CONSUMERS + 2 + EWARPS) * 32;
 constexpr int CONSUMER_BARRIER = 1;               // named barriers (0 is __syncthreads')
 constexpr int SETUP_BARRIER = 2;
@@ -74,7 +74,7 @@ constexpr int Q_SLOT_BYTES = Q_ROWS_BYTES + 512;  // then the item's record
 constexpr int MERGE_ROW = D + 4;                  // one row's o, then m and l, padded
 constexpr int MERGE_FLOATS = 8 * MERGE_ROW;       // one warp's 8 queries
 constexpr int MERGE_BYTES = CONSUMERS * MERGE_FLOATS * 4;   // one buffer: every consumer warp's rows
-constexpr int MERGE_BUFS = 2;
+constexpr int MERGE_BUFS = 1;
 constexpr int N_BARRIERS = 2 * STAGES + 2 * Q_SLOTS + 2 * MERGE_BUFS;
 constexpr int MLBUF_BYTES = EWARPS * 8 * 32 * 8;  // per epilogue warp: (m, l) of 32 parts for each of 8 merges in flight
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + Q_SLOTS * Q_SLOT_BYTES + MERGE_BUFS * MERGE_BYTES + N_BARRIERS * 8 + MLBUF_BYTES;
@@ -555,24 +555,25 @@ __device__ __forceinline__ void merge_queries(const float *scratch, const uint32
 }
 
 __device__ __noinline__ void epilogue_loop(const Epilogue E, int lane) {
-    // Merge buffer b, query slot b and epilogue warp b go together (two of each).
-    static_assert(MERGE_BUFS == EWARPS && Q_SLOTS == EWARPS, "one buffer and one slot per epilogue warp");
-    const uint32_t mine = E.first_item;
+    // One merge buffer, handed back and forth between the consumer warps and this warp; the
+    // item's record sits in the query slot of the item's parity.
+    static_assert(MERGE_BUFS == 1 && EWARPS == 1 && Q_SLOTS == 2, "one buffer, one epilogue warp, two query slots");
     uint32_t phase = 0;
     const int group = E.group;
 #pragma unroll 1
-    for (uint32_t ii = mine; ii < E.n_items; ii += EWARPS, phase ^= 1u) {
-        mbar_wait(E.efull + 8 * mine, phase, E.abort_flag, E.status, 5);
-        const float *scratch = (const float *)__cvta_shared_to_generic((size_t)(E.merge + mine * MERGE_BYTES));
-        const uint32_t *rec = (const uint32_t *)__cvta_shared_to_generic((size_t)(E.qbase + mine * Q_SLOT_BYTES + Q_ROWS_BYTES));
+    for (uint32_t ii = 0; ii < E.n_items; ii++, phase ^= 1u) {
+        const uint32_t qslot = ii & 1u;
+        mbar_wait(E.efull, phase, E.abort_flag, E.status, 5);
+        const float *scratch = (const float *)__cvta_shared_to_generic((size_t)E.merge);
+        const uint32_t *rec = (const uint32_t *)__cvta_shared_to_generic((size_t)(E.qbase + qslot * Q_SLOT_BYTES + Q_ROWS_BYTES));
         const uint32_t head_rows = rec[IR_HEAD_ROWS];
         const int kvh = (int)(head_rows & 0xffffu), n_rows = (int)(head_rows >> 16);
         // 1. the item's triples
         merge_queries(scratch, rec, E.part_o, E.part_ml, group, 0, 1, lane, E.n_parts, E.status);
         __syncwarp();
-        if (lane == 0) mbar_arrive(E.eempty + 8 * mine);   // the buffer is the consumers' again
+        if (lane == 0) mbar_arrive(E.eempty);   // the buffer is the consumers' again
         if (!E.fused) {
-            if (lane == 0) mbar_arrive(E.qempty + 8 * mine);
+            if (lane == 0) mbar_arrive(E.qempty + 8 * qslot);
             continue;
         }
         // 2. count the item in; merge what it completes
@@ -590,7 +591,7 @@ __device__ __noinline__ void epilogue_loop(const Epilogue E, int lane) {
             merge_completed(E, rec, done_mask, kvh, lane);
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(E.qempty + 8 * mine);   // done with the record too
+        if (lane == 0) mbar_arrive(E.qempty + 8 * qslot);   // done with the record too
     }
 }
 
@@ -614,7 +615,10 @@ __device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe 
     const int q_rows = n_rows * group;
     const float sl2 = 0.08838834764831845f * 1.4426950408889634f;   // log2(e) / sqrt(128)
     const bool exact_q = (P.q_dtype == YX_BF16 && BF16) || (P.q_dtype == YX_F16 && !BF16);
-    const bool low = low_ok && !exact_q;   // f32 queries carry a low part
+    // Queries that are not already of the cache's type carry a low part on bf16 caches (8 bits of
+    // mantissa would not do); on f16 caches the high part's 11 bits are within the bound by a wide
+    // margin, and leaving the low part out takes a third off the tensor work of an item.
+    const bool low = low_ok && !exact_q && BF16;
 
     // The two queries this thread meets in the accumulator fragments: columns 2 t4 and 2 t4 + 1.
     uint32_t klo[2], khi[2];
@@ -845,7 +849,7 @@ __device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe 
 }
 
 template <bool BF16>
-__global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const __grid_constant__ Params P) {
+__global__ void __maxnreg__(168) attend_mma_kernel(const __grid_constant__ Params P) {
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ int abort_flag;
     Shared S;
@@ -891,7 +895,7 @@ __global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const __grid_con
         }
         __syncwarp();
         // The set-up is published through a named barrier that this warp only arrives at (it has
-        // nothing to wait for) and the eleven other warps wait on; they then fetch queries while
+        // nothing to wait for) and the ten other warps wait on; they then fetch queries while
         // this warp starts the first K/V copies.  (Barrier 0, the __syncthreads barrier, reached
         // from two places in the code did not hold the other warps back: they went on to use
         // mbarriers that were not yet initialised.)
@@ -959,8 +963,8 @@ __global__ void __launch_bounds__(THREADS, 1) attend_mma_kernel(const __grid_con
         E.merge = S.merge;
         E.efull = S.efull;
         E.eempty = S.eempty;
-        E.mlbuf = S.mlbuf + (warp - EWARP) * (MLBUF_BYTES / EWARPS);
-        E.first_item = warp - EWARP;
+        E.mlbuf = S.mlbuf;
+        E.first_item = 0;
         epilogue_loop(E, lane);
         return;
     }

@@ -304,101 +304,121 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
         units.swap(all);
     }
 
-    // 4. Cut the tile sequence (units x KV heads) into one span of equal cost per CTA.  A tile
-    //    of an item with many query rows costs more tensor work than its bytes alone; the
-    //    weights keep the CTAs that get such items from finishing last.
+    // 4. Cut the tile sequence (units x KV heads) into one contiguous span per CTA so that the
+    //    most loaded CTA is as light as can be.  A CTA's load is what it was measured to be: a
+    //    weight per tile (a tile of an item with many query rows costs more tensor work than its
+    //    bytes alone) plus a fixed amount per item (queries in, triples merged and written).  The
+    //    smallest limit under which the spans fit the CTAs is found by bisection; under a given
+    //    limit every CTA is simply filled as far as the limit allows.  A piece of a run is at
+    //    least `min_piece` tiles: a shorter one is not worth an item of its own.
     auto weight = [&](const Unit &u) -> uint64_t {
         int mt = padded_rows((int)u.rows.size() * pp.group);
         return mt == 16 ? 16u : (mt == 32 ? (uint64_t)std::max(pp.w32, 1) : (uint64_t)std::max(pp.w64, 1));
     };
-    // Every item also costs its CTA a fixed amount (queries staged, triples written, an
-    // arrival counted): charged per (unit, KV head) here, and again for each extra piece a
-    // unit is cut into, so that a CTA handed many short items gets fewer tiles.
     const uint64_t item_cost = (uint64_t)std::max(pp.item_cost, 0);
-    uint64_t total_tiles = 0, total_cost = 0;
-    for (const Unit &u : units) {
-        uint64_t t = (uint64_t)(u.hi / TILE_KEYS - u.lo / TILE_KEYS + 1) * pp.hkv;
-        total_tiles += t;
-        total_cost += t * weight(u) + item_cost * pp.hkv;
+    const uint32_t min_piece = (uint32_t)std::max(pp.min_piece, 1);
+    struct Run { uint32_t unit, t0, n; uint64_t w; };   // n tiles from t0, for each KV head
+    std::vector<Run> runs;
+    runs.reserve(units.size());
+    uint64_t total_tiles = 0, total_cost = 0, floor_cost = 0;
+    for (size_t ui = 0; ui < units.size(); ui++) {
+        const Unit &u = units[ui];
+        Run r{(uint32_t)ui, u.lo / TILE_KEYS, u.hi / TILE_KEYS - u.lo / TILE_KEYS + 1, weight(u)};
+        runs.push_back(r);
+        total_tiles += (uint64_t)r.n * pp.hkv;
+        total_cost += ((uint64_t)r.n * r.w + item_cost) * pp.hkv;
+        floor_cost = std::max(floor_cost, item_cost + (uint64_t)std::min(r.n, min_piece) * r.w);
     }
     int n_ctas = (int)std::min<uint64_t>((uint64_t)std::max(1, pp.n_ctas), std::max<uint64_t>(total_tiles, 1));
     out.n_ctas = n_ctas;
     out.cta_begin.assign(n_ctas + 1, 0);
     out.merges.assign((size_t)T * pp.hkv, Merge{0, 0});
 
-    // Each CTA's target is set when it is opened: an equal share of what is still unassigned
-    // (`rem`: tiles and one item per run not yet begun) plus the cuts still to come, about one per
-    // CTA boundary.  How many cuts there will be is not known beforehand (a CTA may end on a run
-    // boundary), so a division fixed at the start would starve or overload the last CTAs; this
-    // one corrects itself at every boundary.
-    uint64_t rem = total_cost;
-    uint64_t done = 0;      // cost handed out so far
-    uint64_t cta_end = 0;   // `done` at which the open CTA is full
-    int cta = 0;
-    auto open_cta = [&](bool mid_run) {
-        const uint64_t ahead = (uint64_t)(n_ctas - cta - 1);
-        const uint64_t cuts = item_cost * ahead * 3 / 4 + (mid_run ? item_cost : 0);
-        cta_end = done + (rem + cuts) / (ahead + 1);
+    // How much of a run of `left` tiles goes into a CTA that holds `load` already, under `lim`:
+    // 0 = none (close the CTA first, unless it is empty: then the limit is too small).
+    auto take_under = [&](uint64_t lim, uint64_t load, uint64_t w, uint32_t left) -> uint32_t {
+        if (load + item_cost + w > lim) return 0;
+        uint64_t room = (lim - load - item_cost) / w;
+        if (room >= left) return left;
+        if (room < min_piece) return 0;
+        if (left - room < min_piece) {           // the rest would be a crumb: leave it min_piece tiles
+            if (left < 2 * min_piece) return 0;  // cannot be cut at all: all of it or none
+            room = left - min_piece;
+        }
+        return (uint32_t)room;
     };
-    open_cta(false);
-    // A CTA's last item is the one whose latency nothing hides (queries in, a few tiles, merge,
-    // triples out: about four tiles' time however short it is).  A run is therefore not begun
-    // in a CTA that has room for only a few of its tiles left.
-    const uint64_t min_last = 4;
-    std::vector<uint32_t> seen(2 * (size_t)n_dense, 0);   // (physical page, half) -> most keys read
-    for (const Unit &u : units) {
-        const uint64_t w = weight(u);
-        uint32_t t0 = u.lo / TILE_KEYS, t1 = u.hi / TILE_KEYS + 1;
+    // CTAs needed under `lim`, or n_ctas + 1 if some piece cannot be placed at all.
+    auto ctas_under = [&](uint64_t lim) -> int {
+        int used = 1;
+        uint64_t load = 0;
+        for (const Run &r : runs)
+            for (int kh = 0; kh < pp.hkv; kh++) {
+                uint32_t left = r.n;
+                while (left > 0) {
+                    const uint32_t take = take_under(lim, load, r.w, left);
+                    if (take == 0) {
+                        if (load == 0) return n_ctas + 1;
+                        load = 0;
+                        if (++used > n_ctas) return used;
+                        continue;
+                    }
+                    load += item_cost + (uint64_t)take * r.w;
+                    left -= take;
+                }
+            }
+        return used;
+    };
+    uint64_t lo_lim = std::max<uint64_t>(floor_cost, (total_cost + n_ctas - 1) / n_ctas), hi_lim = std::max<uint64_t>(total_cost, floor_cost);
+    // (an uncuttable run can exceed any share: hi_lim must admit the longest one whole)
+    for (const Run &r : runs) hi_lim = std::max<uint64_t>(hi_lim, item_cost + (uint64_t)r.n * r.w);
+    while (lo_lim < hi_lim) {
+        const uint64_t mid = lo_lim + (hi_lim - lo_lim) / 2;
+        if (ctas_under(mid) <= n_ctas) hi_lim = mid;
+        else lo_lim = mid + 1;
+    }
+    const uint64_t lim = hi_lim;
+
+    std::vector<uint32_t> &seen = out.scratch_seen;   // (physical page, half) -> most keys read
+    seen.assign(2 * (size_t)n_dense, 0);
+    int cta = 0;
+    uint64_t load = 0;
+    for (const Run &r : runs) {
+        const Unit &u = units[r.unit];
+        const uint32_t t0 = r.t0, t1 = r.t0 + r.n;
         for (uint32_t t = t0; t < t1; t++) {
             uint32_t a = std::max(u.lo, t * TILE_KEYS), b = std::min(u.hi, t * TILE_KEYS + TILE_KEYS - 1);
             uint32_t n = b - a + 1;
-            uint32_t &s = seen[((size_t)dense[u.pt_off + t * TILE_KEYS / PAGE] << 1) | (t & 1)];
-            s = std::max(s, n);
+            uint32_t &sn = seen[((size_t)dense[u.pt_off + t * TILE_KEYS / PAGE] << 1) | (t & 1)];
+            sn = std::max(sn, n);
         }
+        Item proto{};
+        proto.key_lo = u.lo;
+        proto.key_hi = u.hi;
+        proto.pt_off = u.pt_off;
+        proto.n_rows = (uint16_t)u.rows.size();
+        proto.mt = (uint32_t)padded_rows((int)u.rows.size() * pp.group);
+        proto.flags = (u.reused ? 1u : 0u) | (u.fresh_from << 1);   // bit 0: reused; the rest: fresh_from (positions < 2^31)
+        for (size_t k = 0; k < u.rows.size(); k++) proto.rows[k] = u.rows[k];
         for (int kh = 0; kh < pp.hkv; kh++) {
             uint32_t t = t0;
-            if (pp.resolve && cta < n_ctas - 1 && (uint32_t)out.cta_begin[cta] < out.items.size()) {
-                const uint64_t room = cta_end > done + item_cost ? (cta_end - done - item_cost) / w : 0;
-                if (room < min_last && room < (uint64_t)(t1 - t0)) {
-                    cta++;
-                    out.cta_begin[cta] = (uint32_t)out.items.size();
-                    open_cta(false);
-                }
-            }
             while (t < t1) {
-                // Move on when less than half a tile's cost is left in this CTA's span.
-                while (cta < n_ctas - 1 && done + w / 2 >= cta_end) {
-                    cta++;
-                    out.cta_begin[cta] = (uint32_t)out.items.size();
-                    open_cta(t != t0);
+                uint32_t take = take_under(lim, load, r.w, t1 - t);
+                if (take == 0) {
+                    if (load > 0 && cta < n_ctas - 1) {
+                        cta++;
+                        out.cta_begin[cta] = (uint32_t)out.items.size();
+                        load = 0;
+                        continue;
+                    }
+                    take = t1 - t;   // cannot happen under a feasible limit; never lose tiles
                 }
-                uint64_t left = cta_end > done + item_cost ? cta_end - done - item_cost : 0;
-                uint64_t room = cta == n_ctas - 1 ? UINT64_MAX : (left + w / 2) / w;
-                uint32_t take = (uint32_t)std::min<uint64_t>(std::max<uint64_t>(room, 1), t1 - t);
-                // No crumbs: a piece of fewer than min_piece tiles is not worth an item of its
-                // own.  What little is left of the run joins this piece, and a piece that would
-                // start with little room in this CTA starts in the next one instead.
-                const uint32_t min_piece = (uint32_t)std::max(pp.min_piece, 1);
-                if (take < min_piece) take = std::min(min_piece, t1 - t);
-                if (t1 - t - take < min_piece) take = t1 - t;
-                Item it{};
+                Item it = proto;
                 it.tile_begin = t;
                 it.tile_end = t + take;
-                it.key_lo = u.lo;
-                it.key_hi = u.hi;
-                it.pt_off = u.pt_off;
                 it.kv_head = (uint16_t)kh;
-                it.n_rows = (uint16_t)u.rows.size();
-                it.mt = (uint32_t)padded_rows((int)u.rows.size() * pp.group);
-                it.flags = (u.reused ? 1u : 0u) | (u.fresh_from << 1);   // bit 0: reused; the rest: fresh_from (positions < 2^31)
-                for (size_t r = 0; r < u.rows.size(); r++) {
-                    it.rows[r] = u.rows[r];
-                    out.merges[(size_t)u.rows[r] * pp.hkv + kh].count++;
-                }
+                for (size_t k = 0; k < u.rows.size(); k++) out.merges[(size_t)u.rows[k] * pp.hkv + kh].count++;
                 out.items.push_back(it);
-                // `rem` holds one item per run; a cut's extra item is charged to the CTA only.
-                done += take * w + item_cost;
-                rem -= take * w + (t == t0 ? item_cost : 0);
+                load += item_cost + (uint64_t)take * r.w;
                 t += take;
             }
         }

@@ -112,7 +112,7 @@ constexpr int IRR_KLO = 0, IRR_KHI = 1, IRR_PART = 2, IRR_ROW = 3, IRR_FIRST = 4
 // travels in kernel-parameter space: the CTA's span, its first tiles and the rows of its first
 // item.  A cold global load at kernel start costs over a microsecond, and three of them in a
 // chain (span -> descriptors -> data) were once the largest single cost of the kernel.
-constexpr int PROLOGUE_TILES = 3;
+constexpr int PROLOGUE_TILES = 4;
 struct CtaPrologue {
     CtaHdr hdr;
     TileDesc first[PROLOGUE_TILES];
