@@ -185,3 +185,26 @@ def test_empty_pass():
     meta = PassMeta()
     info, items = probe(meta, 8, 4)
     assert info.n_items == 0 and info.tiles == 0
+
+
+@pytest.mark.parametrize("window", [0, 2048, 100])
+def test_patched_plans_equal_plans_built_from_scratch(window):
+    # A decode loop: every step each row is one key further.  Most steps have the shape of the step
+    # before (no run a tile longer) and the plan is patched in place; it must be, word for word, the
+    # plan a fresh planner builds for the same pass.  The page tables have room for the steps.
+    rng = np.random.default_rng(3)
+    ctx_len = [1536 + int(x) for x in rng.integers(0, 2561, 16)]
+    tables, nxt = [], 12
+    for c in ctx_len:
+        n = (c + 200) // 128 + 1
+        tables.append(np.array(list(range(12)) + list(range(nxt, nxt + n - 12)), np.uint32))
+        nxt += n - 12
+    from yaxus_b200.kvcache import PassMeta
+    meta = PassMeta.from_rows([(sq, ctx_len[sq]) for sq in range(16)], tables)
+    L = _lib.cuda_lib()
+    p = lambda a: np.ascontiguousarray(a, np.uint32).ctypes.data_as(ctypes.POINTER(ctypes.c_uint32))
+    pos, off, pages = (np.ascontiguousarray(x, np.uint32) for x in (meta.pos, meta.pt_off, meta.pages))
+    patched = ctypes.c_int(0)
+    differing = L.yx_hook_plan_steps(len(pos), p(pos), p(off), p(pages), len(pages), 8, 4, window, 8, 148, 150, ctypes.byref(patched))
+    assert differing == 0
+    assert 75 <= patched.value < 150      # a row crosses a tile every 64 steps: most steps are patched, not all

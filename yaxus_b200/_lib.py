@@ -86,6 +86,8 @@ SIGNATURES = {
 HOOK_SIGNATURES = {
     "yx_plan_probe": (c_int, [c_uint32, _U32P, _U32P, _U32P, c_uint32, c_int, c_int, c_int64, c_uint64, c_uint64,
                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, POINTER(PlanInfo), _U32P, c_uint32]),
+    "yx_hook_plan_steps": (c_int, [c_uint32, _U32P, _U32P, _U32P, c_uint32, c_int, c_int, c_int64, c_int, c_int, c_int, POINTER(c_int)]),
+    "yx_hook_forget_plan_shape": (c_int, [c_void_p]),
     "yx_hook_skip_merge": (c_int, [c_void_p, c_int]),
     "yx_hook_expire_wait": (c_int, [c_void_p, c_uint64]),
     "yx_hook_set_trace": (c_int, [c_void_p, c_void_p]),

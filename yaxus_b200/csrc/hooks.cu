@@ -63,6 +63,76 @@ extern "C" int yx_plan_probe(uint32_t rows, const uint32_t *pos, const uint32_t 
     return YX_OK;
 }
 
+namespace {
+
+bool same_plan(const yx::Plan &a, const yx::Plan &b) {
+    using namespace yx;
+    if (a.tiles.size() != b.tiles.size() || a.items.size() != b.items.size() || a.n_ctas != b.n_ctas || a.n_parts != b.n_parts ||
+        a.prologue.size() != b.prologue.size() || a.merges.size() != b.merges.size() || a.cta_hdr.size() != b.cta_hdr.size())
+        return false;
+    if (memcmp(a.tiles.data(), b.tiles.data(), a.tiles.size() * sizeof(TileDesc))) return false;
+    if (memcmp(a.items.data(), b.items.data(), a.items.size() * sizeof(Item))) return false;
+    if (memcmp(a.prologue.data(), b.prologue.data(), a.prologue.size() * sizeof(CtaPrologue))) return false;
+    if (memcmp(a.merges.data(), b.merges.data(), a.merges.size() * sizeof(Merge))) return false;
+    if (memcmp(a.cta_hdr.data(), b.cta_hdr.data(), a.cta_hdr.size() * sizeof(CtaHdr))) return false;
+    for (size_t i = 0; i < a.items.size(); i++) {   // the words of a record that are read
+        if (memcmp(a.recs[i].w, b.recs[i].w, 16)) return false;
+        if (memcmp(a.recs[i].w + IR_ROW0, b.recs[i].w + IR_ROW0, a.items[i].n_rows * IR_ROW_WORDS * 4)) return false;
+    }
+    return a.info.unique_kv_bytes == b.info.unique_kv_bytes && a.info.logical_kv_bytes == b.info.logical_kv_bytes &&
+           a.info.tiles == b.info.tiles && a.single_use == b.single_use && a.has_empty_rows == b.has_empty_rows;
+}
+
+}  // namespace
+
+extern "C" int yx_hook_plan_steps(uint32_t rows, const uint32_t *pos, const uint32_t *pt_off, const uint32_t *pages,
+                                  uint32_t n_pages, int hkv, int group, int64_t window, int max_rows, int n_ctas, int steps,
+                                  int *patched_out) {
+    if (rows && (!pos || !pt_off)) return -1;
+    yx::PassHost pass;
+    pass.rows = rows;
+    pass.pos.assign(pos, pos + rows);
+    pass.pt_off.assign(pt_off, pt_off + rows);
+    pass.pages.assign(pages, pages + n_pages);
+    yx::PlanParams pp{};
+    pp.hkv = hkv;
+    pp.group = group;
+    pp.window = window > 0 ? window : 0;
+    pp.key_lo = 0;
+    pp.key_hi = UINT64_MAX;
+    pp.max_rows = max_rows;
+    pp.n_ctas = n_ctas;
+    pp.share_prefix = true;
+    pp.esize = 2;
+    pp.w32 = 16;
+    pp.w64 = 40;
+    pp.resolve = true;
+    pp.min_piece = 2;
+    pp.item_cost = 14;
+    yx::Plan running;
+    int patched = 0, differing = 0;
+    try {
+        for (int s = 0; s < steps; s++) {
+            yx::build_split_plan(pass, pp, running);
+            yx::Plan fresh;
+            yx::build_split_plan(pass, pp, fresh);
+            patched += running.patched ? 1 : 0;
+            differing += same_plan(running, fresh) ? 0 : 1;
+            for (uint32_t &p : pass.pos) p++;
+        }
+    } catch (const std::string &) {
+        return -1;
+    }
+    if (patched_out) *patched_out = patched;
+    return differing;
+}
+
+extern "C" int yx_hook_forget_plan_shape(yx_ctx *ctx) {
+    if (!ctx) return YX_ERR_INVALID;
+    for (auto &cp : ctx->plans) cp.plan.sig_valid = false;
+    return YX_OK;
+}
+
 extern "C" int yx_hook_skip_merge(yx_ctx *ctx, int on) {
     if (!ctx) return YX_ERR_INVALID;
     ctx->skip_merge = on != 0;

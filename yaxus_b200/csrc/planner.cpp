@@ -55,21 +55,11 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
     if (pp.hkv <= 0 || pp.group <= 0) throw std::string("bad head counts");
     if (pp.max_rows < 1 || pp.max_rows > MAX_ITEM_ROWS) throw std::string("bad rows per item");
     if (T > 65535) throw std::string("a pass holds at most 65535 rows");
-    // The plan object is reused from call to call: its arrays keep their capacity.
-    out.path = 0;
-    out.n_ctas = 0;
-    out.items.clear();
-    out.cta_begin.clear();
-    out.merges.clear();
-    out.n_parts = 0;
+    // The plan object is reused from call to call: its arrays keep their capacity, and what the
+    // last plan was built from is remembered (see `try_patch` below).
     out.tile_items.clear();
     out.tile_cta_begin.clear();
-    out.cta_hdr.clear();
-    out.tiles.clear();
-    out.prologue.clear();   // (recs keeps its records: every word that is read is rewritten below)
-    out.single_use = false;
-    out.has_empty_rows = false;
-    out.info = yx_plan_info{};
+    out.patched = false;
 
     // Dense ids of the physical pages named in this pass (page-table entry -> id), so that
     // per-page bookkeeping below is a flat array.  Found with a small open-addressing table:
@@ -304,6 +294,97 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
         units.swap(all);
     }
 
+    // Keys streamed and distinct keys streamed (for the plan's byte counts).
+    std::vector<uint32_t> &seen = out.scratch_seen;   // (physical page, half) -> most keys read
+    seen.assign(2 * (size_t)n_dense, 0);
+    for (const Unit &u : units)
+        for (uint32_t t = u.lo / TILE_KEYS; t <= u.hi / TILE_KEYS; t++) {
+            const uint32_t a = std::max(u.lo, t * TILE_KEYS), b = std::min(u.hi, t * TILE_KEYS + TILE_KEYS - 1);
+            uint32_t &sn = seen[((size_t)dense[u.pt_off + t * TILE_KEYS / PAGE] << 1) | (t & 1)];
+            sn = std::max(sn, b - a + 1);
+        }
+    uint64_t uniq = 0;
+    for (uint32_t v : seen) uniq += v;
+    const int64_t per_key = (int64_t)2 * D * pp.esize * pp.hkv;   // K and V of every KV head
+
+    // 3b. The short way.  The next decode step has the shape of the last one: the same rows over
+    //     the same page tables, every row a key or so further, no run a tile longer.  Then the
+    //     cut into spans, the partial slots and all but the two end tiles of every item stand as
+    //     they are; only the key ranges move.  Building a plan from scratch costs several times
+    //     what the rest of a decode step's host work does.
+    const int params[10] = {pp.hkv, pp.group, pp.max_rows, pp.n_ctas, pp.share_prefix ? 1 : 0, pp.esize, pp.w32, pp.w64,
+                            pp.item_cost, pp.min_piece};
+    auto same_shape = [&]() -> bool {
+        if (!out.sig_valid || !pp.resolve || !out.tile_items.empty()) return false;
+        if (out.sig_rows_in_pass != T || out.sig_window != pp.window || pp.key_lo != 0 || pp.key_hi != UINT64_MAX) return false;
+        if (memcmp(params, out.sig_params, sizeof params) != 0 || pp.share_rows != 0) return false;
+        if (out.sig_units.size() != units.size() || out.sig_pages.size() != pass.pages.size()) return false;
+        if (!pass.pages.empty() && memcmp(out.sig_pages.data(), pass.pages.data(), pass.pages.size() * 4) != 0) return false;
+        size_t at = 0;
+        for (size_t ui = 0; ui < units.size(); ui++) {
+            const Unit &u = units[ui];
+            const Plan::UnitSig &g = out.sig_units[ui];
+            if (g.pt_off != u.pt_off || g.t0 != u.lo / TILE_KEYS || g.n != u.hi / TILE_KEYS - u.lo / TILE_KEYS + 1 ||
+                g.n_rows != u.rows.size() || g.reused != (u.reused ? 1u : 0u) || g.fresh_tile != u.fresh_from / TILE_KEYS)
+                return false;
+            if (at + u.rows.size() > out.sig_unit_rows.size() ||
+                memcmp(out.sig_unit_rows.data() + at, u.rows.data(), u.rows.size() * sizeof(uint16_t)) != 0)
+                return false;
+            at += u.rows.size();
+        }
+        return true;
+    };
+    if (same_shape()) {
+        const uint32_t hkv = (uint32_t)pp.hkv;
+        TileDesc *td = out.tiles.data();
+        for (size_t i = 0; i < out.items.size(); i++) {
+            Item &it = out.items[i];
+            const Unit &u = units[out.item_unit[i]];
+            it.key_lo = u.lo;
+            it.key_hi = u.hi;
+            it.flags = (u.reused ? 1u : 0u) | (u.fresh_from << 1);
+            const uint32_t flags = u.reused ? TILE_REUSED : 0u;
+            const uint32_t ends[2] = {it.tile_begin, it.tile_end - 1};
+            for (int e = 0; e < 2; e++) {
+                const uint32_t t = ends[e], k0 = t * TILE_KEYS;
+                const uint32_t a = std::max(it.key_lo, k0), b = std::min(it.key_hi, k0 + TILE_KEYS - 1);
+                TileDesc &d = td[out.item_tile0[i] + (t - it.tile_begin)];
+                d.info = (t & 1u) | ((a - k0) << 1) | ((b - a + 1) << 8) | flags | (b >= u.fresh_from ? TILE_FRESH : 0u);
+            }
+            uint32_t *w = out.recs[i].w;
+            for (int k = 0; k < it.n_rows; k++) {
+                const uint32_t p = pass.pos[it.rows[k]];
+                uint32_t *rw = w + IR_ROW0 + IR_ROW_WORDS * k;
+                rw[IRR_KLO] = std::max(row_lo(p, pp.window), it.key_lo);
+                rw[IRR_KHI] = std::min(p, it.key_hi);
+            }
+        }
+        for (int c = 0; c < out.n_ctas; c++) {
+            CtaPrologue &pr = out.prologue[c];
+            for (uint32_t j = 0; j < (uint32_t)PROLOGUE_TILES && pr.hdr.tile_begin + j < pr.hdr.tile_end; j++)
+                pr.first[j] = td[pr.hdr.tile_begin + j];
+        }
+        (void)hkv;
+        out.info.unique_kv_bytes = (int64_t)uniq * per_key;
+        out.info.logical_kv_bytes = (int64_t)logical * per_key;
+        out.patched = true;
+        return;
+    }
+    out.sig_valid = false;
+    out.path = 0;
+    out.n_ctas = 0;
+    out.items.clear();
+    out.item_unit.clear();
+    out.cta_begin.clear();
+    out.merges.clear();
+    out.n_parts = 0;
+    out.cta_hdr.clear();
+    out.tiles.clear();
+    out.prologue.clear();   // (recs keeps its records: every word that is read is rewritten below)
+    out.single_use = false;
+    out.has_empty_rows = false;
+    out.info = yx_plan_info{};
+
     // 4. Cut the tile sequence (units x KV heads) into one contiguous span per CTA so that the
     //    most loaded CTA is as light as can be.  A CTA's load is what it was measured to be: a
     //    weight per tile (a tile of an item with many query rows costs more tensor work than its
@@ -368,29 +449,55 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
             }
         return used;
     };
-    uint64_t lo_lim = std::max<uint64_t>(floor_cost, (total_cost + n_ctas - 1) / n_ctas), hi_lim = std::max<uint64_t>(total_cost, floor_cost);
-    // (an uncuttable run can exceed any share: hi_lim must admit the longest one whole)
-    for (const Run &r : runs) hi_lim = std::max<uint64_t>(hi_lim, item_cost + (uint64_t)r.n * r.w);
-    while (lo_lim < hi_lim) {
-        const uint64_t mid = lo_lim + (hi_lim - lo_lim) / 2;
-        if (ctas_under(mid) <= n_ctas) hi_lim = mid;
-        else lo_lim = mid + 1;
+    // The smallest limit that fits, among the multiples of a tile's weight (so that the answer
+    // does not depend on where the search starts).  The limit the plan object found last time is
+    // tried first: a decode pass differs from the one before it by a key per row, and its answer
+    // is the same or a step away, so the search is two or three passes over the runs instead of
+    // a bisection from scratch.
+    const uint64_t step = 16;
+    auto up16 = [&](uint64_t x) { return (x + step - 1) / step * step; };
+    const uint64_t lo_lim = up16(std::max<uint64_t>(floor_cost, (total_cost + n_ctas - 1) / n_ctas));
+    uint64_t hi_lim = std::max<uint64_t>(total_cost, floor_cost);
+    for (const Run &r : runs) hi_lim = std::max<uint64_t>(hi_lim, item_cost + (uint64_t)r.n * r.w);   // admits any run whole
+    hi_lim = up16(hi_lim);
+    uint64_t good, bad;   // a limit known to fit, and one known not to (both multiples of `step`)
+    const uint64_t guess = out.last_limit >= lo_lim && out.last_limit <= hi_lim && out.last_limit % step == 0
+                               ? out.last_limit : std::min(hi_lim, up16(lo_lim + lo_lim / 16));
+    if (ctas_under(guess) <= n_ctas) {
+        good = guess;
+        bad = lo_lim - step;
+        while (good > lo_lim) {             // walk down a tile at a time while it still fits
+            if (ctas_under(good - step) > n_ctas) {
+                bad = good - step;
+                break;
+            }
+            good -= step;
+        }
+    } else {
+        bad = guess;
+        good = hi_lim;
+        for (uint64_t up = step; bad + up < hi_lim; up *= 2) {   // gallop up to a limit that fits
+            if (ctas_under(bad + up) <= n_ctas) {
+                good = bad + up;
+                break;
+            }
+            bad += up;
+        }
+        while (good - bad > step) {          // and close in
+            const uint64_t mid = bad + (good - bad) / (2 * step) * step;
+            if (ctas_under(mid) <= n_ctas) good = mid;
+            else bad = mid;
+        }
     }
+    hi_lim = good;
+    out.last_limit = good;
     const uint64_t lim = hi_lim;
 
-    std::vector<uint32_t> &seen = out.scratch_seen;   // (physical page, half) -> most keys read
-    seen.assign(2 * (size_t)n_dense, 0);
     int cta = 0;
     uint64_t load = 0;
     for (const Run &r : runs) {
         const Unit &u = units[r.unit];
         const uint32_t t0 = r.t0, t1 = r.t0 + r.n;
-        for (uint32_t t = t0; t < t1; t++) {
-            uint32_t a = std::max(u.lo, t * TILE_KEYS), b = std::min(u.hi, t * TILE_KEYS + TILE_KEYS - 1);
-            uint32_t n = b - a + 1;
-            uint32_t &sn = seen[((size_t)dense[u.pt_off + t * TILE_KEYS / PAGE] << 1) | (t & 1)];
-            sn = std::max(sn, n);
-        }
         Item proto{};
         proto.key_lo = u.lo;
         proto.key_hi = u.hi;
@@ -418,6 +525,7 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
                 it.kv_head = (uint16_t)kh;
                 for (size_t k = 0; k < u.rows.size(); k++) out.merges[(size_t)u.rows[k] * pp.hkv + kh].count++;
                 out.items.push_back(it);
+                out.item_unit.push_back(r.unit);
                 load += item_cost + (uint64_t)take * r.w;
                 t += take;
             }
@@ -448,6 +556,7 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
         out.cta_hdr.resize(n_ctas);
         if (out.recs.size() < out.items.size()) out.recs.resize(out.items.size());   // words a record does not use keep old values
         out.tiles.resize((size_t)total_tiles);
+        out.item_tile0.resize(out.items.size());
         TileDesc *td = out.tiles.data();
         const uint32_t *pages = pass.pages.data(), *pos = pass.pos.data();
         const Item *items = out.items.data();
@@ -462,6 +571,7 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
             h.tile_begin = (uint32_t)n_tiles;
             for (uint32_t i = h.item_begin; i < h.item_end; i++) {
                 const Item &it = items[i];
+                out.item_tile0[i] = (uint32_t)n_tiles;
                 const uint32_t *pt = pages + it.pt_off;
                 const uint32_t flags = (it.flags & 1u) ? TILE_REUSED : 0u, fresh_from = it.flags >> 1;
                 for (uint32_t t = it.tile_begin; t < it.tile_end; t++) {
@@ -506,13 +616,10 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
         }
     }
 
-    uint64_t uniq = 0;
-    for (uint32_t v : seen) uniq += v;
     out.info.n_ctas = n_ctas;
     out.info.n_items = (int)out.items.size();
     out.info.n_parts = (int)out.n_parts;
     out.info.tiles = (int64_t)total_tiles;
-    const int64_t per_key = (int64_t)2 * D * pp.esize * pp.hkv;   // K and V of every KV head
     out.info.unique_kv_bytes = (int64_t)uniq * per_key;
     out.info.logical_kv_bytes = (int64_t)logical * per_key;
     out.info.shared_groups = shared_groups;
@@ -533,6 +640,21 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
         uint64_t distinct = 0;
         for (uint32_t v : once) distinct += v;
         out.single_use = streamed <= distinct;
+    }
+    // What this plan was built from, for the short way next time.
+    if (pp.resolve && out.tile_items.empty()) {
+        out.sig_rows_in_pass = T;
+        out.sig_window = pp.window;
+        memcpy(out.sig_params, params, sizeof params);
+        out.sig_pages.assign(pass.pages.begin(), pass.pages.end());
+        out.sig_units.clear();
+        out.sig_unit_rows.clear();
+        for (const Unit &u : units) {
+            out.sig_units.push_back({u.pt_off, u.lo / TILE_KEYS, u.hi / TILE_KEYS - u.lo / TILE_KEYS + 1, (uint32_t)u.rows.size(),
+                                     u.reused ? 1u : 0u, u.fresh_from / TILE_KEYS});
+            out.sig_unit_rows.insert(out.sig_unit_rows.end(), u.rows.begin(), u.rows.end());
+        }
+        out.sig_valid = pp.share_rows == 0;
     }
 }
 

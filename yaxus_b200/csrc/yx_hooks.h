@@ -23,6 +23,20 @@ int yx_plan_probe(uint32_t rows, const uint32_t *pos_host, const uint32_t *pt_of
                   int max_rows, int n_ctas, int share_prefix, int esize, int cost32, int cost64, int item_cost,
                   int min_piece, yx_plan_info *info, uint32_t *items_out, uint32_t max_items);
 
+/* The planner's short way (a plan patched in place when the next pass has the shape of the last
+ * one) against plans built from scratch: runs `steps` decode steps from the given pass, every row one
+ * key further each step, through one plan object, and builds a fresh plan beside it every time.
+ * Returns the number of steps whose plans differed (0 is the only good answer), or -1 on a
+ * malformed pass; *patched_out receives how many steps took the short way.  Needs no device. */
+int yx_hook_plan_steps(uint32_t rows, const uint32_t *pos_host, const uint32_t *pt_off_host, const uint32_t *pages_host,
+                       uint32_t n_pages, int hkv, int group, int64_t window, int max_rows, int n_ctas, int steps,
+                       int *patched_out);
+
+/* Measurement only.  Makes the context's next plans be built from scratch, as they are in a decode
+ * loop whenever a row's keys grow into a new 64-key tile (a benchmark that repeats one pass would
+ * otherwise always take the planner's short way). */
+int yx_hook_forget_plan_shape(yx_ctx *ctx);
+
 /* Measurement only.  on != 0: yx_attend runs its split-key kernel and skips the merge of the
  * triples (the call then produces no output), so that back-to-back calls time that kernel alone. */
 int yx_hook_skip_merge(yx_ctx *ctx, int on);

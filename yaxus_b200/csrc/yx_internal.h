@@ -150,6 +150,20 @@ struct Plan {
     std::vector<CtaPrologue> prologue;  // one per CTA (resolved form)
     std::vector<uint32_t> scratch_dense, scratch_seen, scratch_once;   // planner scratch, kept for its capacity
     std::vector<uint64_t> scratch_table;
+    uint64_t last_limit = 0;            // per-CTA load limit the last plan settled on (starting point of the next search)
+    // What the last plan was built from, so that a pass with the same shape (the next decode step:
+    // every row one key further, no new tile, no new page) only has its key ranges patched in.
+    struct UnitSig { uint32_t pt_off, t0, n, n_rows, reused, fresh_tile; };
+    bool sig_valid = false;
+    uint32_t sig_rows_in_pass = 0;
+    int sig_params[10] = {};
+    int64_t sig_window = 0;
+    std::vector<UnitSig> sig_units;
+    std::vector<uint16_t> sig_unit_rows;
+    std::vector<uint32_t> sig_pages;
+    std::vector<uint32_t> item_unit;    // the unit each item is a piece of
+    std::vector<uint32_t> item_tile0;   // index of each item's first tile descriptor
+    bool patched = false;               // the last build took the short way
     bool single_use = false;            // every tile not marked as reused is read by exactly one item
     bool has_empty_rows = false;        // some (row, kv head) has no item: no live key in the range
     yx_plan_info info{};
