@@ -104,3 +104,23 @@ def test_last_chunk_of_the_full_configuration(backend, oracle):
                         None, K, V)
     assert_close(got[sample], ref, what="chunk 7 of 8 x 4096")
     kv.close()
+
+
+def test_bf16_values_beyond_f16_take_the_two_part_path(backend, oracle):
+    # On a bf16 cache the tile kernel turns V pages into f16 in shared memory and multiplies once;
+    # that is exact unless the cache holds a V value of magnitude 65536 or more, which the kernels
+    # that write V record.  Here one appended value and, in a second cache, one imported value are
+    # that large: the kernel's two-part variant must do the work, with the same result as ever.
+    for where in ("appended", "imported"):
+        s = W.prefill_chunk(seed=31, n_seq=2, done=256, chunk=256, kv_dtype=BF16, hq=8, hkv=2, total=512)
+        if where == "appended":
+            s.v_new[5, 17] = 1.0e5
+            s.v_new[300, 200] = -3.0e6
+        else:
+            big = W.to_bits(np.array([2.5e5], np.float32), BF16)[0]
+            s.v_bits[int(s.tables[0][1]) * 128 + 3, 77] = big
+        kv = load(backend, s)
+        got = run_step(backend, kv, s, q_dtype=torch.bfloat16)
+        assert backend.last_plan().path == 3
+        assert_close(got, oracle_step(oracle, s, q=q_rounded(s)), what=f"large V value {where}")
+        kv.close()

@@ -370,6 +370,7 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
         t.out = out;
         t.out_dtype = out_dtype;
         t.pairs = pp.tile_pairs;
+        t.wide_v = kv->wide_v_dev;
         if (int rc = launch_prefill_tc(ctx, t)) return rc;
     }
     // With every row in the tiled kernel's hands and no partial triples asked for, the merge
@@ -600,6 +601,8 @@ int yx_kv_create(yx_ctx *ctx, int n_layers, const yx_layer *layers, uint32_t pag
     int rc = check_cuda(ctx, cudaMalloc((void **)&kv->k_base, total), "new_kv: cudaMalloc K");
     if (!rc) rc = check_cuda(ctx, cudaMalloc((void **)&kv->v_base, total), "new_kv: cudaMalloc V");
     if (!rc) rc = check_cuda(ctx, cudaMalloc(&kv->rope_dev, sizeof(yx_rope) * n_layers), "new_kv: cudaMalloc rope");
+    if (!rc) rc = check_cuda(ctx, cudaMalloc((void **)&kv->wide_v_dev, 256), "new_kv: cudaMalloc flag");
+    if (!rc) rc = check_cuda(ctx, cudaMemsetAsync(kv->wide_v_dev, 0, 256, ctx->stream), "new_kv: zero flag");
     // Zeroed like the reference's arenas (cpu lib.rs:466-468).
     if (!rc) rc = check_cuda(ctx, cudaMemsetAsync(kv->k_base, 0, total, ctx->stream), "new_kv: zero K");
     if (!rc) rc = check_cuda(ctx, cudaMemsetAsync(kv->v_base, 0, total, ctx->stream), "new_kv: zero V");
@@ -624,6 +627,7 @@ void yx_kv_destroy(yx_ctx *ctx, yx_kv *kv) {
         if (kv->k_base) cudaFree(kv->k_base);
         if (kv->v_base) cudaFree(kv->v_base);
         if (kv->rope_dev) cudaFree(kv->rope_dev);
+        if (kv->wide_v_dev) cudaFree(kv->wide_v_dev);
     }
     delete kv;
 }

@@ -16,11 +16,14 @@ __device__ __forceinline__ uint16_t to_storage(float x, int dtype) {
     return __bfloat16_as_ushort(__float2bfloat16_rn(x));
 }
 
+// A packed pair of bf16 values holds one that f16 cannot: magnitude 65536 or more, infinite or NaN.
+__device__ __forceinline__ bool bf16_pair_is_wide(uint32_t w) { return (w & 0x7fffu) >= 0x4780u || ((w >> 16) & 0x7fffu) >= 0x4780u; }
+
 // One thread per 8 consecutive dims of one (row, kv head) of K or V.
 // grid.x covers rows * hkv * 16 chunks, grid.y: 0 = K, 1 = V.
 __global__ void append_kernel(const void *__restrict__ k_rows, const void *__restrict__ v_rows, int src_dtype,
                               const uint32_t *__restrict__ kv_slot, uint32_t rows, int hkv, int kv_dtype,
-                              char *__restrict__ k_arena, char *__restrict__ v_arena) {
+                              char *__restrict__ k_arena, char *__restrict__ v_arena, uint32_t *__restrict__ wide_v) {
     uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
     uint32_t total = rows * (uint32_t)hkv * 16u;
     if (idx >= total) return;
@@ -54,6 +57,9 @@ __global__ void append_kernel(const void *__restrict__ k_rows, const void *__res
     } else {
         packed = *(const uint4 *)(src + src_elem * 2);
     }
+    if (is_v && kv_dtype == YX_BF16 &&
+        (bf16_pair_is_wide(packed.x) || bf16_pair_is_wide(packed.y) || bf16_pair_is_wide(packed.z) || bf16_pair_is_wide(packed.w)))
+        atomicOr(wide_v, 1u);
     *(uint4 *)(arena + kv_off16(page, hkv, (int)h, tok, dim) * 2) = packed;
 }
 
@@ -67,7 +73,7 @@ __global__ void qk_rope_append_kernel(const float *__restrict__ qkv, const float
                                       const uint32_t *__restrict__ kv_slot, uint32_t rows, int hq, int hkv,
                                       float eps, const yx_rope *__restrict__ rope, int kv_dtype,
                                       char *__restrict__ k_arena, char *__restrict__ v_arena,
-                                      float *__restrict__ q_out) {
+                                      float *__restrict__ q_out, uint32_t *__restrict__ wide_v) {
     const int heads = hq + 2 * hkv;
     uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     int lane = threadIdx.x & 31;
@@ -117,6 +123,7 @@ __global__ void qk_rope_append_kernel(const float *__restrict__ qkv, const float
     } else {
         uint32_t a = (uint32_t)to_storage(r0, kv_dtype) | ((uint32_t)to_storage(r1, kv_dtype) << 16);
         uint32_t b = (uint32_t)to_storage(r2, kv_dtype) | ((uint32_t)to_storage(r3, kv_dtype) << 16);
+        if (!is_k && kv_dtype == YX_BF16 && (bf16_pair_is_wide(a) || bf16_pair_is_wide(b))) atomicOr(wide_v, 1u);
         uint16_t *base = (uint16_t *)arena;
         *(uint32_t *)(base + kv_off16(page, hkv, h, tok, 2 * lane)) = a;
         *(uint32_t *)(base + kv_off16(page, hkv, h, tok, 64 + 2 * lane)) = b;
@@ -139,7 +146,7 @@ __global__ void copy_page_kernel(char *k_base, char *v_base, size_t layer_bytes,
 // Page import/export between the private layout and the reference's `[tok][hkv*128]`.
 // One thread per element.
 __global__ void page_io_kernel(char *k_arena, char *v_arena, int hkv, int kv_dtype, uint32_t first_page,
-                               uint32_t n_pages, char *k_lin, char *v_lin, int write) {
+                               uint32_t n_pages, char *k_lin, char *v_lin, int write, uint32_t *wide_v) {
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t per_page = (size_t)PAGE * hkv * D;
     if (idx >= per_page * n_pages) return;
@@ -158,8 +165,12 @@ __global__ void page_io_kernel(char *k_arena, char *v_arena, int hkv, int kv_dty
     } else {
         uint16_t *a = (uint16_t *)arena + kv_off16(page, hkv, h, tok, dim);
         uint16_t *l = (uint16_t *)lin + idx;
-        if (write) *a = *l;
-        else *l = *a;
+        if (write) {
+            *a = *l;
+            if (blockIdx.y && kv_dtype == YX_BF16 && (*l & 0x7fffu) >= 0x4780u) atomicOr(wide_v, 1u);
+        } else {
+            *l = *a;
+        }
     }
 }
 
@@ -176,7 +187,7 @@ int launch_append(yx_ctx *ctx, yx_kv *kv, int layer, const void *k_rows, const v
         ctx->smem_configured[4] = true;
     }
     append_kernel<<<grid, 256, 0, ctx->stream>>>(k_rows, v_rows, src_dtype, ctx->d_slot, rows, kv->hkv, kv->dtype,
-                                                  kv->k(layer), kv->v(layer));
+                                                  kv->k(layer), kv->v(layer), kv->wide_v_dev);
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "append kernel");
 }
@@ -193,7 +204,7 @@ int launch_qk_rope_append(yx_ctx *ctx, yx_kv *kv, int layer, const float *qkv, c
     }
     qk_rope_append_kernel<<<blocks, 256, 0, ctx->stream>>>(qkv, q_norm, k_norm, ctx->d_pos, ctx->d_slot, rows, hq,
                                                           kv->hkv, eps, (const yx_rope *)kv->rope_dev + layer,
-                                                          kv->dtype, kv->k(layer), kv->v(layer), q_out);
+                                                          kv->dtype, kv->k(layer), kv->v(layer), q_out, kv->wide_v_dev);
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "qk_rope_append kernel");
 }
@@ -211,7 +222,7 @@ int launch_page_io(yx_ctx *ctx, yx_kv *kv, int layer, uint32_t first_page, uint3
     size_t total = (size_t)n_pages * PAGE * kv->hkv * D;
     dim3 grid((unsigned)((total + 255) / 256), 2);
     page_io_kernel<<<grid, 256, 0, ctx->stream>>>(kv->k(layer), kv->v(layer), kv->hkv, kv->dtype, first_page, n_pages,
-                                                   (char *)k_lin, (char *)v_lin, write ? 1 : 0);
+                                                   (char *)k_lin, (char *)v_lin, write ? 1 : 0, kv->wide_v_dev);
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "page_io kernel");
 }

@@ -60,6 +60,7 @@ struct TileParams {
     yx_dev_status *status;
     long long *trace;   // diagnostics: clock stamps of CTA 0's pipeline, or null
     const uint32_t *cta_begin;   // items of persistent CTA c: [cta_begin[c], cta_begin[c + 1])
+    const uint32_t *wide_v;      // non-zero: the bf16 cache holds V values that f16 cannot
 };
 
 // Shared-memory matrix descriptor: start address, leading / stride byte offsets (16-byte
@@ -468,10 +469,11 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const TileParams
 // Ten warps: 0-3 softmax of A, 4-7 softmax of B, 8 producer, 9 MMA issuer.
 // =============================================================================================
 constexpr int T2_K_STAGES = 2, T2_V_STAGES = 3;
-constexpr int T2_PRODUCER = 8, T2_MMA = 9;
+constexpr int T2_PRODUCER = 8, T2_MMA = 9, T2_CONVERT = 10;
 constexpr int T2_THREADS = 10 * 32;
-// barriers: q_full, k_full[2], v_full[3], s_full_a, s_full_b[2], p_half[2][2], pv_done[2]
-constexpr int T2_BARS = 1 + T2_K_STAGES + T2_V_STAGES + 1 + T2_K_STAGES + 4 + 2;
+constexpr int T2_THREADS_CONVERT = 12 * 32;   // with the two warps that convert V pages (see VCONV below)
+// barriers: q_full, k_full[2], v_full[3], s_full_a, s_full_b[2], p_half[2][2], pv_done[2], v_ready[3]
+constexpr int T2_BARS = 1 + T2_K_STAGES + T2_V_STAGES + 1 + T2_K_STAGES + 4 + 2 + T2_V_STAGES;
 constexpr int T2_SMEM_BYTES = PAGE_BYTES * (2 + T2_K_STAGES + T2_V_STAGES) + T2_BARS * 8 + 64;
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -591,8 +593,30 @@ __device__ __forceinline__ void store_half(uint32_t p_addr, const uint32_t (&x)[
     if (BF16) tmem_st32_pair(p_addr + 64, x, y, 16);
 }
 
-template <bool BF16>
-__global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TileParams P) {
+// Two packed bf16 values as two packed f16 values.  Exact for magnitudes in [2^-14, 65536); smaller
+// ones lose at most 2^-25, larger ones clamp to the largest f16 (a cache that holds such values
+// runs the other variant of the kernel; what clamps here is stale data behind a ragged page, which
+// meets zero probabilities and only has to stay finite).
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t w) {
+    uint32_t d;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(__uint_as_float(w & 0xffff0000u)), "f"(__uint_as_float(w << 16)));
+    return d;
+}
+
+// BF16: the cache (and Q) are bf16, else f16.  VCONV (bf16 caches only): two more warps turn every
+// V page into f16 in shared memory as it lands, probabilities are written as f16, and P V is ONE
+// f16 MMA per K-step; without it a bf16 cache pays two (probabilities as a high and a low bf16
+// part), because 8 bits of mantissa are not enough for them.  bf16 -> f16 is exact for every value
+// below 65536 in magnitude; whether the cache holds anything larger is recorded by the kernels
+// that write V (the cache's `wide_v` flag), both variants are launched, and the one the flag does
+// not ask for leaves at once.
+template <bool BF16, bool VCONV>
+__global__ void __launch_bounds__(VCONV ? T2_THREADS_CONVERT : T2_THREADS, 1) prefill_tc2_kernel(const TileParams P) {
+    static_assert(BF16 || !VCONV, "only bf16 pages are converted");
+    constexpr bool PB = BF16 && !VCONV;   // probabilities and V go to the tensor core as bf16 (two parts)
+    if constexpr (BF16) {
+        if ((__ldg(P.wide_v) != 0u) == VCONV) return;   // the other variant's launch does this call's work
+    }
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_flag;
@@ -612,6 +636,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
     const uint32_t b_k_full = bars + 8, b_v_full = b_k_full + 8 * T2_K_STAGES;
     const uint32_t b_s_full_a = b_v_full + 8 * T2_V_STAGES, b_s_full_b = b_s_full_a + 8;
     const uint32_t b_p_half = b_s_full_b + 8 * T2_K_STAGES, b_pv_done = b_p_half + 32;
+    const uint32_t b_v_ready = b_pv_done + 16;   // V stage converted (VCONV): one arrival per converting warp
     volatile int *abortp = &abort_flag;
 
     // The CTA is persistent: the host dealt it items [item0, item_end) of the list.  `g` counts
@@ -628,7 +653,10 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
             mbar_init(b_k_full + 8 * s, 1);
             mbar_init(b_s_full_b + 8 * s, 1);
         }
-        for (int s = 0; s < T2_V_STAGES; s++) mbar_init(b_v_full + 8 * s, 1);
+        for (int s = 0; s < T2_V_STAGES; s++) {
+            mbar_init(b_v_full + 8 * s, 1);
+            mbar_init(b_v_ready + 8 * s, 2);
+        }
         mbar_init(b_s_full_a, 1);
         for (int t = 0; t < 2; t++) {
             mbar_init(b_p_half + 16 * t, 4);       // one arrival per softmax warp,
@@ -639,7 +667,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
     }
     // Rows of a V stage that a ragged page leaves unwritten meet zero probabilities: they must
     // hold finite numbers (afterwards they hold earlier pages' values, which are).
-    for (int i = threadIdx.x; i < T2_V_STAGES * PAGE_BYTES / 16; i += T2_THREADS)
+    for (int i = threadIdx.x; i < T2_V_STAGES * PAGE_BYTES / 16; i += blockDim.x)
         ((uint4 *)(smem + (2 + T2_K_STAGES) * PAGE_BYTES))[i] = make_uint4(0, 0, 0, 0);
     if (warp == T2_MMA) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "n"(TMEM_COLS) : "memory");
@@ -707,7 +735,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
     } else if (warp == T2_MMA) {
         // ---- MMA issuer ----------------------------------------------------------------------
         if (lane == 0) {
-            const uint32_t idesc_qk = instr_desc(BF16, 0), idesc_pv = instr_desc(BF16, 1);
+            const uint32_t idesc_qk = instr_desc(BF16, 0), idesc_pv = instr_desc(PB, 1);
             // Low descriptor words of the tiles at offset 0; a K-step adds a constant.
             const uint32_t qa_lo = desc_lo(s_qa, 16), qb_lo = desc_lo(s_qb, 16), k_lo = desc_lo(s_k, 16),
                            v_lo = desc_lo(s_v, HALF_BYTES);
@@ -735,7 +763,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
                     for (int k = 4 * h; k < 4 * h + 4; k++) {
                         const uint32_t vk_lo = vv_lo + ((k * 16 * 128) >> 4);
                         umma_ts_lo(tmem + 256 + t * 128, tmem + t * 128 + k * 8, vk_lo, idesc_pv, (!first || k > 0) ? 1u : 0u);
-                        if (BF16) umma_ts_lo(tmem + 256 + t * 128, tmem + t * 128 + 64 + k * 8, vk_lo, idesc_pv, 1u);
+                        if (PB) umma_ts_lo(tmem + 256 + t * 128, tmem + t * 128 + 64 + k * 8, vk_lo, idesc_pv, 1u);
                     }
                 }
                 if (last) umma_commit(b_pv_done + 8 * t);
@@ -751,7 +779,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
                 issue_s(1, g & 1);
                 for (uint32_t j = 0; j < n_tiles && !*abortp; j++, g++) {
                     const bool more = j + 1 < n_tiles;
-                    mbar_wait(b_v_full + 8 * (g % 3), (g / 3) & 1u, abortp, P.status, 47);
+                    mbar_wait((VCONV ? b_v_ready : b_v_full) + 8 * (g % 3), (g / 3) & 1u, abortp, P.status, 47);
                     stamp(g, 0);
                     issue_pv(0, g, j == 0, !more);
                     stamp(g, 2);
@@ -767,6 +795,33 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
                     if (more) issue_s(1, (g + 1) & 1);
                     stamp(g, 7);
                 }
+            }
+        }
+    } else if (VCONV && warp >= T2_CONVERT) {
+        // ---- V pages, bf16 -> f16 in place, a 64-dim half of the page per warp ------------------
+        const uint32_t half = (uint32_t)(warp - T2_CONVERT) * HALF_BYTES;
+        uint32_t g = 0;
+        for (uint32_t n = 0; item0 + n < item_end && !*abortp; n++) {
+            const TileItem it = P.items[item0 + n];
+            const uint32_t n_tiles = it.page_end - it.page_begin;
+            for (uint32_t j = 0; j < n_tiles && !*abortp; j++, g++) {
+                mbar_wait(b_v_full + 8 * (g % 3), (g / 3) & 1u, abortp, P.status, 60);
+                if (*abortp) break;
+                const uint32_t base = s_v + (g % 3) * PAGE_BYTES + half;
+#pragma unroll 4
+                for (int i = lane; i < HALF_BYTES / 16; i += 32) {
+                    uint32_t a, b, c, d;
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(base + 16u * i));
+                    a = bf16x2_to_f16x2(a);
+                    b = bf16x2_to_f16x2(b);
+                    c = bf16x2_to_f16x2(c);
+                    d = bf16x2_to_f16x2(d);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + 16u * i), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+                }
+                // the tensor core reads the page through the async proxy
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(b_v_ready + 8 * (g % 3));
             }
         }
     } else {
@@ -908,18 +963,18 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_kernel(const TilePa
                 const float ms = (m_used == -INFINITY ? 0.f : m_used) * sl2;
                 float sum0 = 0.f, sum1 = 0.f;
                 // Keys [0, 64) first, handed to the tensor core while the other half is computed.
-                exp_chunk<BF16>(s0, sl2, ms, sum0, sum1);
-                exp_chunk<BF16>(s1, sl2, ms, sum0, sum1);
-                store_half<BF16>(s_addr, s0, s1);
+                exp_chunk<PB>(s0, sl2, ms, sum0, sum1);
+                exp_chunk<PB>(s1, sl2, ms, sum0, sum1);
+                store_half<PB>(s_addr, s0, s1);
                 // the stores' latency passes under the next chunk's exponentials
-                exp_chunk<BF16>(s2, sl2, ms, sum0, sum1);
+                exp_chunk<PB>(s2, sl2, ms, sum0, sum1);
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(b_p_half + 16 * t);
                 if (tr) P.trace[(t * 64 + g) * 8 + 1] = clock64();
-                exp_chunk<BF16>(s3, sl2, ms, sum0, sum1);
-                store_half<BF16>(s_addr + 32, s2, s3);
+                exp_chunk<PB>(s3, sl2, ms, sum0, sum1);
+                store_half<PB>(s_addr + 32, s2, s3);
                 tmem_st_wait();
                 l += sum0 + sum1;
                 tc_fence_before();
@@ -1007,21 +1062,31 @@ int launch_prefill_tc(yx_ctx *ctx, const TileArgs &a) {
     P.q_lo = P.bf16 && a.q_dtype == YX_F32;
     P.status = ctx->dev_status;
     P.trace = (long long *)ctx->trace_buf;
+    P.wide_v = a.wide_v;
     if (a.pairs) {
         // Each item names the first of two query heads of one KV head.
         if (!ctx->smem_configured[7]) {
-            if (int rc = check_cuda(ctx, cudaFuncSetAttribute(prefill_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES),
+            if (int rc = check_cuda(ctx, cudaFuncSetAttribute(prefill_tc2_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES),
                                     "prefill_tc2: shared memory attribute"))
                 return rc;
-            if (int rc = check_cuda(ctx, cudaFuncSetAttribute(prefill_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES),
+            if (int rc = check_cuda(ctx, cudaFuncSetAttribute(prefill_tc2_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES),
+                                    "prefill_tc2: shared memory attribute"))
+                return rc;
+            if (int rc = check_cuda(ctx, cudaFuncSetAttribute(prefill_tc2_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES),
                                     "prefill_tc2: shared memory attribute"))
                 return rc;
             ctx->smem_configured[7] = true;
         }
         P.cta_begin = a.cta_begin;
         const int grid = a.n_ctas;   // persistent: at most one CTA per SM
-        if (P.bf16) prefill_tc2_kernel<true><<<grid, T2_THREADS, T2_SMEM_BYTES, ctx->stream>>>(P);
-        else prefill_tc2_kernel<false><<<grid, T2_THREADS, T2_SMEM_BYTES, ctx->stream>>>(P);
+        if (P.bf16) {
+            // Both variants; each reads the cache's flag and the one it does not ask for leaves at once.
+            prefill_tc2_kernel<true, true><<<grid, T2_THREADS_CONVERT, T2_SMEM_BYTES, ctx->stream>>>(P);
+            prefill_tc2_kernel<true, false><<<grid, T2_THREADS, T2_SMEM_BYTES, ctx->stream>>>(P);
+            ctx->launches++;
+        } else {
+            prefill_tc2_kernel<false, false><<<grid, T2_THREADS, T2_SMEM_BYTES, ctx->stream>>>(P);
+        }
     } else {
         prefill_tc_kernel<<<a.n_items, THREADS, SMEM_BYTES, ctx->stream>>>(P);
     }

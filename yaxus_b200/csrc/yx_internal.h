@@ -212,6 +212,10 @@ struct yx_kv {
     char *k_base = nullptr;            // [layer][arena]
     char *v_base = nullptr;
     void *rope_dev = nullptr;          // yx_rope per layer
+    // Set (and never cleared) by the kernels that write V when a bf16 value of magnitude 65536 or
+    // more, or a non-finite one, goes into the cache: such a value does not fit f16, and the tile
+    // kernel then keeps V in bf16 (two MMAs per product) instead of converting it (one).
+    uint32_t *wide_v_dev = nullptr;
     char *k(int layer) const { return k_base + (size_t)layer * layer_bytes; }
     char *v(int layer) const { return v_base + (size_t)layer * layer_bytes; }
 };
@@ -373,6 +377,7 @@ struct TileArgs {
     void *out;
     int out_dtype;
     bool pairs;              // items name the first of two query heads of one KV head
+    const uint32_t *wide_v;  // the cache's "V holds values f16 cannot" flag (device)
 };
 int launch_prefill_tc(yx_ctx *ctx, const TileArgs &a);
 int launch_attend_simt(yx_ctx *ctx, const AttendArgs &a);
