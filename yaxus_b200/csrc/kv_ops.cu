@@ -24,6 +24,9 @@ __device__ __forceinline__ bool bf16_pair_is_wide(uint32_t w) { return (w & 0x7f
 __global__ void append_kernel(const void *__restrict__ k_rows, const void *__restrict__ v_rows, int src_dtype,
                               const uint32_t *__restrict__ kv_slot, uint32_t rows, int hkv, int kv_dtype,
                               char *__restrict__ k_arena, char *__restrict__ v_arena, uint32_t *__restrict__ wide_v) {
+    // The attention kernel that follows is launched as a programmatic dependent: it may be made
+    // resident now, and copies K/V tiles that this kernel does not write while this kernel runs.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
     uint32_t total = rows * (uint32_t)hkv * 16u;
     if (idx >= total) return;
@@ -74,6 +77,7 @@ __global__ void qk_rope_append_kernel(const float *__restrict__ qkv, const float
                                       float eps, const yx_rope *__restrict__ rope, int kv_dtype,
                                       char *__restrict__ k_arena, char *__restrict__ v_arena,
                                       float *__restrict__ q_out, uint32_t *__restrict__ wide_v) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // see append_kernel
     const int heads = hq + 2 * hkv;
     uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     int lane = threadIdx.x & 31;
