@@ -656,7 +656,7 @@ SUB_WORKLOADS = ("prefill", "verify", "single_decode", "long_decode", "long_deco
 def run_cuda(args):
     env = Env()
     warm = max(args.warmup, 3)
-    calls = max(args.steps, MIN_TIMED_CALLS)
+    calls = args.calls if args.calls > 0 else max(args.steps, MIN_TIMED_CALLS)
     head_name = args.workload or "batched_decode"
     if head_name == "prefill":
         head = run_prefill(env, max(1, min(args.steps, 50)), warm, args.kv_dtype or "bf16", check=not args.no_check, e2e=True)
@@ -704,6 +704,8 @@ def main():
     ap.add_argument("--kv-dtype", default=None, choices=["f16", "bf16"],
                     help="cache storage type of the prefill workload (default bf16)")
     ap.add_argument("--headline-only", action="store_true", help="leave the other workloads' records out")
+    ap.add_argument("--calls", type=int, default=0,
+                    help="time exactly this many calls of the headline workload (for profiler captures; default: at least 2000)")
     ap.add_argument("--no-check", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
