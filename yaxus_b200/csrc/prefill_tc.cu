@@ -608,15 +608,11 @@ __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t w) {
 // f16 MMA per K-step; without it a bf16 cache pays two (probabilities as a high and a low bf16
 // part), because 8 bits of mantissa are not enough for them.  bf16 -> f16 is exact for every value
 // below 65536 in magnitude; whether the cache holds anything larger is recorded by the kernels
-// that write V (the cache's `wide_v` flag), both variants are launched, and the one the flag does
-// not ask for leaves at once.
+// that write V (the cache's `wide_v` flag), and the bf16 kernel below picks the variant from it.
 template <bool BF16, bool VCONV>
-__global__ void __launch_bounds__(VCONV ? T2_THREADS_CONVERT : T2_THREADS, 1) prefill_tc2_kernel(const TileParams P) {
+__device__ __forceinline__ void tc2_body(const TileParams P) {
     static_assert(BF16 || !VCONV, "only bf16 pages are converted");
     constexpr bool PB = BF16 && !VCONV;   // probabilities and V go to the tensor core as bf16 (two parts)
-    if constexpr (BF16) {
-        if ((__ldg(P.wide_v) != 0u) == VCONV) return;   // the other variant's launch does this call's work
-    }
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_flag;
@@ -797,6 +793,8 @@ __global__ void __launch_bounds__(VCONV ? T2_THREADS_CONVERT : T2_THREADS, 1) pr
                 }
             }
         }
+    } else if (!VCONV && warp >= T2_CONVERT) {
+        // (the bf16 kernel is launched with the converting variant's twelve warps; here they idle)
     } else if (VCONV && warp >= T2_CONVERT) {
         // ---- V pages, bf16 -> f16 in place, a 64-dim half of the page per warp ------------------
         const uint32_t half = (uint32_t)(warp - T2_CONVERT) * HALF_BYTES;
@@ -1034,6 +1032,25 @@ __global__ void __launch_bounds__(VCONV ? T2_THREADS_CONVERT : T2_THREADS, 1) pr
     }
 }
 
+// f16 caches.
+__global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc2_f16_kernel(const TileParams P) {
+    // Launched as a programmatic dependent of the kernel before it (the append of this pass's rows):
+    // everything that kernel wrote is read only after this wait.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    tc2_body<false, false>(P);
+}
+
+// The two-part variant for bf16 caches, out of line: it is the rare path, and kept apart it does not
+// weigh on the register allocation of the variant that normally runs.
+__device__ __noinline__ void tc2_two_part(const TileParams &P) { tc2_body<true, false>(P); }
+
+// bf16 caches: V pages converted to f16 on the way in, unless the cache holds a value f16 cannot.
+__global__ void __launch_bounds__(T2_THREADS_CONVERT, 1) prefill_tc2_bf16_kernel(const TileParams P) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // (the flag below is the append kernel's to set)
+    if (*(volatile const uint32_t *)P.wide_v != 0u) tc2_two_part(P);
+    else tc2_body<true, true>(P);
+}
+
 }  // namespace
 
 int launch_prefill_tc(yx_ctx *ctx, const TileArgs &a) {
@@ -1066,27 +1083,27 @@ int launch_prefill_tc(yx_ctx *ctx, const TileArgs &a) {
     if (a.pairs) {
         // Each item names the first of two query heads of one KV head.
         if (!ctx->smem_configured[7]) {
-            if (int rc = check_cuda(ctx, cudaFuncSetAttribute(prefill_tc2_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES),
+            if (int rc = check_cuda(ctx, cudaFuncSetAttribute(prefill_tc2_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES),
                                     "prefill_tc2: shared memory attribute"))
                 return rc;
-            if (int rc = check_cuda(ctx, cudaFuncSetAttribute(prefill_tc2_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES),
-                                    "prefill_tc2: shared memory attribute"))
-                return rc;
-            if (int rc = check_cuda(ctx, cudaFuncSetAttribute(prefill_tc2_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES),
+            if (int rc = check_cuda(ctx, cudaFuncSetAttribute(prefill_tc2_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES),
                                     "prefill_tc2: shared memory attribute"))
                 return rc;
             ctx->smem_configured[7] = true;
         }
         P.cta_begin = a.cta_begin;
-        const int grid = a.n_ctas;   // persistent: at most one CTA per SM
-        if (P.bf16) {
-            // Both variants; each reads the cache's flag and the one it does not ask for leaves at once.
-            prefill_tc2_kernel<true, true><<<grid, T2_THREADS_CONVERT, T2_SMEM_BYTES, ctx->stream>>>(P);
-            prefill_tc2_kernel<true, false><<<grid, T2_THREADS, T2_SMEM_BYTES, ctx->stream>>>(P);
-            ctx->launches++;
-        } else {
-            prefill_tc2_kernel<false, false><<<grid, T2_THREADS, T2_SMEM_BYTES, ctx->stream>>>(P);
-        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)a.n_ctas);   // persistent: at most one CTA per SM
+        cfg.blockDim = dim3(P.bf16 ? T2_THREADS_CONVERT : T2_THREADS);
+        cfg.dynamicSmemBytes = T2_SMEM_BYTES;
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t le = P.bf16 ? cudaLaunchKernelEx(&cfg, prefill_tc2_bf16_kernel, P) : cudaLaunchKernelEx(&cfg, prefill_tc2_f16_kernel, P);
+        if (int rc = check_cuda(ctx, le, "prefill_tc2 kernel launch")) return rc;
     } else {
         prefill_tc_kernel<<<a.n_items, THREADS, SMEM_BYTES, ctx->stream>>>(P);
     }
