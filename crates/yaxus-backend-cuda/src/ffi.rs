@@ -63,6 +63,7 @@ pub struct yx_tuning {
     pub fused_merge: i32,
     pub tile_single: i32,
     pub min_piece: i32,
+    pub overlap_calls: i32,
 }
 
 #[repr(C)]

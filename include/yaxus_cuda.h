@@ -77,6 +77,8 @@ typedef struct yx_tuning {
     int32_t fused_merge;     /* 1: the split-key kernel merges the triples itself; 0: a combine kernel does */
     int32_t tile_single;     /* 1: the tcgen05 tile kernel takes one query head per CTA (default: two) */
     int32_t min_piece;       /* fewest 64-key tiles the planner makes an item of when it cuts a run (0: default) */
+    int32_t overlap_calls;   /* 2: an attention call that directly follows another one on the stream waits for it
+                                before it reads anything (0: default, it waits before its first write) */
 } yx_tuning;
 
 /* What the last yx_attend / yx_attention call planned; for tests and benchmarks. */

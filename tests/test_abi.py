@@ -60,7 +60,7 @@ def test_rust_ffi_block_matches_the_header():
 def test_struct_sizes():
     assert ctypes.sizeof(_lib.Rope) == 65 * 4
     assert ctypes.sizeof(_lib.Layer) == 66 * 4
-    assert ctypes.sizeof(_lib.Tuning) == 48
+    assert ctypes.sizeof(_lib.Tuning) == 52
     assert ctypes.sizeof(_lib.PlanInfo) == 48
 
 

@@ -276,6 +276,38 @@ def test_long_context_decode_at_full_size(backend, oracle, window):
     kv.close()
 
 
+@pytest.mark.parametrize("kv_dtype", [F16, BF16])
+def test_back_to_back_calls_each_get_their_own_answer(backend, oracle, kv_dtype):
+    # An attention call that directly follows another one starts reading before the one ahead has
+    # finished and waits only before it writes.  Forty calls in a row, alternating between two
+    # layers (the second holds the first's values negated), two query tensors and four output
+    # buffers: every buffer must hold the answer of the last call that wrote it, and the same bits
+    # as with the overlap switched off.
+    s = W.batched_decode(kv_dtype=kv_dtype)
+    kv = load(backend, s, n_layers=2)
+    backend.write_pages(kv, 1, 0, s.k_bits, s.v_bits ^ np.uint16(0x8000))
+    rng = np.random.default_rng(5)
+    qs = [s.q, rng.standard_normal(s.q.shape).astype(np.float32)]
+    refs = [oracle_step(oracle, s, q=q) for q in qs]
+    results = []
+    for overlap in (0, 2):
+        backend.set_tuning(overlap_calls=overlap)
+        backend.begin_pass(s.meta)
+        backend.kv_append(kv, 0, dev(backend, s.k_new), dev(backend, s.v_new))
+        backend.kv_append(kv, 1, dev(backend, s.k_new), dev(backend, -s.v_new))
+        q_dev = [dev(backend, q) for q in qs]
+        outs = [torch.zeros(s.meta.rows, s.hq * 128, device=backend.device) for _ in range(4)]
+        for i in range(40):
+            backend.attend(kv, i % 2, q_dev[(i // 2) % 2], s.hq, out=outs[i % 4])
+        results.append([backend.to_host(o) for o in outs])
+    backend.set_tuning()
+    for i, got in enumerate(results[0]):      # buffer i was last written by call 36 + i
+        sign = -1.0 if i % 2 else 1.0
+        assert_close(got, sign * refs[(i // 2) % 2], what=f"call {36 + i}")
+        assert np.array_equal(got, results[1][i])
+    kv.close()
+
+
 def test_empty_pass(backend):
     s = W.build("e", 1, 8, 2, F16, [10], [1])
     kv = load(backend, s)

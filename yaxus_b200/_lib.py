@@ -30,7 +30,7 @@ class Layer(ctypes.Structure):
 
 class Tuning(ctypes.Structure):
     _fields_ = [("force_path", c_int32), ("ctas_per_sm", c_int32), ("share_prefix", c_int32),
-                ("tile_min_rows", c_int32), ("cost32", c_int32), ("cost64", c_int32), ("stages", c_int32), ("share_rows", c_int32), ("item_cost", c_int32), ("fused_merge", c_int32), ("tile_single", c_int32), ("min_piece", c_int32)]
+                ("tile_min_rows", c_int32), ("cost32", c_int32), ("cost64", c_int32), ("stages", c_int32), ("share_rows", c_int32), ("item_cost", c_int32), ("fused_merge", c_int32), ("tile_single", c_int32), ("min_piece", c_int32), ("overlap_calls", c_int32)]
 
 
 class PlanInfo(ctypes.Structure):

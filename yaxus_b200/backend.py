@@ -148,9 +148,9 @@ class CudaBackend:
 
     def set_tuning(self, force_path: int = 0, ctas_per_sm: int = 0, share_prefix: int = 0, tile_min_rows: int = 0,
                    cost32: int = 0, cost64: int = 0, stages: int = 0, share_rows: int = 0,
-                   item_cost: int = 0, fused_merge: int = 0, tile_single: int = 0, min_piece: int = 0):
+                   item_cost: int = 0, fused_merge: int = 0, tile_single: int = 0, min_piece: int = 0, overlap_calls: int = 0):
         t = _lib.Tuning(force_path, ctas_per_sm, share_prefix, tile_min_rows, cost32, cost64, stages, share_rows, item_cost,
-                        fused_merge, tile_single, min_piece)
+                        fused_merge, tile_single, min_piece, overlap_calls)
         self._L.yx_set_tuning(self._ctx, ctypes.byref(t))
 
     def hook_skip_merge(self, on: bool) -> None:

@@ -290,8 +290,9 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     pp.min_piece = ctx->tuning.min_piece > 0 ? ctx->tuning.min_piece : (path == 2 ? 2 : 1);
     pp.item_cost = ctx->tuning.item_cost > 0 ? ctx->tuning.item_cost - 1 : (path == 2 ? 14 : 0);
     // (taken before get_plan, whose upload of a new plan is itself an ordering point on the stream)
+    const bool predecessor_is_split_key_call = ctx->last_launch == yx_ctx::LAST_SPLIT_KEY;
     const bool predecessor_wrote_marked_tiles_only =
-        ctx->last_launch == yx_ctx::LAST_ATTEND ||
+        ctx->last_launch == yx_ctx::LAST_ATTEND || ctx->last_launch == yx_ctx::LAST_SPLIT_KEY ||
         (ctx->last_launch == yx_ctx::LAST_APPEND && ctx->last_append_serial == ctx->pass_serial);
     yx_ctx::CachedPlan *cp = nullptr;
     if (int rc = get_plan(ctx, pp, &cp)) return rc;
@@ -344,6 +345,10 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     a.n_stages = ctx->tuning.stages;
     a.early_kv = predecessor_wrote_marked_tiles_only;
     a.fused = ctx->tuning.fused_merge == 1;
+    // (anything this call put on the stream before the kernel - a new plan, a grown buffer, zeroed
+    // counters - is an ordering point of its own and was counted in ctx->launches or reset last_launch)
+    a.late_wait = predecessor_is_split_key_call && ctx->last_launch == yx_ctx::LAST_SPLIT_KEY && !a.fused &&
+                  ctx->tuning.overlap_calls != 2 && !ctx->profiling;
     a.counters = ctx->counters;
     a.out = out;
     a.out_dtype = out_dtype;
@@ -400,7 +405,8 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
                 return rc;
         profile_mark(ctx, 3);
     }
-    if (ctx->launches != launches0) ctx->last_launch = yx_ctx::LAST_ATTEND;
+    if (ctx->launches != launches0)
+        ctx->last_launch = path == 2 && !pl.items.empty() && pl.tile_items.empty() && !a.fused ? yx_ctx::LAST_SPLIT_KEY : yx_ctx::LAST_ATTEND;
     ctx->last_plan = pl.info;
     ctx->last_plan.path = pl.tile_items.empty() ? path : (pl.items.empty() ? 3 : 5);
     ctx->last_plan.launches = (int)(ctx->launches - launches0);

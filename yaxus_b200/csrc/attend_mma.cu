@@ -117,6 +117,7 @@ struct Params {
     int fused;                       // merge in this kernel (arrival counters) or leave it to the combine kernel
     int n_stages;                    // stages of the ring in use (2..STAGES): bytes in flight per SM
     int early_kv;                    // tiles not marked TILE_FRESH may be copied before the grid dependency wait
+    int late_wait;                   // nothing this kernel reads can still be written: only its writers wait
     uint32_t n_items, n_tiles, n_parts;   // sizes of the plan's arrays and of the partial buffers, for the kernel's own checks
     unsigned long long q_bytes;      // size of the query tensor
     int has_prologue;
@@ -229,8 +230,8 @@ __device__ void produce(const Params &P, const Shared &S, const CtaHdr hdr, int 
     I.n_stages = P.n_stages;
     // Until the grid dependency has been waited for, only tiles that the kernel ahead of this one
     // cannot have written are copied; the first marked tile makes the warp wait.
-    bool waited = false;
-    if (!P.early_kv) {
+    bool waited = P.late_wait != 0;
+    if (!P.early_kv && !waited) {
         grid_dependency_wait();
         waited = true;
     }
@@ -245,6 +246,7 @@ __device__ void produce(const Params &P, const Shared &S, const CtaHdr hdr, int 
     const uint32_t skip = P.has_prologue ? min(min((uint32_t)PROLOGUE_TILES, (uint32_t)P.n_stages), hdr.tile_end - hdr.tile_begin) : 0u;
     for (uint32_t j = 0; j < skip && alive; j++) {
         const TileDesc t = P.pro[blockIdx.x].first[j];
+        if (YX_TR(P.trace != nullptr) && lane == 0 && j == 0) P.trace[16 * blockIdx.x + 15] = gtime() + (t.block & 1u);
         gate(t.info);
         alive = issue_tile(I, pipe, t.block, t.info, lane);
         if (YX_TR(P.trace != nullptr) && lane == 0 && j == 0) P.trace[16 * blockIdx.x + 2] = gtime();
@@ -399,6 +401,7 @@ struct Epilogue {
     volatile int *abort_flag;
     int out_dtype, hq, hkv, group;
     int fused;               // count items in and merge here (else a separate combine kernel merges)
+    int late_wait;           // the grid dependency has not been waited for yet: do so before the first store
     uint32_t n_parts;        // slots in the partial buffers
     uint32_t n_items, first_item;    // this warp takes items first_item, first_item + EWARPS, ...
     uint32_t qbase, qempty, merge, efull, eempty, mlbuf;   // shared-space addresses
@@ -564,6 +567,7 @@ __device__ __noinline__ void epilogue_loop(const Epilogue E, int lane) {
     for (uint32_t ii = 0; ii < E.n_items; ii++, phase ^= 1u) {
         const uint32_t qslot = ii & 1u;
         mbar_wait(E.efull, phase, E.abort_flag, E.status, 5);
+        if (ii == 0 && E.late_wait) grid_dependency_wait();   // the merge ahead has read the partial buffers
         const float *scratch = (const float *)__cvta_shared_to_generic((size_t)E.merge);
         const uint32_t *rec = (const uint32_t *)__cvta_shared_to_generic((size_t)(E.qbase + qslot * Q_SLOT_BYTES + Q_ROWS_BYTES));
         const uint32_t head_rows = rec[IR_HEAD_ROWS];
@@ -834,6 +838,7 @@ __device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe 
             // themselves, a share of the queries each, instead of queueing it behind one
             // epilogue warp at the very end of the kernel.
             asm volatile("bar.sync %0, %1;" ::"n"(CONSUMER_BARRIER), "n"(CONSUMERS * 32) : "memory");
+            if (P.late_wait) grid_dependency_wait();   // the merge ahead has read the partial buffers
             const float *scratch = (const float *)__cvta_shared_to_generic((size_t)(S.merge + epipe.stage * MERGE_BYTES));
             merge_queries(scratch, rec, P.part_o, P.part_ml, group, warp, CONSUMERS, lane, P.n_parts, P.status);
             return;
@@ -849,7 +854,7 @@ __device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe 
 }
 
 template <bool BF16>
-__global__ void __maxnreg__(168) attend_mma_kernel(const __grid_constant__ Params P) {
+__global__ void __maxnreg__(152) attend_mma_kernel(const __grid_constant__ Params P) {
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ int abort_flag;
     Shared S;
@@ -867,9 +872,10 @@ __global__ void __maxnreg__(168) attend_mma_kernel(const __grid_constant__ Param
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // The kernels behind this one in the stream (the merge, then the next attention call) may be
-    // made resident from here on; each waits for its own grid dependency before it reads or
-    // writes anything this kernel touches.
-    if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // made resident once every CTA has said so.  The next call's kernel may then read keys, values
+    // and queries without waiting (late_wait), so this is said only when everything ahead of this
+    // kernel is complete: at once if that was true at the launch, else after the wait below.
+    if (P.late_wait && threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     unsigned long long *tr = YX_TR(P.trace != nullptr) ? P.trace + 16 * blockIdx.x : nullptr;
     if (tr && threadIdx.x == 0) tr[0] = gtime();
     const CtaHdr hdr = P.has_prologue ? P.pro[blockIdx.x].hdr : *(const CtaHdr *)(P.cta_hdr + blockIdx.x);
@@ -901,13 +907,18 @@ __global__ void __maxnreg__(168) attend_mma_kernel(const __grid_constant__ Param
         // mbarriers that were not yet initialised.)
         __threadfence_block();
         asm volatile("bar.arrive %0, %1;" ::"n"(SETUP_BARRIER), "n"(THREADS) : "memory");
+        if (tr && lane == 0) tr[14] = gtime();
         produce(P, S, hdr, lane);
         return;
     }
     asm volatile("bar.sync %0, %1;" ::"n"(SETUP_BARRIER), "n"(THREADS) : "memory");
     // Nothing written by earlier kernels (queries, the partial buffers' previous readers) is
-    // touched by these warps before this wait.
-    grid_dependency_wait();
+    // touched by these warps before this wait.  With late_wait the queries are long written, and
+    // the warps that write wait before their first store instead.
+    if (!P.late_wait) {
+        grid_dependency_wait();
+        if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
     if (tr && threadIdx.x == 0) tr[1] = gtime();
 
     if (warp == QWARP) {
@@ -955,6 +966,7 @@ __global__ void __maxnreg__(168) attend_mma_kernel(const __grid_constant__ Param
         E.hkv = P.hkv;
         E.group = P.group;
         E.fused = P.fused;
+        E.late_wait = P.late_wait;
         E.n_parts = P.n_parts;
         E.n_items = hdr.item_end - hdr.item_begin;
         if (!P.fused && E.n_items > 0) E.n_items--;   // the last item is the consumer warps' own
@@ -1034,6 +1046,7 @@ int launch_attend_mma(yx_ctx *ctx, const AttendArgs &a) {
     P.fused = a.fused ? 1 : 0;
     P.n_stages = a.n_stages >= 2 && a.n_stages <= STAGES ? a.n_stages : STAGES;
     P.early_kv = a.early_kv ? 1 : 0;
+    P.late_wait = a.late_wait ? 1 : 0;
     P.n_items = a.plan ? (uint32_t)a.plan->items.size() : 0u;
     P.n_tiles = a.plan ? (uint32_t)a.plan->tiles.size() : 0u;
     P.n_parts = a.plan ? a.plan->n_parts : 0u;

@@ -245,7 +245,10 @@ struct yx_ctx {
     // What this context last put on its stream, for the split-key kernel's early K/V copies: it may
     // copy tiles before waiting for the kernel ahead of it only if that kernel cannot have written
     // them (an append of the current pass writes the marked tiles only; attention kernels write none).
-    enum { LAST_OTHER = 0, LAST_APPEND, LAST_ATTEND, LAST_KV_WRITE };
+    // LAST_SPLIT_KEY is LAST_ATTEND narrowed: the call launched the split-key kernel (and its merge) and
+    // nothing else.  The split-key kernel of the next call may then do all its reading without waiting
+    // (see AttendArgs::late_wait).
+    enum { LAST_OTHER = 0, LAST_APPEND, LAST_ATTEND, LAST_KV_WRITE, LAST_SPLIT_KEY };
     int last_launch = LAST_OTHER;
     uint64_t last_append_serial = 0;
 
@@ -358,6 +361,10 @@ struct AttendArgs {
     const Plan *plan;        // host copy, for what is passed in kernel-parameter space
     int n_stages;            // copy ring depth (0 = default)
     bool early_kv;           // unmarked tiles may be copied before the grid dependency wait
+    bool late_wait;          // the kernels ahead are a split-key attention call of this context and its merge, and
+                             // everything before that call is complete once this kernel runs: keys, values,
+                             // queries and the plan are read at once, and the grid dependency is waited for only
+                             // before the first write (the partial buffers, which the merge ahead still reads)
     bool fused;              // merge inside the split-key kernel
     uint32_t *counters;      // one per (pass row, kv head), zero between launches
     void *out;               // normalised output, or null
