@@ -91,6 +91,7 @@ HOOK_SIGNATURES = {
     "yx_hook_skip_merge": (c_int, [c_void_p, c_int]),
     "yx_hook_expire_wait": (c_int, [c_void_p, c_uint64]),
     "yx_hook_set_trace": (c_int, [c_void_p, c_void_p]),
+    "yx_hook_host_times": (c_int, [c_void_p, POINTER(ctypes.c_double), c_int]),
 }
 
 HOST_SIGNATURES = {

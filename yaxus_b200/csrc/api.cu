@@ -155,6 +155,7 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
             slot = &ctx->plans.back();
         }
     }
+    host_clock_lap(ctx, 0);
     try {
         build_split_plan(ctx->pass, pp, slot->plan);
     } catch (const std::string &msg) {
@@ -164,6 +165,7 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
         slot->pass_serial = 0;
         return fail(ctx, YX_ERR_OOM, "attention plan: out of host memory");
     }
+    host_clock_lap(ctx, 1);
     slot->pass_serial = ctx->pass_serial;
     slot->hkv = pp.hkv;
     slot->group = pp.group;
@@ -190,7 +192,11 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
     const size_t mer_b = pad16(pl.merges.size() * sizeof(Merge));
     const size_t hdr_b = pad16(pl.cta_hdr.size() * sizeof(CtaHdr));
     const size_t til_b = pad16(pl.tiles.size() * sizeof(TileDesc));
-    const size_t rec_b = pp.resolve ? pl.items.size() * sizeof(ItemRec) : 0;   // (the array may be longer: capacity kept)
+    // Item records go up packed: only the words that the item with the most rows uses, each.
+    int most_rows = 1;
+    for (const Item &it : pl.items) most_rows = std::max(most_rows, (int)it.n_rows);
+    const size_t rec_stride = pad16((size_t)(IR_ROW0 + IR_ROW_WORDS * most_rows) * 4);
+    const size_t rec_b = pp.resolve ? pl.items.size() * rec_stride : 0;
     const size_t tit_b = pl.tile_items.size() * sizeof(TileItem);
     const size_t tcb_b = pad16(pl.tile_cta_begin.size() * sizeof(uint32_t));
     const size_t total = items_b + cta_b + mer_b + hdr_b + til_b + rec_b + tit_b + tcb_b;
@@ -217,19 +223,26 @@ int get_plan(yx_ctx *ctx, const PlanParams &pp, yx_ctx::CachedPlan **out) {
     const size_t o_mer = put(pl.merges.data(), pl.merges.size() * sizeof(Merge), mer_b);
     const size_t o_hdr = put(pl.cta_hdr.data(), pl.cta_hdr.size() * sizeof(CtaHdr), hdr_b);
     const size_t o_til = put(pl.tiles.data(), pl.tiles.size() * sizeof(TileDesc), til_b);
-    const size_t o_rec = put(pl.recs.data(), rec_b, rec_b);
+    const size_t o_rec = at;
+    if (rec_b) {
+        for (size_t i = 0; i < pl.items.size(); i++) memcpy(blob + at + i * rec_stride, pl.recs[i].w, rec_stride);
+        at += rec_b;
+    }
     const size_t o_tit = put(pl.tile_items.data(), tit_b, tit_b);
     const size_t o_tcb = put(pl.tile_cta_begin.data(), pl.tile_cta_begin.size() * sizeof(uint32_t), tcb_b);
+    host_clock_lap(ctx, 2);
     if (int rc = total > 0 ? stage_commit(ctx, slot->dev, total) : YX_OK) {
         slot->pass_serial = 0;
         return rc;
     }
+    host_clock_lap(ctx, 3);
     slot->d_items = (Item *)(slot->dev + o_items);
     slot->d_cta_begin = (uint32_t *)(slot->dev + o_cta);
     slot->d_merges = (Merge *)(slot->dev + o_mer);
     slot->d_cta_hdr = (CtaHdr *)(slot->dev + o_hdr);
     slot->d_tiles = (TileDesc *)(slot->dev + o_til);
-    slot->d_recs = (ItemRec *)(slot->dev + o_rec);
+    slot->d_recs = slot->dev + o_rec;
+    slot->rec_stride = (uint32_t)rec_stride;
     slot->d_tile_items = (TileItem *)(slot->dev + o_tit);
     slot->d_tile_cta_begin = (uint32_t *)(slot->dev + o_tcb);
     *out = slot;
@@ -243,10 +256,19 @@ int pick_path(const yx_ctx *ctx, const yx_kv *kv) {
     return 2;
 }
 
-// Shared body of yx_attend / yx_attend_partial: split-key kernel, then the merge.
+// What yx_attention does to the step's rows before it attends: norm, RoPE, append, queries to `q`.
+struct RopeAppend {
+    const float *qkv, *q_norm, *k_norm;
+    float eps;
+};
+
+// Shared body of yx_attend / yx_attend_partial / yx_attention: (the rows' norm, RoPE and append,)
+// the split-key kernel, then the merge.  With `pre`, the plan is made and uploaded first and the
+// three kernels follow one another on the stream with no copy between them: the attention kernel
+// is then a programmatic dependent of the append and starts its copies beside it.
 int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, int hq, int64_t window,
                 uint64_t key_lo, uint64_t key_hi, void *out, int out_dtype, float *m_out, float *l_out,
-                float *o_out) {
+                float *o_out, const RopeAppend *pre = nullptr) {
     if (!ctx || !kv) return YX_ERR_INVALID;
     if (ctx->status != YX_OK) return ctx->status;
     if (!ctx->have_pass) return fail(ctx, YX_ERR_STATE, "attention without begin_pass");
@@ -318,6 +340,17 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
         }
     }
 
+    bool early_kv = predecessor_wrote_marked_tiles_only;
+    if (pre) {
+        // write_rows, then attend (cpu lib.rs:526-529): all rows' K/V land before any row attends.
+        if (int rc = launch_qk_rope_append(ctx, kv, layer, pre->qkv, pre->q_norm, pre->k_norm, hq, pre->eps, (float *)q))
+            return rc;
+        host_clock_lap(ctx, 4);
+        ctx->last_launch = yx_ctx::LAST_APPEND;
+        ctx->last_append_serial = ctx->pass_serial;
+        early_kv = true;   // an append of this pass writes marked tiles only
+    }
+
     AttendArgs a{};
     a.rows = ctx->pass.rows;
     a.q = q;
@@ -340,10 +373,11 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     a.cta_hdr = cp->d_cta_hdr;
     a.tiles = cp->d_tiles;
     a.recs = cp->d_recs;
+    a.rec_stride = cp->rec_stride;
     a.single_use = pl.single_use;
     a.plan = &pl;
     a.n_stages = ctx->tuning.stages;
-    a.early_kv = predecessor_wrote_marked_tiles_only;
+    a.early_kv = early_kv;
     a.fused = ctx->tuning.fused_merge == 1;
     // (anything this call put on the stream before the kernel - a new plan, a grown buffer, zeroed
     // counters - is an ordering point of its own and was counted in ctx->launches or reset last_launch)
@@ -356,6 +390,7 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     a.l_out = l_out;
     a.o_out = o_out;
     profile_mark(ctx, 0);
+    host_clock_lap(ctx, 0);
     if (!pl.tile_items.empty()) {
         TileArgs t{};
         t.q = q;
@@ -387,12 +422,14 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
             if (int rc = launch_fill_empty(ctx, (size_t)ctx->pass.rows * hq, m_out, l_out, o_out)) return rc;
         if (!pl.items.empty())
             if (int rc = launch_attend_mma(ctx, a)) return rc;
+        host_clock_lap(ctx, 5);
         profile_mark(ctx, 1);
         profile_mark(ctx, 2);
         if (!a.fused && need_combine)
             if (int rc = launch_combine(ctx, cp->d_merges, ctx->ws_o, ctx->ws_ml, (int)ctx->pass.rows, hq, group, out,
                                         out_dtype, m_out, l_out, o_out))
                 return rc;
+        host_clock_lap(ctx, 6);
         profile_mark(ctx, 3);
     } else {
         if (!pl.items.empty())
@@ -772,17 +809,13 @@ int yx_attention(yx_ctx *ctx, yx_kv *kv, int layer, const float *qkv, const floa
     if (ctx->pass.rows == 0) return YX_OK;
     if (!qkv || !q_norm || !k_norm || !out) return fail(ctx, YX_ERR_INVALID, "null tensor");
     if (ctx->pass.max_slot_seen / PAGE >= kv->pages) return fail(ctx, YX_ERR_INVALID, "kv_slot outside the KV arena");
+    host_clock_start(ctx);
     DeviceGuard guard(ctx->device);
     size_t q_bytes = (size_t)ctx->pass.rows * hq * D * sizeof(float);
     if (int rc = ensure_buffer(ctx, (void **)&ctx->q_tmp, &ctx->q_tmp_cap, q_bytes)) return rc;
-    // write_rows, then attend (cpu lib.rs:526-529): all rows' K/V land before any row attends.
-    if (int rc = launch_qk_rope_append(ctx, kv, layer, qkv, q_norm, k_norm, hq, eps, ctx->q_tmp)) return rc;
-    ctx->last_launch = yx_ctx::LAST_APPEND;
-    ctx->last_append_serial = ctx->pass_serial;
-    int64_t launches0 = ctx->launches - 1;
-    int rc = attend_impl(ctx, kv, layer, ctx->q_tmp, YX_F32, hq, -1, 0, UINT64_MAX, out, YX_F32, nullptr, nullptr, nullptr);
-    ctx->last_plan.launches = (int)(ctx->launches - launches0);
-    return rc;
+    host_clock_lap(ctx, 0);
+    const RopeAppend pre{qkv, q_norm, k_norm, eps};
+    return attend_impl(ctx, kv, layer, ctx->q_tmp, YX_F32, hq, -1, 0, UINT64_MAX, out, YX_F32, nullptr, nullptr, nullptr, &pre);
 }
 
 int yx_lse_combine(yx_ctx *ctx, int n_parts, const float *m, const float *l, const float *o, size_t n, void *out,

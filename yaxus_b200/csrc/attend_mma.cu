@@ -34,9 +34,21 @@
 //    or, when asked for, this kernel's own: the CTA that delivers the last triple of a
 //    (row, KV head) merges them and writes the output, found by an arrival counter in global
 //    scratch that the merging CTA resets.
-//  * 168 registers per thread and eleven warps: 352 x 168 leaves room in the register file for a
-//    CTA of the merge kernel (128 threads x 48) beside this one, which is what lets the merge
-//    kernel and, behind it, the next attention call be resident before this call has finished.
+//  * When the kernels ahead on the stream are another split-key call of the same context and its
+//    merge (a decode loop over layers with nothing between the calls), keys, values, queries
+//    and the plan are all long written: the kernel then reads at once and waits for the grid
+//    dependency only before its first write, of the partial buffers the merge ahead still
+//    reads.  Calls then overlap SM by SM: a CTA starts when the CTA of the call before leaves
+//    its SM, and the merge runs beside it.  A kernel says "launch my dependents" only once
+//    everything ahead of it is complete (at its top in this mode, after its wait otherwise), which
+//    is what makes the early reads of the call behind it safe.
+//  * 152 registers per thread and eleven warps.  The register file is four partitions of 16384;
+//    a partition holds three of this CTA's warps (3 x 152 x 32 = 14592), which leaves 1792: one
+//    warp of the merge kernel (48 x 32 = 1536).  So a CTA of the merge kernel (four warps, one per
+//    partition) is resident beside this one, and the merge kernel and, behind it, the next
+//    attention call are resident before this call has finished.  At 168 registers the sum over the
+//    SM still fits but no partition has room, and the merge CTAs then wait for these CTAs to leave
+//    and keep the next call's CTAs out in their turn (measured: 23.3 us a call against 20.1).
 //
 // Every wait on an mbarrier is bounded: on expiry the CTA records the failure in the
 // context's status word, stops waiting anywhere, waits (bounded) for the copies it has in
@@ -105,7 +117,8 @@ struct Params {
     uint32_t n_blocks;               // (page, kv head) blocks in an arena
     const CtaHdr *cta_hdr;
     const TileDesc *tiles;
-    const ItemRec *recs;
+    const char *recs;                // item records, rec_stride bytes apart
+    uint32_t rec_stride;
     int single_use;
     float *part_o, *part_ml;
     uint32_t *counters;
@@ -281,7 +294,8 @@ __device__ void produce(const Params &P, const Shared &S, const CtaHdr hdr, int 
 // nothing after it - and the consumers waited for their queries until the wait ran out.)
 struct QStage {
     const char *q;
-    const ItemRec *recs;
+    const char *recs;
+    uint32_t rec_stride;
     yx_dev_status *status;
     int hq, group;
     uint32_t row_bytes, stride;           // of one query row in global and in shared memory
@@ -313,7 +327,7 @@ __device__ __forceinline__ void stage_queries(const QStage &A, int lane) {
             head_rows = 0;
             return;
         }
-        const uint32_t *rec = A.recs[ii].w;
+        const uint32_t *rec = (const uint32_t *)(A.recs + (size_t)ii * A.rec_stride);
         head_rows = __ldg(rec + IR_HEAD_ROWS);
 #pragma unroll
         for (int h = 0; h < 2; h++) {
@@ -360,15 +374,15 @@ __device__ __forceinline__ void stage_queries(const QStage &A, int lane) {
         }
         const uint32_t n_ok = __popc(__ballot_sync(0xffffffffu, ok[0])) + __popc(__ballot_sync(0xffffffffu, ok[1]));
         if (!rec_ok && lane == 0) record_bad_index(A.status, 303, ii, A.n_items);
-        if (lane == 0) mbar_expect_tx(bar, n_ok * A.row_bytes + (rec_ok ? (uint32_t)sizeof(ItemRec) : 0u));
+        if (lane == 0) mbar_expect_tx(bar, n_ok * A.row_bytes + (rec_ok ? A.rec_stride : 0u));
         __syncwarp();
 #pragma unroll
         for (int h = 0; h < 2; h++)
             if (ok[h]) bulk_g2s(slot + (uint32_t)(32 * h + lane) * A.stride, A.q + elem[h] * A.row_bytes, A.row_bytes, bar);
-        if (lane == 0 && rec_ok) bulk_g2s(slot + Q_ROWS_BYTES, A.recs + ii, (uint32_t)sizeof(ItemRec), bar);
+        if (lane == 0 && rec_ok) bulk_g2s(slot + Q_ROWS_BYTES, A.recs + (size_t)ii * A.rec_stride, A.rec_stride, bar);
         if (YX_TR(A.trace != nullptr) && lane == 0 && ii == A.item_begin) {
             A.trace[10] = gtime();
-            A.trace[11] = ((unsigned long long)n_ok << 32) | (unsigned long long)(n_ok * A.row_bytes + (rec_ok ? 512u : 0u));
+            A.trace[11] = ((unsigned long long)n_ok << 32) | (unsigned long long)(n_ok * A.row_bytes + (rec_ok ? A.rec_stride : 0u));
             A.trace[12] = ((unsigned long long)head_rows << 32) | bar;
             A.trace[13] = (unsigned long long)(uintptr_t)(A.q + elem[0] * A.row_bytes);
         }
@@ -392,7 +406,6 @@ __device__ __forceinline__ void stage_queries(const QStage &A, int lane) {
 //     `attn_combine`, crates/yaxus-backend-gpu/src/shaders.rs:1581-1637), writes the output
 //     and resets the counter.
 struct Epilogue {
-    const ItemRec *recs;     // not used for reading rows: the staged slot holds the record
     float *part_o, *part_ml;
     uint32_t *counters;
     void *out;
@@ -925,6 +938,7 @@ __global__ void __maxnreg__(152) attend_mma_kernel(const __grid_constant__ Param
         QStage A;
         A.q = (const char *)P.q;
         A.recs = P.recs;
+        A.rec_stride = P.rec_stride;
         A.status = P.status;
         A.hq = P.hq;
         A.group = P.group;
@@ -951,7 +965,6 @@ __global__ void __maxnreg__(152) attend_mma_kernel(const __grid_constant__ Param
     }
     if (warp >= EWARP) {
         Epilogue E;
-        E.recs = P.recs;
         E.part_o = P.part_o;
         E.part_ml = P.part_ml;
         E.counters = P.counters;
@@ -1031,6 +1044,7 @@ int launch_attend_mma(yx_ctx *ctx, const AttendArgs &a) {
     P.cta_hdr = a.cta_hdr;
     P.tiles = a.tiles;
     P.recs = a.recs;
+    P.rec_stride = a.rec_stride;
     P.single_use = a.single_use ? 1 : 0;
     P.part_o = a.part_o;
     P.part_ml = a.part_ml;

@@ -38,10 +38,11 @@ __global__ void __launch_bounds__(128) combine_kernel(const Merge *__restrict__ 
     int h = (int)(idx % (uint32_t)hq), kvh = h / group, g = h % group;
     Merge mg = merges[(size_t)row * (hq / group) + kvh];   // host-written: not the split-key kernel's output
     // Launched as a programmatic dependent of the split-key kernel: it is resident beside that
-    // kernel's CTAs (48 registers a thread: a CTA fits in what the split-key kernel leaves of
-    // the register file) long before they finish.  The kernel behind this one, usually the next
-    // attention call, may be made resident in turn.  The triples are read only after the whole
-    // grid before this one is complete and its writes are visible.
+    // kernel's CTAs (four warps of 48 registers a thread: one warp fits in what three warps of the
+    // split-key kernel leave of each register file partition) long before they finish.  The
+    // kernel behind this one, usually the next attention call, may be made resident in turn.  The
+    // triples are read only after the whole grid before this one is complete and its writes are
+    // visible.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (mg.count == 0 && !o_out) return;   // the row was another kernel's (tiled path)

@@ -174,6 +174,33 @@ extern "C" int yx_hook_expire_wait(yx_ctx *ctx, uint64_t limit_cycles) {
     return rc;
 }
 
+#ifdef YX_TRACE
+#include <chrono>
+static int64_t host_now_ns() {
+    return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+void host_clock_start(yx_ctx *ctx) { ctx->host_mark = host_now_ns(); }
+void host_clock_lap(yx_ctx *ctx, int phase) {
+    const int64_t now = host_now_ns();
+    ctx->host_ns[phase & 7] += (double)(now - ctx->host_mark);
+    ctx->host_mark = now;
+}
+#endif
+
+extern "C" int yx_hook_host_times(yx_ctx *ctx, double *out8, int reset) {
+    if (!ctx || !out8) return YX_ERR_INVALID;
+#ifdef YX_TRACE
+    for (int i = 0; i < 8; i++) {
+        out8[i] = ctx->host_ns[i];
+        if (reset) ctx->host_ns[i] = 0.0;
+    }
+    return YX_OK;
+#else
+    (void)reset;
+    return YX_ERR_UNSUPPORTED;
+#endif
+}
+
 extern "C" int yx_hook_set_trace(yx_ctx *ctx, void *dev_buf) {
     if (!ctx) return YX_ERR_INVALID;
 #ifdef YX_TRACE

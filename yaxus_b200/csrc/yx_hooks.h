@@ -53,6 +53,12 @@ int yx_hook_expire_wait(yx_ctx *ctx, uint64_t limit_cycles);
  * YX_ERR_UNSUPPORTED. */
 int yx_hook_set_trace(yx_ctx *ctx, void *dev_buf);
 
+/* Host time the context has spent in the phases of its attention calls since the last reset, in
+ * nanoseconds: [0] checks, [1] planning, [2] laying the plan out in its staging buffer, [3] the
+ * upload call, [4] the append launch, [5] the attention kernel launches, [6] the merge launch.
+ * Measured only by a library built with -DYX_TRACE; otherwise YX_ERR_UNSUPPORTED. */
+int yx_hook_host_times(yx_ctx *ctx, double *out8, int reset);
+
 #ifdef __cplusplus
 }
 #endif

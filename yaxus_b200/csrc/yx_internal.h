@@ -96,7 +96,8 @@ struct TileDesc {
 constexpr uint32_t TILE_REUSED = 1u << 16;
 constexpr uint32_t TILE_FRESH = 1u << 17;
 
-// An item as the kernel reads it: 128 words, fetched by a warp with four coalesced loads.
+// An item as the kernel reads it: a header and six words per pass row.  On the device the records
+// are packed at the size of the plan's longest one (rounded up to 16 bytes, one bulk copy each).
 struct alignas(16) ItemRec {
     uint32_t w[128];
 };
@@ -104,7 +105,7 @@ constexpr int IR_TILES = 0;       // tiles of the item
 constexpr int IR_KEY0 = 1;        // logical position of the first tile's first key
 constexpr int IR_HEAD_ROWS = 2;   // kv_head | n_rows << 16
 constexpr int IR_MT = 3;          // padded query rows: 16, 32, 64
-constexpr int IR_ROW0 = 32;       // then six words per pass row:
+constexpr int IR_ROW0 = 4;        // then six words per pass row:
 constexpr int IR_ROW_WORDS = 6;   //   first key seen, last key seen, partial slot, pass row, first slot, slots
 constexpr int IRR_KLO = 0, IRR_KHI = 1, IRR_PART = 2, IRR_ROW = 3, IRR_FIRST = 4, IRR_COUNT = 5;
 
@@ -229,6 +230,15 @@ struct yx_dev_status {
 
 struct ncclComm;
 
+struct yx_ctx;
+#ifdef YX_TRACE
+void host_clock_start(yx_ctx *ctx);
+void host_clock_lap(yx_ctx *ctx, int phase);   // adds the time since the last start or lap to host_ns[phase]
+#else
+inline void host_clock_start(yx_ctx *) {}
+inline void host_clock_lap(yx_ctx *, int) {}
+#endif
+
 struct yx_ctx {
     int device = 0;
     int sm_count = 0;
@@ -241,6 +251,11 @@ struct yx_ctx {
     int64_t launches = 0;
     bool smem_configured[8] = {};          // per-kernel opt-in to large dynamic shared memory
     void *trace_buf = nullptr;             // device buffer for per-CTA kernel timestamps (builds with -DYX_TRACE)
+    // Host time spent in the phases of an attention call, in ns (builds with -DYX_TRACE): 0 pass checks,
+    // 1 planning, 2 laying the plan out in the staging buffer, 3 its upload call, 4 the append launch,
+    // 5 the attention kernel launches, 6 the merge launch.
+    double host_ns[8] = {};
+    int64_t host_mark = 0;
     bool skip_merge = false;               // measurement hook: leave the merge of the triples out
     // What this context last put on its stream, for the split-key kernel's early K/V copies: it may
     // copy tiles before waiting for the kernel ahead of it only if that kernel cannot have written
@@ -293,7 +308,8 @@ struct yx_ctx {
         yx::Merge *d_merges = nullptr;
         yx::CtaHdr *d_cta_hdr = nullptr;
         yx::TileDesc *d_tiles = nullptr;
-        yx::ItemRec *d_recs = nullptr;
+        const char *d_recs = nullptr;   // records packed at rec_stride bytes each
+        uint32_t rec_stride = 0;
         yx::TileItem *d_tile_items = nullptr;
         uint32_t *d_tile_cta_begin = nullptr;
         int tile_min_rows = 0;
@@ -356,7 +372,8 @@ struct AttendArgs {
     // resolved plan and fused merge (tensor kernel)
     const CtaHdr *cta_hdr;
     const TileDesc *tiles;
-    const ItemRec *recs;
+    const char *recs;        // item records, rec_stride bytes apart (only the words the items' rows use are uploaded)
+    uint32_t rec_stride;
     bool single_use;
     const Plan *plan;        // host copy, for what is passed in kernel-parameter space
     int n_stages;            // copy ring depth (0 = default)
