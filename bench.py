@@ -677,7 +677,7 @@ def run_cuda(args):
                     s = long_s if name == "long_decode" else dataclasses.replace(long_s, window=2048)
                     rec = run_split_key(env, name, s, 300, warm, check=not args.no_check)
                 else:
-                    rec = run_split_key(env, name, make_scenario(name, env.rank), 500, warm, check=not args.no_check)
+                    rec = run_split_key(env, name, make_scenario(name, env.rank), 500, warm, check=not args.no_check, kernel_only=True)
             except AssertionError as e:     # a parity failure is reported, not hidden
                 rec = {"error": str(e)[:300]} if env.rank == 0 else None
             if rec is not None:

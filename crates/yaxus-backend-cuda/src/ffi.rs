@@ -120,6 +120,16 @@ extern "C" {
     pub fn yx_comm_create(ctx: *mut yx_ctx, n_ranks: c_int, rank: c_int, id128: *const c_void) -> c_int;
     pub fn yx_comm_destroy(ctx: *mut yx_ctx) -> c_int;
     pub fn yx_attend_allgather(ctx: *mut yx_ctx, kv: *mut yx_kv, layer: c_int, q_dev: *const c_void, q_dtype: c_int, hq: c_int, window: i64, key_lo: u64, key_hi: u64, out_dev: *mut c_void, out_dtype: c_int) -> c_int;
+    // ---- the other operators of the Backend trait
+    pub fn yx_embed(ctx: *mut yx_ctx, table_bf16_dev: *const c_void, vocab: u32, h: u32, ids_host: *const u32, rows: u32, out_dev: *mut f32) -> c_int;
+    pub fn yx_rmsnorm(ctx: *mut yx_ctx, x_dev: *const f32, w_dev: *const f32, rows: u32, cols: u32, offset: f32, eps: f32, out_dev: *mut f32) -> c_int;
+    pub fn yx_add_norm(ctx: *mut yx_ctx, x_dev: *mut f32, delta_dev: *const f32, post_w_dev: *const f32, post_offset: f32, pre_w_dev: *const f32, pre_offset: f32, eps: f32, rows: u32, cols: u32, out_dev: *mut f32) -> c_int;
+    pub fn yx_matmul(ctx: *mut yx_ctx, x_dev: *const f32, w_bf16_dev: *const c_void, rows: u32, n: u32, k: u32, out_dev: *mut f32) -> c_int;
+    pub fn yx_matmul_glu(ctx: *mut yx_ctx, x_dev: *const f32, w_bf16_dev: *const c_void, rows: u32, n: u32, k: u32, out_dev: *mut f32) -> c_int;
+    pub fn yx_swiglu(ctx: *mut yx_ctx, x_dev: *const f32, rows: u32, inner: u32, out_dev: *mut f32) -> c_int;
+    pub fn yx_add_assign(ctx: *mut yx_ctx, a_dev: *mut f32, b_dev: *const f32, n: usize) -> c_int;
+    pub fn yx_select_rows(ctx: *mut yx_ctx, x_dev: *const f32, src_rows: u32, cols: u32, rows_host: *const u32, n: u32, out_dev: *mut f32) -> c_int;
+    pub fn yx_argmax_rows(ctx: *mut yx_ctx, logits_dev: *const f32, rows: u32, cols: u32, out_host: *mut u32) -> c_int;
     // ---- attention without allocation
     pub fn yx_attend_static(ctx: *mut yx_ctx, kv: *mut yx_kv, layer: c_int, q_dev: *const c_void, q_dtype: c_int, hq: c_int, window: i64, out_dev: *mut c_void, out_dtype: c_int) -> c_int;
 }

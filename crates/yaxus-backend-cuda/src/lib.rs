@@ -3,14 +3,11 @@
 //! `CudaBackend`: yaxus's `Backend` (crates/yaxus-model/src/lib.rs:95-171) and `SyncReadback`
 //! (:177-185) over libyaxus_cuda, for NVIDIA B200 (sm_100a).
 //!
-//! What is real here is the attention path: `new_kv`, `copy_page`, `begin_pass`, `attention`
-//! and the read-back (`to_host`), each a thin call into the C ABI (`ffi.rs`), with the error
-//! behaviour the trait prescribes: `attention`, `copy_page` and `begin_pass` cannot fail by
-//! signature, so the library keeps the first error and the next read-back reports it, which is
-//! where the reference surfaces a lost device too (crates/yaxus-model/src/lib.rs:187-197).
-//! The methods outside that path (`embed`, `rmsnorm`, `matmul`, ...) are `todo!()` with the
-//! trait's signatures: `Model<CudaBackend>` type-checks against this file, and does not run
-//! until they are written (cuBLASLt for `matmul`, a few elementwise kernels for the rest).
+//! Every method is a thin call into the C ABI (`ffi.rs`), with the error behaviour the trait
+//! prescribes: the operators cannot fail by signature, so the library keeps the first error and
+//! the next read-back reports it, which is where the reference surfaces a lost device too
+//! (crates/yaxus-model/src/lib.rs:187-197).  Weights are taken as bf16 (`Quant::Bf16`); the
+//! reference's quantised formats are refused at load.
 //!
 //! The page tables, the page allocator and prefix sharing stay in yaxus-model
 //! (crates/yaxus-model/src/kv.rs); they reach the library only as `PassMeta` arrays and
@@ -161,22 +158,27 @@ impl Backend for CudaBackend {
         self.weight_bytes
     }
 
-    /// Vectors (the q/k norm weights this path needs) are uploaded as f32.  Matrices belong
-    /// to `matmul`, which is not written.
-    fn load_weight(&mut self, t: &TensorRef, _quant: Quant) -> Result<Weight> {
-        if t.shape.len() != 1 {
-            todo!("2-D weights: bf16 / quantized layouts for a cuBLASLt matmul");
+    /// Vectors are uploaded as f32 (the library's norm entries take f32, like the GPU backend's
+    /// `Weight::Vector`); matrices and the embedding table as the bf16 the file holds
+    /// (cpu lib.rs:455-462).  Quantised formats are the reference's other backends' business.
+    fn load_weight(&mut self, t: &TensorRef, quant: Quant) -> Result<Weight> {
+        if t.shape.len() != 1 && !matches!(quant, Quant::Bf16) {
+            bail!("the CUDA backend takes bf16 weights only (asked for {quant:?})");
         }
-        let v = t.to_f32_vec()?;
-        let bytes = v.len() * 4;
+        let host: Vec<u8> = if t.shape.len() == 1 {
+            t.to_f32_vec()?.iter().flat_map(|v| v.to_le_bytes()).collect()
+        } else {
+            t.to_bf16_vec().iter().flat_map(|v| v.to_le_bytes()).collect()
+        };
+        let bytes = host.len();
         let mut ptr = std::ptr::null_mut();
         let ctx = self.ctx.lock().unwrap();
         let rc = unsafe { ffi::yx_tensor_alloc(ctx.0, bytes, &mut ptr) };
         if rc != ffi::YX_OK {
             bail!("load_weight: {}", last_error(&ctx));
         }
-        // Pageable source: the copy is synchronous with respect to the host.
-        let rc = unsafe { ffi::yx_upload(ctx.0, ptr, v.as_ptr() as *const c_void, bytes) };
+        // Pageable source: the library copies it into its pinned ring before the call returns.
+        let rc = unsafe { ffi::yx_upload(ctx.0, ptr, host.as_ptr() as *const c_void, bytes) };
         if rc != ffi::YX_OK || unsafe { ffi::yx_sync(ctx.0) } != ffi::YX_OK {
             bail!("load_weight: {}", last_error(&ctx));
         }
@@ -254,16 +256,66 @@ impl Backend for CudaBackend {
         };
     }
 
-    fn embed(&mut self, _table: &Weight) -> Tensor {
-        todo!("gather of the pass's token ids from the embedding table")
+    /// crates/yaxus-model/src/lib.rs:125.
+    fn embed(&mut self, table: &Weight) -> Tensor {
+        let (vocab, h) = (table.shape[0], table.shape[1]);
+        let out = self.alloc(self.ids.len(), h);
+        let ctx = self.ctx.lock().unwrap();
+        unsafe { ffi::yx_embed(ctx.0, table.ptr, vocab as u32, h as u32, self.ids.as_ptr(), self.ids.len() as u32, out.ptr as *mut f32) };
+        drop(ctx);
+        out
     }
 
-    fn rmsnorm(&mut self, _x: &Tensor, _w: &Weight, _offset: f32, _eps: f32) -> Tensor {
-        todo!("row-wise RMSNorm kernel")
+    /// crates/yaxus-model/src/lib.rs:126.
+    fn rmsnorm(&mut self, x: &Tensor, w: &Weight, offset: f32, eps: f32) -> Tensor {
+        let out = self.alloc(x.rows, x.cols);
+        let ctx = self.ctx.lock().unwrap();
+        unsafe { ffi::yx_rmsnorm(ctx.0, x.ptr as *const f32, w.ptr as *const f32, x.rows as u32, x.cols as u32, offset, eps, out.ptr as *mut f32) };
+        drop(ctx);
+        out
     }
 
-    fn matmul(&mut self, _x: &Tensor, _w: &Weight) -> Tensor {
-        todo!("cuBLASLt bf16 GEMM")
+    /// crates/yaxus-model/src/lib.rs:128: `x [T, K] . w[N, K]^T -> [T, N]`.
+    fn matmul(&mut self, x: &Tensor, w: &Weight) -> Tensor {
+        assert_eq!(x.cols, w.shape[1], "matmul inner dim"); // as the CPU backend asserts (cpu lib.rs:316)
+        let out = self.alloc(x.rows, w.shape[0]);
+        let ctx = self.ctx.lock().unwrap();
+        unsafe { ffi::yx_matmul(ctx.0, x.ptr as *const f32, w.ptr, x.rows as u32, w.shape[0] as u32, w.shape[1] as u32, out.ptr as *mut f32) };
+        drop(ctx);
+        out
+    }
+
+    /// crates/yaxus-model/src/lib.rs:164-168, one call instead of the default's two.
+    fn matmul_glu(&mut self, x: &Tensor, w: &Weight) -> Tensor {
+        assert_eq!(x.cols, w.shape[1], "matmul inner dim");
+        let out = self.alloc(x.rows, w.shape[0] / 2);
+        let ctx = self.ctx.lock().unwrap();
+        unsafe { ffi::yx_matmul_glu(ctx.0, x.ptr as *const f32, w.ptr, x.rows as u32, w.shape[0] as u32, w.shape[1] as u32, out.ptr as *mut f32) };
+        drop(ctx);
+        out
+    }
+
+    /// crates/yaxus-model/src/lib.rs:149-162, one kernel instead of the default's three.
+    fn add_norm(&mut self, x: &mut Tensor, delta: &Tensor, post_w: &Weight, post_offset: f32, pre_w: &Weight, pre_offset: f32, eps: f32) -> Tensor {
+        let out = self.alloc(x.rows, x.cols);
+        let ctx = self.ctx.lock().unwrap();
+        unsafe {
+            ffi::yx_add_norm(
+                ctx.0,
+                x.ptr as *mut f32,
+                delta.ptr as *const f32,
+                post_w.ptr as *const f32,
+                post_offset,
+                pre_w.ptr as *const f32,
+                pre_offset,
+                eps,
+                x.rows as u32,
+                x.cols as u32,
+                out.ptr as *mut f32,
+            )
+        };
+        drop(ctx);
+        out
     }
 
     /// crates/yaxus-model/src/lib.rs:132-140: per-head q/k RMSNorm and RoPE, K/V written to each
@@ -289,24 +341,46 @@ impl Backend for CudaBackend {
         out
     }
 
-    fn swiglu(&mut self, _x: &Tensor) -> Tensor {
-        todo!("elementwise silu(a) * b kernel")
+    /// crates/yaxus-model/src/lib.rs:142.
+    fn swiglu(&mut self, x: &Tensor) -> Tensor {
+        let out = self.alloc(x.rows, x.cols / 2);
+        let ctx = self.ctx.lock().unwrap();
+        unsafe { ffi::yx_swiglu(ctx.0, x.ptr as *const f32, x.rows as u32, (x.cols / 2) as u32, out.ptr as *mut f32) };
+        drop(ctx);
+        out
     }
 
-    fn add_assign(&mut self, _a: &mut Tensor, _b: &Tensor) {
-        todo!("elementwise add kernel")
+    /// crates/yaxus-model/src/lib.rs:144.
+    fn add_assign(&mut self, a: &mut Tensor, b: &Tensor) {
+        assert_eq!(a.rows * a.cols, b.rows * b.cols); // cpu lib.rs:545
+        let ctx = self.ctx.lock().unwrap();
+        unsafe { ffi::yx_add_assign(ctx.0, a.ptr as *mut f32, b.ptr as *const f32, a.rows * a.cols) };
     }
 
-    fn select_rows(&mut self, _x: &Tensor, _rows: &[usize]) -> Tensor {
-        todo!("row gather kernel")
+    /// crates/yaxus-model/src/lib.rs:170.
+    fn select_rows(&mut self, x: &Tensor, rows: &[usize]) -> Tensor {
+        let idx: Vec<u32> = rows.iter().map(|&r| r as u32).collect();
+        let out = self.alloc(idx.len(), x.cols);
+        let ctx = self.ctx.lock().unwrap();
+        unsafe { ffi::yx_select_rows(ctx.0, x.ptr as *const f32, x.rows as u32, x.cols as u32, idx.as_ptr(), idx.len() as u32, out.ptr as *mut f32) };
+        drop(ctx);
+        out
     }
 }
 
 impl SyncReadback for CudaBackend {
-    fn argmax_rows(&mut self, _logits: &Tensor) -> Vec<u32> {
-        // The same read-back point as `to_host`: `self.check()` first, then a row-wise argmax
-        // kernel and a download of `rows` u32.
-        todo!("row-wise argmax kernel")
+    /// crates/yaxus-model/src/lib.rs:182.  A read-back: it waits for the device, and a sticky
+    /// error is raised to the engine here, as in `to_host`.
+    fn argmax_rows(&mut self, logits: &Tensor) -> Vec<u32> {
+        let mut v = vec![0u32; logits.rows];
+        {
+            let ctx = self.ctx.lock().unwrap();
+            unsafe { ffi::yx_argmax_rows(ctx.0, logits.ptr as *const f32, logits.rows as u32, logits.cols as u32, v.as_mut_ptr()) };
+        }
+        if let Err(e) = self.check() {
+            panic!("{e:#}");
+        }
+        v
     }
 
     /// crates/yaxus-model/src/lib.rs:184.  The trait gives no way to return an error here; like

@@ -203,6 +203,43 @@ int yx_attend_allgather(yx_ctx *ctx, yx_kv *kv, int layer, const void *q_dev, in
 
 /* ---- attention without allocation ----------------------------------------------------------- */
 
+/* ---- The other operators of the reference's `Backend` trait --------------------------------
+ * What `Model::forward` calls either side of attention (crates/yaxus-model/src/lib.rs:124-171), with
+ * the CPU backend's arithmetic (crates/yaxus-backend-cpu/src/lib.rs:485-562).  Activations are
+ * row-major f32 on the device; matrix weights and the embedding table are bf16 `[N, K]` as the
+ * model files store them (upload them with yx_tensor_alloc + yx_upload: `load_weight`, cpu
+ * lib.rs:455-462; the quantised formats of the reference are not taken); norm vectors are f32, as
+ * for yx_attention.  All calls enqueue on the context's stream; only yx_argmax_rows waits. */
+
+/* `embed` (lib.rs:125; cpu :485-497): out[r] = f32(table[ids[r]]), `table` bf16 [vocab, h].  The
+ * reference takes the ids from the pass; here they come with the call and are copied at once. */
+int yx_embed(yx_ctx *ctx, const void *table_bf16_dev, uint32_t vocab, uint32_t h, const uint32_t *ids_host,
+             uint32_t rows, float *out_dev);
+/* `rmsnorm` (lib.rs:126; cpu :296-302, :499-507): out = (offset + w) * (x * rsqrt(mean(x^2) + eps)). */
+int yx_rmsnorm(yx_ctx *ctx, const float *x_dev, const float *w_dev, uint32_t rows, uint32_t cols, float offset,
+               float eps, float *out_dev);
+/* `add_norm` (lib.rs:149-162): x += rmsnorm(delta, post_w, post_offset); out = rmsnorm(x, pre_w,
+ * pre_offset).  One kernel. */
+int yx_add_norm(yx_ctx *ctx, float *x_dev, const float *delta_dev, const float *post_w_dev, float post_offset,
+                const float *pre_w_dev, float pre_offset, float eps, uint32_t rows, uint32_t cols, float *out_dev);
+/* `matmul` (lib.rs:128; cpu :314-357, :509-514): out [rows, n] = x [rows, k] . w[n, k]^T, f32 sums. */
+int yx_matmul(yx_ctx *ctx, const float *x_dev, const void *w_bf16_dev, uint32_t rows, uint32_t n, uint32_t k,
+              float *out_dev);
+/* `matmul_glu` (lib.rs:164-168): swiglu(x . w^T) for w = [gate; up]; out is [rows, n / 2]. */
+int yx_matmul_glu(yx_ctx *ctx, const float *x_dev, const void *w_bf16_dev, uint32_t rows, uint32_t n, uint32_t k,
+                  float *out_dev);
+/* `swiglu` (lib.rs:142; cpu :532-542): [rows, 2 inner] -> [rows, inner], g / (1 + exp(-g)) * u. */
+int yx_swiglu(yx_ctx *ctx, const float *x_dev, uint32_t rows, uint32_t inner, float *out_dev);
+/* `add_assign` (lib.rs:144; cpu :544-547): a += b over n elements. */
+int yx_add_assign(yx_ctx *ctx, float *a_dev, const float *b_dev, size_t n);
+/* `select_rows` (lib.rs:170; cpu :549-552): out[i] = x[rows[i]]. */
+int yx_select_rows(yx_ctx *ctx, const float *x_dev, uint32_t src_rows, uint32_t cols, const uint32_t *rows_host,
+                   uint32_t n, float *out_dev);
+/* `SyncReadback::argmax_rows` (lib.rs:177-185; cpu :430-441, :556-558): the first largest value of
+ * every row, NaNs skipped, 0 for a row without a number.  Waits for the device, and so reports
+ * whatever error the stream's earlier work raised.  `to_host` is yx_download with wait = 1. */
+int yx_argmax_rows(yx_ctx *ctx, const float *logits_dev, uint32_t rows, uint32_t cols, uint32_t *out_host);
+
 /* No counterpart in the reference.  Same result as yx_attend (cpu lib.rs:389-427) for passes of
  * at most YX_STATIC_MAX_ROW_HEADS (row, query head) pairs, but the call allocates nothing: the
  * partial triples of its split-key kernel (YX_STATIC_SPLITS runs of keys per row and KV head) live

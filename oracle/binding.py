@@ -58,6 +58,16 @@ class Oracle:
         L.yxref_combine.argtypes = [_F, _F, _F, c_size_t, c_size_t, c_size_t, _F]
         L.yxref_copy_page.argtypes = [_F, _F, c_size_t, c_uint32, c_uint32]
         L.yxref_max_threads.restype = c_int
+        _H = POINTER(c_uint16)
+        L.yxref_dot_bf16.restype = c_float
+        L.yxref_dot_bf16.argtypes = [_H, _F, c_size_t]
+        L.yxref_matmul_bf16.argtypes = [_F, _H, c_size_t, c_size_t, c_size_t, _F, c_int]
+        L.yxref_swiglu.argtypes = [_F, c_size_t, c_size_t, _F]
+        L.yxref_embed.argtypes = [_H, c_size_t, _U, c_size_t, _F]
+        L.yxref_rmsnorm.argtypes = [_F, _F, c_size_t, c_size_t, c_float, c_float, _F]
+        L.yxref_add_norm.argtypes = [_F, _F, _F, c_float, _F, c_float, c_float, c_size_t, c_size_t, _F]
+        L.yxref_argmax.restype = c_uint32
+        L.yxref_argmax.argtypes = [_F, c_size_t]
         self.L = L
 
     def selftest(self) -> float:
@@ -130,3 +140,57 @@ class Oracle:
 
     def copy_page(self, K, V, kvd, src, dst):
         self.L.yxref_copy_page(_f(K), _f(V), kvd, src, dst)
+
+    # ---- the other Backend operators ----
+
+    def to_bf16(self, x) -> np.ndarray:
+        """f32 -> bf16 bits, round to nearest even (crates/yaxus-model/src/weights.rs:100-111)."""
+        return _bf16_bits(_f32(x))
+
+    def matmul(self, x, w_bits, threads=0) -> np.ndarray:
+        x, w_bits = _f32(x), np.ascontiguousarray(w_bits, np.uint16)
+        (T, K), (N, K2) = x.shape, w_bits.shape
+        assert K == K2
+        out = np.zeros((T, N), np.float32)
+        self.L.yxref_matmul_bf16(_f(x), w_bits.ctypes.data_as(POINTER(c_uint16)), T, N, K, _f(out), threads)
+        return out
+
+    def swiglu(self, x) -> np.ndarray:
+        x = _f32(x)
+        T, two_i = x.shape
+        out = np.zeros((T, two_i // 2), np.float32)
+        self.L.yxref_swiglu(_f(x), T, two_i // 2, _f(out))
+        return out
+
+    def embed(self, table_bits, ids) -> np.ndarray:
+        table_bits, ids = np.ascontiguousarray(table_bits, np.uint16), _u32(ids)
+        out = np.zeros((len(ids), table_bits.shape[1]), np.float32)
+        self.L.yxref_embed(table_bits.ctypes.data_as(POINTER(c_uint16)), table_bits.shape[1], _u(ids), len(ids), _f(out))
+        return out
+
+    def rmsnorm(self, x, w, offset, eps) -> np.ndarray:
+        x = _f32(x)
+        out = np.zeros_like(x)
+        self.L.yxref_rmsnorm(_f(x), _f(_f32(w)), x.shape[0], x.shape[1], offset, eps, _f(out))
+        return out
+
+    def add_norm(self, x, delta, post_w, post_offset, pre_w, pre_offset, eps):
+        """Returns (x after the add, the normalised output); `x` itself is left alone."""
+        x, delta = _f32(x).copy(), _f32(delta)
+        out = np.zeros_like(x)
+        self.L.yxref_add_norm(_f(x), _f(delta), _f(_f32(post_w)), post_offset, _f(_f32(pre_w)), pre_offset, eps,
+                              x.shape[0], x.shape[1], _f(out))
+        return x, out
+
+    def argmax_rows(self, x) -> np.ndarray:
+        x = _f32(x)
+        return np.array([self.L.yxref_argmax(_f(x[r]), x.shape[1]) for r in range(x.shape[0])], np.uint32)
+
+
+def _bf16_bits(x: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even bf16 bits of an f32 array, NaNs quieted (weights.rs:100-111), vectorised."""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32)
+    nan = (u & 0x7fffffff) > 0x7f800000
+    r = (u + 0x7fff + ((u >> 16) & 1)) >> 16
+    r = np.where(nan, (u >> 16) | 0x40, r)
+    return r.astype(np.uint16).reshape(x.shape)

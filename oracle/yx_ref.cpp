@@ -308,6 +308,67 @@ void yxref_copy_page(float *K, float *V, size_t kvd, uint32_t src, uint32_t dst)
     memmove(V + (size_t)dst * n, V + (size_t)src * n, n * sizeof(float));
 }
 
+float yxref_dot_bf16(const uint16_t *w, const float *x, size_t n) {
+    float acc[16];
+    for (int i = 0; i < 16; i++) acc[i] = 0.0f;
+    size_t full = n / 16 * 16;
+    for (size_t c = 0; c < full; c += 16)
+        for (int i = 0; i < 16; i++) acc[i] += yxref_bf16_to_f32(w[c + i]) * x[c + i];
+    float s = 0.0f;
+    for (int i = 0; i < 16; i++) s += acc[i];
+    for (size_t i = full; i < n; i++) s += yxref_bf16_to_f32(w[i]) * x[i];
+    return s;
+}
+
+void yxref_matmul_bf16(const float *x, const uint16_t *w, size_t T, size_t N, size_t K, float *out, int threads) {
+    // One task per weight row, as the reference's par_chunks_mut over the transposed result.
+#ifdef _OPENMP
+    int nt = threads > 0 ? threads : omp_get_max_threads();
+#pragma omp parallel for schedule(static) num_threads(nt)
+#endif
+    for (long j = 0; j < (long)N; j++)
+        for (size_t i = 0; i < T; i++) out[i * N + (size_t)j] = yxref_dot_bf16(w + (size_t)j * K, x + i * K, K);
+    (void)threads;
+}
+
+void yxref_swiglu(const float *x, size_t T, size_t inner, float *out) {
+    for (size_t r = 0; r < T; r++)
+        for (size_t j = 0; j < inner; j++) {
+            float g = x[r * 2 * inner + j];
+            out[r * inner + j] = g / (1.0f + expf(-g)) * x[r * 2 * inner + inner + j];
+        }
+}
+
+void yxref_embed(const uint16_t *table, size_t h, const uint32_t *ids, size_t T, float *out) {
+    for (size_t r = 0; r < T; r++)
+        for (size_t c = 0; c < h; c++) out[r * h + c] = yxref_bf16_to_f32(table[(size_t)ids[r] * h + c]);
+}
+
+void yxref_rmsnorm(const float *x, const float *w, size_t T, size_t cols, float offset, float eps, float *out) {
+    for (size_t r = 0; r < T; r++) yxref_rmsnorm_row(x + r * cols, w, offset, eps, out + r * cols, cols);
+}
+
+void yxref_add_norm(float *x, const float *delta, const float *post_w, float post_offset, const float *pre_w,
+                    float pre_offset, float eps, size_t T, size_t cols, float *out) {
+    std::vector<float> d(cols);
+    for (size_t r = 0; r < T; r++) {
+        yxref_rmsnorm_row(delta + r * cols, post_w, post_offset, eps, d.data(), cols);
+        for (size_t c = 0; c < cols; c++) x[r * cols + c] += d[c];
+        yxref_rmsnorm_row(x + r * cols, pre_w, pre_offset, eps, out + r * cols, cols);
+    }
+}
+
+uint32_t yxref_argmax(const float *row, size_t n) {
+    size_t best = 0;
+    float best_v = -INFINITY;
+    for (size_t i = 0; i < n; i++)
+        if (row[i] > best_v) {
+            best = i;
+            best_v = row[i];
+        }
+    return (uint32_t)best;
+}
+
 void yxref_values(float *out, size_t n, uint64_t seed) {
     uint64_t s = (seed * 0x9e3779b97f4a7c15ull) | 1ull;
     for (size_t i = 0; i < n; i++) {

@@ -105,6 +105,32 @@ void yxref_combine(const float *m, const float *l, const float *o, size_t n_part
 /* copy_page for one layer's K and V (cpu lib.rs:472-479). */
 void yxref_copy_page(float *K, float *V, size_t kvd, uint32_t src, uint32_t dst);
 
+/* ---- the other Backend operators (the model's path either side of attention) ---- */
+
+/* dot_bf16 (cpu lib.rs:234-249): bf16 weights times f32 activations, 16 lanes, then the tail. */
+float yxref_dot_bf16(const uint16_t *w, const float *x, size_t n);
+
+/* matmul (cpu lib.rs:314-357): out [T][N] = x [T][K] . w[N][K]^T.  Below four rows the reference
+ * takes dot_bf16 per output, from four rows on it widens the weight row to f32 and takes `dot`:
+ * the same products summed in the same order, so one routine restates both. */
+void yxref_matmul_bf16(const float *x, const uint16_t *w, size_t T, size_t N, size_t K, float *out, int threads);
+
+/* swiglu (cpu lib.rs:532-542): [T][2I] -> [T][I], g / (1 + exp(-g)) * u. */
+void yxref_swiglu(const float *x, size_t T, size_t inner, float *out);
+
+/* embed (cpu lib.rs:485-497): out[r] = f32(table[ids[r]]), table bf16 [V][H]. */
+void yxref_embed(const uint16_t *table, size_t h, const uint32_t *ids, size_t T, float *out);
+
+/* rmsnorm over rows (cpu lib.rs:499-507). */
+void yxref_rmsnorm(const float *x, const float *w, size_t T, size_t cols, float offset, float eps, float *out);
+
+/* add_norm (crates/yaxus-model/src/lib.rs:149-162): x += rmsnorm(delta, post); out = rmsnorm(x, pre). */
+void yxref_add_norm(float *x, const float *delta, const float *post_w, float post_offset, const float *pre_w,
+                    float pre_offset, float eps, size_t T, size_t cols, float *out);
+
+/* argmax (cpu lib.rs:430-441): first maximum, NaNs skipped, 0 when the row holds no number. */
+uint32_t yxref_argmax(const float *row, size_t n);
+
 /* The reference test's value generator (cpu lib.rs:572-582): xorshift64 in [-1, 1). */
 void yxref_values(float *out, size_t n, uint64_t seed);
 

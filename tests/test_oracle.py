@@ -120,3 +120,64 @@ def test_golden_fixture(oracle):
         out = oracle.attend(q, g["pos"], g["pt_off"], g["pages"], int(g["hq"]), int(g["hkv"]), 128, window, K, V)
         assert np.array_equal(out, g[f"out_{tag}"])
         assert np.array_equal(q, g["q_rot"])
+
+
+# ---- the operators either side of attention ------------------------------------------------
+
+def test_bf16_rounding_matches_the_reference_formula(oracle):
+    # f32_to_bf16 (crates/yaxus-model/src/weights.rs:100-106): round to nearest even, NaN stays NaN.
+    x = np.array([0.0, 1.0, -1.0, 1.00390625, 1.01171875, 3.14159274, 65504.0, 1e-40, np.inf, -np.inf], np.float32)
+    bits = oracle.to_bf16(x)
+    assert [int(oracle.L.yxref_f32_to_bf16(float(v))) for v in x] == [int(b) for b in bits]
+    assert bits[3] == 0x3F80 and bits[4] == 0x3F82      # ties go to the even mantissa
+    assert oracle.to_bf16(np.array([np.nan], np.float32))[0] & 0x7FC0 == 0x7FC0
+
+
+def test_matmul_matches_a_plain_loop(oracle):
+    # matmul_matches_a_plain_loop (cpu lib.rs:716-744), bf16 arm: n, k = 40, 64; t in 1, 3, 9;
+    # values(n*k, 7) for the weights, values(t*k, t) for the rows; tolerance 1e-4 x the sum of |terms|.
+    n, k = 40, 64
+    w_bits = oracle.to_bf16(oracle.values(n * k, 7)).reshape(n, k)
+    w = (w_bits.astype(np.uint32) << 16).view(np.float32)
+    for t in (1, 3, 9):
+        x = oracle.values(t * k, t).reshape(t, k)
+        y = oracle.matmul(x, w_bits)
+        assert y.shape == (t, n)
+        terms = w[None, :, :] * x[:, None, :]
+        want = np.zeros((t, n), np.float32)
+        scale = np.zeros((t, n), np.float32)
+        for c in range(k):          # the reference folds left to right
+            want = (want + terms[:, :, c]).astype(np.float32)
+            scale = (scale + np.abs(terms[:, :, c])).astype(np.float32)
+        assert (np.abs(y - want) <= 1e-4 * np.maximum(scale, 1.0)).all()
+
+
+def test_argmax_takes_the_first_maximum_and_skips_nans(oracle):
+    # argmax_takes_the_first_maximum_and_skips_nans (cpu lib.rs:746-752)
+    nan = np.nan
+    rows = [([1.0, 3.0, 3.0, 2.0], 1), ([nan, 1.0, 2.0], 2), ([0.5, nan, 0.2], 0), ([nan, nan], 0)]
+    for row, want in rows:
+        assert int(oracle.argmax_rows(np.array([row], np.float32))[0]) == want
+
+
+def test_elementwise_operators_against_numpy(oracle):
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((5, 96)).astype(np.float32)
+    w = rng.standard_normal(96).astype(np.float32)
+    # rmsnorm_row (cpu lib.rs:296-302)
+    got = oracle.rmsnorm(x, w, 1.0, 1e-6)
+    ref = (1.0 + w) * (x / np.sqrt((x.astype(np.float64) ** 2).mean(1, keepdims=True) + 1e-6))
+    assert np.abs(got - ref).max() < 1e-5
+    # swiglu (cpu lib.rs:532-542)
+    g, u = x[:, :48].astype(np.float64), x[:, 48:].astype(np.float64)
+    assert np.abs(oracle.swiglu(x) - g / (1 + np.exp(-g)) * u).max() < 1e-6
+    # add_norm (crates/yaxus-model/src/lib.rs:149-162) is the three calls of the default method
+    d = rng.standard_normal((5, 96)).astype(np.float32)
+    w2 = rng.standard_normal(96).astype(np.float32)
+    x2, out = oracle.add_norm(x, d, w, 0.0, w2, 1.0, 1e-6)
+    step = x + oracle.rmsnorm(d, w, 0.0, 1e-6)
+    assert np.array_equal(x2, step) and np.array_equal(out, oracle.rmsnorm(step, w2, 1.0, 1e-6))
+    # embed (cpu lib.rs:485-497)
+    table = oracle.to_bf16(rng.standard_normal((10, 32)).astype(np.float32))
+    e = oracle.embed(table, [3, 3, 9, 0])
+    assert np.array_equal(e, (table[[3, 3, 9, 0]].astype(np.uint32) << 16).view(np.float32))

@@ -71,6 +71,15 @@ SIGNATURES = {
     "yx_attention": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
     "yx_kv_append": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int]),
     "yx_attend": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int64, c_void_p, c_int]),
+    "yx_embed": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, _U32P, c_uint32, c_void_p]),
+    "yx_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_float, c_float, c_void_p]),
+    "yx_add_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_float, c_float, c_uint32, c_uint32, c_void_p]),
+    "yx_matmul": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_void_p]),
+    "yx_matmul_glu": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_void_p]),
+    "yx_swiglu": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, c_void_p]),
+    "yx_add_assign": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t]),
+    "yx_select_rows": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, _U32P, c_uint32, c_void_p]),
+    "yx_argmax_rows": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, _U32P]),
     "yx_attend_static": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int64, c_void_p, c_int]),
     "yx_attend_partial": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int64, c_uint64, c_uint64,
                                   c_void_p, c_void_p, c_void_p]),

@@ -104,6 +104,7 @@ class CudaBackend:
             raise BackendError(rc, "yx_ctx_create failed (is this an sm_100 GPU?)")
         self._ctx = ctx
         self._rows = 0
+        self._ids = None
         self.world_size, self.rank = 1, 0
 
     def close(self):
@@ -205,7 +206,95 @@ class CudaBackend:
         """Backend::begin_pass (lib.rs:123)."""
         pos, slot, off, pages = _u32(meta.pos), _u32(meta.kv_slot), _u32(meta.pt_off), _u32(meta.pages)
         self._rows = len(pos)
+        self._ids = _u32(meta.ids) if len(meta.ids) == len(pos) else None
         self._L.yx_begin_pass(self._ctx, len(pos), _u32p(pos), _u32p(slot), _u32p(off), _u32p(pages), len(pages))
+
+    # ---- the operators either side of attention (lib.rs:124-171) --------------------------
+    def load_weight(self, values, shape=None) -> torch.Tensor:
+        """Backend::load_weight with Quant::Bf16 (lib.rs:104-106; cpu :455-462).  `values`: bf16 bit
+        patterns (uint16 array) or a tensor.  Matrices and the embedding table stay bf16 on the
+        device; vectors are widened to f32, as the reference's `vector_f32` does (cpu :200-202)."""
+        if isinstance(values, np.ndarray) and values.dtype == np.uint16:
+            t = torch.from_numpy(np.ascontiguousarray(values).view(np.int16)).view(torch.bfloat16)
+        else:
+            t = torch.as_tensor(values).to(torch.bfloat16)
+        if shape is not None:
+            t = t.reshape(tuple(shape))
+        t = t.to(self.device).contiguous()
+        self._weight_bytes = getattr(self, "_weight_bytes", 0) + t.numel() * 2
+        return t.float() if t.dim() == 1 else t
+
+    def weight_bytes(self) -> int:
+        return getattr(self, "_weight_bytes", 0)
+
+    def _f32(self, rows: int, cols: int) -> torch.Tensor:
+        return torch.empty(rows, cols, dtype=torch.float32, device=self.device)
+
+    def embed(self, table: torch.Tensor) -> torch.Tensor:
+        """Backend::embed (lib.rs:125): the embedding rows of the pass's token ids."""
+        assert table.dtype == torch.bfloat16 and table.dim() == 2 and table.is_contiguous()
+        if self._ids is None:
+            raise AssertionError("the pass carries no token ids")
+        out = self._f32(len(self._ids), table.shape[1])
+        self._L.yx_embed(self._ctx, _ptr(table), table.shape[0], table.shape[1], _u32p(self._ids), len(self._ids), _ptr(out))
+        return out
+
+    def rmsnorm(self, x: torch.Tensor, w: torch.Tensor, offset: float, eps: float) -> torch.Tensor:
+        assert x.dtype == torch.float32 and x.is_contiguous() and w.dtype == torch.float32 and w.numel() == x.shape[1]
+        out = torch.empty_like(x)
+        self._L.yx_rmsnorm(self._ctx, _ptr(x), _ptr(w), x.shape[0], x.shape[1], offset, eps, _ptr(out))
+        return out
+
+    def add_norm(self, x: torch.Tensor, delta: torch.Tensor, post_w: torch.Tensor, post_offset: float,
+                 pre_w: torch.Tensor, pre_offset: float, eps: float) -> torch.Tensor:
+        """Backend::add_norm (lib.rs:149-162): `x` is updated in place, the return is pre_norm(x)."""
+        assert x.shape == delta.shape and x.dtype == delta.dtype == torch.float32 and x.is_contiguous() and delta.is_contiguous()
+        out = torch.empty_like(x)
+        self._L.yx_add_norm(self._ctx, _ptr(x), _ptr(delta), _ptr(post_w), post_offset, _ptr(pre_w), pre_offset, eps,
+                            x.shape[0], x.shape[1], _ptr(out))
+        return out
+
+    def matmul(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """Backend::matmul (lib.rs:128): `x [T, K] . w[N, K]^T -> [T, N]`, w a bf16 matrix."""
+        assert x.dtype == torch.float32 and x.is_contiguous() and w.dtype == torch.bfloat16 and w.is_contiguous()
+        assert x.shape[1] == w.shape[1], "matmul inner dim"
+        out = self._f32(x.shape[0], w.shape[0])
+        self._L.yx_matmul(self._ctx, _ptr(x), _ptr(w), x.shape[0], w.shape[0], w.shape[1], _ptr(out))
+        return out
+
+    def matmul_glu(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """Backend::matmul_glu (lib.rs:164-168): swiglu(x . w^T) for w = [gate; up]."""
+        assert x.dtype == torch.float32 and x.is_contiguous() and w.dtype == torch.bfloat16 and w.is_contiguous()
+        assert x.shape[1] == w.shape[1], "matmul inner dim"
+        out = self._f32(x.shape[0], w.shape[0] // 2)
+        self._L.yx_matmul_glu(self._ctx, _ptr(x), _ptr(w), x.shape[0], w.shape[0], w.shape[1], _ptr(out))
+        return out
+
+    def swiglu(self, x: torch.Tensor) -> torch.Tensor:
+        assert x.dtype == torch.float32 and x.is_contiguous() and x.shape[1] % 2 == 0
+        out = self._f32(x.shape[0], x.shape[1] // 2)
+        self._L.yx_swiglu(self._ctx, _ptr(x), x.shape[0], x.shape[1] // 2, _ptr(out))
+        return out
+
+    def add_assign(self, a: torch.Tensor, b: torch.Tensor) -> None:
+        assert a.numel() == b.numel() and a.dtype == b.dtype == torch.float32 and a.is_contiguous() and b.is_contiguous()
+        self._L.yx_add_assign(self._ctx, _ptr(a), _ptr(b), a.numel())
+
+    def select_rows(self, x: torch.Tensor, rows) -> torch.Tensor:
+        assert x.dtype == torch.float32 and x.is_contiguous()
+        idx = _u32(np.asarray(rows))
+        out = self._f32(len(idx), x.shape[1])
+        self._L.yx_select_rows(self._ctx, _ptr(x), x.shape[0], x.shape[1], _u32p(idx), len(idx), _ptr(out))
+        return out
+
+    def argmax_rows(self, logits: torch.Tensor) -> np.ndarray:
+        """SyncReadback::argmax_rows (lib.rs:177-185): waits for the device; raises its sticky error."""
+        assert logits.dtype == torch.float32 and logits.is_contiguous()
+        out = np.zeros(logits.shape[0], np.uint32)
+        rc = self._L.yx_argmax_rows(self._ctx, _ptr(logits), logits.shape[0], logits.shape[1], _u32p(out))
+        if rc != _lib.YX_OK:
+            raise BackendError(rc, self.last_error())
+        return out
 
     def attention(self, qkv: torch.Tensor, q_norm: torch.Tensor, k_norm: torch.Tensor, kv: Kv, hq: int, eps: float,
                   layer: LayerMeta) -> torch.Tensor:

@@ -8,7 +8,7 @@ CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libyaxus_cuda.so")
 HOST_OUT = os.path.join(HERE, "libyaxus_host.so")
 TRACE_OUT = os.path.join(HERE, "libyaxus_cuda_trace.so")
-CUDA_SOURCES = ["api.cu", "kv_ops.cu", "attend_simt.cu", "attend_mma.cu", "prefill_tc.cu", "combine.cu", "dist.cu", "attend_static.cu", "planner.cpp",
+CUDA_SOURCES = ["api.cu", "kv_ops.cu", "attend_simt.cu", "attend_mma.cu", "prefill_tc.cu", "combine.cu", "dist.cu", "attend_static.cu", "model_ops.cu", "planner.cpp",
                 "hooks.cu"]
 HOST_SOURCES = [os.path.join("host", "kv_cache.cpp")]
 NVCC_FLAGS = [

@@ -506,6 +506,8 @@ void yx_ctx_destroy(yx_ctx *ctx) {
     if (ctx->ws_ml) cudaFree(ctx->ws_ml);
     if (ctx->q_tmp) cudaFree(ctx->q_tmp);
     if (ctx->counters) cudaFree(ctx->counters);
+    if (ctx->mm_part) cudaFree(ctx->mm_part);
+    if (ctx->idx_dev) cudaFree(ctx->idx_dev);
     if (ctx->gather_buf) cudaFree(ctx->gather_buf);
     if (ctx->dev_status) cudaFreeHost(ctx->dev_status);
     for (auto &e : ctx->prof_events)

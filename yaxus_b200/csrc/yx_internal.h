@@ -249,7 +249,7 @@ struct yx_ctx {
     yx_tuning tuning{};
     yx_plan_info last_plan{};
     int64_t launches = 0;
-    bool smem_configured[8] = {};          // per-kernel opt-in to large dynamic shared memory
+    bool smem_configured[12] = {};          // per-kernel opt-in to large dynamic shared memory
     void *trace_buf = nullptr;             // device buffer for per-CTA kernel timestamps (builds with -DYX_TRACE)
     // Host time spent in the phases of an attention call, in ns (builds with -DYX_TRACE): 0 pass checks,
     // 1 planning, 2 laying the plan out in the staging buffer, 3 its upload call, 4 the append launch,
@@ -325,6 +325,10 @@ struct yx_ctx {
     size_t q_tmp_cap = 0;
     uint32_t *counters = nullptr;   // arrival counters of the fused merge; all zero between launches
     size_t counters_cap = 0;
+    float *mm_part = nullptr;              // per-k-chunk partial sums of the matmul
+    size_t mm_part_cap = 0;
+    uint32_t *idx_dev = nullptr;           // token ids / row indices / argmax results of the model operators
+    size_t idx_cap = 0;
 
     // multi-GPU
     ncclComm *comm = nullptr;
