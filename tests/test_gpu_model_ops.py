@@ -37,16 +37,23 @@ def test_reference_matmul_test(backend, oracle):
 
 
 @pytest.mark.parametrize("t,n,k", [(1, 256, 1024), (16, 1000, 2048), (5, 129, 96), (16, 4096, 4096), (33, 512, 3072),
-                                   (80, 384, 1024), (7, 64, 40)])
+                                   (80, 384, 1024), (7, 64, 40), (512, 1536, 2048), (3, 40, 128)])
 def test_matmul_shapes(backend, oracle, t, n, k):
-    # decode-sized passes over model-sized weights, rows past one launch's 32, ragged N, K off the
-    # tensor-core kernel's 32 (the warp-per-output kernel)
+    # decode-sized passes over model-sized weights, passes of more than 32 rows (cuBLASLt; and the
+    # row kernel taking them 32 at a time, which is what runs where that library is missing),
+    # ragged N, K off the tensor-core kernel's 128 (the warp-per-output kernel)
     rng = np.random.default_rng(t * 1000 + n)
     x = rng.standard_normal((t, k)).astype(np.float32)
     w_bits = oracle.to_bf16((rng.standard_normal((n, k)) / np.sqrt(k)).astype(np.float32))
     w = backend.load_weight(w_bits)
+    ref = oracle.matmul(x, w_bits)
     got = backend.to_host(backend.matmul(dev(backend, x), w))
-    assert_matmul_close(got, x, w_bits, oracle.matmul(x, w_bits), tol=2e-5)
+    assert_matmul_close(got, x, w_bits, ref, tol=2e-5)
+    if t > 32:
+        backend.set_tuning(force_path=2)
+        got = backend.to_host(backend.matmul(dev(backend, x), w))
+        backend.set_tuning()
+        assert_matmul_close(got, x, w_bits, ref, tol=2e-5)
 
 
 @pytest.mark.parametrize("t,inner,k", [(16, 1024, 2048), (3, 100, 64), (40, 256, 512)])

@@ -507,6 +507,9 @@ void yx_ctx_destroy(yx_ctx *ctx) {
     if (ctx->q_tmp) cudaFree(ctx->q_tmp);
     if (ctx->counters) cudaFree(ctx->counters);
     if (ctx->mm_part) cudaFree(ctx->mm_part);
+    if (ctx->mm_packed) cudaFree(ctx->mm_packed);
+    if (ctx->lt_workspace) cudaFree(ctx->lt_workspace);
+    release_matmul_library(ctx);
     if (ctx->idx_dev) cudaFree(ctx->idx_dev);
     if (ctx->gather_buf) cudaFree(ctx->gather_buf);
     if (ctx->dev_status) cudaFreeHost(ctx->dev_status);

@@ -7,13 +7,20 @@
 // pass has at most 16 rows, so `x [T,K] . w[N,K]^T` streams the weight matrix once and does
 // 2 T flops per weight byte.  It is taken transposed, out^T = W x^T, with `mma.sync.m16n8k16`:
 // the 16-row side holds weight rows (always full), the 8-column side holds pass rows, as in the
-// split-key attention kernel.  Activations stay f32 in the interface; a CTA turns its K-chunk of
-// them into a high and a low bf16 part in shared memory (x = hi + lo to 16 bits of mantissa),
-// already in the order the MMA's B fragments want, and every weight fragment is used twice.
+// split-key attention kernel.  Activations stay f32 in the interface; a small kernel first turns
+// them into a high and a low bf16 part (x = hi + lo to 16 bits of mantissa), laid out in the
+// order the MMA's B fragments want, and every weight fragment is used twice.
 // Weights go from global memory straight into A fragments with 16-byte loads: a thread takes
-// eight consecutive k of one weight row, which permutes k inside a 32-wide step the same way
-// for both operands, so the products pair up correctly and every sector fetched is used whole.
+// eight consecutive k of one weight row, which permutes k inside a step the same way for both
+// operands, so the products pair up correctly.
+//
+// Passes of more than 32 rows (prompt chunks) are a plain GEMM and go to cuBLASLt, loaded at run
+// time like NCCL; the activations' high and low bf16 parts are two GEMMs into one f32 result.
+// Without the library the row kernel takes the rows 32 at a time, streaming the weights again
+// for each block.
+#include <cublasLt.h>
 #include <cuda_bf16.h>
+#include <dlfcn.h>
 
 #include <algorithm>
 
@@ -22,10 +29,11 @@
 namespace yx {
 namespace {
 
-constexpr int MM_WARPS = 8;
-constexpr int MM_ROWS = MM_WARPS * 16;   // weight rows per CTA
-constexpr int MM_KC = 1024;              // k per CTA (grid.y walks K)
+constexpr int MM_WARPS = 4;
+constexpr int MM_AHEAD = 4;               // steps of weights in flight per thread
+constexpr int MM_CTAS_PER_SM = 5;
 constexpr int MM_STEP = 32;              // k per warp step: one 16-byte load per thread and row half
+constexpr int MM_PAIR = 64;              // two steps: the four threads of a weight row read one whole 128-byte line
 constexpr int MM_MAX_T = 32;             // pass rows per launch (four 8-column tiles)
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -41,76 +49,112 @@ __device__ __forceinline__ uint4 ldg_stream(const void *p) {
     return v;
 }
 
-// part[ky][t][n] = sum over this CTA's k-chunk of x[t][k] * w[n][k], for t0 <= t < t0 + T.
-// NT = 8-column tiles of pass rows.  Shared memory: per 32-k step, per column tile, a 512-byte
-// block of high parts and one of low parts, lane-major (lane = 4 g + t holds x[8 tile + g][k0 + 8 t ..+7]).
+// The activations of up to 32 pass rows as the MMA's B fragments want them: per 32-k step and
+// 8-row column tile a 512-byte block of high parts and one of low parts, lane-major (lane =
+// 4 g + t holds the eight k that thread t of a weight row's four loads in that step: steps come in
+// pairs over 64 k, thread t owning k = 16 t .. 16 t + 15 of the pair, the lower eight in the even step).
+// Rows past T are zero.
 template <int NT>
-__global__ void __launch_bounds__(MM_WARPS * 32) matmul_rows_kernel(const float *__restrict__ x, const __nv_bfloat16 *__restrict__ w,
-                                                                     uint32_t T, uint32_t N, uint32_t K, float *__restrict__ part) {
-    extern __shared__ __align__(16) unsigned char xs[];
-    const uint32_t k_begin = blockIdx.y * MM_KC, k_len = min((uint32_t)MM_KC, K - k_begin);
-    const uint32_t steps = k_len / MM_STEP;
-    // Stage the activations of this chunk: coalesced f32 reads, two 2-byte stores each.
-    for (uint32_t idx = threadIdx.x; idx < (uint32_t)NT * 8u * k_len; idx += blockDim.x) {
-        const uint32_t n = idx / k_len, k = idx - n * k_len;
-        const float v = n < T ? x[(size_t)n * K + k_begin + k] : 0.0f;
-        const __nv_bfloat16 hi = __float2bfloat16_rn(v);
-        const __nv_bfloat16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
-        const uint32_t s = k / MM_STEP, t = (k % MM_STEP) / 8, j = k % 8, tile = n / 8, g = n % 8;
-        const uint32_t at = ((s * NT + tile) * 2u) * 512u + (g * 4u + t) * 16u + j * 2u;
-        *(__nv_bfloat16 *)(xs + at) = hi;
-        *(__nv_bfloat16 *)(xs + at + 512u) = lo;
-    }
-    __syncthreads();
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
-    const uint32_t row0 = blockIdx.x * MM_ROWS + warp * 16;
-    // Rows past N repeat the last row (their results are not stored).
-    const uint32_t ra = min(row0 + g, N - 1), rb = min(row0 + g + 8, N - 1);
-    const __nv_bfloat16 *pa = w + (size_t)ra * K + k_begin + t4 * 8, *pb = w + (size_t)rb * K + k_begin + t4 * 8;
-    float acc[NT][4];
+__global__ void pack_rows_kernel(const float *__restrict__ x, uint32_t T, uint32_t K, uint4 *__restrict__ packed) {
+    const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;   // one thread per 16-byte pair of blocks
+    const uint32_t steps = K / MM_STEP;
+    if (idx >= steps * NT * 32u) return;
+    const uint32_t lane = idx & 31u, tile = (idx >> 5) % NT, s = (idx >> 5) / NT;
+    const uint32_t n = tile * 8 + (lane >> 2), k0 = (s >> 1) * MM_PAIR + (lane & 3u) * 16 + (s & 1u) * 8;
+    uint32_t hi[4], lo[4];
 #pragma unroll
-    for (int n = 0; n < NT; n++) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
+    for (int j = 0; j < 4; j++) {
+        float v[2] = {0.0f, 0.0f};
+        if (n < T) {
+            const float2 p = *(const float2 *)(x + (size_t)n * K + k0 + 2 * j);
+            v[0] = p.x;
+            v[1] = p.y;
+        }
+        const __nv_bfloat16 h0 = __float2bfloat16_rn(v[0]), h1 = __float2bfloat16_rn(v[1]);
+        const __nv_bfloat16 l0 = __float2bfloat16_rn(v[0] - __bfloat162float(h0)), l1 = __float2bfloat16_rn(v[1] - __bfloat162float(h1));
+        hi[j] = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
+        lo[j] = (uint32_t)__bfloat16_as_ushort(l0) | ((uint32_t)__bfloat16_as_ushort(l1) << 16);
+    }
+    uint4 *dst = packed + ((size_t)(s * NT + tile) * 2u) * 32u + lane;
+    dst[0] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    dst[32] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+}
 
-    constexpr int AHEAD = 4;   // steps of weights in flight per thread
+// part[ky][t][n] = sum over k-chunk ky of x[t][k] * w[n][k].  NT = 8-column tiles of pass rows.
+// The work is cut into items of 16 weight rows x one chunk of kc columns, dealt round-robin to the
+// warps of a grid that just fills the machine.  A warp's weights come straight from global memory
+// into A fragments, AHEAD steps in flight, and the prefetch runs on into the warp's next item, so
+// the stream never drains; the packed activations are read through L1.  kc is a multiple of 32 AHEAD.
+template <int NT>
+__global__ void __launch_bounds__(MM_WARPS * 32, 5) matmul_rows_kernel(const uint4 *__restrict__ packed, const __nv_bfloat16 *__restrict__ w,
+                                                                        uint32_t T, uint32_t N, uint32_t K, uint32_t kc, uint32_t chunks,
+                                                                        float *__restrict__ part) {
+    constexpr int AHEAD = MM_AHEAD;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const uint32_t steps = kc / MM_STEP;
+    const uint32_t total = ((N + 15u) / 16u) * chunks, n_warps = gridDim.x * MM_WARPS;
+    uint32_t item = blockIdx.x * MM_WARPS + warp;
+    if (item >= total) return;
+    auto at = [](uint32_t s) { return (size_t)(s >> 1) * MM_PAIR + (s & 1u) * 8; };   // element offset of step s
+    // Rows past N repeat the last row (their results are not stored).
+    auto row_ptr = [&](uint32_t it, uint32_t half) {
+        const uint32_t r = min((it / chunks) * 16u + g + half * 8u, N - 1u);
+        return w + (size_t)r * K + (size_t)(it % chunks) * kc + t4 * 16;
+    };
+    // The prefetch position: AHEAD steps ahead of the consumer.
+    uint32_t pf_item = item, pf_step = 0;
+    const __nv_bfloat16 *pf_a = row_ptr(item, 0), *pf_b = row_ptr(item, 1);
     uint4 wa[AHEAD], wb[AHEAD];
 #pragma unroll
-    for (int i = 0; i < AHEAD; i++) {
-        wa[i] = wb[i] = make_uint4(0u, 0u, 0u, 0u);
-        if ((uint32_t)i < steps) {
-            wa[i] = ldg_stream(pa + i * MM_STEP);
-            wb[i] = ldg_stream(pb + i * MM_STEP);
-        }
+    for (int i = 0; i < AHEAD; i++) {   // (steps >= AHEAD)
+        wa[i] = ldg_stream(pf_a + at(pf_step));
+        wb[i] = ldg_stream(pf_b + at(pf_step));
+        pf_step++;
     }
-    for (uint32_t s0 = 0; s0 < steps; s0 += AHEAD) {
+    for (; item < total; item += n_warps) {
+        const uint32_t ky = item % chunks, row0 = (item / chunks) * 16u;
+        const uint4 *xp = packed + (size_t)ky * steps * NT * 64u + lane;
+        float acc[NT][4];
 #pragma unroll
-        for (int i = 0; i < AHEAD; i++) {
-            const uint32_t s = s0 + i;
-            if (s >= steps) break;
-            const uint4 a = wa[i], b = wb[i];
-            if (s + AHEAD < steps) {
-                wa[i] = ldg_stream(pa + (size_t)(s + AHEAD) * MM_STEP);
-                wb[i] = ldg_stream(pb + (size_t)(s + AHEAD) * MM_STEP);
-            }
+        for (int n = 0; n < NT; n++) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
+        for (uint32_t s0 = 0; s0 < steps; s0 += AHEAD) {
 #pragma unroll
-            for (int n = 0; n < NT; n++) {
-                const uint4 hi = *(const uint4 *)(xs + ((s * NT + n) * 2u) * 512u + lane * 16u);
-                const uint4 lo = *(const uint4 *)(xs + ((s * NT + n) * 2u + 1u) * 512u + lane * 16u);
-                mma_bf16(acc[n], a.x, b.x, a.y, b.y, hi.x, hi.y);
-                mma_bf16(acc[n], a.z, b.z, a.w, b.w, hi.z, hi.w);
-                mma_bf16(acc[n], a.x, b.x, a.y, b.y, lo.x, lo.y);
-                mma_bf16(acc[n], a.z, b.z, a.w, b.w, lo.z, lo.w);
+            for (int i = 0; i < AHEAD; i++) {
+                const uint32_t s = s0 + i;
+                const uint4 a = wa[i], b = wb[i];
+                if (pf_step == steps) {   // on to this warp's next item
+                    pf_step = 0;
+                    pf_item += n_warps;
+                    if (pf_item < total) {
+                        pf_a = row_ptr(pf_item, 0);
+                        pf_b = row_ptr(pf_item, 1);
+                    }
+                }
+                if (pf_item < total) {
+                    wa[i] = ldg_stream(pf_a + at(pf_step));
+                    wb[i] = ldg_stream(pf_b + at(pf_step));
+                    pf_step++;
+                }
+#pragma unroll
+                for (int n = 0; n < NT; n++) {
+                    const uint4 hi = __ldg(xp + ((size_t)s * NT + n) * 64u);
+                    const uint4 lo = __ldg(xp + ((size_t)s * NT + n) * 64u + 32u);
+                    mma_bf16(acc[n], a.x, b.x, a.y, b.y, hi.x, hi.y);
+                    mma_bf16(acc[n], a.z, b.z, a.w, b.w, hi.z, hi.w);
+                    mma_bf16(acc[n], a.x, b.x, a.y, b.y, lo.x, lo.y);
+                    mma_bf16(acc[n], a.z, b.z, a.w, b.w, lo.z, lo.w);
+                }
             }
         }
-    }
-    // c0,c1: weight row g, pass rows 2 t4, 2 t4 + 1 of the tile; c2,c3: weight row g + 8.
-    float *dst = part + (size_t)blockIdx.y * T * N;
+        // c0,c1: weight row g, pass rows 2 t4, 2 t4 + 1 of the tile; c2,c3: weight row g + 8.
+        float *dst = part + (size_t)ky * T * N;
 #pragma unroll
-    for (int n = 0; n < NT; n++) {
+        for (int n = 0; n < NT; n++) {
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
-            const uint32_t tok = n * 8 + t4 * 2 + (c & 1), row = row0 + g + (c >> 1) * 8;
-            if (tok < T && row < N) dst[(size_t)tok * N + row] = acc[n][c];
+            for (int c = 0; c < 4; c++) {
+                const uint32_t tok = n * 8 + t4 * 2 + (c & 1), row = row0 + g + (c >> 1) * 8;
+                if (tok < T && row < N) dst[(size_t)tok * N + row] = acc[n][c];
+            }
         }
     }
 }
@@ -132,7 +176,7 @@ __global__ void matmul_finish_kernel(const float *__restrict__ part, uint32_t ch
     out[idx] = glu ? a / (1.0f + expf(-a)) * b : a;
 }
 
-// Any shape the tensor-core kernel does not take (K not a multiple of 32): a warp per output.
+// Any shape the tensor-core kernel does not take (K not a multiple of 128): a warp per output.
 __global__ void matmul_any_kernel(const float *__restrict__ x, const __nv_bfloat16 *__restrict__ w, uint32_t T, uint32_t N,
                                   uint32_t K, float *__restrict__ out) {
     const uint32_t o = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
@@ -274,19 +318,140 @@ int launched(yx_ctx *ctx, const char *what) {
     return check_cuda(ctx, cudaGetLastError(), what);
 }
 
+// ---- cuBLASLt, for passes of many rows --------------------------------------------------------
+struct Lt {
+    void *lib = nullptr;
+    bool tried = false;
+    cublasStatus_t (*create)(cublasLtHandle_t *) = nullptr;
+    cublasStatus_t (*destroy)(cublasLtHandle_t) = nullptr;
+    cublasStatus_t (*desc_create)(cublasLtMatmulDesc_t *, cublasComputeType_t, cudaDataType_t) = nullptr;
+    cublasStatus_t (*desc_destroy)(cublasLtMatmulDesc_t) = nullptr;
+    cublasStatus_t (*desc_set)(cublasLtMatmulDesc_t, cublasLtMatmulDescAttributes_t, const void *, size_t) = nullptr;
+    cublasStatus_t (*layout_create)(cublasLtMatrixLayout_t *, cudaDataType_t, uint64_t, uint64_t, int64_t) = nullptr;
+    cublasStatus_t (*layout_destroy)(cublasLtMatrixLayout_t) = nullptr;
+    cublasStatus_t (*pref_create)(cublasLtMatmulPreference_t *) = nullptr;
+    cublasStatus_t (*pref_destroy)(cublasLtMatmulPreference_t) = nullptr;
+    cublasStatus_t (*pref_set)(cublasLtMatmulPreference_t, cublasLtMatmulPreferenceAttributes_t, const void *, size_t) = nullptr;
+    cublasStatus_t (*heuristic)(cublasLtHandle_t, cublasLtMatmulDesc_t, cublasLtMatrixLayout_t, cublasLtMatrixLayout_t,
+                                cublasLtMatrixLayout_t, cublasLtMatrixLayout_t, cublasLtMatmulPreference_t, int,
+                                cublasLtMatmulHeuristicResult_t *, int *) = nullptr;
+    cublasStatus_t (*matmul)(cublasLtHandle_t, cublasLtMatmulDesc_t, const void *, const void *, cublasLtMatrixLayout_t,
+                             const void *, cublasLtMatrixLayout_t, const void *, const void *, cublasLtMatrixLayout_t, void *,
+                             cublasLtMatrixLayout_t, const cublasLtMatmulAlgo_t *, void *, size_t, cudaStream_t) = nullptr;
+    bool ok() const { return matmul != nullptr; }
+};
+
+Lt &lt() {
+    static Lt l;
+    if (l.tried) return l;
+    l.tried = true;
+    const char *names[] = {"libcublasLt.so.12", "libcublasLt.so", "/usr/local/cuda/lib64/libcublasLt.so.12"};
+    for (const char *n : names) {
+        l.lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+        if (l.lib) break;
+    }
+    if (!l.lib) return l;
+    auto sym = [&](const char *n) { return dlsym(l.lib, n); };
+    l.create = (decltype(l.create))sym("cublasLtCreate");
+    l.destroy = (decltype(l.destroy))sym("cublasLtDestroy");
+    l.desc_create = (decltype(l.desc_create))sym("cublasLtMatmulDescCreate");
+    l.desc_destroy = (decltype(l.desc_destroy))sym("cublasLtMatmulDescDestroy");
+    l.desc_set = (decltype(l.desc_set))sym("cublasLtMatmulDescSetAttribute");
+    l.layout_create = (decltype(l.layout_create))sym("cublasLtMatrixLayoutCreate");
+    l.layout_destroy = (decltype(l.layout_destroy))sym("cublasLtMatrixLayoutDestroy");
+    l.pref_create = (decltype(l.pref_create))sym("cublasLtMatmulPreferenceCreate");
+    l.pref_destroy = (decltype(l.pref_destroy))sym("cublasLtMatmulPreferenceDestroy");
+    l.pref_set = (decltype(l.pref_set))sym("cublasLtMatmulPreferenceSetAttribute");
+    l.heuristic = (decltype(l.heuristic))sym("cublasLtMatmulAlgoGetHeuristic");
+    auto mm = (decltype(l.matmul))sym("cublasLtMatmul");
+    if (l.create && l.destroy && l.desc_create && l.desc_destroy && l.desc_set && l.layout_create && l.layout_destroy &&
+        l.pref_create && l.pref_destroy && l.pref_set && l.heuristic)
+        l.matmul = mm;
+    return l;
+}
+
+// x [T][K] f32 -> hi [T][K] and lo [T][K] bf16, x = hi + lo to 16 bits of mantissa.
+__global__ void split_rows_kernel(const float *__restrict__ x, size_t n, __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ lo) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const float v = x[idx];
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    hi[idx] = h;
+    lo[idx] = __float2bfloat16_rn(v - __bfloat162float(h));
+}
+
+constexpr size_t LT_WORKSPACE = 32u << 20;
+
+// out [T][N] (row-major f32) = x . w^T through cuBLASLt.  In its column-major terms the result is
+// the N x T matrix w^T(K x N, transposed) times x^T (K x T).  Returns -1 when the library or a
+// kernel for the shape is not there (the caller then uses the row kernel), else a yx_error.
+int matmul_lt(yx_ctx *ctx, const float *x, const __nv_bfloat16 *w, uint32_t T, uint32_t N, uint32_t K, float *out) {
+    Lt &l = lt();
+    if (!l.ok()) return -1;
+    if (!ctx->lt_handle) {
+        cublasLtHandle_t h = nullptr;
+        if (l.create(&h) != CUBLAS_STATUS_SUCCESS) return -1;
+        ctx->lt_handle = h;
+    }
+    if (int rc = ensure_buffer(ctx, (void **)&ctx->mm_packed, &ctx->mm_packed_cap, (size_t)T * K * 4)) return rc;
+    if (int rc = ensure_buffer(ctx, (void **)&ctx->lt_workspace, &ctx->lt_workspace_cap, LT_WORKSPACE)) return rc;
+    __nv_bfloat16 *hi = (__nv_bfloat16 *)ctx->mm_packed, *lo = hi + (size_t)T * K;
+    const size_t n = (size_t)T * K;
+    split_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(x, n, hi, lo);
+    if (int rc = launched(ctx, "matmul: activation split kernel")) return rc;
+
+    cublasLtMatmulDesc_t desc = nullptr;
+    cublasLtMatrixLayout_t la = nullptr, lb = nullptr, lc = nullptr;
+    cublasLtMatmulPreference_t pref = nullptr;
+    int result = -1;
+    do {
+        if (l.desc_create(&desc, CUBLAS_COMPUTE_32F, CUDA_R_32F) != CUBLAS_STATUS_SUCCESS) break;
+        const cublasOperation_t ta = CUBLAS_OP_T, tb = CUBLAS_OP_N;
+        if (l.desc_set(desc, CUBLASLT_MATMUL_DESC_TRANSA, &ta, sizeof ta) != CUBLAS_STATUS_SUCCESS) break;
+        if (l.desc_set(desc, CUBLASLT_MATMUL_DESC_TRANSB, &tb, sizeof tb) != CUBLAS_STATUS_SUCCESS) break;
+        if (l.layout_create(&la, CUDA_R_16BF, K, N, K) != CUBLAS_STATUS_SUCCESS) break;   // w: K x N, column-major
+        if (l.layout_create(&lb, CUDA_R_16BF, K, T, K) != CUBLAS_STATUS_SUCCESS) break;   // x parts: K x T
+        if (l.layout_create(&lc, CUDA_R_32F, N, T, N) != CUBLAS_STATUS_SUCCESS) break;    // out: N x T
+        if (l.pref_create(&pref) != CUBLAS_STATUS_SUCCESS) break;
+        const size_t ws = LT_WORKSPACE;
+        if (l.pref_set(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &ws, sizeof ws) != CUBLAS_STATUS_SUCCESS) break;
+        cublasLtMatmulHeuristicResult_t heur{};
+        int found = 0;
+        if (l.heuristic((cublasLtHandle_t)ctx->lt_handle, desc, la, lb, lc, lc, pref, 1, &heur, &found) != CUBLAS_STATUS_SUCCESS || found == 0)
+            break;
+        const float one = 1.0f, zero = 0.0f;
+        cublasStatus_t st = l.matmul((cublasLtHandle_t)ctx->lt_handle, desc, &one, w, la, hi, lb, &zero, out, lc, out, lc, &heur.algo,
+                                     ctx->lt_workspace, LT_WORKSPACE, ctx->stream);
+        if (st == CUBLAS_STATUS_SUCCESS)
+            st = l.matmul((cublasLtHandle_t)ctx->lt_handle, desc, &one, w, la, lo, lb, &one, out, lc, out, lc, &heur.algo,
+                          ctx->lt_workspace, LT_WORKSPACE, ctx->stream);
+        if (st != CUBLAS_STATUS_SUCCESS) {
+            result = fail(ctx, YX_ERR_CUDA, "matmul: cublasLtMatmul failed with status " + std::to_string((int)st));
+            break;
+        }
+        ctx->launches += 2;
+        ctx->last_launch = yx_ctx::LAST_OTHER;
+        result = YX_OK;
+    } while (false);
+    if (pref) l.pref_destroy(pref);
+    if (lc) l.layout_destroy(lc);
+    if (lb) l.layout_destroy(lb);
+    if (la) l.layout_destroy(la);
+    if (desc) l.desc_destroy(desc);
+    return result;
+}
+
 template <int NT>
 int launch_matmul_rows(yx_ctx *ctx, const float *x, const __nv_bfloat16 *w, uint32_t T, uint32_t N, uint32_t K, float *part,
-                       uint32_t chunks) {
-    const size_t smem = (size_t)(MM_KC / MM_STEP) * NT * 2 * 512;
-    const int slot = NT == 1 ? 8 : (NT == 2 ? 9 : 10);
-    if (!ctx->smem_configured[slot]) {
-        if (int rc = check_cuda(ctx, cudaFuncSetAttribute(matmul_rows_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                                "matmul: shared memory attribute"))
-            return rc;
-        ctx->smem_configured[slot] = true;
-    }
-    dim3 grid((N + MM_ROWS - 1) / MM_ROWS, chunks);
-    matmul_rows_kernel<NT><<<grid, MM_WARPS * 32, smem, ctx->stream>>>(x, w, T, N, K, part);
+                       uint32_t kc, uint32_t chunks) {
+    const size_t packed_bytes = (size_t)(K / MM_STEP) * NT * 2 * 512;
+    if (int rc = ensure_buffer(ctx, (void **)&ctx->mm_packed, &ctx->mm_packed_cap, packed_bytes)) return rc;
+    const uint32_t pack_threads = (K / MM_STEP) * NT * 32u;
+    pack_rows_kernel<NT><<<(pack_threads + 255) / 256, 256, 0, ctx->stream>>>(x, T, K, (uint4 *)ctx->mm_packed);
+    if (int rc = launched(ctx, "matmul: activation packing kernel")) return rc;
+    const uint32_t items = ((N + 15u) / 16u) * chunks;
+    const uint32_t grid = std::min<uint32_t>((items + MM_WARPS - 1) / MM_WARPS, (uint32_t)ctx->sm_count * MM_CTAS_PER_SM);
+    matmul_rows_kernel<NT><<<grid, MM_WARPS * 32, 0, ctx->stream>>>((const uint4 *)ctx->mm_packed, w, T, N, K, kc, chunks, part);
     return launched(ctx, "matmul kernel");
 }
 
@@ -315,7 +480,7 @@ int matmul_impl(yx_ctx *ctx, const float *x, const void *w_bf16, uint32_t T, uin
     Guard guard(ctx->device);
     const __nv_bfloat16 *w = (const __nv_bfloat16 *)w_bf16;
     const uint32_t cols = glu ? N / 2 : N;
-    if (K % MM_STEP != 0 || ((uintptr_t)w & 15u) != 0) {
+    if (K % (MM_STEP * MM_AHEAD) != 0 || ((uintptr_t)w & 15u) != 0) {
         float *dst = out;
         if (glu) {
             if (int rc = ensure_buffer(ctx, (void **)&ctx->mm_part, &ctx->mm_part_cap, (size_t)T * N * sizeof(float))) return rc;
@@ -331,16 +496,38 @@ int matmul_impl(yx_ctx *ctx, const float *x, const void *w_bf16, uint32_t T, uin
         }
         return YX_OK;
     }
-    const uint32_t chunks = (K + MM_KC - 1) / MM_KC;
+    if (T > MM_MAX_T && ctx->tuning.force_path != 2) {
+        float *dst = out;
+        if (glu) {
+            if (int rc = ensure_buffer(ctx, (void **)&ctx->mm_part, &ctx->mm_part_cap, (size_t)T * N * sizeof(float))) return rc;
+            dst = ctx->mm_part;
+        }
+        const int rc = matmul_lt(ctx, x, w, T, N, K, dst);
+        if (rc > 0) return rc;
+        if (rc == YX_OK) {
+            if (!glu) return YX_OK;
+            const uint64_t n = (uint64_t)T * cols;
+            swiglu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(dst, T, cols, out);
+            return launched(ctx, "swiglu kernel");
+        }
+        // (no cuBLASLt, or no kernel of its for this shape: the row kernel below)
+    }
+    // K is cut into chunks (an item is 16 weight rows of one chunk) until every resident warp has
+    // a few items to take, which evens the warps' loads out; no more than eight chunks, whose
+    // partial sums the finishing kernel adds up.
+    const uint32_t row_items = (N + 15) / 16, warps = (uint32_t)ctx->sm_count * MM_CTAS_PER_SM * MM_WARPS;
+    uint32_t kc = K;
+    while (kc % (2 * MM_STEP * MM_AHEAD) == 0 && K / (kc / 2) <= 8 && row_items * (K / kc) < 4 * warps) kc /= 2;
+    const uint32_t chunks = K / kc;
     // Pass rows go 32 at a time; each block of them streams the weights again.
     for (uint32_t t0 = 0; t0 < T; t0 += MM_MAX_T) {
         const uint32_t tn = std::min<uint32_t>(MM_MAX_T, T - t0);
         if (int rc = ensure_buffer(ctx, (void **)&ctx->mm_part, &ctx->mm_part_cap, (size_t)chunks * MM_MAX_T * N * sizeof(float)))
             return rc;
         const float *xt = x + (size_t)t0 * K;
-        int rc = tn <= 8    ? launch_matmul_rows<1>(ctx, xt, w, tn, N, K, ctx->mm_part, chunks)
-                 : tn <= 16 ? launch_matmul_rows<2>(ctx, xt, w, tn, N, K, ctx->mm_part, chunks)
-                            : launch_matmul_rows<4>(ctx, xt, w, tn, N, K, ctx->mm_part, chunks);
+        int rc = tn <= 8    ? launch_matmul_rows<1>(ctx, xt, w, tn, N, K, ctx->mm_part, kc, chunks)
+                 : tn <= 16 ? launch_matmul_rows<2>(ctx, xt, w, tn, N, K, ctx->mm_part, kc, chunks)
+                            : launch_matmul_rows<4>(ctx, xt, w, tn, N, K, ctx->mm_part, kc, chunks);
         if (rc) return rc;
         const uint64_t n = (uint64_t)tn * cols;
         matmul_finish_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(ctx->mm_part, chunks, tn, N, glu,
@@ -351,6 +538,12 @@ int matmul_impl(yx_ctx *ctx, const float *x, const void *w_bf16, uint32_t T, uin
 }
 
 }  // namespace
+
+void release_matmul_library(yx_ctx *ctx) {
+    if (ctx->lt_handle && lt().ok()) lt().destroy((cublasLtHandle_t)ctx->lt_handle);
+    ctx->lt_handle = nullptr;
+}
+
 }  // namespace yx
 
 using namespace yx;

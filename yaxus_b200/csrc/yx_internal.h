@@ -327,6 +327,11 @@ struct yx_ctx {
     size_t counters_cap = 0;
     float *mm_part = nullptr;              // per-k-chunk partial sums of the matmul
     size_t mm_part_cap = 0;
+    void *mm_packed = nullptr;             // the pass rows of a matmul as bf16 MMA fragments
+    size_t mm_packed_cap = 0;
+    void *lt_handle = nullptr;             // cublasLtHandle_t, made at the first matmul of many rows
+    void *lt_workspace = nullptr;
+    size_t lt_workspace_cap = 0;
     uint32_t *idx_dev = nullptr;           // token ids / row indices / argmax results of the model operators
     size_t idx_cap = 0;
 
@@ -346,6 +351,8 @@ int check_cuda(yx_ctx *ctx, cudaError_t e, const char *what);
 // Stream-ordered upload of `bytes` from pageable host memory through the pinned ring.
 int upload_ordered(yx_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes);
 int ensure_buffer(yx_ctx *ctx, void **buf, size_t *cap, size_t bytes);
+// Destroys the context's cuBLASLt handle, if it made one.
+void release_matmul_library(yx_ctx *ctx);
 
 // Kernel launchers (each returns a yx_error and counts its launches in ctx->launches).
 int launch_append(yx_ctx *ctx, yx_kv *kv, int layer, const void *k_rows, const void *v_rows, int src_dtype);
