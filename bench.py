@@ -452,6 +452,58 @@ def cpu_baseline(s, oracle_state=None):
             "sample": f"the whole step ({s.meta.rows} rows x {s.hq} heads), best of 3", "ms_per_step": best * 1e3}
 
 
+def run_matmul(env, calls, warm, check=True):
+    """The decode step's largest operator outside attention (Backend::matmul_glu, the fused gate/up
+    projection of a layer with hidden 4096 and intermediate 14336): 16 pass rows against a bf16
+    weight of [28672, 4096].  Bandwidth-bound on the weights, which is what the record counts."""
+    torch, b, dev = env.torch, env.b, env.dev
+    T, N, K = 16, 28672, 4096
+    w_bytes = N * K * 2
+    n_w = max(2, int(math.ceil(4.0 * L2_BYTES / w_bytes)))
+    g = torch.Generator(device="cpu").manual_seed(77 + env.rank)
+    ws = [(torch.randn(N, K, generator=g) * (1.0 / math.sqrt(K))).to(torch.bfloat16).to(dev) for _ in range(n_w)]
+    x = torch.randn(T, K, generator=g).to(dev)
+    max_err = None
+    if check and env.rank == 0:
+        from oracle.binding import Oracle
+        o = Oracle()
+        rows = slice(0, 2048)        # the oracle on the first 2048 gate rows and their up rows
+        sub = torch.cat([ws[0][:2048], ws[0][N // 2:N // 2 + 2048]]).contiguous()
+        got = b.to_host(b.matmul_glu(x, sub))
+        w_bits = sub.view(torch.int16).cpu().numpy().view(np.uint16)
+        ref = o.swiglu(o.matmul(x.cpu().numpy(), w_bits, threads=host_cores()))
+        max_err = float(np.abs(got - ref).max())
+        assert max_err <= 2e-5 * max(1.0, float(np.abs(ref).max())), f"matmul_glu parity: {max_err}"
+        full = b.to_host(b.matmul_glu(x, ws[0]))      # and the full weight agrees with its slice
+        assert np.array_equal(full[:, rows], got), "matmul_glu: the full weight differs from its slice"
+    env.barrier()
+    out = torch.empty(T, N // 2, dtype=torch.float32, device=dev)
+
+    def step(i):
+        b._L.yx_matmul_glu(b._ctx, x.data_ptr(), ws[i % n_w].data_ptr(), T, N, K, out.data_ptr())
+
+    launches0 = b.launch_count()
+    step(0)
+    launches_per_call = b.launch_count() - launches0
+    ms, host_us, clocks = env.timed(step, calls, warm)
+    rec = None
+    if env.rank == 0:
+        peaks = measured_peaks()
+        achieved = w_bytes / (ms * 1e-3) / 1e9
+        rec = {"metric": "decode matmul_glu weight GB/s", "value": env.world * achieved, "unit": "GB/s", "ms_per_step": ms,
+               "scaling": "weak", "dtype": "bf16 weights, f32 activations (as two bf16 parts), f32 sums",
+               "config": {"workload": "decode_matmul_glu", "rows": T, "n": N, "k": K, "timed_calls": calls,
+                          "l2": f"calls rotate over {n_w} weights ({n_w} x {w_bytes >> 20} MiB > L2)"},
+               "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
+                            "frac": achieved / peaks["hbm"], "traffic": None, "peak_source": peaks["source"],
+                            "kernel": "matmul_rows_kernel", "algorithmic_bytes": float(w_bytes),
+                            "how": "the whole call (packing, the matmul kernel, the finishing kernel) between two CUDA events"},
+               "host_us_per_call": host_us, "clocks": clocks, "gpu_launches": int(launches_per_call * calls),
+               "parity_max_abs": max_err}
+    del ws
+    return rec
+
+
 def run_prefill(env, steps, warm, kv_name="bf16", check=True, e2e=False):
     """Chunked causal prefill: 8 sequences x 4096 tokens in 512-row chunks, 16-bit Q/K/V, f32
     softmax and accumulation.  A step is the whole prefill of the batch (eight passes, each
@@ -539,7 +591,7 @@ def run_prefill(env, steps, warm, kv_name="bf16", check=True, e2e=False):
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["bf16"], "frac_of_burst_peak": achieved / peaks["bf16_burst"],
                          "traffic": traffic, "traffic_source": traffic_source,
-                         "peak_source": peaks["source"] + " (sustained)", "kernel": "prefill_tc2_kernel",
+                         "peak_source": peaks["source"] + " (sustained)", "kernel": f"prefill_tc2_{kv_name}_kernel",
                          "kernel_ms_per_step": kernel_ms_per_step,
                          "how": "events around every launch of the tile kernel, summed over the step's eight passes"},
             "host_us_per_call": host_us, "clocks": clocks, "gpu_launches": int(launches_per_step * steps),
@@ -650,7 +702,7 @@ def run_reference(args):
         "gpu_launches": 0}))
 
 
-SUB_WORKLOADS = ("prefill", "verify", "single_decode", "long_decode", "long_decode_window")
+SUB_WORKLOADS = ("prefill", "verify", "single_decode", "long_decode", "long_decode_window", "decode_matmul_glu")
 
 
 def run_cuda(args):
@@ -671,6 +723,8 @@ def run_cuda(args):
             try:
                 if name == "prefill":
                     rec = run_prefill(env, 5, 3, "bf16", check=not args.no_check)
+                elif name == "decode_matmul_glu":
+                    rec = run_matmul(env, 300, warm, check=not args.no_check)
                 elif name.startswith("long_decode"):
                     if long_s is None:
                         long_s = make_scenario("long_decode", 0)
