@@ -71,7 +71,7 @@ typedef struct yx_tuning {
     int32_t tile_min_rows;   /* rows of one sequence from which the tcgen05 tile kernel is used */
     int32_t cost32;          /* planner cost of a 64-key tile of an item with 32 padded query rows, */
     int32_t cost64;          /* and with 64, in 16ths of the cost of a 16-row item's tile */
-    int32_t stages;          /* 64-key tiles in flight per SM in the tensor split-key kernel (2..4) */
+    int32_t stages;          /* 64-key tiles in flight per SM in the tensor split-key kernel (2..5) */
     int32_t share_rows;      /* pass rows a shared-prefix item may hold (0: 16 / group, one MMA tile) */
     int32_t item_cost;       /* planner cost of starting an item, in 16ths of a tile, plus one (0: default) */
     int32_t fused_merge;     /* 1: the split-key kernel merges the triples itself; 0: a combine kernel does */

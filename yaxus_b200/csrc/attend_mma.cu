@@ -63,7 +63,7 @@ namespace {
 
 using namespace dev;
 
-constexpr int STAGES = 4;
+constexpr int STAGES = 5;
 constexpr int SUB_BYTES = TILE_KEYS * 128;        // one 64-dim half of a 64-key tile
 constexpr int STAGE_BYTES = 4 * SUB_BYTES;        // K lo, K hi, V lo, V hi
 constexpr int CONSUMERS = 8;                      // warps 0..7, two per scheduler
@@ -82,18 +82,24 @@ constexpr int Q_STRIDE_F32 = 512 + 32;
 constexpr int Q_STRIDE_16 = 256 + 16;
 constexpr int Q_ROWS_BYTES = 32 * Q_STRIDE_F32;
 static_assert(Q_ROWS_BYTES == 64 * Q_STRIDE_16, "both query forms fill the slot");
-constexpr int Q_SLOT_BYTES = Q_ROWS_BYTES + 512;  // then the item's record
+// The query rows have one buffer: the consumer warps turn them into MMA fragments in registers at
+// the start of an item and hand the buffer back at once, so the next item's rows are copied while
+// this item's tiles stream.  The items' records, which are read to the end of an item, have two
+// slots.  (Two full query slots cost a fifth copy stage; one slot held for the whole item cost a
+// bubble at every item change.)
+constexpr int REC_BYTES = 512;
 constexpr int MERGE_ROW = D + 4;                  // one row's o, then m and l, padded
 constexpr int MERGE_FLOATS = 8 * MERGE_ROW;       // one warp's 8 queries
 constexpr int MERGE_BYTES = CONSUMERS * MERGE_FLOATS * 4;   // one buffer: every consumer warp's rows
 constexpr int MERGE_BUFS = 1;
-constexpr int N_BARRIERS = 2 * STAGES + 2 * Q_SLOTS + 2 * MERGE_BUFS;
+constexpr int N_BARRIERS = 2 * STAGES + 2 * Q_SLOTS + 2 * MERGE_BUFS + 1;
 constexpr int MLBUF_BYTES = EWARPS * 8 * 32 * 8;  // per epilogue warp: (m, l) of 32 parts for each of 8 merges in flight
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + Q_SLOTS * Q_SLOT_BYTES + MERGE_BUFS * MERGE_BYTES + N_BARRIERS * 8 + MLBUF_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + Q_ROWS_BYTES + Q_SLOTS * REC_BYTES + MERGE_BUFS * MERGE_BYTES + N_BARRIERS * 8 + MLBUF_BYTES;
+static_assert(SMEM_BYTES + 1024 <= 227 * 1024, "the CTA's shared memory");
 
 struct Shared {
-    uint32_t stages, q, merge;          // shared-space addresses
-    uint32_t full, empty, qfull, qempty, efull, eempty, mlbuf;
+    uint32_t stages, q, rec, merge;     // shared-space addresses
+    uint32_t full, empty, qfull, qempty, qrows_free, efull, eempty, mlbuf;
     volatile int *abort_flag;
 };
 
@@ -302,7 +308,7 @@ struct QStage {
     uint32_t item_begin, item_end;
     int have_first;                       // the first item's header came with the parameters
     uint32_t first_head_rows, first_row0, first_row1;   // first_row<h>: the pass row of query row 32 h + lane
-    uint32_t qbase, qfull, qempty;        // shared-space addresses
+    uint32_t qbase, recbase, qfull, qempty, qrows_free;   // shared-space addresses
     volatile int *abort_flag;
     uint32_t n_items;                     // records in `recs`
     unsigned long long q_bytes;           // bytes in `q`
@@ -343,6 +349,9 @@ __device__ __forceinline__ void stage_queries(const QStage &A, int lane) {
         int stop = 0;
         if (lane == 0) {
             mbar_wait(A.qempty + 8 * pipe.stage, pipe.phase ^ 1u, A.abort_flag, A.status, 3);
+            // ... and the rows buffer: the consumers have built the fragments of the item before
+            // (one phase an item; a barrier never used reads as complete for the phase before its first)
+            mbar_wait(A.qrows_free, ((ii - A.item_begin) & 1u) ^ 1u, A.abort_flag, A.status, 7);
             stop = *A.abort_flag;
         }
         if (__shfl_sync(0xffffffffu, stop, 0)) {
@@ -350,7 +359,7 @@ __device__ __forceinline__ void stage_queries(const QStage &A, int lane) {
             break;
         }
         if (YX_TR(A.trace != nullptr) && lane == 0 && ii == A.item_begin) A.trace[9] = gtime();
-        const uint32_t slot = A.qbase + pipe.stage * Q_SLOT_BYTES, bar = A.qfull + 8 * pipe.stage;
+        const uint32_t slot = A.qbase, rec_slot = A.recbase + pipe.stage * REC_BYTES, bar = A.qfull + 8 * pipe.stage;
         const int kvh = (int)(head_rows & 0xffffu);
         int q_rows = (int)(head_rows >> 16) * A.group;
         // The kernel's own checks: a record outside the array, more query rows than a slot holds, a
@@ -379,7 +388,7 @@ __device__ __forceinline__ void stage_queries(const QStage &A, int lane) {
 #pragma unroll
         for (int h = 0; h < 2; h++)
             if (ok[h]) bulk_g2s(slot + (uint32_t)(32 * h + lane) * A.stride, A.q + elem[h] * A.row_bytes, A.row_bytes, bar);
-        if (lane == 0 && rec_ok) bulk_g2s(slot + Q_ROWS_BYTES, A.recs + (size_t)ii * A.rec_stride, A.rec_stride, bar);
+        if (lane == 0 && rec_ok) bulk_g2s(rec_slot, A.recs + (size_t)ii * A.rec_stride, A.rec_stride, bar);
         if (YX_TR(A.trace != nullptr) && lane == 0 && ii == A.item_begin) {
             A.trace[10] = gtime();
             A.trace[11] = ((unsigned long long)n_ok << 32) | (unsigned long long)(n_ok * A.row_bytes + (rec_ok ? A.rec_stride : 0u));
@@ -417,7 +426,7 @@ struct Epilogue {
     int late_wait;           // the grid dependency has not been waited for yet: do so before the first store
     uint32_t n_parts;        // slots in the partial buffers
     uint32_t n_items, first_item;    // this warp takes items first_item, first_item + EWARPS, ...
-    uint32_t qbase, qempty, merge, efull, eempty, mlbuf;   // shared-space addresses
+    uint32_t recbase, qempty, merge, efull, eempty, mlbuf;   // shared-space addresses
 };
 
 // Eight (row, head) pairs at a time, four lanes each: two round trips to L2 per round (the
@@ -582,7 +591,7 @@ __device__ __noinline__ void epilogue_loop(const Epilogue E, int lane) {
         mbar_wait(E.efull, phase, E.abort_flag, E.status, 5);
         if (ii == 0 && E.late_wait) grid_dependency_wait();   // the merge ahead has read the partial buffers
         const float *scratch = (const float *)__cvta_shared_to_generic((size_t)E.merge);
-        const uint32_t *rec = (const uint32_t *)__cvta_shared_to_generic((size_t)(E.qbase + qslot * Q_SLOT_BYTES + Q_ROWS_BYTES));
+        const uint32_t *rec = (const uint32_t *)__cvta_shared_to_generic((size_t)(E.recbase + qslot * REC_BYTES));
         const uint32_t head_rows = rec[IR_HEAD_ROWS];
         const int kvh = (int)(head_rows & 0xffffu), n_rows = (int)(head_rows >> 16);
         // 1. the item's triples
@@ -625,8 +634,8 @@ __device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe 
     constexpr int PARTS = KBW == 1 ? 4 : (KBW == 2 ? 2 : 1);   // partial sums per key block: short MMA chains
     const int g = lane >> 2, t4 = lane & 3;
     const int group = P.group;
-    const uint32_t slot = S.q + qpipe.stage * Q_SLOT_BYTES;
-    const uint32_t *rec = (const uint32_t *)__cvta_shared_to_generic((size_t)(slot + Q_ROWS_BYTES));
+    const uint32_t slot = S.q;
+    const uint32_t *rec = (const uint32_t *)__cvta_shared_to_generic((size_t)(S.rec + qpipe.stage * REC_BYTES));
     const uint32_t n_tiles = rec[IR_TILES], key_base = rec[IR_KEY0];
     const int n_rows = (int)(rec[IR_HEAD_ROWS] >> 16);
     const int q_rows = n_rows * group;
@@ -696,6 +705,10 @@ __device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe 
             }
         }
     }
+
+    // The rows buffer is the stager's again (the fragments are in registers).
+    __syncwarp();
+    if (lane == 0) mbar_arrive(S.qrows_free);
 
     float o[8][4];   // O^T: dims 16 n + g (+8), queries 2 t4 (+1)
 #pragma unroll
@@ -873,12 +886,14 @@ __global__ void __maxnreg__(152) attend_mma_kernel(const __grid_constant__ Param
     Shared S;
     S.stages = smem_u32(smem);
     S.q = S.stages + STAGES * STAGE_BYTES;
-    S.merge = S.q + Q_SLOTS * Q_SLOT_BYTES;
+    S.rec = S.q + Q_ROWS_BYTES;
+    S.merge = S.rec + Q_SLOTS * REC_BYTES;
     S.full = S.merge + MERGE_BUFS * MERGE_BYTES;
     S.empty = S.full + 8 * STAGES;
     S.qfull = S.empty + 8 * STAGES;
     S.qempty = S.qfull + 8 * Q_SLOTS;
-    S.efull = S.qempty + 8 * Q_SLOTS;
+    S.qrows_free = S.qempty + 8 * Q_SLOTS;
+    S.efull = S.qrows_free + 8;
     S.eempty = S.efull + 8 * MERGE_BUFS;
     S.mlbuf = S.eempty + 8 * MERGE_BUFS;
     S.abort_flag = &abort_flag;
@@ -905,6 +920,7 @@ __global__ void __maxnreg__(152) attend_mma_kernel(const __grid_constant__ Param
                 mbar_init(S.qfull + 8 * s, 1);
                 mbar_init(S.qempty + 8 * s, CONSUMERS + 1);   // the consumer warps and the epilogue warp
             }
+            mbar_init(S.qrows_free, CONSUMERS);
             for (int s = 0; s < MERGE_BUFS; s++) {
                 mbar_init(S.efull + 8 * s, CONSUMERS);
                 mbar_init(S.eempty + 8 * s, 1);
@@ -954,8 +970,10 @@ __global__ void __maxnreg__(152) attend_mma_kernel(const __grid_constant__ Param
             A.first_row1 = P.pro[blockIdx.x].rows[min((32 + lane) / P.group, MAX_ITEM_ROWS - 1)];
         }
         A.qbase = S.q;
+        A.recbase = S.rec;
         A.qfull = S.qfull;
         A.qempty = S.qempty;
+        A.qrows_free = S.qrows_free;
         A.abort_flag = S.abort_flag;
         A.n_items = P.n_items;
         A.q_bytes = P.q_bytes;
@@ -983,7 +1001,7 @@ __global__ void __maxnreg__(152) attend_mma_kernel(const __grid_constant__ Param
         E.n_parts = P.n_parts;
         E.n_items = hdr.item_end - hdr.item_begin;
         if (!P.fused && E.n_items > 0) E.n_items--;   // the last item is the consumer warps' own
-        E.qbase = S.q;
+        E.recbase = S.rec;
         E.qempty = S.qempty;
         E.merge = S.merge;
         E.efull = S.efull;
@@ -998,9 +1016,9 @@ __global__ void __maxnreg__(152) attend_mma_kernel(const __grid_constant__ Param
         // The staged slot holds the item's record and queries.
         mbar_wait(S.qfull + 8 * qpipe.stage, qpipe.phase, S.abort_flag, P.status, 4);
         if (tr && threadIdx.x == 0 && ii == hdr.item_begin) tr[3] = gtime();
-        const uint32_t mt = *(const uint32_t *)__cvta_shared_to_generic((size_t)(S.q + qpipe.stage * Q_SLOT_BYTES + Q_ROWS_BYTES + 4 * IR_MT));
+        const uint32_t mt = *(const uint32_t *)__cvta_shared_to_generic((size_t)(S.rec + qpipe.stage * REC_BYTES + 4 * IR_MT));
         const bool last = !P.fused && ii + 1 == hdr.item_end;   // merged by the consumer warps themselves
-        const uint32_t hr = *(const uint32_t *)__cvta_shared_to_generic((size_t)(S.q + qpipe.stage * Q_SLOT_BYTES + Q_ROWS_BYTES + 4 * IR_HEAD_ROWS));
+        const uint32_t hr = *(const uint32_t *)__cvta_shared_to_generic((size_t)(S.rec + qpipe.stage * REC_BYTES + 4 * IR_HEAD_ROWS));
         const int q_rows = (int)(hr >> 16) * P.group;
         // Who takes what of a 64-key tile (the epilogue warp's merge knows the same table):
         //   up to 8 queries: column tile 0 everywhere, a 16-key block each, warps 0-3 even tiles and 4-7 odd ones;
