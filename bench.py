@@ -292,11 +292,18 @@ def run_split_key(env, name, s, calls, warm, check=True, e2e=False, cpu=False, k
             b.kv_append(kv, l, k_new, v_new)
     out = torch.empty(s.meta.rows, s.hq * 128, dtype=torch.float32, device=dev)
 
+    # The timed call is the C entry point itself (through ctypes, arguments prepared once): the
+    # Python wrapper's checks and conversions would be half of the host time of a 20 us call.
+    import ctypes
+    vp = ctypes.c_void_p
+    q_p, out_p = vp(q.data_ptr()), vp(out.data_ptr())
+    yx_attend, ctx_p, kv_p, hq = b._L.yx_attend, b._ctx, kv._h, s.hq
+
     def step(i):
         if split_kv:
             b.attend_allgather(kv, i % n_layers, q, s.hq, -1, key_lo, key_hi, out=out)
         else:
-            b.attend(kv, i % n_layers, q, s.hq, out=out)
+            yx_attend(ctx_p, kv_p, i % n_layers, q_p, 0, hq, -1, out_p, 0)
 
     # parity of what is about to be timed (layer 0 holds the unrotated data)
     max_err, cpu_s, oracle_state = None, None, None
