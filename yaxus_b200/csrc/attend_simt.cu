@@ -4,7 +4,8 @@
 // Same contract as the reference's `attn_split` (crates/yaxus-backend-gpu/src/shaders.rs:1466-1579):
 // per item (rows, one KV head, a run of keys) it emits, for every query head of the KV head's
 // group, the running maximum m, the sum of exponentials l and the unnormalised output o.
-// A CTA of four warps walks the items the planner gave it.  A warp takes every fourth key;
+// A CTA of four warps walks the items the planner gave it.  A warp takes every fourth key, eight of
+// them in flight;
 // a lane holds four of the 128 dims, so a K or V row is one coalesced 512-byte (f32) or
 // 256-byte (16-bit) read per warp; the four warps' triples are merged in shared memory.
 // K and V are read straight from global memory: each byte is used once per head chunk.
@@ -18,6 +19,7 @@ namespace {
 
 constexpr int WARPS = 4;
 constexpr int HC = 4;  // query heads per sweep over the keys
+constexpr int KU = 8;  // keys a warp has in flight
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ float4 load4(const char *arena, int kv_dtype, uint32_t page, int hkv, int kvh, int tok,
@@ -57,6 +59,11 @@ attend_simt_kernel(const void *__restrict__ q, int q_dtype, int hq, int group, c
     __shared__ float sm_ml[WARPS][HC][2];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float scale = 0.08838834764831845f;   // 1 / sqrt(128), the reference's f32 value
+    // A programmatic dependent of the kernel before it: resident while that kernel finishes, it
+    // waits here for everything earlier to be complete, and only then lets the merge kernel behind
+    // it become resident in turn.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t ib = cta_begin[blockIdx.x], ie = cta_begin[blockIdx.x + 1];
     for (uint32_t ii = ib; ii < ie; ii++) {
         const Item it = items[ii];
@@ -80,39 +87,60 @@ attend_simt_kernel(const void *__restrict__ q, int q_dtype, int hq, int group, c
                     l[g] = 0.0f;
                     o[g] = make_float4(0.f, 0.f, 0.f, 0.f);
                 }
-                for (uint64_t key = (uint64_t)k0 + warp; key <= k1; key += WARPS) {
-                    uint32_t page = pages[it.pt_off + (uint32_t)(key / PAGE)];
-                    if (page >= kv_pages) {   // recorded, the access is skipped
-                        if (lane == 0 && atomicCAS(&status->code, 0, 1) == 0) {
-                            status->where = 100;
-                            status->a = (int)page;
-                            status->b = (int)row;
-                        }
-                        continue;
+                // KU keys of this warp at a time: their page ids, then their K and V rows, are asked
+                // for together, so a round costs two memory latencies instead of two per key.
+                for (uint64_t key0 = (uint64_t)k0 + warp; key0 <= k1; key0 += (uint64_t)WARPS * KU) {
+                    float4 kk[KU], vv[KU];
+                    bool live[KU];
+                    uint32_t page[KU];
+#pragma unroll
+                    for (int u = 0; u < KU; u++) {
+                        const uint64_t key = key0 + (uint64_t)u * WARPS;
+                        live[u] = key <= k1;
+                        page[u] = live[u] ? pages[it.pt_off + (uint32_t)(key / PAGE)] : 0u;
                     }
-                    int tok = (int)(key % PAGE);
-                    float4 kk = load4(k_arena, kv_dtype, page, hkv, kvh, tok, lane);
-                    float4 vv = load4(v_arena, kv_dtype, page, hkv, kvh, tok, lane);
-                    float s[HC];
 #pragma unroll
-                    for (int g = 0; g < HC; g++)
-                        s[g] = qv[g].x * kk.x + qv[g].y * kk.y + qv[g].z * kk.z + qv[g].w * kk.w;
+                    for (int u = 0; u < KU; u++) {
+                        const uint64_t key = key0 + (uint64_t)u * WARPS;
+                        if (live[u] && page[u] >= kv_pages) {   // recorded, the access is skipped
+                            if (lane == 0 && atomicCAS(&status->code, 0, 1) == 0) {
+                                status->where = 100;
+                                status->a = (int)page[u];
+                                status->b = (int)row;
+                            }
+                            live[u] = false;
+                        }
+                        kk[u] = vv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (live[u]) {
+                            const int tok = (int)(key % PAGE);
+                            kk[u] = load4(k_arena, kv_dtype, page[u], hkv, kvh, tok, lane);
+                            vv[u] = load4(v_arena, kv_dtype, page[u], hkv, kvh, tok, lane);
+                        }
+                    }
 #pragma unroll
-                    for (int off = 16; off > 0; off >>= 1)
+                    for (int u = 0; u < KU; u++) {
+                        if (!live[u]) continue;   // (uniform over the warp)
+                        float s[HC];
 #pragma unroll
-                        for (int g = 0; g < HC; g++) s[g] += __shfl_xor_sync(0xffffffffu, s[g], off);
+                        for (int g = 0; g < HC; g++)
+                            s[g] = qv[g].x * kk[u].x + qv[g].y * kk[u].y + qv[g].z * kk[u].z + qv[g].w * kk[u].w;
 #pragma unroll
-                    for (int g = 0; g < HC; g++) {
-                        float sc = s[g] * scale;
-                        float mn = fmaxf(m[g], sc);
-                        float a = exp2f((m[g] - mn) * LOG2E);   // 0 on the first key (m = -inf)
-                        float e = exp2f((sc - mn) * LOG2E);
-                        l[g] = l[g] * a + e;
-                        o[g].x = o[g].x * a + e * vv.x;
-                        o[g].y = o[g].y * a + e * vv.y;
-                        o[g].z = o[g].z * a + e * vv.z;
-                        o[g].w = o[g].w * a + e * vv.w;
-                        m[g] = mn;
+                        for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+                            for (int g = 0; g < HC; g++) s[g] += __shfl_xor_sync(0xffffffffu, s[g], off);
+#pragma unroll
+                        for (int g = 0; g < HC; g++) {
+                            float sc = s[g] * scale;
+                            float mn = fmaxf(m[g], sc);
+                            float a = exp2f((m[g] - mn) * LOG2E);   // 0 on the first key (m = -inf)
+                            float e = exp2f((sc - mn) * LOG2E);
+                            l[g] = l[g] * a + e;
+                            o[g].x = o[g].x * a + e * vv[u].x;
+                            o[g].y = o[g].y * a + e * vv[u].y;
+                            o[g].z = o[g].z * a + e * vv[u].z;
+                            o[g].w = o[g].w * a + e * vv[u].w;
+                            m[g] = mn;
+                        }
                     }
                 }
 #pragma unroll
@@ -157,10 +185,23 @@ attend_simt_kernel(const void *__restrict__ q, int q_dtype, int hq, int group, c
 }  // namespace
 
 int launch_attend_simt(yx_ctx *ctx, const AttendArgs &a) {
-    attend_simt_kernel<<<a.n_ctas, WARPS * 32, 0, ctx->stream>>>(
-        a.q, a.q_dtype, a.hq, a.group, a.k_arena, a.v_arena, a.hkv, a.kv_dtype, a.kv_pages,
-        (uint32_t)std::max<int64_t>(a.window, 0), ctx->d_pos, ctx->d_pages, a.items, a.cta_begin, a.part_o, a.part_ml,
-        ctx->dev_status);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)a.n_ctas);
+    cfg.blockDim = dim3(WARPS * 32);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const uint32_t window = (uint32_t)std::max<int64_t>(a.window, 0);
+    if (int rc = check_cuda(ctx,
+                            cudaLaunchKernelEx(&cfg, attend_simt_kernel, a.q, a.q_dtype, a.hq, a.group, (const char *)a.k_arena,
+                                               (const char *)a.v_arena, a.hkv, a.kv_dtype, a.kv_pages, window,
+                                               (const uint32_t *)ctx->d_pos, (const uint32_t *)ctx->d_pages, a.items, a.cta_begin,
+                                               a.part_o, a.part_ml, ctx->dev_status),
+                            "attend_simt kernel launch"))
+        return rc;
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "attend_simt kernel");
 }
