@@ -308,6 +308,27 @@ def test_back_to_back_calls_each_get_their_own_answer(backend, oracle, kv_dtype)
     kv.close()
 
 
+def test_a_call_fed_by_the_call_before_waits_for_it(backend, oracle):
+    # Back-to-back calls overlap only when the second one's queries cannot be the first one's
+    # output.  Here they are: the second call must see the finished result of the first.
+    s = W.batched_decode(seed=9)
+    kv = load(backend, s, n_layers=2)
+    backend.begin_pass(s.meta)
+    for l in range(2):
+        backend.kv_append(kv, l, dev(backend, s.k_new), dev(backend, s.v_new))
+    q = dev(backend, s.q)
+    warm = torch.empty_like(q)
+    backend.attend(kv, 0, q, s.hq, out=warm)          # so that the next two calls follow an attention call
+    mid = torch.zeros_like(q)
+    backend.attend(kv, 0, q, s.hq, out=mid)
+    out = backend.attend(kv, 1, mid, s.hq)            # reads what the call before wrote
+    ref_mid = oracle_step(oracle, s)
+    ref = oracle_step(oracle, s, q=ref_mid)
+    assert_close(backend.to_host(mid), ref_mid, what="first call")
+    assert_close(backend.to_host(out), ref, what="second call")
+    kv.close()
+
+
 def test_empty_pass(backend):
     s = W.build("e", 1, 8, 2, F16, [10], [1])
     kv = load(backend, s)

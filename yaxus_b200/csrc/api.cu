@@ -383,6 +383,18 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     // counters - is an ordering point of its own and was counted in ctx->launches or reset last_launch)
     a.late_wait = predecessor_is_split_key_call && ctx->last_launch == yx_ctx::LAST_SPLIT_KEY && !a.fused &&
                   ctx->tuning.overlap_calls != 2 && !ctx->profiling;
+    {
+        // ... unless these queries are what the call ahead wrote (its merge may still be running).
+        const uintptr_t q_lo = (uintptr_t)q, q_hi = q_lo + (size_t)ctx->pass.rows * hq * D * (q_dtype == YX_F32 ? 4 : 2);
+        for (const auto &w : ctx->last_written)
+            if (w.hi > w.lo && q_lo < w.hi && w.lo < q_hi) a.late_wait = false;
+        const size_t n = (size_t)ctx->pass.rows * hq;
+        const size_t out_b = n * D * (out_dtype == YX_F32 ? 4 : 2);
+        ctx->last_written[0] = {(uintptr_t)out, out ? (uintptr_t)out + out_b : 0};
+        ctx->last_written[1] = {(uintptr_t)o_out, o_out ? (uintptr_t)o_out + n * D * 4 : 0};
+        ctx->last_written[2] = {(uintptr_t)m_out, m_out ? (uintptr_t)m_out + n * 4 : 0};
+        ctx->last_written[3] = {(uintptr_t)l_out, l_out ? (uintptr_t)l_out + n * 4 : 0};
+    }
     a.counters = ctx->counters;
     a.out = out;
     a.out_dtype = out_dtype;

@@ -265,6 +265,11 @@ struct yx_ctx {
     // (see AttendArgs::late_wait).
     enum { LAST_OTHER = 0, LAST_APPEND, LAST_ATTEND, LAST_KV_WRITE, LAST_SPLIT_KEY };
     int last_launch = LAST_OTHER;
+    // What the last attention call wrote (its output and, for partial calls, its triples): a call whose
+    // queries lie in there reads the result of the call ahead and must wait for it like any other.
+    struct Range {
+        uintptr_t lo = 0, hi = 0;
+    } last_written[4];
     uint64_t last_append_serial = 0;
 
     yx_dev_status *dev_status = nullptr;   // pinned, mapped
@@ -392,7 +397,8 @@ struct AttendArgs {
     bool late_wait;          // the kernels ahead are a split-key attention call of this context and its merge, and
                              // everything before that call is complete once this kernel runs: keys, values,
                              // queries and the plan are read at once, and the grid dependency is waited for only
-                             // before the first write (the partial buffers, which the merge ahead still reads)
+                             // before the first write (the partial buffers, which the merge ahead still reads).
+                             // Not set when the queries overlap what that call writes.
     bool fused;              // merge inside the split-key kernel
     uint32_t *counters;      // one per (pass row, kv head), zero between launches
     void *out;               // normalised output, or null
