@@ -125,31 +125,58 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
                 }
             }
         }
-        std::stable_sort(out.tile_items.begin(), out.tile_items.end(), [](const TileItem &a, const TileItem &b) {
-            return a.page_end - a.page_begin > b.page_end - b.page_begin;
-        });
         // Deal the items to the persistent CTAs of the tiled kernel: longest first, each to the
-        // CTA with the least work so far.  An item costs its pages plus a fixed part (Q tile in,
-        // output tile out, pipeline fill), about three pages' worth.
+        // CTA with the least work so far (among equals the one that has waited longest).  An item
+        // costs its pages plus a fixed part (Q tile in, output tile out, pipeline fill), about
+        // three pages' worth.  Costs are small integers, so "longest first" is a counting sort and
+        // "least loaded" a row of FIFO buckets by load: this runs on the critical path of every
+        // prompt pass, and a heap of 148 CTAs and a list per CTA cost 45 us of its 100.
         if (!out.tile_items.empty()) {
             const int n_items = (int)out.tile_items.size();
             const int G = std::max(1, std::min(n_items, pp.tile_ctas > 0 ? pp.tile_ctas : n_items));
-            using Load = std::pair<uint64_t, int>;   // (work, CTA)
-            std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
-            for (int c = 0; c < G; c++) heap.push({0, c});
-            std::vector<std::vector<TileItem>> per(G);
+            std::vector<TileItem> &sorted = out.scratch_tile_items;
+            sorted.resize(n_items);
+            uint32_t max_len = 0;
+            uint64_t total_cost = 0;
             for (const TileItem &ti : out.tile_items) {
-                Load top = heap.top();
-                heap.pop();
-                per[top.second].push_back(ti);
-                heap.push({top.first + (ti.page_end - ti.page_begin) + 3, top.second});
+                max_len = std::max(max_len, ti.page_end - ti.page_begin);
+                total_cost += ti.page_end - ti.page_begin + 3;
             }
-            out.tile_items.clear();
-            out.tile_cta_begin.assign(1, 0);
-            for (int c = 0; c < G; c++) {
-                out.tile_items.insert(out.tile_items.end(), per[c].begin(), per[c].end());
-                out.tile_cta_begin.push_back((uint32_t)out.tile_items.size());
+            std::vector<uint32_t> &at = out.scratch_lengths;   // counting sort by length, longest first, stable
+            at.assign((size_t)max_len + 2, 0);
+            for (const TileItem &ti : out.tile_items) at[max_len - (ti.page_end - ti.page_begin) + 1]++;
+            for (uint32_t l = 1; l <= max_len + 1; l++) at[l] += at[l - 1];
+            for (const TileItem &ti : out.tile_items) sorted[at[max_len - (ti.page_end - ti.page_begin)]++] = ti;
+            // FIFO buckets of CTAs by load; a load never exceeds the even share plus one item.
+            const size_t n_loads = (size_t)(total_cost / (uint64_t)G) + max_len + 3 + 2;
+            std::vector<uint32_t> &links = out.scratch_links;   // head[n_loads] | tail[n_loads] | next[G] | cta_of[n_items] | count[G + 1]
+            const uint32_t NONE = UINT32_MAX;
+            links.assign(2 * n_loads + (size_t)G + (size_t)n_items + (size_t)G + 1, NONE);
+            uint32_t *head = links.data(), *tail = head + n_loads, *next = tail + n_loads, *cta_of = next + G, *count = cta_of + n_items;
+            for (int c = 0; c < G; c++) {   // all at load 0, in order
+                next[c] = c + 1 < G ? (uint32_t)c + 1 : NONE;
+                count[c] = 0;
             }
+            count[G] = 0;
+            head[0] = 0;
+            tail[0] = (uint32_t)G - 1;
+            size_t lowest = 0;
+            for (int i = 0; i < n_items; i++) {
+                while (head[lowest] == NONE) lowest++;
+                const uint32_t c = head[lowest];
+                head[lowest] = next[c];
+                if (head[lowest] == NONE) tail[lowest] = NONE;
+                const size_t load = lowest + (sorted[i].page_end - sorted[i].page_begin) + 3;
+                next[c] = NONE;
+                if (head[load] == NONE) head[load] = c;
+                else next[tail[load]] = c;
+                tail[load] = c;
+                cta_of[i] = c;
+                count[c + 1]++;
+            }
+            for (int c = 0; c < G; c++) count[c + 1] += count[c];
+            out.tile_cta_begin.assign(count, count + G + 1);
+            for (int i = 0; i < n_items; i++) out.tile_items[count[cta_of[i]]++] = sorted[i];
         }
     }
 
@@ -413,7 +440,9 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
     int n_ctas = (int)std::min<uint64_t>((uint64_t)std::max(1, pp.n_ctas), std::max<uint64_t>(total_tiles, 1));
     out.n_ctas = n_ctas;
     out.cta_begin.assign(n_ctas + 1, 0);
-    out.merges.assign((size_t)T * pp.hkv, Merge{0, 0});
+    // (a pass that the tiled kernel takes whole has nothing to merge)
+    const bool merges_needed = !units.empty() || out.tile_items.empty();
+    if (merges_needed) out.merges.assign((size_t)T * pp.hkv, Merge{0, 0});
 
     // How much of a run of `left` tiles goes into a CTA that holds `load` already, under `lim`:
     // 0 = none (close the CTA first, unless it is empty: then the limit is too small).
@@ -548,6 +577,7 @@ void build_split_plan(const PassHost &pass, const PlanParams &pp, Plan &out) {
         }
     for (const Merge &m : out.merges)
         if (m.count == 0) out.has_empty_rows = true;
+    if (!merges_needed) out.has_empty_rows = false;
 
     // 6. The resolved form: page tables walked here, once, instead of by every CTA.  (Plain
     //    pointers into arrays sized up front: this loop is most of the cost of planning a decode

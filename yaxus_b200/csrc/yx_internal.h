@@ -151,6 +151,8 @@ struct Plan {
     std::vector<CtaPrologue> prologue;  // one per CTA (resolved form)
     std::vector<uint32_t> scratch_dense, scratch_seen, scratch_once;   // planner scratch, kept for its capacity
     std::vector<uint64_t> scratch_table;
+    std::vector<TileItem> scratch_tile_items;
+    std::vector<uint32_t> scratch_lengths, scratch_links;
     uint64_t last_limit = 0;            // per-CTA load limit the last plan settled on (starting point of the next search)
     // What the last plan was built from, so that a pass with the same shape (the next decode step:
     // every row one key further, no new tile, no new page) only has its key ranges patched in.
