@@ -330,7 +330,8 @@ def run_split_key(env, name, s, calls, warm, check=True, e2e=False, cpu=False, k
     bracketed_ms = split_ms / max(n_prof, 1)
     (bracketed_ms,) = env.max_over_ranks([bracketed_ms])
     kernel_ms = bracketed_ms
-    if kernel_only and not split_kv:
+    chain_timed = kernel_only and (not split_kv or world == 1)
+    if chain_timed:
         # ... and as it runs in the stream: back-to-back launches of that kernel between two events
         b.hook_skip_merge(True)
         kernel_ms, _, _ = env.timed(step, calls, 20)
@@ -357,7 +358,7 @@ def run_split_key(env, name, s, calls, warm, check=True, e2e=False, cpu=False, k
                          "how": ("kernel_ms: back-to-back launches of the kernel alone between two CUDA events (its "
                                  "issue interval in the stream, programmatic dependent launch in effect); "
                                  "kernel_ms_bracketed: events around every single launch"
-                                 if kernel_only and not split_kv else "kernel_ms: events around every single launch"),
+                                 if chain_timed else "kernel_ms: events around every single launch"),
                          "combine_ms": combine_ms / max(n_prof, 1), "algorithmic_bytes": per_rank_bytes},
             "host_us_per_call": host_us, "clocks": clocks, "gpu_launches": int(launches_per_call * calls),
             "plan": {"path": info.path, "ctas": info.n_ctas, "items": info.n_items, "parts": info.n_parts,
@@ -736,7 +737,7 @@ def run_cuda(args):
                     if long_s is None:
                         long_s = make_scenario("long_decode", 0)
                     s = long_s if name == "long_decode" else dataclasses.replace(long_s, window=2048)
-                    rec = run_split_key(env, name, s, 300, warm, check=not args.no_check)
+                    rec = run_split_key(env, name, s, 300, warm, check=not args.no_check, kernel_only=True)
                 else:
                     rec = run_split_key(env, name, make_scenario(name, env.rank), 500, warm, check=not args.no_check, kernel_only=True)
             except AssertionError as e:     # a parity failure is reported, not hidden

@@ -463,6 +463,12 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
 }
 
 }  // namespace
+
+int attend_key_range(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, int hq, int64_t window, uint64_t key_lo,
+                     uint64_t key_hi, void *out, int out_dtype) {
+    return attend_impl(ctx, kv, layer, q, q_dtype, hq, window, key_lo, key_hi, out, out_dtype, nullptr, nullptr, nullptr);
+}
+
 }  // namespace yx
 
 using namespace yx;

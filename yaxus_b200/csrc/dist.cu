@@ -115,6 +115,8 @@ int yx_attend_allgather(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_
     if (ctx->n_ranks > 1 && !ctx->comm) return fail(ctx, YX_ERR_STATE, "attend_allgather without a communicator");
     const size_t n = (size_t)ctx->pass.rows * hq;
     if (n == 0) return YX_OK;
+    // One rank has nothing to exchange: the split-key kernel's merge writes the output itself.
+    if (ctx->n_ranks <= 1) return attend_key_range(ctx, kv, layer, q, q_dtype, hq, window, key_lo, key_hi, out, out_dtype);
     const size_t block = n * (D + 2);   // floats per rank: m | l | o
     int prev = -1;
     cudaGetDevice(&prev);

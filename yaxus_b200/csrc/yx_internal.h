@@ -358,6 +358,9 @@ int check_cuda(yx_ctx *ctx, cudaError_t e, const char *what);
 // Stream-ordered upload of `bytes` from pageable host memory through the pinned ring.
 int upload_ordered(yx_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes);
 int ensure_buffer(yx_ctx *ctx, void **buf, size_t *cap, size_t bytes);
+// yx_attend over the keys [key_lo, key_hi) only: what one rank alone has to do for yx_attend_allgather.
+int attend_key_range(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, int hq, int64_t window, uint64_t key_lo,
+                     uint64_t key_hi, void *out, int out_dtype);
 // Destroys the context's cuBLASLt handle, if it made one.
 void release_matmul_library(yx_ctx *ctx);
 
