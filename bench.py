@@ -8,7 +8,7 @@ The line it prints is headed by batched paged decode attention: 16 sequences sha
 32 query / 8 KV heads, head_dim 128, f16 cache, f32 accumulation.  A step is one attention
 call over the batch (one layer); steps rotate over several layers' arenas, so the pages of a
 step are not in L2 from the step before.  The metric is HBM GB/s over the step's unique K+V
-bytes.  At least 2000 calls are timed whatever K is (`config.timed_calls`).
+bytes.  At least 10000 calls are timed whatever K is (`config.timed_calls`).
 
 Under `workloads` the same line carries the other configurations of the path, each with its
 own value, roofline and parity: chunked causal prefill (bf16, 8 x 4096 tokens in 512-row
@@ -42,7 +42,7 @@ from yaxus_b200 import workloads as W  # noqa: E402
 from yaxus_b200._lib import BF16, F16, F32  # noqa: E402
 
 METRIC = "paged decode-attn HBM GB/s @B=16"
-MIN_TIMED_CALLS = 2000
+MIN_TIMED_CALLS = 10000   # 0.2 s of device time: the clock sampler (one line per 100 ms) sees the timed region
 DTYPE_NAME = {F32: "f32", F16: "f16", BF16: "bf16"}
 L2_BYTES = 126e6
 
@@ -732,14 +732,14 @@ def run_cuda(args):
                 if name == "prefill":
                     rec = run_prefill(env, 5, 3, "bf16", check=not args.no_check)
                 elif name == "decode_matmul_glu":
-                    rec = run_matmul(env, 300, warm, check=not args.no_check)
+                    rec = run_matmul(env, 2000, warm, check=not args.no_check)
                 elif name.startswith("long_decode"):
                     if long_s is None:
                         long_s = make_scenario("long_decode", 0)
                     s = long_s if name == "long_decode" else dataclasses.replace(long_s, window=2048)
-                    rec = run_split_key(env, name, s, 300, warm, check=not args.no_check, kernel_only=True)
+                    rec = run_split_key(env, name, s, 3000, warm, check=not args.no_check, kernel_only=True)
                 else:
-                    rec = run_split_key(env, name, make_scenario(name, env.rank), 500, warm, check=not args.no_check, kernel_only=True)
+                    rec = run_split_key(env, name, make_scenario(name, env.rank), 3000, warm, check=not args.no_check, kernel_only=True)
             except AssertionError as e:     # a parity failure is reported, not hidden
                 rec = {"error": str(e)[:300]} if env.rank == 0 else None
             if rec is not None:
@@ -767,7 +767,7 @@ def main():
                     help="cache storage type of the prefill workload (default bf16)")
     ap.add_argument("--headline-only", action="store_true", help="leave the other workloads' records out")
     ap.add_argument("--calls", type=int, default=0,
-                    help="time exactly this many calls of the headline workload (for profiler captures; default: at least 2000)")
+                    help="time exactly this many calls of the headline workload (for profiler captures; default: at least 10000)")
     ap.add_argument("--no-check", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

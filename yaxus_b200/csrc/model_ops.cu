@@ -341,9 +341,8 @@ struct Lt {
     bool ok() const { return matmul != nullptr; }
 };
 
-Lt &lt() {
-    static Lt l;
-    if (l.tried) return l;
+Lt load_lt() {
+    Lt l;
     l.tried = true;
     const char *names[] = {"libcublasLt.so.12", "libcublasLt.so", "/usr/local/cuda/lib64/libcublasLt.so.12"};
     for (const char *n : names) {
@@ -367,6 +366,12 @@ Lt &lt() {
     if (l.create && l.destroy && l.desc_create && l.desc_destroy && l.desc_set && l.layout_create && l.layout_destroy &&
         l.pref_create && l.pref_destroy && l.pref_set && l.heuristic)
         l.matmul = mm;
+    return l;
+}
+
+// (initialised once, by whichever thread comes first)
+Lt &lt() {
+    static Lt l = load_lt();
     return l;
 }
 
