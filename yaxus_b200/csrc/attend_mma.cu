@@ -267,7 +267,30 @@ __device__ void produce(const Params &P, const Shared &S, const CtaHdr hdr, int 
         const TileDesc t = P.pro[blockIdx.x].first[j];
         if (YX_TR(P.trace != nullptr) && lane == 0 && j == 0) P.trace[16 * blockIdx.x + 15] = gtime() + (t.block & 1u);
         gate(t.info);
-        alive = issue_tile(I, pipe, t.block, t.info, lane);
+        // The CTA's very first tiles go out by the shortest way there is: their stages have never
+        // been used (nothing to wait for) and a whole tile needs no zeroing.
+        const uint32_t half = t.info & 1u, r0 = (t.info >> 1) & 127u, n = (t.info >> 8) & 255u;
+        if (j == 0 && n == (uint32_t)TILE_KEYS && r0 == 0u && t.block < P.n_blocks && pipe.phase == 0u) {
+            if (lane == 0) {
+                const uint32_t bar = S.full + 8 * pipe.stage, dst = S.stages + pipe.stage * STAGE_BYTES;
+                const size_t off = (size_t)t.block * (PAGE * D * 2) + (size_t)(half * TILE_KEYS) * 128;
+                mbar_expect_tx(bar, 4 * SUB_BYTES);
+                if (P.single_use && !(t.info & TILE_REUSED)) {
+                    bulk_g2s_hint(dst, P.k_arena + off, SUB_BYTES, bar, I.policy);
+                    bulk_g2s_hint(dst + SUB_BYTES, P.k_arena + off + PAGE * 128, SUB_BYTES, bar, I.policy);
+                    bulk_g2s_hint(dst + 2 * SUB_BYTES, P.v_arena + off, SUB_BYTES, bar, I.policy);
+                    bulk_g2s_hint(dst + 3 * SUB_BYTES, P.v_arena + off + PAGE * 128, SUB_BYTES, bar, I.policy);
+                } else {
+                    bulk_g2s(dst, P.k_arena + off, SUB_BYTES, bar);
+                    bulk_g2s(dst + SUB_BYTES, P.k_arena + off + PAGE * 128, SUB_BYTES, bar);
+                    bulk_g2s(dst + 2 * SUB_BYTES, P.v_arena + off, SUB_BYTES, bar);
+                    bulk_g2s(dst + 3 * SUB_BYTES, P.v_arena + off + PAGE * 128, SUB_BYTES, bar);
+                }
+            }
+            pipe.advance(P.n_stages);
+        } else {
+            alive = issue_tile(I, pipe, t.block, t.info, lane);
+        }
         if (YX_TR(P.trace != nullptr) && lane == 0 && j == 0) P.trace[16 * blockIdx.x + 2] = gtime();
     }
     c += skip;
