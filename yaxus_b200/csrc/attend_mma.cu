@@ -115,6 +115,9 @@ struct Pipe {
 };
 
 constexpr int MAX_PROLOGUE_CTAS = 160;
+#ifndef YX_FAST_TILES
+#define YX_FAST_TILES 1   // tiles of a CTA issued by the short way (more than one: see the notes on what was tried)
+#endif
 
 struct Params {
     const void *q;
@@ -270,7 +273,7 @@ __device__ void produce(const Params &P, const Shared &S, const CtaHdr hdr, int 
         // The CTA's very first tiles go out by the shortest way there is: their stages have never
         // been used (nothing to wait for) and a whole tile needs no zeroing.
         const uint32_t half = t.info & 1u, r0 = (t.info >> 1) & 127u, n = (t.info >> 8) & 255u;
-        if (j == 0 && n == (uint32_t)TILE_KEYS && r0 == 0u && t.block < P.n_blocks && pipe.phase == 0u) {
+        if (j < YX_FAST_TILES && n == (uint32_t)TILE_KEYS && r0 == 0u && t.block < P.n_blocks && pipe.phase == 0u) {
             if (lane == 0) {
                 const uint32_t bar = S.full + 8 * pipe.stage, dst = S.stages + pipe.stage * STAGE_BYTES;
                 const size_t off = (size_t)t.block * (PAGE * D * 2) + (size_t)(half * TILE_KEYS) * 128;

@@ -5,7 +5,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
-#include "yx_internal.h"
+#include "yx_device.cuh"
 
 namespace yx {
 namespace {
@@ -30,7 +30,9 @@ __device__ __forceinline__ void store_out(void *out, int out_dtype, size_t elem,
 // loads independent of one another: the merge costs two memory latencies, not two per part.
 __global__ void __launch_bounds__(128) combine_kernel(const Merge *__restrict__ merges, const float *__restrict__ part_o,
                                const float *__restrict__ part_ml, uint32_t n, int hq, int group, void *out,
-                               int out_dtype, float *m_out, float *l_out, float *o_out) {
+                               int out_dtype, float *m_out, float *l_out, float *o_out, unsigned long long *trace) {
+    // (diagnostic build: when this CTA entered and when its wait returned)
+    if (YX_TR(trace != nullptr) && threadIdx.x == 0) trace[TRACE_MERGE_BASE + 4 * blockIdx.x] = dev::gtime();
     uint32_t idx = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     int lane = threadIdx.x & 31;
     if (idx >= n) return;
@@ -45,6 +47,7 @@ __global__ void __launch_bounds__(128) combine_kernel(const Merge *__restrict__ 
     // visible.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (YX_TR(trace != nullptr) && threadIdx.x == 0) trace[TRACE_MERGE_BASE + 4 * blockIdx.x + 1] = dev::gtime();
     if (mg.count == 0 && !o_out) return;   // the row was another kernel's (tiled path)
     float mx = -1e30f, l = 0.0f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -120,6 +123,7 @@ __global__ void __launch_bounds__(128) combine_kernel(const Merge *__restrict__ 
             l_out[idx] = l;
         }
     }
+    if (YX_TR(trace != nullptr) && threadIdx.x == 0) trace[TRACE_MERGE_BASE + 4 * blockIdx.x + 2] = dev::gtime();
 }
 
 // Part c of element idx: m[c * sm + idx], l[c * sl + idx], o[c * so + idx * 128 ..].
@@ -188,7 +192,8 @@ int launch_combine(yx_ctx *ctx, const Merge *merges, const float *part_o, const 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (int rc = check_cuda(ctx, cudaLaunchKernelEx(&cfg, combine_kernel, merges, part_o, part_ml, n, hq, group, out, out_dtype, m_out, l_out, o_out),
+    if (int rc = check_cuda(ctx, cudaLaunchKernelEx(&cfg, combine_kernel, merges, part_o, part_ml, n, hq, group, out, out_dtype, m_out, l_out, o_out,
+                                                    (unsigned long long *)ctx->trace_buf),
                             "combine kernel launch"))
         return rc;
     ctx->launches++;

@@ -93,6 +93,9 @@ struct TileDesc {
 // pass: the kernel that ran just before the attention kernel (the append) may have written it.
 // Every other tile was complete before that kernel started, so the attention kernel may copy it
 // before it waits for its grid dependency.
+// Where the merge kernel's time stamps start in a diagnostic trace buffer (u64 slots; the split-key
+// kernel has 16 per CTA below it), four per merge CTA.
+constexpr int TRACE_MERGE_BASE = 160 * 16;
 constexpr uint32_t TILE_REUSED = 1u << 16;
 constexpr uint32_t TILE_FRESH = 1u << 17;
 
