@@ -503,7 +503,8 @@ def run_matmul(env, calls, warm, check=True):
                "config": {"workload": "decode_matmul_glu", "rows": T, "n": N, "k": K, "timed_calls": calls,
                           "l2": f"calls rotate over {n_w} weights ({n_w} x {w_bytes >> 20} MiB > L2)"},
                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
-                            "frac": achieved / peaks["hbm"], "traffic": None, "peak_source": peaks["source"],
+                            "frac": achieved / peaks["hbm"], "traffic": captured_traffic("matmul_rows_kernel_decode_matmul_glu")[0],
+                            "traffic_source": captured_traffic("matmul_rows_kernel_decode_matmul_glu")[1], "peak_source": peaks["source"],
                             "kernel": "matmul_rows_kernel", "algorithmic_bytes": float(w_bytes),
                             "how": "the whole call (packing, the matmul kernel, the finishing kernel) between two CUDA events"},
                "host_us_per_call": host_us, "clocks": clocks, "gpu_launches": int(launches_per_call * calls),
@@ -720,6 +721,8 @@ def run_cuda(args):
     head_name = args.workload or "batched_decode"
     if head_name == "prefill":
         head = run_prefill(env, max(1, min(args.steps, 50)), warm, args.kv_dtype or "bf16", check=not args.no_check, e2e=True)
+    elif head_name == "decode_matmul_glu":
+        head = run_matmul(env, args.calls if args.calls > 0 else 2000, warm, check=not args.no_check)
     else:
         head = run_split_key(env, head_name, make_scenario(head_name, env.rank), calls, warm, check=not args.no_check,
                              e2e=True, cpu=not args.no_cpu, kernel_only=True)
