@@ -485,7 +485,7 @@ int matmul_impl(yx_ctx *ctx, const float *x, const void *w_bf16, uint32_t T, uin
     Guard guard(ctx->device);
     const __nv_bfloat16 *w = (const __nv_bfloat16 *)w_bf16;
     const uint32_t cols = glu ? N / 2 : N;
-    if (K % (MM_STEP * MM_AHEAD) != 0 || ((uintptr_t)w & 15u) != 0) {
+    if (K % (MM_STEP * MM_AHEAD) != 0 || ((uintptr_t)w & 15u) != 0 || ((uintptr_t)x & 7u) != 0) {
         float *dst = out;
         if (glu) {
             if (int rc = ensure_buffer(ctx, (void **)&ctx->mm_part, &ctx->mm_part_cap, (size_t)T * N * sizeof(float))) return rc;
