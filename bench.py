@@ -221,8 +221,9 @@ def make_scenario(name, rank):
 
 
 def layers_needed(bytes_per_call):
-    """Arenas to rotate over so that a call does not find its pages in L2 from an earlier call."""
-    return max(1, min(48, int(math.ceil(4.0 * L2_BYTES / max(bytes_per_call, 1)))))
+    """Arenas to rotate over so that a call does not find its pages in L2 from an earlier call (at least
+    two, also where one arena is several times L2: consecutive calls overlap on the device)."""
+    return max(2, min(48, int(math.ceil(4.0 * L2_BYTES / max(bytes_per_call, 1)))))
 
 
 def workload_config(name, s, n_gpus, n_layers, split_kv):

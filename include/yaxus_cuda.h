@@ -78,7 +78,8 @@ typedef struct yx_tuning {
     int32_t tile_single;     /* 1: the tcgen05 tile kernel takes one query head per CTA (default: two) */
     int32_t min_piece;       /* fewest 64-key tiles the planner makes an item of when it cuts a run (0: default) */
     int32_t overlap_calls;   /* 2: an attention call that directly follows another one on the stream waits for it
-                                before it reads anything (0: default, it waits before its first write) */
+                                before it reads anything; 3: it waits before its first write (0: default, that or,
+                                where the call ahead filled every SM, before its CTAs leave) */
 } yx_tuning;
 
 /* What the last yx_attend / yx_attention call planned; for tests and benchmarks. */

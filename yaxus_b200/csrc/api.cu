@@ -325,10 +325,16 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     if (ctx->pass.max_page_seen >= kv->pages && !ctx->pass.pages.empty() && key_lo == 0 && key_hi == UINT64_MAX)
         return fail(ctx, YX_ERR_INVALID, "page id outside the KV arena");
 
-    size_t o_bytes = (size_t)std::max<uint32_t>(pl.n_parts, 1) * group * D * sizeof(float);
-    size_t ml_bytes = (size_t)std::max<uint32_t>(pl.n_parts, 1) * group * 2 * sizeof(float);
-    if (int rc = ensure_buffer(ctx, (void **)&ctx->ws_o, &ctx->ws_o_cap, o_bytes)) return rc;
-    if (int rc = ensure_buffer(ctx, (void **)&ctx->ws_ml, &ctx->ws_ml_cap, ml_bytes)) return rc;
+    // Two sets of partial buffers, taken in turn by successive calls: a split-key kernel that runs
+    // while the merge of the call ahead still reads that call's triples writes its own elsewhere
+    // (see AttendArgs::late_wait).
+    const size_t o_bytes = ((size_t)std::max<uint32_t>(pl.n_parts, 1) * group * D * sizeof(float) + 255) / 256 * 256;
+    const size_t ml_bytes = ((size_t)std::max<uint32_t>(pl.n_parts, 1) * group * 2 * sizeof(float) + 255) / 256 * 256;
+    if (int rc = ensure_buffer(ctx, (void **)&ctx->ws_o, &ctx->ws_o_cap, 2 * o_bytes)) return rc;
+    if (int rc = ensure_buffer(ctx, (void **)&ctx->ws_ml, &ctx->ws_ml_cap, 2 * ml_bytes)) return rc;
+    ctx->ws_set ^= 1;
+    float *const part_o = ctx->ws_o + (size_t)ctx->ws_set * (o_bytes / sizeof(float));
+    float *const part_ml = ctx->ws_ml + (size_t)ctx->ws_set * (ml_bytes / sizeof(float));
     if (path == 2) {
         // Arrival counters of the fused merge: zero when allocated, and every launch leaves
         // them zero again.
@@ -368,8 +374,8 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     a.items = cp->d_items;
     a.cta_begin = cp->d_cta_begin;
     a.n_ctas = pl.n_ctas;
-    a.part_o = ctx->ws_o;
-    a.part_ml = ctx->ws_ml;
+    a.part_o = part_o;
+    a.part_ml = part_ml;
     a.cta_hdr = cp->d_cta_hdr;
     a.tiles = cp->d_tiles;
     a.recs = cp->d_recs;
@@ -395,6 +401,12 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
         ctx->last_written[2] = {(uintptr_t)m_out, m_out ? (uintptr_t)m_out + n * 4 : 0};
         ctx->last_written[3] = {(uintptr_t)l_out, l_out ? (uintptr_t)l_out + n * 4 : 0};
     }
+    // When the kernel of the call ahead had a CTA for every SM, no CTA of this kernel can run before
+    // one of that kernel's has left, which it does only once everything ahead of it is complete
+    // (the merge that last read the set of partial buffers this call writes included).  The wait can
+    // then move from before a CTA's first write to before it leaves.
+    a.wait_at_end = a.late_wait && ctx->last_split_ctas >= ctx->sm_count && ctx->tuning.overlap_calls != 3;
+    ctx->last_split_ctas = path == 2 && !pl.items.empty() ? pl.n_ctas : 0;
     a.counters = ctx->counters;
     a.out = out;
     a.out_dtype = out_dtype;
@@ -438,7 +450,7 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
         profile_mark(ctx, 1);
         profile_mark(ctx, 2);
         if (!a.fused && need_combine)
-            if (int rc = launch_combine(ctx, cp->d_merges, ctx->ws_o, ctx->ws_ml, (int)ctx->pass.rows, hq, group, out,
+            if (int rc = launch_combine(ctx, cp->d_merges, part_o, part_ml, (int)ctx->pass.rows, hq, group, out,
                                         out_dtype, m_out, l_out, o_out))
                 return rc;
         host_clock_lap(ctx, 6);
@@ -449,7 +461,7 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
         profile_mark(ctx, 1);
         profile_mark(ctx, 2);
         if (need_combine)
-            if (int rc = launch_combine(ctx, cp->d_merges, ctx->ws_o, ctx->ws_ml, (int)ctx->pass.rows, hq, group, out,
+            if (int rc = launch_combine(ctx, cp->d_merges, part_o, part_ml, (int)ctx->pass.rows, hq, group, out,
                                         out_dtype, m_out, l_out, o_out))
                 return rc;
         profile_mark(ctx, 3);

@@ -140,6 +140,7 @@ struct Params {
     int n_stages;                    // stages of the ring in use (2..STAGES): bytes in flight per SM
     int early_kv;                    // tiles not marked TILE_FRESH may be copied before the grid dependency wait
     int late_wait;                   // nothing this kernel reads can still be written: only its writers wait
+    int wait_at_end;                 // ... and they do so before the CTA leaves, not before its first write
     uint32_t n_items, n_tiles, n_parts;   // sizes of the plan's arrays and of the partial buffers, for the kernel's own checks
     unsigned long long q_bytes;      // size of the query tensor
     int has_prologue;
@@ -449,7 +450,7 @@ struct Epilogue {
     volatile int *abort_flag;
     int out_dtype, hq, hkv, group;
     int fused;               // count items in and merge here (else a separate combine kernel merges)
-    int late_wait;           // the grid dependency has not been waited for yet: do so before the first store
+    int late_wait;           // 1: the grid dependency has not been waited for yet, do so before the first store; 2: the kernel waits at its end
     uint32_t n_parts;        // slots in the partial buffers
     uint32_t n_items, first_item;    // this warp takes items first_item, first_item + EWARPS, ...
     uint32_t recbase, qempty, merge, efull, eempty, mlbuf;   // shared-space addresses
@@ -615,7 +616,7 @@ __device__ __noinline__ void epilogue_loop(const Epilogue E, int lane) {
     for (uint32_t ii = 0; ii < E.n_items; ii++, phase ^= 1u) {
         const uint32_t qslot = ii & 1u;
         mbar_wait(E.efull, phase, E.abort_flag, E.status, 5);
-        if (ii == 0 && E.late_wait) grid_dependency_wait();   // the merge ahead has read the partial buffers
+        if (ii == 0 && E.late_wait == 1) grid_dependency_wait();   // the merge ahead has read the partial buffers
         const float *scratch = (const float *)__cvta_shared_to_generic((size_t)E.merge);
         const uint32_t *rec = (const uint32_t *)__cvta_shared_to_generic((size_t)(E.recbase + qslot * REC_BYTES));
         const uint32_t head_rows = rec[IR_HEAD_ROWS];
@@ -890,7 +891,7 @@ __device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe 
             // themselves, a share of the queries each, instead of queueing it behind one
             // epilogue warp at the very end of the kernel.
             asm volatile("bar.sync %0, %1;" ::"n"(CONSUMER_BARRIER), "n"(CONSUMERS * 32) : "memory");
-            if (P.late_wait) grid_dependency_wait();   // the merge ahead has read the partial buffers
+            if (P.late_wait && !P.wait_at_end) grid_dependency_wait();   // the merge ahead has read the partial buffers
             const float *scratch = (const float *)__cvta_shared_to_generic((size_t)(S.merge + epipe.stage * MERGE_BYTES));
             merge_queries(scratch, rec, P.part_o, P.part_ml, group, warp, CONSUMERS, lane, P.n_parts, P.status);
             return;
@@ -1023,7 +1024,7 @@ __global__ void __maxnreg__(152) attend_mma_kernel(const __grid_constant__ Param
         E.hkv = P.hkv;
         E.group = P.group;
         E.fused = P.fused;
-        E.late_wait = P.late_wait;
+        E.late_wait = P.late_wait ? (P.wait_at_end ? 2 : 1) : 0;
         E.n_parts = P.n_parts;
         E.n_items = hdr.item_end - hdr.item_begin;
         if (!P.fused && E.n_items > 0) E.n_items--;   // the last item is the consumer warps' own
@@ -1035,6 +1036,12 @@ __global__ void __maxnreg__(152) attend_mma_kernel(const __grid_constant__ Param
         E.mlbuf = S.mlbuf;
         E.first_item = 0;
         epilogue_loop(E, lane);
+        // A CTA that has not waited yet (with wait_at_end: none has; without: an empty one, or one
+        // whose only item the consumer warps merged) does so here, through this warp: the kernel
+        // then completes after the kernels ahead, as the stream's order says, and no CTA leaves
+        // its SM to a CTA of the next call before the merge that reads the partial buffers that
+        // call will write has finished.
+        if (P.late_wait) grid_dependency_wait();
         return;
     }
     Pipe pipe{0, 0}, qpipe{0, 0}, epipe{0, 0};
@@ -1105,6 +1112,7 @@ int launch_attend_mma(yx_ctx *ctx, const AttendArgs &a) {
     P.n_stages = a.n_stages >= 2 && a.n_stages <= STAGES ? a.n_stages : STAGES;
     P.early_kv = a.early_kv ? 1 : 0;
     P.late_wait = a.late_wait ? 1 : 0;
+    P.wait_at_end = a.wait_at_end ? 1 : 0;
     P.n_items = a.plan ? (uint32_t)a.plan->items.size() : 0u;
     P.n_tiles = a.plan ? (uint32_t)a.plan->tiles.size() : 0u;
     P.n_parts = a.plan ? a.plan->n_parts : 0u;

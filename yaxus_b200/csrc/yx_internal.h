@@ -331,6 +331,8 @@ struct yx_ctx {
     float *ws_o = nullptr;   // [n_parts][group][128]
     float *ws_ml = nullptr;  // [n_parts][group][2]
     size_t ws_o_cap = 0, ws_ml_cap = 0;
+    int ws_set = 0;          // which of the two sets of partial buffers the last attention call took
+    int last_split_ctas = 0; // CTAs of the last call's split-key kernel (0: that call had none)
     float *q_tmp = nullptr;  // normalised, rotated q of yx_attention
     size_t q_tmp_cap = 0;
     uint32_t *counters = nullptr;   // arrival counters of the fused merge; all zero between launches
@@ -407,6 +409,8 @@ struct AttendArgs {
                              // queries and the plan are read at once, and the grid dependency is waited for only
                              // before the first write (the partial buffers, which the merge ahead still reads).
                              // Not set when the queries overlap what that call writes.
+    bool wait_at_end;        // with late_wait: the CTAs wait before they leave instead of before their first write
+                             // (the call ahead had a CTA on every SM: see attend_impl)
     bool fused;              // merge inside the split-key kernel
     uint32_t *counters;      // one per (pass row, kv head), zero between launches
     void *out;               // normalised output, or null
