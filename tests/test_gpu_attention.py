@@ -276,14 +276,17 @@ def test_long_context_decode_at_full_size(backend, oracle, window):
     kv.close()
 
 
+@pytest.mark.parametrize("small", [False, True])
 @pytest.mark.parametrize("kv_dtype", [F16, BF16])
-def test_back_to_back_calls_each_get_their_own_answer(backend, oracle, kv_dtype):
+def test_back_to_back_calls_each_get_their_own_answer(backend, oracle, kv_dtype, small):
     # An attention call that directly follows another one starts reading before the one ahead has
     # finished and waits only before it writes.  Forty calls in a row, alternating between two
     # layers (the second holds the first's values negated), two query tensors and four output
     # buffers: every buffer must hold the answer of the last call that wrote it, and the same bits
-    # as with the overlap switched off.
-    s = W.batched_decode(kv_dtype=kv_dtype)
+    # as with the overlap switched off.  (`small`: a plan with fewer CTAs than SMs, for which the
+    # overlapping call waits before its first write; the full batch has a CTA for every SM, and the
+    # call behind it waits only before its CTAs leave.)
+    s = W.batched_decode(seed=3, n_seq=4, prefix=256, max_suffix=300, kv_dtype=kv_dtype) if small else W.batched_decode(kv_dtype=kv_dtype)
     kv = load(backend, s, n_layers=2)
     backend.write_pages(kv, 1, 0, s.k_bits, s.v_bits ^ np.uint16(0x8000))
     rng = np.random.default_rng(5)
