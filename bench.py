@@ -208,7 +208,9 @@ class Env:
 
 def make_scenario(name, rank):
     if name == "batched_decode":
-        return W.batched_decode(seed=W.SEED0 + 1 + 1000 * rank)
+        # Weak scaling: every rank the same work (rank 0's sequence lengths, in another order) over
+        # its own pages and values.
+        return W.batched_decode(seed=W.SEED0 + 1 + 1000 * rank, length_seed=W.SEED0 + 1, rotate=3 * rank)
     if name == "verify":
         return W.verify(seed=W.SEED0 + 2 + 1000 * rank)
     if name == "single_decode":
@@ -234,7 +236,9 @@ def workload_config(name, s, n_gpus, n_layers, split_kv):
            "l2": (f"steps rotate over {n_layers} layer arenas ({n_layers} x working set > L2)" if n_layers > 1
                   else "one arena: the working set of a step is larger than L2"),
            "parallelism": (f"keys split over {n_gpus} GPU(s), NCCL all-gather of the (m, l, o) triples" if split_kv
-                           else f"by sequence, {n_gpus} GPU(s), no collective")}
+                           else f"by sequence, {n_gpus} GPU(s), no collective"
+                                + ("; every rank its own pages and values with rank 0's sequence lengths in another order"
+                                   if name == "batched_decode" and n_gpus > 1 else ""))}
     if s.window:
         cfg["window"] = s.window
     return cfg

@@ -173,11 +173,15 @@ def single_decode(seed: int = SEED0 + 0, ctx: int = 1024) -> Scenario:
 
 
 def batched_decode(seed: int = SEED0 + 1, n_seq: int = 16, prefix: int = 1536, max_suffix: int = 2560,
-                   kv_dtype: int = F16, hq: int = 32, hkv: int = 8, fill: bool = True) -> Scenario:
+                   kv_dtype: int = F16, hq: int = 32, hkv: int = 8, fill: bool = True,
+                   length_seed: Optional[int] = None, rotate: int = 0) -> Scenario:
     """`n_seq` sequences sharing a `prefix`-token prefix through the same physical pages, each
-    with a private suffix of seeded uniform length in [0, max_suffix], one query token each."""
-    rng = np.random.default_rng(seed ^ 0xABCDEF)
+    with a private suffix of seeded uniform length in [0, max_suffix], one query token each.
+    `length_seed` draws the lengths from another seed than the pages and values (shards of equal
+    work: every shard the same lengths, rotated by `rotate` sequences, over its own data)."""
+    rng = np.random.default_rng((seed if length_seed is None else length_seed) ^ 0xABCDEF)
     suffix = [int(x) for x in rng.integers(0, max_suffix + 1, n_seq)]
+    suffix = suffix[rotate % n_seq:] + suffix[:rotate % n_seq]
     return build("batched_decode", seed, hq, hkv, kv_dtype, [prefix + s for s in suffix], [1] * n_seq,
                  shared_prefix=prefix, fill=fill)
 
