@@ -66,7 +66,8 @@ typedef struct yx_layer {
  * (crates/yaxus-backend-gpu/src/device.rs:96-167).  Zero means "library default". */
 typedef struct yx_tuning {
     int32_t force_path;      /* 0 auto, 1 SIMT split-key, 2 tensor split-key, 3 tcgen05 tiles */
-    int32_t ctas_per_sm;     /* persistent CTAs per SM for the split-key kernels */
+    int32_t ctas_per_sm;     /* persistent CTAs per SM for the split-key kernels (0: default, 4 for the SIMT kernel and
+                                for the tensor kernel one per SM with one SM left spare for the call behind) */
     int32_t share_prefix;    /* 0 default (on), 1 on, 2 off: read pages shared by several rows once */
     int32_t tile_min_rows;   /* rows of one sequence from which the tcgen05 tile kernel is used */
     int32_t cost32;          /* planner cost of a 64-key tile of an item with 32 padded query rows, */

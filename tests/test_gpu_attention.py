@@ -276,16 +276,18 @@ def test_long_context_decode_at_full_size(backend, oracle, window):
     kv.close()
 
 
-@pytest.mark.parametrize("small", [False, True])
+@pytest.mark.parametrize("shape", ["default", "small", "every_sm"])
 @pytest.mark.parametrize("kv_dtype", [F16, BF16])
-def test_back_to_back_calls_each_get_their_own_answer(backend, oracle, kv_dtype, small):
+def test_back_to_back_calls_each_get_their_own_answer(backend, oracle, kv_dtype, shape):
     # An attention call that directly follows another one starts reading before the one ahead has
     # finished and waits only before it writes.  Forty calls in a row, alternating between two
     # layers (the second holds the first's values negated), two query tensors and four output
     # buffers: every buffer must hold the answer of the last call that wrote it, and the same bits
-    # as with the overlap switched off.  (`small`: a plan with fewer CTAs than SMs, for which the
-    # overlapping call waits before its first write; the full batch has a CTA for every SM, and the
-    # call behind it waits only before its CTAs leave.)
+    # as with the overlap switched off.  The default plan leaves one SM spare and `small` has far
+    # fewer CTAs than SMs: the overlapping call waits before its first write.  `every_sm` asks for
+    # a CTA on every SM, after which the call behind waits only before its CTAs leave.
+    small = shape == "small"
+    per_sm = 1 if shape == "every_sm" else 0
     s = W.batched_decode(seed=3, n_seq=4, prefix=256, max_suffix=300, kv_dtype=kv_dtype) if small else W.batched_decode(kv_dtype=kv_dtype)
     kv = load(backend, s, n_layers=2)
     backend.write_pages(kv, 1, 0, s.k_bits, s.v_bits ^ np.uint16(0x8000))
@@ -294,7 +296,7 @@ def test_back_to_back_calls_each_get_their_own_answer(backend, oracle, kv_dtype,
     refs = [oracle_step(oracle, s, q=q) for q in qs]
     results = []
     for overlap in (0, 2):
-        backend.set_tuning(overlap_calls=overlap)
+        backend.set_tuning(overlap_calls=overlap, ctas_per_sm=per_sm)
         backend.begin_pass(s.meta)
         backend.kv_append(kv, 0, dev(backend, s.k_new), dev(backend, s.v_new))
         backend.kv_append(kv, 1, dev(backend, s.k_new), dev(backend, -s.v_new))
@@ -303,6 +305,9 @@ def test_back_to_back_calls_each_get_their_own_answer(backend, oracle, kv_dtype,
         for i in range(40):
             backend.attend(kv, i % 2, q_dev[(i // 2) % 2], s.hq, out=outs[i % 4])
         results.append([backend.to_host(o) for o in outs])
+        if not small:
+            sms = torch.cuda.get_device_properties(backend.device).multi_processor_count
+            assert backend.last_plan().n_ctas == sms - (0 if per_sm else 1)
     backend.set_tuning()
     for i, got in enumerate(results[0]):      # buffer i was last written by call 36 + i
         sign = -1.0 if i % 2 else 1.0

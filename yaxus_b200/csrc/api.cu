@@ -294,6 +294,13 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
     pp.esize = kv->esize;
     const int per_sm = ctx->tuning.ctas_per_sm > 0 ? ctx->tuning.ctas_per_sm : (path == 1 ? 4 : 1);
     pp.n_ctas = ctx->sm_count * per_sm;
+    // The tensor split-key kernel is planned for one CTA fewer than there are SMs unless the
+    // tuning asks for a count.  These calls run back to back, each one's grid launched while the
+    // one ahead still runs; a plan that keeps every SM busy to its last tile leaves that grid no
+    // SM to place its first CTA on, and the interval between such calls was 19.5 us where plans
+    // of the same batch for 140..147 CTAs all gave 18.8 us (the kernel is bound by HBM, not by
+    // the number of CTAs).  With an SM spare one CTA of the call behind always runs a call ahead.
+    if (path == 2 && ctx->tuning.ctas_per_sm <= 0 && pp.n_ctas > 1) pp.n_ctas -= 1;
     // (a slot of the split-key kernel holds 32 query rows of f32 or 64 of a 16-bit type)
     pp.max_rows = path == 1 ? 1 : std::max(1, std::min(MAX_ITEM_ROWS, (q_dtype == YX_F32 ? 32 : 64) / group));
     pp.share_prefix = path != 1 && ctx->tuning.share_prefix != 2;
