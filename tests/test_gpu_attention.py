@@ -276,7 +276,7 @@ def test_long_context_decode_at_full_size(backend, oracle, window):
     kv.close()
 
 
-@pytest.mark.parametrize("shape", ["default", "small", "every_sm"])
+@pytest.mark.parametrize("shape", ["default", "small", "every_sm", "verify"])
 @pytest.mark.parametrize("kv_dtype", [F16, BF16])
 def test_back_to_back_calls_each_get_their_own_answer(backend, oracle, kv_dtype, shape):
     # An attention call that directly follows another one starts reading before the one ahead has
@@ -285,10 +285,13 @@ def test_back_to_back_calls_each_get_their_own_answer(backend, oracle, kv_dtype,
     # buffers: every buffer must hold the answer of the last call that wrote it, and the same bits
     # as with the overlap switched off.  The default plan leaves one SM spare and `small` has far
     # fewer CTAs than SMs: the overlapping call waits before its first write.  `every_sm` asks for
-    # a CTA on every SM, after which the call behind waits only before its CTAs leave.
+    # a CTA on every SM, after which the call behind waits only before its CTAs leave.  `verify`:
+    # five rows a sequence, whose merge kernel in such a run takes several (row, head) pairs a warp.
     small = shape == "small"
     per_sm = 1 if shape == "every_sm" else 0
     s = W.batched_decode(seed=3, n_seq=4, prefix=256, max_suffix=300, kv_dtype=kv_dtype) if small else W.batched_decode(kv_dtype=kv_dtype)
+    if shape == "verify":
+        s = W.verify(kv_dtype=kv_dtype)
     kv = load(backend, s, n_layers=2)
     backend.write_pages(kv, 1, 0, s.k_bits, s.v_bits ^ np.uint16(0x8000))
     rng = np.random.default_rng(5)

@@ -458,7 +458,7 @@ int attend_impl(yx_ctx *ctx, yx_kv *kv, int layer, const void *q, int q_dtype, i
         profile_mark(ctx, 2);
         if (!a.fused && need_combine)
             if (int rc = launch_combine(ctx, cp->d_merges, part_o, part_ml, (int)ctx->pass.rows, hq, group, out,
-                                        out_dtype, m_out, l_out, o_out))
+                                        out_dtype, m_out, l_out, o_out, a.late_wait != 0))
                 return rc;
         host_clock_lap(ctx, 6);
         profile_mark(ctx, 3);

@@ -684,6 +684,7 @@ __device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe 
         khi[c] = valid ? rec[base + IRR_KHI] : 0xffffffffu;
     }
     const int lm = lane >> 3, lr = lane & 7;
+    const bool idle = j * 8 >= q_rows;   // this warp's eight columns are all padding: its (o, m, l) stay (0, -inf, 0)
     // Query fragments (the column operand), held for the whole item, built from the raw rows the
     // stager's copies left in the slot: this thread holds dims 16 ks + 2 t4 (+1) and + 8 of query
     // j * 8 + g.  f32 queries (and 16-bit ones of the other type) become a high part in the cache's
@@ -745,8 +746,10 @@ __device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe 
     for (uint32_t ti = 0; ti < n_tiles; ti++) {
         const long long w0 = (YX_TR(P.trace != nullptr) && threadIdx.x == 0) ? clock64() : 0;
         mbar_wait(S.full + 8 * pipe.stage, pipe.phase, S.abort_flag, P.status, 2);
-        if (turn >= 0 && (int)(ti & 1u) != turn) {
-            // The other warps' tile.  It is still waited for and released: a warp that skipped
+        if (idle || (turn >= 0 && (int)(ti & 1u) != turn)) {
+            // The other warps' tile, or a column tile without a query (20 or 24 query rows in a
+            // 32-row item leave the fourth one empty: its warps' share of the tensor work goes
+            // to the other six).  The tile is still waited for and released: a warp that skipped
             // ahead without looking could meet a barrier two phases on, which a parity wait
             // cannot tell from the phase it expects.
             if (lane == 0) mbar_arrive(S.empty + 8 * pipe.stage);

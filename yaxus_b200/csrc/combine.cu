@@ -34,11 +34,9 @@ __global__ void __launch_bounds__(128) combine_kernel(const Merge *__restrict__ 
     // (diagnostic build: when this CTA entered and when its wait returned)
     if (YX_TR(trace != nullptr) && threadIdx.x == 0) trace[TRACE_MERGE_BASE + 4 * blockIdx.x] = dev::gtime();
     uint32_t idx = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t warps = (gridDim.x * blockDim.x) >> 5;   // the grid may be smaller than the work: see launch_combine
     int lane = threadIdx.x & 31;
     if (idx >= n) return;
-    uint32_t row = idx / (uint32_t)hq;
-    int h = (int)(idx % (uint32_t)hq), kvh = h / group, g = h % group;
-    Merge mg = merges[(size_t)row * (hq / group) + kvh];   // host-written: not the split-key kernel's output
     // Launched as a programmatic dependent of the split-key kernel: it is resident beside that
     // kernel's CTAs (four warps of 48 registers a thread: one warp fits in what three warps of the
     // split-key kernel leave of each register file partition) long before they finish.  The
@@ -48,7 +46,11 @@ __global__ void __launch_bounds__(128) combine_kernel(const Merge *__restrict__ 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (YX_TR(trace != nullptr) && threadIdx.x == 0) trace[TRACE_MERGE_BASE + 4 * blockIdx.x + 1] = dev::gtime();
-    if (mg.count == 0 && !o_out) return;   // the row was another kernel's (tiled path)
+    for (; idx < n; idx += warps) {
+    const uint32_t row = idx / (uint32_t)hq;
+    const int h = (int)(idx % (uint32_t)hq), kvh = h / group, g = h % group;
+    const Merge mg = merges[(size_t)row * (hq / group) + kvh];   // host-written: not the split-key kernel's output
+    if (mg.count == 0 && !o_out) continue;   // the row was another kernel's (tiled path)
     float mx = -1e30f, l = 0.0f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     // The first few vectors are asked for together with the (m, l) pairs: a row and KV head has
@@ -123,6 +125,7 @@ __global__ void __launch_bounds__(128) combine_kernel(const Merge *__restrict__ 
             l_out[idx] = l;
         }
     }
+    }
     if (YX_TR(trace != nullptr) && threadIdx.x == 0) trace[TRACE_MERGE_BASE + 4 * blockIdx.x + 2] = dev::gtime();
 }
 
@@ -171,9 +174,16 @@ int launch_fill_empty(yx_ctx *ctx, size_t n, float *m, float *l, float *o) {
 }
 
 int launch_combine(yx_ctx *ctx, const Merge *merges, const float *part_o, const float *part_ml, int rows, int hq,
-                   int group, void *out, int out_dtype, float *m_out, float *l_out, float *o_out) {
+                   int group, void *out, int out_dtype, float *m_out, float *l_out, float *o_out, bool chained) {
     uint32_t n = (uint32_t)rows * (uint32_t)hq;
     uint32_t blocks = (n * 32 + 127) / 128;
+    // In a run of back-to-back attention calls the next call's kernel is this kernel's programmatic
+    // dependent: it cannot start before every CTA of this grid has started, and beside a CTA of
+    // the split-key kernel an SM has room for one of these only.  A verification pass (80 rows, 640
+    // CTAs) then held the next call back until the split-key kernel's CTAs had left: 35.8 us a
+    // call where a grid of one CTA per SM, each taking several (row, head) pairs in turn, gives
+    // 29.5 us (grids of 1.5 to 3 CTAs per SM: 37-39 us).  Prompt-sized passes keep the full grid.
+    if (chained && blocks > (uint32_t)ctx->sm_count && blocks <= 6u * (uint32_t)ctx->sm_count) blocks = (uint32_t)ctx->sm_count;
     if (!ctx->smem_configured[2]) {
         // Same shared-memory carve-out as the split-key kernel it follows, so that the SMs are
         // not reconfigured between the two on every attention call.

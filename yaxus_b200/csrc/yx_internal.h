@@ -438,7 +438,7 @@ int launch_attend_mma(yx_ctx *ctx, const AttendArgs &a);
 // Writes the empty mark (-1e30, 0, 0) for n (row, head) triples.
 int launch_fill_empty(yx_ctx *ctx, size_t n, float *m, float *l, float *o);
 int launch_combine(yx_ctx *ctx, const Merge *merges, const float *part_o, const float *part_ml, int rows,
-                   int hq, int group, void *out, int out_dtype, float *m_out, float *l_out, float *o_out);
+                   int hq, int group, void *out, int out_dtype, float *m_out, float *l_out, float *o_out, bool chained = false);
 // Parts with strides (in floats) sm, sl, so between consecutive parts of m, l and o.
 int launch_combine_strided(yx_ctx *ctx, int n_parts, const float *m, const float *l, const float *o, size_t sm,
                            size_t sl, size_t so, size_t n, void *out, int out_dtype);
