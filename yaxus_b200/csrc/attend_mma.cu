@@ -684,7 +684,8 @@ __device__ void consume_item(const Params &P, const Shared &S, Pipe &pipe, Pipe 
         khi[c] = valid ? rec[base + IRR_KHI] : 0xffffffffu;
     }
     const int lm = lane >> 3, lr = lane & 7;
-    const bool idle = j * 8 >= q_rows;   // this warp's eight columns are all padding: its (o, m, l) stay (0, -inf, 0)
+    // (32-row items only: for the others the test is dropped at compile time)
+    const bool idle = KBW >= 2 && j * 8 >= q_rows;   // this warp's eight columns are all padding: its (o, m, l) stay (0, -inf, 0)
     // Query fragments (the column operand), held for the whole item, built from the raw rows the
     // stager's copies left in the slot: this thread holds dims 16 ks + 2 t4 (+1) and + 8 of query
     // j * 8 + g.  f32 queries (and 16-bit ones of the other type) become a high part in the cache's

@@ -28,6 +28,8 @@ __device__ __forceinline__ void store_out(void *out, int out_dtype, size_t elem,
 // slot s and head-in-group g sits at index s * group + g.  Lane c reads the (m, l) of part c,
 // the warp agrees on the maximum and the weights, and only then are the o vectors read, all
 // loads independent of one another: the merge costs two memory latencies, not two per part.
+// LOOP: the grid has fewer warps than there are (row, head) pairs, and a warp takes several in turn.
+template <bool LOOP>
 __global__ void __launch_bounds__(128) combine_kernel(const Merge *__restrict__ merges, const float *__restrict__ part_o,
                                const float *__restrict__ part_ml, uint32_t n, int hq, int group, void *out,
                                int out_dtype, float *m_out, float *l_out, float *o_out, unsigned long long *trace) {
@@ -37,6 +39,8 @@ __global__ void __launch_bounds__(128) combine_kernel(const Merge *__restrict__ 
     const uint32_t warps = (gridDim.x * blockDim.x) >> 5;   // the grid may be smaller than the work: see launch_combine
     int lane = threadIdx.x & 31;
     if (idx >= n) return;
+    // The first pair's record is asked for before the wait (host-written: not the split-key kernel's output).
+    Merge mg = merges[(size_t)(idx / (uint32_t)hq) * (hq / group) + (idx % (uint32_t)hq) / group];
     // Launched as a programmatic dependent of the split-key kernel: it is resident beside that
     // kernel's CTAs (four warps of 48 registers a thread: one warp fits in what three warps of the
     // split-key kernel leave of each register file partition) long before they finish.  The
@@ -46,10 +50,9 @@ __global__ void __launch_bounds__(128) combine_kernel(const Merge *__restrict__ 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (YX_TR(trace != nullptr) && threadIdx.x == 0) trace[TRACE_MERGE_BASE + 4 * blockIdx.x + 1] = dev::gtime();
-    for (; idx < n; idx += warps) {
-    const uint32_t row = idx / (uint32_t)hq;
-    const int h = (int)(idx % (uint32_t)hq), kvh = h / group, g = h % group;
-    const Merge mg = merges[(size_t)row * (hq / group) + kvh];   // host-written: not the split-key kernel's output
+    for (bool first = true; idx < n; idx = LOOP ? idx + warps : n, first = false) {
+    const int g = (int)(idx % (uint32_t)hq) % group;
+    if (!first) mg = merges[(size_t)(idx / (uint32_t)hq) * (hq / group) + (idx % (uint32_t)hq) / group];
     if (mg.count == 0 && !o_out) continue;   // the row was another kernel's (tiled path)
     float mx = -1e30f, l = 0.0f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -183,11 +186,13 @@ int launch_combine(yx_ctx *ctx, const Merge *merges, const float *part_o, const 
     // CTAs) then held the next call back until the split-key kernel's CTAs had left: 35.8 us a
     // call where a grid of one CTA per SM, each taking several (row, head) pairs in turn, gives
     // 29.5 us (grids of 1.5 to 3 CTAs per SM: 37-39 us).  Prompt-sized passes keep the full grid.
-    if (chained && blocks > (uint32_t)ctx->sm_count && blocks <= 6u * (uint32_t)ctx->sm_count) blocks = (uint32_t)ctx->sm_count;
+    const bool loop = chained && blocks > (uint32_t)ctx->sm_count && blocks <= 6u * (uint32_t)ctx->sm_count;
+    if (loop) blocks = (uint32_t)ctx->sm_count;
     if (!ctx->smem_configured[2]) {
         // Same shared-memory carve-out as the split-key kernel it follows, so that the SMs are
         // not reconfigured between the two on every attention call.
-        cudaFuncSetAttribute(combine_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(combine_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(combine_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         ctx->smem_configured[2] = true;
     }
     // Programmatic stream serialisation: the launch is set up while the kernel before it still
@@ -202,7 +207,7 @@ int launch_combine(yx_ctx *ctx, const Merge *merges, const float *part_o, const 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (int rc = check_cuda(ctx, cudaLaunchKernelEx(&cfg, combine_kernel, merges, part_o, part_ml, n, hq, group, out, out_dtype, m_out, l_out, o_out,
+    if (int rc = check_cuda(ctx, cudaLaunchKernelEx(&cfg, loop ? combine_kernel<true> : combine_kernel<false>, merges, part_o, part_ml, n, hq, group, out, out_dtype, m_out, l_out, o_out,
                                                     (unsigned long long *)ctx->trace_buf),
                             "combine kernel launch"))
         return rc;
