@@ -185,8 +185,10 @@ int launch_combine(yx_ctx *ctx, const Merge *merges, const float *part_o, const 
     // the split-key kernel an SM has room for one of these only.  A verification pass (80 rows, 640
     // CTAs) then held the next call back until the split-key kernel's CTAs had left: 35.8 us a
     // call where a grid of one CTA per SM, each taking several (row, head) pairs in turn, gives
-    // 29.5 us (grids of 1.5 to 3 CTAs per SM: 37-39 us).  Prompt-sized passes keep the full grid.
-    const bool loop = chained && blocks > (uint32_t)ctx->sm_count && blocks <= 6u * (uint32_t)ctx->sm_count;
+    // 29.5 us (grids of 1.5 to 3 CTAs per SM: 37-39 us).  Up to about seven pairs a warp this pays
+    // (128 rows: 36.4 against 41.3 us); with nine (160 rows: 39.1 against 37.3 us) the merge is too
+    // long to hide, and such passes, like prompt-sized ones, keep the full grid.
+    const bool loop = chained && blocks > (uint32_t)ctx->sm_count && blocks <= 8u * (uint32_t)ctx->sm_count;
     if (loop) blocks = (uint32_t)ctx->sm_count;
     if (!ctx->smem_configured[2]) {
         // Same shared-memory carve-out as the split-key kernel it follows, so that the SMs are
