@@ -2,8 +2,9 @@
 // verification and rows over shared prefixes.  Bandwidth-bound: the job of this kernel is to
 // keep every SM's share of HBM busy from the first microsecond to the last.
 //
-//  * Persistent: one CTA per SM, eleven warps (eight consumers, a producer, a query stager, an
-//    epilogue warp), walks the span of 64-key tiles the planner cut for it.
+//  * Persistent: one CTA to an SM (by default one SM is left without, for the call behind),
+//    eleven warps (eight consumers, a producer, a query stager, an epilogue warp); a CTA walks
+//    the span of 64-key tiles the planner cut for it.
 //  * Nothing on the device walks a page table.  The host planner resolves every tile to its
 //    (page, KV head) block; the producer warp reads 32 tile descriptors with one coalesced
 //    load and feeds the copy engine from them, across item boundaries, never draining.
