@@ -181,3 +181,59 @@ def test_elementwise_operators_against_numpy(oracle):
     table = oracle.to_bf16(rng.standard_normal((10, 32)).astype(np.float32))
     e = oracle.embed(table, [3, 3, 9, 0])
     assert np.array_equal(e, (table[[3, 3, 9, 0]].astype(np.uint32) << 16).view(np.float32))
+
+
+def _tiny_model(oracle):
+    from tests.test_gpu_forward import TinyWeights
+    from yaxus_b200.backend import LayerMeta, Rope
+    metas = [LayerMeta(index=0, window=None, rope=Rope.default()), LayerMeta(index=1, window=48, rope=Rope.default(theta=5000.0))]
+    return TinyWeights(oracle, len(metas), seed=11), metas
+
+
+def _arenas(metas, pages):
+    from tests.test_gpu_forward import D, HKV
+    from yaxus_b200._lib import PAGE
+    return [(np.zeros((pages * PAGE, HKV * D), np.float32), np.zeros((pages * PAGE, HKV * D), np.float32)) for _ in metas]
+
+
+def test_a_prompt_in_chunks_gives_the_logits_of_the_prompt_at_once(oracle):
+    # The property chunked prefill rests on (crates/yaxus-model/src/lib.rs:475-482): feeding a prompt
+    # in chunks leaves the same cache and the same last-row logits as feeding it whole.  Here on the
+    # oracle's own operators composed in Model::forward's order, over the host-side page bookkeeping.
+    from tests.test_gpu_forward import VOCAB, forward_oracle
+    from yaxus_b200.kvcache import KvCache
+    w, metas = _tiny_model(oracle)
+    prompt = np.random.default_rng(3).integers(0, VOCAB, 150)
+    results = []
+    for chunks in ((150,), (100, 50), (128, 1, 21)):
+        cache, arenas = KvCache(4, 1024), _arenas(metas, 4)
+        seq, at = cache.new_seq(), 0
+        for n in chunks:
+            logits = forward_oracle(oracle, w, arenas, metas, cache.append([(seq, prompt[at:at + n])]), F32)
+            at += n
+        results.append((logits, arenas))
+    for logits, arenas in results[1:]:
+        assert np.abs(logits - results[0][0]).max() <= 2e-5
+        for (K, V), (K0, V0) in zip(arenas, results[0][1]):
+            assert np.abs(K - K0).max() <= 2e-6 and np.abs(V - V0).max() <= 2e-6
+
+
+def test_a_fork_continues_like_the_sequence_it_came_from(oracle):
+    # KvCache::fork (crates/yaxus-model/src/kv.rs:277-295): the fork shares the full pages, gets a copy
+    # of the half-filled one, and the same next token gives it the same logits as its parent.
+    from tests.test_gpu_forward import D, HKV, VOCAB, forward_oracle
+    from yaxus_b200.kvcache import KvCache
+    w, metas = _tiny_model(oracle)
+    cache, arenas = KvCache(6, 1024), _arenas(metas, 6)
+    prompt = np.random.default_rng(4).integers(0, VOCAB, 140)
+    a = cache.new_seq()
+    forward_oracle(oracle, w, arenas, metas, cache.append([(a, prompt)]), BF16)
+    b = cache.fork(a, 140)
+    meta = cache.append([(a, [7]), (b, [7])])
+    copies = cache.take_copies()
+    assert len(copies) == 1 and cache.page_refs(int(cache.seq_pages(a)[0])) == 2
+    for src, dst in copies:
+        for K, V in arenas:
+            oracle.copy_page(K, V, HKV * D, src, dst)
+    logits = forward_oracle(oracle, w, arenas, metas, meta, BF16)
+    assert logits.shape == (2, VOCAB) and np.array_equal(logits[0], logits[1])
